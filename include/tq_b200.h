@@ -1,0 +1,172 @@
+/*
+ * tq_b200.h -- C ABI of libtq_sm100.so: TurboQuant vector quantisation on NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the array arithmetic of Project-Tensor's
+ * tensor_gpu_v2/_quant.py (TurboQuantMSE / TurboQuantProd).  That file has no FFI of its own:
+ * its boundary is a handful of NumPy/CuPy array expressions inside Python methods.  Each entry
+ * point below names the reference lines whose arithmetic it takes over; the Python classes in
+ * project_tensor_b200/turboquant.py keep the reference's names and signatures and call these
+ * functions through ctypes.
+ *
+ * Conventions
+ *   - Every function returns 0 (TQ_OK) or a negative TQ_ERR_* code, never throws, never aborts.
+ *     tq_last_error() gives a human-readable message for the calling thread's last failure.
+ *   - Arguments are validated on the host before anything is launched.
+ *   - All data pointers are DEVICE pointers (on the plan's device) unless a parameter is marked
+ *     "host".  The caller owns every buffer.  The library allocates device memory only in
+ *     tq_plan_create (the constants of one quantizer) and frees it in tq_plan_destroy.
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued asynchronously on it.
+ *   - `x`, `out`, `scores`, `q` are dense row-major float32.  Pointers must be 16-byte aligned.
+ *
+ * Packed layouts (row = one vector / key)
+ *   codes : row stride tq_code_row_bytes() = 4*ceil(d*bits/32) bytes; coordinate j occupies bits
+ *           [j*bits, (j+1)*bits) of the row read as a little-endian bit stream; padding bits are 0.
+ *   signs : row stride tq_sign_row_bytes() = 4*ceil(d/32) bytes; bit j is 1 when the QJL sign of
+ *           coordinate j is +1 (the reference stores +1/-1 int8, _quant.py:67-70).
+ */
+#ifndef TQ_B200_H
+#define TQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_VERSION 100
+
+#define TQ_OK 0
+#define TQ_ERR_INVALID_ARGUMENT (-1)  /* null pointer, bad size, misaligned pointer */
+#define TQ_ERR_UNSUPPORTED (-2)       /* dimension / bit width outside what the kernels cover */
+#define TQ_ERR_CUDA (-3)              /* a CUDA runtime or driver call failed */
+#define TQ_ERR_SCRATCH_TOO_SMALL (-4) /* scratch buffer smaller than the matching *_scratch_bytes query says */
+#define TQ_ERR_NO_DEVICE (-5)         /* no sm_100 device, or the requested device is absent */
+
+/* Which arithmetic tq_*_quantize / tq_*_dequantize / tq_score_batched use. */
+#define TQ_PATH_AUTO 0    /* tensor-core kernels where they exist for (d, bits), else exact kernels */
+#define TQ_PATH_EXACT 1   /* float32 kernels that accumulate in the reference's order */
+#define TQ_PATH_TENSOR 2  /* tensor-core kernels; TQ_ERR_UNSUPPORTED if (d, bits) has none */
+
+typedef struct tq_plan tq_plan;
+
+int tq_version(void);
+const char* tq_last_error(void);
+
+/* Number of CUDA devices this process can see, or a negative TQ_ERR_*. */
+int tq_device_count(void);
+
+/*
+ * Upload the constants of one quantizer to `device`.
+ * Replaces the per-call `xp.asarray(self.rotation / codebook / boundaries / projection)` of
+ * _quant.py:215-222,294-295.  rotation: host float32[d*d] row-major (TurboQuantMSE.rotation,
+ * _quant.py:193-201); codebook: host float32[2^bits_mse], sorted (:203-211); projection: host
+ * float32[d*d] or NULL for an MSE-only plan (TurboQuantProd.projection, :283-292).
+ * Boundaries are derived as 0.5f*(c[k]+c[k+1]) in float32 exactly as _quant.py:212 does.
+ * Limits: 2 <= d <= 1024, 1 <= bits_mse <= 8.
+ */
+int tq_plan_create(int d, int bits_mse, const float* rotation, const float* codebook,
+                   const float* projection, int device, tq_plan** out);
+void tq_plan_destroy(tq_plan* plan);
+int tq_plan_set_path(tq_plan* plan, int path);
+/* 1 when tensor-core kernels exist for this plan's (d, bits_mse), else 0. */
+int tq_plan_has_tensor_path(const tq_plan* plan);
+
+int64_t tq_code_row_bytes(const tq_plan* plan);
+int64_t tq_sign_row_bytes(const tq_plan* plan);
+/* Scratch bytes tq_mse_quantize / tq_prod_quantize need for n rows (may be 0). */
+int64_t tq_quantize_scratch_bytes(const tq_plan* plan, int64_t n);
+/* Scratch bytes tq_score_batched needs when topk > 0 (0 when topk == 0). */
+int64_t tq_topk_scratch_bytes(const tq_plan* plan, int groups, int q_per_group,
+                              int64_t keys_per_group, int topk);
+
+/*
+ * TurboQuantMSE.quantize, array part (_quant.py:224-236 called from :244-249):
+ * norms[i] = ||x_i||_2; unit = x_i / norm (rows whose norm is not > 0 become 0);
+ * codes[i][j] = number of boundaries strictly below (unit R^T)[j]  (searchsorted side="left").
+ */
+int tq_mse_quantize(const tq_plan* plan, const float* x, int64_t n, void* codes, float* norms,
+                    void* scratch, size_t scratch_bytes, void* stream);
+
+/* TurboQuantMSE.dequantize (_quant.py:238-242,251-254): out_i = (codebook[codes_i] R) * norms[i]. */
+int tq_mse_dequantize(const tq_plan* plan, const void* codes, const float* norms, int64_t n,
+                      float* out, void* stream);
+
+/*
+ * TurboQuantProd.quantize, array part (_quant.py:300-308): the MSE stage above, then
+ * residual = unit - codebook[codes] R, residual_norms = ||residual||_2,
+ * signs = (residual S^T >= 0).
+ */
+int tq_prod_quantize(const tq_plan* plan, const float* x, int64_t n, void* codes, void* signs,
+                     float* residual_norms, float* norms, void* scratch, size_t scratch_bytes,
+                     void* stream);
+
+/*
+ * TurboQuantProd.dequantize (_quant.py:317-332):
+ * out_i = (codebook[codes_i] R + sqrt(pi/2)/d * residual_norms[i] * (qjl_i S)) * norms[i].
+ */
+int tq_prod_dequantize(const tq_plan* plan, const void* codes, const void* signs,
+                       const float* residual_norms, const float* norms, int64_t n, float* out,
+                       void* stream);
+
+/*
+ * TurboQuantProd.attention_score with one query row broadcast over n keys
+ * (_quant.py:338-341,347-358): scores[i] = norms[i] * ( q . (codebook[codes_i] R)
+ *   + sqrt(pi/2)/d * residual_norms[i] * ((S q) . qjl_i) ).   q: float32[d].
+ */
+int tq_score_broadcast(const tq_plan* plan, const float* q, const void* codes, const void* signs,
+                       const float* residual_norms, const float* norms, int64_t n, float* scores,
+                       void* stream);
+
+/* Same formula with one query row per key (_quant.py:342-358).  q: float32[n*d]. */
+int tq_score_pairwise(const tq_plan* plan, const float* q, const void* codes, const void* signs,
+                      const float* residual_norms, const float* norms, int64_t n, float* scores,
+                      void* stream);
+
+/*
+ * Many queries against shared keys in one pass.  The reference has no such call: its users loop
+ * attention_score over query rows and stack the results (validate_turboquant.py:92-95,
+ * test_turboquant.py:117-118); this computes the same numbers without re-reading the keys.
+ * Keys are split into `groups` consecutive blocks of keys_per_group rows; queries are
+ * float32[groups][q_per_group][d]; query (g, a) is scored against the keys of block g only.
+ *   scores     : float32[groups][q_per_group][keys_per_group], or NULL to skip the matrix.
+ *   topk > 0   : also return, per query, the topk largest scores in descending order
+ *                (ties: lower key index first) as top_scores float32[groups][q_per_group][topk]
+ *                and top_idx int64[...] = idx_base + row index within the whole key array.
+ *                Slots beyond keys_per_group hold -inf / -1.  1 <= topk <= 1024.
+ */
+int tq_score_batched(const tq_plan* plan, const float* q, int groups, int q_per_group,
+                     const void* codes, const void* signs, const float* residual_norms,
+                     const float* norms, int64_t keys_per_group, float* scores, int topk,
+                     float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
+                     size_t scratch_bytes, void* stream);
+
+/*
+ * Merge `lists` candidate lists per query (e.g. one per GPU after an all-gather) into one
+ * descending top-k.  in_scores/in_idx: [lists][queries][topk]; out: [queries][topk].
+ * No reference counterpart (the reference is single-device).
+ */
+int tq_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
+                  float* out_scores, int64_t* out_idx, void* stream);
+
+/*
+ * Conversions between the packed layouts and the reference's array fields
+ * (TurboQuantMSEEncoding.indices uint8[n][d], TurboQuantProdEncoding.qjl int8[n][d] of +1/-1,
+ * _quant.py:156-169).
+ */
+int tq_unpack_codes(const tq_plan* plan, const void* codes, int64_t n, uint8_t* indices, void* stream);
+int tq_pack_codes(const tq_plan* plan, const uint8_t* indices, int64_t n, void* codes, void* stream);
+int tq_unpack_signs(const tq_plan* plan, const void* signs, int64_t n, int8_t* qjl, void* stream);
+int tq_pack_signs(const tq_plan* plan, const int8_t* qjl, int64_t n, void* signs, void* stream);
+
+/*
+ * Counters of the last tq_*_quantize call on this plan, read back from the device (synchronises
+ * `stream`): rows the tensor-core kernel handed to the exact kernel because a coordinate fell
+ * within the guard band of a decision boundary.  Diagnostic only.
+ */
+int tq_plan_last_recheck_rows(const tq_plan* plan, void* stream, int64_t* rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQ_B200_H */

@@ -1,0 +1,105 @@
+// Shared declarations for libtq_sm100.so (TurboQuant on B200).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/tq_b200.h"
+
+#define TQ_MAX_DIM 1024
+#define TQ_MAX_BITS 8
+#define TQ_MAX_TOPK 1024
+
+// Guard band (in units of a rotated unit-vector coordinate) inside which the tensor-core kernels
+// do not trust their own comparison against a decision boundary and hand the row to the exact
+// kernel.  The tensor-core rotation is accurate to ~1e-7; the band leaves a wide margin.
+#define TQ_CODE_GUARD 2.0e-6f
+// Same idea for the QJL projection, whose sign is taken at zero.
+#define TQ_SIGN_GUARD 4.0e-6f
+
+// Device-side view of a plan: plain pointers, passed to kernels by value.
+struct TqDev {
+    int d;             // vector dimension
+    int bits;          // bits per coordinate of the MSE stage
+    int levels;        // 1 << bits
+    int code_words;    // 32-bit words per packed code row
+    int sign_words;    // 32-bit words per packed sign row
+    float alpha;       // float32(sqrt(pi/2) / d), _quant.py:322-324,351-353
+    const float* R;    // rotation, row-major [j][k]
+    const float* Rt;   // its transpose [k][j]
+    const float* S;    // projection, row-major [j][k] (null for MSE-only plans)
+    const float* St;   // its transpose
+    const float* codebook;    // [levels]
+    const float* boundaries;  // [levels-1]
+};
+
+struct TensorConsts;  // defined in tq_tensor.cu
+
+struct tq_plan {
+    TqDev dev;
+    int device;
+    int path;
+    bool has_projection;
+    bool tensor_ok;          // tensor-core kernels cover this (d, bits)
+    void* slab;              // one device allocation holding every constant
+    TensorConsts* tensor;    // host-side bookkeeping for the tensor-core kernels (may be null)
+    unsigned long long* counters;  // device: [0] rows re-done by the exact kernel in the last quantize
+};
+
+// ---- error plumbing (tq_api.cu) -------------------------------------------------------------
+int tq_fail(int code, const char* fmt, ...);
+#define TQ_CUDA_TRY(expr)                                                                   \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            return tq_fail(TQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
+    } while (0)
+
+// ---- launchers implemented in the kernel files -----------------------------------------------
+// Exact (reference-order float32) kernels.  `rowmask` (may be null) restricts the work to rows
+// whose bit is set: bit (i & 31) of word (i >> 5).
+int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
+                             uint32_t* signs, float* rnorms, float* norms, const uint32_t* rowmask,
+                             unsigned long long* redo_counter, cudaStream_t st);
+int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs,
+                               const float* rnorms, const float* norms, int64_t n, float* out,
+                               cudaStream_t st);
+int tq_launch_exact_pairwise(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs,
+                             const float* rnorms, const float* norms, int64_t n, float* scores,
+                             cudaStream_t st);
+
+// Tensor-core (tcgen05) kernels.
+bool tq_tensor_supported(int d, int bits);
+int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection);
+void tq_tensor_plan_free(tq_plan* p);
+int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
+                              uint32_t* signs, float* rnorms, float* norms, uint32_t* rowmask,
+                              cudaStream_t st);
+
+// Scoring kernels.
+int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                            const uint32_t* signs, const float* rnorms, const float* norms,
+                            int64_t keys_per_group, float* scores, int topk, float* top_scores,
+                            int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
+                            cudaStream_t st);
+int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk);
+int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
+                         float* out_scores, int64_t* out_idx, cudaStream_t st);
+
+// Packing helpers.
+int tq_launch_unpack_codes(const tq_plan* p, const uint32_t* codes, int64_t n, uint8_t* out, cudaStream_t st);
+int tq_launch_pack_codes(const tq_plan* p, const uint8_t* in, int64_t n, uint32_t* codes, cudaStream_t st);
+int tq_launch_unpack_signs(const tq_plan* p, const uint32_t* signs, int64_t n, int8_t* out, cudaStream_t st);
+int tq_launch_pack_signs(const tq_plan* p, const int8_t* in, int64_t n, uint32_t* signs, cudaStream_t st);
+
+// ---- small device helpers ---------------------------------------------------------------------
+// Code of coordinate j in a packed row (little-endian bit stream, `bits` <= 8).
+__device__ __forceinline__ uint32_t tq_get_code(const uint32_t* row, int j, int bits) {
+    const int bit = j * bits;
+    const int w = bit >> 5, s = bit & 31;
+    uint32_t v = row[w] >> s;
+    if (s + bits > 32) v |= row[w + 1] << (32 - s);
+    return v & ((1u << bits) - 1u);
+}

@@ -1,0 +1,315 @@
+// Scoring kernels for TurboQuantProd encodings (any d <= 1024, bits <= 8).
+//
+// score(q, key i) = norms[i] * ( (R q) . codebook[codes_i]  +  alpha * residual_norms[i] * ((S q) . qjl_i) )
+//
+// which is TurboQuantProd.attention_score (_quant.py:347-357) with the inverse rotation moved from
+// the keys to the query: q . (codebook[codes] R) == (R q) . codebook[codes].  The reference
+// de-rotates every key on every call; here the query is rotated and projected once per block into
+// shared memory and the packed keys are streamed once.
+//
+// Optional fused per-query top-k: every block keeps, per query, a candidate buffer in shared
+// memory with a rising threshold, prunes it with a bitonic sort when it fills, and writes its k
+// best (score, row) pairs as 64-bit sortable keys; a second kernel merges the per-block lists.
+#include "tq_common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kQT = 8;  // queries scored together per pass over a block's keys
+
+__device__ __forceinline__ uint32_t ordered_bits(float s) {
+    const uint32_t u = __float_as_uint(s);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float unordered_bits(uint32_t o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+// Larger key = better candidate: higher score first, then lower row index.
+__device__ __forceinline__ unsigned long long make_key(float s, uint32_t row) {
+    return ((unsigned long long)ordered_bits(s) << 32) | (unsigned long long)(0xffffffffu - row);
+}
+
+// In-place descending bitonic sort of `n2` (power of two) keys in shared memory by the whole block.
+__device__ void block_sort_desc(unsigned long long* a, int n2) {
+    for (int k = 2; k <= n2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const unsigned long long x = a[i], y = a[l];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (x < y) : (x > y)) { a[i] = y; a[l] = x; }
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads)
+score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __restrict__ codes,
+             const uint32_t* __restrict__ signs, const float* __restrict__ rnorms,
+             const float* __restrict__ norms, int64_t keys_per_group, int64_t keys_per_block,
+             float* __restrict__ scores, int topk, int cap2, unsigned long long* __restrict__ part) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int d = p.d;
+    float* qraw = reinterpret_cast<float*>(smraw);       // [kQT][d]   raw queries
+    float* qs = qraw + kQT * d;                           // [kQT][2][d] rotated | projected
+    float* cb = qs + kQT * 2 * d;                         // [256] codebook
+    unsigned long long* buf = reinterpret_cast<unsigned long long*>(cb + 256);  // [kQT][cap2]
+    __shared__ int cnt[kQT];
+    __shared__ unsigned long long thr[kQT];
+    __shared__ int need_prune;
+
+    const int g = blockIdx.y;
+    const int64_t k0 = (int64_t)blockIdx.x * keys_per_block;
+    int64_t k1 = k0 + keys_per_block;
+    if (k1 > keys_per_group) k1 = keys_per_group;
+    const int64_t gbase = (int64_t)g * keys_per_group;  // first row of this group in the key arrays
+
+    for (int i = threadIdx.x; i < 256; i += kThreads) cb[i] = i < p.levels ? p.codebook[i] : 0.f;
+
+    for (int q0 = 0; q0 < qpg; q0 += kQT) {
+        const int nq = min(kQT, qpg - q0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kQT * d; i += kThreads) {
+            const int t = i / d;
+            qraw[i] = t < nq ? q[((int64_t)g * qpg + q0 + t) * d + (i - t * d)] : 0.f;
+        }
+        if (threadIdx.x < kQT) { cnt[threadIdx.x] = 0; thr[threadIdx.x] = 0ull; }
+        if (threadIdx.x == 0) need_prune = 0;
+        __syncthreads();
+        // rotated / projected queries: qs[t][0][j] = sum_k R[j][k] q[k],  qs[t][1][j] = sum_k S[j][k] q[k]
+        for (int i = threadIdx.x; i < kQT * 2 * d; i += kThreads) {
+            const int t = i / (2 * d), r = i - t * 2 * d, which = r / d, j = r - which * d;
+            const float* M = which ? p.St : p.Rt;
+            const float* qv = qraw + t * d;
+            float acc = 0.f;
+            for (int k = 0; k < d; ++k) acc = fmaf(qv[k], __ldg(M + (size_t)k * d + j), acc);
+            qs[i] = acc;
+        }
+        __syncthreads();
+
+        for (int64_t kb = k0; kb < k1; kb += kThreads) {
+            const int64_t key = kb + threadIdx.x;
+            const bool live = key < k1;
+            float a1[kQT], a2[kQT];
+#pragma unroll
+            for (int t = 0; t < kQT; ++t) { a1[t] = 0.f; a2[t] = 0.f; }
+            if (live) {
+                const uint32_t* crow = codes + (gbase + key) * p.code_words;
+                const uint32_t* srow = signs + (gbase + key) * p.sign_words;
+                uint32_t sw = 0;
+                for (int j = 0; j < d; ++j) {
+                    if ((j & 31) == 0) sw = srow[j >> 5];
+                    const float c = cb[tq_get_code(crow, j, p.bits)];
+                    const float s = (sw >> (j & 31)) & 1u ? 1.f : -1.f;
+#pragma unroll
+                    for (int t = 0; t < kQT; ++t) {
+                        a1[t] = fmaf(c, qs[(t * 2) * d + j], a1[t]);
+                        a2[t] = fmaf(s, qs[(t * 2 + 1) * d + j], a2[t]);
+                    }
+                }
+                const float nrm = norms[gbase + key];
+                const float arn = p.alpha * rnorms[gbase + key];
+#pragma unroll
+                for (int t = 0; t < kQT; ++t) {
+                    if (t < nq) {
+                        const float s = nrm * (a1[t] + arn * a2[t]);
+                        if (scores) scores[((int64_t)g * qpg + q0 + t) * keys_per_group + key] = s;
+                        if (topk > 0) {
+                            const unsigned long long ck = make_key(s, (uint32_t)(gbase + key));
+                            if (ck > thr[t]) {
+                                const int pos = atomicAdd(&cnt[t], 1);
+                                buf[(size_t)t * cap2 + pos] = ck;  // capacity is guaranteed by the prune rule
+                            }
+                        }
+                    }
+                }
+            }
+            if (topk > 0) {
+                __syncthreads();
+                if (threadIdx.x < nq && cnt[threadIdx.x] + kThreads > cap2) need_prune = 1;
+                __syncthreads();
+                if (need_prune) {
+                    for (int t = 0; t < nq; ++t) {
+                        const int c = cnt[t];
+                        if (c + kThreads > cap2) {
+                            unsigned long long* b = buf + (size_t)t * cap2;
+                            for (int i = c + threadIdx.x; i < cap2; i += kThreads) b[i] = 0ull;
+                            block_sort_desc(b, cap2);
+                            if (threadIdx.x == 0) { cnt[t] = topk; thr[t] = b[topk - 1]; }
+                        }
+                    }
+                    __syncthreads();
+                    if (threadIdx.x == 0) need_prune = 0;
+                    __syncthreads();
+                }
+            }
+        }
+        if (topk > 0) {
+            __syncthreads();
+            for (int t = 0; t < nq; ++t) {
+                const int c = cnt[t];
+                unsigned long long* b = buf + (size_t)t * cap2;
+                for (int i = c + threadIdx.x; i < cap2; i += kThreads) b[i] = 0ull;
+                block_sort_desc(b, cap2);
+                unsigned long long* dst = part + (((size_t)g * gridDim.x + blockIdx.x) * qpg + q0 + t) * topk;
+                for (int i = threadIdx.x; i < topk; i += kThreads) dst[i] = b[i];
+            }
+        }
+    }
+}
+
+// Merge `lists` sorted-or-not lists of `topk` sortable keys per query into the final top-k.
+// part: [groups][lists][qpg][topk]; one block per (query, group).
+__global__ void __launch_bounds__(256)
+merge_keys_kernel(const unsigned long long* __restrict__ part, int lists, int qpg, int topk, int k2,
+                  int64_t idx_base, float* __restrict__ top_scores, int64_t* __restrict__ top_idx) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    unsigned long long* a = reinterpret_cast<unsigned long long*>(smraw);  // [2*k2]
+    const int qi = blockIdx.x, g = blockIdx.y;
+    for (int i = threadIdx.x; i < 2 * k2; i += blockDim.x) a[i] = 0ull;
+    __syncthreads();
+    for (int l = 0; l < lists; ++l) {
+        const unsigned long long* src = part + (((size_t)g * lists + l) * qpg + qi) * topk;
+        for (int i = threadIdx.x; i < k2; i += blockDim.x) a[k2 + i] = i < topk ? src[i] : 0ull;
+        block_sort_desc(a, 2 * k2);
+    }
+    for (int i = threadIdx.x; i < topk; i += blockDim.x) {
+        const unsigned long long ck = a[i];
+        const size_t o = ((size_t)g * qpg + qi) * topk + i;
+        if (ck == 0ull) {
+            top_scores[o] = -INFINITY;
+            top_idx[o] = -1;
+        } else {
+            top_scores[o] = unordered_bits((uint32_t)(ck >> 32));
+            top_idx[o] = idx_base + (int64_t)(0xffffffffu - (uint32_t)ck);
+        }
+    }
+}
+
+// Merge (score, index) lists gathered from several shards: [lists][queries][topk] -> [queries][topk].
+__global__ void __launch_bounds__(256)
+merge_pairs_kernel(const float* __restrict__ in_scores, const int64_t* __restrict__ in_idx, int lists,
+                   int queries, int topk, int k2, float* __restrict__ out_scores,
+                   int64_t* __restrict__ out_idx) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    unsigned long long* a = reinterpret_cast<unsigned long long*>(smraw);  // [2*k2]
+    const int qi = blockIdx.x;
+    for (int i = threadIdx.x; i < 2 * k2; i += blockDim.x) a[i] = 0ull;
+    __syncthreads();
+    for (int l = 0; l < lists; ++l) {
+        const size_t base = ((size_t)l * queries + qi) * topk;
+        for (int i = threadIdx.x; i < k2; i += blockDim.x) {
+            unsigned long long ck = 0ull;
+            // position in the concatenation of all lists stands in for the index: earlier list and
+            // earlier slot win ties, which is ascending row order for contiguous shards
+            if (i < topk && in_idx[base + i] >= 0) ck = make_key(in_scores[base + i], (uint32_t)(l * topk + i));
+            a[k2 + i] = ck;
+        }
+        block_sort_desc(a, 2 * k2);
+    }
+    for (int i = threadIdx.x; i < topk; i += blockDim.x) {
+        const unsigned long long ck = a[i];
+        const size_t o = (size_t)qi * topk + i;
+        if (ck == 0ull) {
+            out_scores[o] = -INFINITY;
+            out_idx[o] = -1;
+        } else {
+            const uint32_t pos = 0xffffffffu - (uint32_t)ck;
+            const size_t src = ((size_t)(pos / topk) * queries + qi) * topk + (pos % topk);
+            out_scores[o] = in_scores[src];
+            out_idx[o] = in_idx[src];
+        }
+    }
+}
+
+int pow2_at_least(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+struct ScoreGeometry {
+    int nblk;
+    int64_t keys_per_block;
+    int cap2;
+};
+
+ScoreGeometry geometry(int groups, int64_t keys_per_group, int topk) {
+    ScoreGeometry s;
+    int64_t want = (148 * 8 + groups - 1) / groups;  // about 8 blocks per SM over all groups
+    int64_t maxb = (keys_per_group + kThreads - 1) / kThreads;
+    if (want > maxb) want = maxb;
+    if (want < 1) want = 1;
+    int64_t kpb = (keys_per_group + want - 1) / want;
+    kpb = (kpb + kThreads - 1) / kThreads * kThreads;
+    if (kpb < kThreads) kpb = kThreads;
+    s.keys_per_block = kpb;
+    s.nblk = (int)((keys_per_group + kpb - 1) / kpb);
+    if (s.nblk < 1) s.nblk = 1;
+    s.cap2 = topk > 0 ? pow2_at_least(topk + kThreads) : 0;
+    return s;
+}
+
+}  // namespace
+
+int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk) {
+    (void)p;
+    if (topk <= 0) return 0;
+    const ScoreGeometry s = geometry(groups, keys_per_group, topk);
+    return (int64_t)groups * s.nblk * qpg * topk * (int64_t)sizeof(unsigned long long);
+}
+
+int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                            const uint32_t* signs, const float* rnorms, const float* norms,
+                            int64_t keys_per_group, float* scores, int topk, float* top_scores,
+                            int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
+                            cudaStream_t st) {
+    const ScoreGeometry s = geometry(groups, keys_per_group, topk);
+    if (topk > 0) {
+        const int64_t need = tq_score_topk_scratch(p, groups, qpg, keys_per_group, topk);
+        if (!scratch || (int64_t)scratch_bytes < need)
+            return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "top-k scratch: need %lld bytes, got %zu", (long long)need, scratch_bytes);
+    }
+    if (keys_per_group == 0 || groups == 0 || qpg == 0) {
+        if (topk > 0 && groups > 0 && qpg > 0) {
+            // no keys: every slot is empty
+            const size_t cnt = (size_t)groups * qpg * topk;
+            TQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, cnt * sizeof(unsigned long long), st));
+            merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * pow2_at_least(topk) * sizeof(unsigned long long), st>>>(
+                static_cast<unsigned long long*>(scratch), 1, qpg, topk, pow2_at_least(topk), idx_base, top_scores, top_idx);
+            TQ_CUDA_TRY(cudaGetLastError());
+        }
+        return TQ_OK;
+    }
+    const int d = p->dev.d;
+    const size_t sm = (size_t)(kQT * d + kQT * 2 * d + 256) * sizeof(float) + (size_t)kQT * s.cap2 * sizeof(unsigned long long);
+    if (sm > 200 * 1024) return tq_fail(TQ_ERR_UNSUPPORTED, "score kernel needs %zu bytes of shared memory", sm);
+    TQ_CUDA_TRY(cudaFuncSetAttribute(score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    score_kernel<<<dim3(s.nblk, groups), kThreads, sm, st>>>(p->dev, q, qpg, codes, signs, rnorms, norms,
+                                                             keys_per_group, s.keys_per_block, scores, topk, s.cap2,
+                                                             static_cast<unsigned long long*>(scratch));
+    TQ_CUDA_TRY(cudaGetLastError());
+    if (topk > 0) {
+        const int k2 = pow2_at_least(topk);
+        merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * k2 * sizeof(unsigned long long), st>>>(
+            static_cast<unsigned long long*>(scratch), s.nblk, qpg, topk, k2, idx_base, top_scores, top_idx);
+        TQ_CUDA_TRY(cudaGetLastError());
+    }
+    return TQ_OK;
+}
+
+int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
+                         float* out_scores, int64_t* out_idx, cudaStream_t st) {
+    if (queries == 0) return TQ_OK;
+    const int k2 = pow2_at_least(topk);
+    merge_pairs_kernel<<<queries, 256, 2 * k2 * sizeof(unsigned long long), st>>>(in_scores, in_idx, lists, queries,
+                                                                                  topk, k2, out_scores, out_idx);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}

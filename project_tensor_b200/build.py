@@ -42,7 +42,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(SRC_DIR, s) for s in SOURCES]
-    cmd += ["-o", LIB_PATH, "-lcuda"]
+    cmd += ["-o", LIB_PATH]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)

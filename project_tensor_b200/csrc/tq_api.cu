@@ -164,7 +164,7 @@ int tq_plan_create(int d, int bits_mse, const float* rotation, const float* code
             delete p;
             return r;
         }
-        p->tensor_ok = true;
+        p->tensor_ok = p->tensor != nullptr;
     }
     *out = p;
     return TQ_OK;
@@ -389,10 +389,11 @@ int tq_plan_last_recheck_rows(const tq_plan* p, void* stream, int64_t* rows) {
     TQ_TRY(check_plan(p, false));
     if (!rows) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "rows is null");
     DeviceScope scope(p->device);
-    unsigned long long v = 0;
-    TQ_CUDA_TRY(cudaMemcpyAsync(&v, p->counters, sizeof(v), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    unsigned long long v[2] = {0, 0};
+    TQ_CUDA_TRY(cudaMemcpyAsync(v, p->counters, sizeof(v), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
     TQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-    *rows = (int64_t)v;
+    *rows = (int64_t)v[0];
+    if (v[1] != 0) return tq_fail(TQ_ERR_CUDA, "a tensor-core kernel gave up on a bounded wait (status %llu)", v[1]);
     return TQ_OK;
 }
 

@@ -1,8 +1,805 @@
-// placeholder while the exact path is brought up
+// Tensor-core quantizers for B200 (sm_100a): TMA in, tcgen05.mma with TMEM accumulators, SIMT epilogue.
+//
+// One persistent CTA per SM walks over tiles of 128 rows.  Per tile:
+//
+//   TMA (1 thread)      x tile, four 128-row x 32-float boxes with the 128-byte swizzle  -> smem ring
+//   converters (8 warps) one thread per half row: sum of squares, scale to unit length * 2^10,
+//                        split every value into fp16 hi + fp16 lo, tcgen05.st both as the A operand
+//                        straight into tensor memory (lane = row) -- A never touches shared memory
+//   MMA (1 thread)      acc = A_hi*B_hi + A_hi*B_lo + A_lo*B_hi with kind::f16, fp32 accumulate in
+//                        TMEM; B = 2^10 * R split the same way, resident in smem for the whole kernel.
+//                        The dropped lo*lo term is 2^-24 relative.
+//   epilogue (4 warps)   one thread per row: tcgen05.ld 32 columns at a time, locate each value among
+//                        the codebook boundaries through a 32-cell lookup table held in the lanes of
+//                        the warp (one shuffle per table), pack codes, and flag the row if any value
+//                        lies inside a guard band around a boundary.
+//   TurboQuantProd adds: rho = value - centroid (still in the rotated basis), |rho|, rho split to
+//                        fp16 hi/lo and stored back into the tile's A columns, a second MMA against
+//                        B2 = 16 * (R S^T), and a sign/guard epilogue on that accumulator.
+//                        residual S^T == rho (R S^T) because the residual is rho R.
+//
+// Flagged rows (about 1% of them) are recomputed afterwards by the exact kernel in the reference's
+// own float32 operation order, so the packed output equals the reference's wherever the reference's
+// own arithmetic decides, while 99% of the rows only ever see the tensor-core pass.
+//
+// Every wait is bounded: on a timeout the kernel records a status word, all roles leave their loops,
+// tensor memory is released and the kernel returns.
 #include "tq_common.cuh"
-bool tq_tensor_supported(int, int) { return false; }
-int tq_tensor_plan_init(tq_plan*, const float*, const float*, const float*) { return TQ_OK; }
-void tq_tensor_plan_free(tq_plan*) {}
-int tq_launch_tensor_quantize(const tq_plan*, bool, const float*, int64_t, uint32_t*, uint32_t*, float*, float*, uint32_t*, cudaStream_t) {
-    return tq_fail(TQ_ERR_UNSUPPORTED, "tensor path not built");
+
+#include <cuda.h>
+#include <math.h>
+#include <string.h>
+
+#include <vector>
+
+namespace {
+
+constexpr int kTileRows = 128;
+constexpr int kThreads = 448;            // 14 warps: TMA, MMA, 8 converters, 4 epilogue
+constexpr int kFirstConvWarp = 2;
+constexpr int kFirstEpiWarp = 10;
+constexpr int kBoxBytes = 128 * 128;     // 128 rows x 32 floats
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+constexpr float kScaleA = 1024.f;        // unit vector -> A operand
+constexpr float kScaleB = 1024.f;        // rotation    -> B operand
+constexpr float kAccScale = kScaleA * kScaleB;  // accumulator = 2^20 * rotated coordinate
+constexpr float kScaleRho = 1.f / 1024.f;       // accumulator units -> 2^10 * rho for the second A operand
+constexpr float kScaleM = 16.f;                 // R S^T -> second B operand
+constexpr int kCells = 32;
+constexpr float kCellMul = 31.99998f;
+
+struct TensorArgs {
+    const __half* bmat;      // [R_hi | R_lo | M_hi | M_lo], each d*d halves in the interleaved layout
+    const float* lut_bnd;    // [32] boundary of each cell (scaled by 2^20) or +inf
+    const int* lut_base;     // [32] number of boundaries in lower cells
+    const float* lut_cent;   // [32] scaled centroids, entry l = centroid (l mod levels)
+    float cell_scale, cell_offset;
+    float code_guard, sign_guard;  // in accumulator units
+    int64_t n;
+    int64_t ntiles;
+    uint32_t* codes;
+    uint32_t* signs;
+    float* norms;
+    float* rnorms;
+    uint32_t* rowmask;
+    unsigned long long* status;  // [0]: set to a non-zero code when a wait timed out
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another thread has already given up.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag);
+}
+
+// Named barrier over `count` threads that also ORs a predicate across them.
+__device__ __forceinline__ bool bar_or(int id, int count, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"(id), "r"(count), "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
+
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]^T, 128 x N x 16, fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrive once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float r;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float fma_rm(float a, float b, float c) {
+    float r;
+    asm("fma.rm.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo_elem, float hi_elem) {
+    const __half2 h = __floats2half2_rn(lo_elem, hi_elem);  // .x (low 16 bits) = first argument
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Shared-memory matrix descriptor of a K-major operand stored without swizzle as 8x8 fp16 core
+// matrices (8 rows x 16 bytes, contiguous): lbo = bytes between core matrices along K, sbo = bytes
+// between 8-row groups.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+    return d;                // layout type 0: no swizzle
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory plan
+// ---------------------------------------------------------------------------------------------
+template <int D, bool PROD>
+struct Smem {
+    static constexpr int kBoxesPerTile = D / 32;
+    static constexpr int kBBytes = D * D * 2;                       // one fp16 operand matrix
+    static constexpr int kNumB = PROD ? 4 : 2;
+    static constexpr int kRingBoxes = PROD ? 5 : 8;
+    static constexpr int kStagePitch = kTileRows + 4;               // words; staging is [word][row]
+    static constexpr int kCodeStageBytes = (D * 4 / 32) * kStagePitch * 4;  // up to 4 bits per coordinate
+    static constexpr int kSignStageBytes = PROD ? (D / 32) * kStagePitch * 4 : 0;
+    static constexpr int off_b = 0;
+    static constexpr int off_ring = off_b + kNumB * kBBytes;
+    static constexpr int off_codes = off_ring + kRingBoxes * kBoxBytes;
+    static constexpr int off_signs = off_codes + kCodeStageBytes;
+    static constexpr int off_misc = off_signs + kSignStageBytes;    // sumsq exchange, force flags, barriers
+    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512;
+    static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
+};
+
+// barrier indices inside the barrier block
+enum {
+    BAR_FULL = 0,                 // [8]  ring slot filled by TMA
+    BAR_EMPTY = 8,                // [8]  ring slot drained by the converters
+    BAR_A_FULL = 16,              // [2]
+    BAR_A_EMPTY = 18,             // [2]
+    BAR_ACC_FULL = 20,            // [2]
+    BAR_ACC_EMPTY = 22,           // [2]
+    BAR_RHO_FULL = 24,            // [2]
+    BAR_ACC2_FULL = 26,           // [1]
+    BAR_ACC2_EMPTY = 27,          // [1]
+    BAR_COUNT = 28
+};
+
+template <int D, int BITS, bool PROD>
+__global__ void __launch_bounds__(kThreads, 1)
+tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
+    static_assert(D == 128, "this kernel is written for d = 128");
+    using L = Smem<D, PROD>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem_base = smem_u32(smem);
+
+    float* ssq = reinterpret_cast<float*>(smem + L::off_misc);                          // [2][128]
+    unsigned char* force = smem + L::off_misc + 2 * kTileRows * 4;                      // [4][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 2 * kTileRows * 4 + 4 * kTileRows);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- one-time set-up ------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8; ++i) { mbar_init(BAR(BAR_FULL + i), 1); mbar_init(BAR(BAR_EMPTY + i), 4); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(BAR_A_FULL + i), 8);
+            mbar_init(BAR(BAR_A_EMPTY + i), 1);
+            mbar_init(BAR(BAR_ACC_FULL + i), 1);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), 4);
+            mbar_init(BAR(BAR_RHO_FULL + i), 4);
+        }
+        mbar_init(BAR(BAR_ACC2_FULL), 1);
+        mbar_init(BAR(BAR_ACC2_EMPTY), 4);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {   // operand matrices: global -> smem, once per CTA
+        const uint4* src = reinterpret_cast<const uint4*>(a.bmat);
+        uint4* dst = reinterpret_cast<uint4*>(smem + L::off_b);
+        for (int i = threadIdx.x; i < L::kNumB * L::kBBytes / 16; i += kThreads) dst[i] = __ldg(src + i);
+        fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+    constexpr int kABlock = D / 2;  // TMEM columns of one fp16 A block (two halves per column)
+    // TMEM column map
+    auto A_COL = [&](int b) { return (uint32_t)(b * 2 * kABlock); };
+    auto ACC_COL = [&](int b) { return (uint32_t)(4 * kABlock + (PROD ? 0 : b * D)); };
+    const uint32_t kAcc2Col = 4 * kABlock + D;
+
+    if (warp == 0) {
+        // ---- TMA producer ----------------------------------------------------------------------
+        if (lane == 0) {
+            int64_t g = 0;
+            for (int64_t i = 0; i < my_tiles; ++i) {
+                const int64_t tile = blockIdx.x + i * gridDim.x;
+                bool ok = true;
+                for (int bx = 0; bx < L::kBoxesPerTile; ++bx, ++g) {
+                    const int slot = (int)(g % L::kRingBoxes);
+                    const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
+                    if (!mbar_wait(BAR(BAR_EMPTY + slot), par ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(BAR(BAR_FULL + slot), kBoxBytes);
+                    tma_load_box(smem_base + L::off_ring + slot * kBoxBytes, &tmap_x, bx * 32, (int)(tile * kTileRows),
+                                 BAR(BAR_FULL + slot));
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ------------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t sbo = (D / 8) * 128, lbo = 128;
+            const uint32_t b_rhi = smem_base + L::off_b, b_rlo = b_rhi + L::kBBytes;
+            const uint32_t b_mhi = b_rlo + L::kBBytes, b_mlo = b_mhi + L::kBBytes;
+            for (int64_t i = 0; i < my_tiles; ++i) {
+                const int b = (int)(i & 1);
+                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                const int ab = PROD ? 0 : b;
+                const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
+                if (!mbar_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
+                if (!mbar_wait(BAR(BAR_ACC_EMPTY + ab), acc_par ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + ACC_COL(ab);
+                const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
+#pragma unroll
+                for (int kb = 0; kb < D / 16; ++kb) {
+                    const uint64_t dh = make_smem_desc(b_rhi + kb * 2 * lbo, lbo, sbo);
+                    const uint64_t dl = make_smem_desc(b_rlo + kb * 2 * lbo, lbo, sbo);
+                    mma_ts(acc, a_hi + kb * 8, dh, kIdesc, kb > 0);
+                    mma_ts(acc, a_hi + kb * 8, dl, kIdesc, 1);
+                    mma_ts(acc, a_lo + kb * 8, dh, kIdesc, 1);
+                }
+                mma_commit(BAR(BAR_ACC_FULL + ab));
+                if (!PROD) {
+                    mma_commit(BAR(BAR_A_EMPTY + b));
+                } else {
+                    if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
+                    if (!mbar_wait(BAR(BAR_ACC2_EMPTY), (uint32_t)(i & 1) ^ 1u, abort_flag)) break;
+                    tc_fence_after();
+                    const uint32_t acc2 = tmem + kAcc2Col;
+#pragma unroll
+                    for (int kb = 0; kb < D / 16; ++kb) {
+                        const uint64_t dh = make_smem_desc(b_mhi + kb * 2 * lbo, lbo, sbo);
+                        const uint64_t dl = make_smem_desc(b_mlo + kb * 2 * lbo, lbo, sbo);
+                        mma_ts(acc2, a_hi + kb * 8, dh, kIdesc, kb > 0);
+                        mma_ts(acc2, a_hi + kb * 8, dl, kIdesc, 1);
+                        mma_ts(acc2, a_lo + kb * 8, dh, kIdesc, 1);
+                    }
+                    mma_commit(BAR(BAR_ACC2_FULL));
+                    mma_commit(BAR(BAR_A_EMPTY + b));
+                }
+            }
+        }
+    } else if (warp < kFirstEpiWarp) {
+        // ---- converters: fp32 rows -> unit length, fp16 hi/lo, into tensor memory ----------------
+        const int cw = warp - kFirstConvWarp;      // 0..7
+        const int half = cw >> 2;                  // which 64 floats of the row
+        const int quarter = warp & 3;              // TMEM lane quarter this warp may touch
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        int64_t g_base = 0;
+        for (int64_t i = 0; i < my_tiles; ++i, g_base += L::kBoxesPerTile) {
+            const int64_t tile = blockIdx.x + i * gridDim.x;
+            const int b = (int)(i & 1);
+            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            float x[64];
+            bool fail = false;
+#pragma unroll
+            for (int bb = 0; bb < 2; ++bb) {
+                const int64_t g = g_base + half * 2 + bb;
+                const int slot = (int)(g % L::kRingBoxes);
+                const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
+                if (!fail && !mbar_wait(BAR(BAR_FULL + slot), par, abort_flag)) fail = true;
+                const unsigned char* box = smem + L::off_ring + slot * kBoxBytes + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 v = fail ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                          : *reinterpret_cast<const float4*>(box + ((c ^ (row & 7)) << 4));
+                    x[bb * 32 + c * 4 + 0] = v.x;
+                    x[bb * 32 + c * 4 + 1] = v.y;
+                    x[bb * 32 + c * 4 + 2] = v.z;
+                    x[bb * 32 + c * 4 + 3] = v.w;
+                }
+                __syncwarp();
+                if (lane == 0 && !fail) mbar_arrive(BAR(BAR_EMPTY + slot));
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < 64; ++k) ss = fmaf(x[k], x[k], ss);
+            ssq[half * kTileRows + row] = ss;
+            if (bar_or(1, 256, fail)) break;
+            const float tot = ssq[row] + ssq[kTileRows + row];
+            const float nrm = sqrtf(tot);
+            const bool ok = nrm > 0.f;
+            // rows the tensor-core pass cannot represent go to the exact kernel: overflowed or
+            // denormal-range norms
+            const bool odd = !(tot < 3.0e38f) || (ok && tot < 1.0e-30f);
+            const float sc = ok ? kScaleA / nrm : 0.f;
+            if (half == 0) {
+                const int64_t grow = tile * kTileRows + row;
+                if (grow < a.n) a.norms[grow] = nrm;
+                force[(i & 3) * kTileRows + row] = odd ? 1 : 0;
+            }
+            if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+            if (bar_or(1, 256, fail)) break;
+            tc_fence_after();
+            const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * 32;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int p = 0; p < 16; ++p) {
+                    const float u0 = (ok && !odd) ? x[s * 32 + 2 * p] * sc : 0.f;
+                    const float u1 = (ok && !odd) ? x[s * 32 + 2 * p + 1] * sc : 0.f;
+                    const __half2 h = __floats2half2_rn(u0, u1);
+                    const float2 hf = __half22float2(h);
+                    hi[p] = *reinterpret_cast<const uint32_t*>(&h);
+                    lo[p] = pack_half2(u0 - hf.x, u1 - hf.y);
+                }
+                tmem_st16(a_hi + s * 16, hi);
+                tmem_st16(a_hi + kABlock + s * 16, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + b));
+        }
+    } else {
+        // ---- epilogue: one thread per row --------------------------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float lut_bnd = a.lut_bnd[lane];
+        const int lut_base = a.lut_base[lane];
+        const float lut_cent = a.lut_cent[lane];
+        uint32_t* code_stage = reinterpret_cast<uint32_t*>(smem + L::off_codes);
+        uint32_t* sign_stage = reinterpret_cast<uint32_t*>(smem + L::off_signs);
+        constexpr int kCodeWords = D * BITS / 32;  // words per packed row
+        const int et = threadIdx.x - kFirstEpiWarp * 32;  // 0..127
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            const int64_t tile = blockIdx.x + i * gridDim.x;
+            const int b = (int)(i & 1);
+            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            const int ab = PROD ? 0 : b;
+            const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
+            const int64_t grow = tile * kTileRows + row;
+            int64_t rows_valid = a.n - tile * kTileRows;
+            if (rows_valid > kTileRows) rows_valid = kTileRows;
+            bool fail = !mbar_wait(BAR(BAR_ACC_FULL + ab), acc_par, abort_flag);
+            if (bar_or(2, 128, fail)) break;
+            tc_fence_after();
+            bool near = force[(i & 3) * kTileRows + row] != 0;
+            float rs = 0.f;
+            const uint32_t acc = tmem + lane_addr + ACC_COL(ab);
+            const uint32_t a_hi = tmem + lane_addr + A_COL(b);
+#pragma unroll 1
+            for (int ch = 0; ch < D / 32; ++ch) {
+                uint32_t v[32];
+                tmem_ld32(acc + ch * 32, v);
+                tmem_wait_ld();
+                uint32_t w[BITS + 1];
+#pragma unroll
+                for (int k = 0; k <= BITS; ++k) w[k] = 0;
+                uint32_t rhi[16], rlo[16];
+                float prev_rho = 0.f;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float f = __uint_as_float(v[e]);
+                    const float u = fma_sat(f, a.cell_scale, a.cell_offset);
+                    const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
+                    const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
+                    const int base = __shfl_sync(0xffffffffu, lut_base, cell);
+                    const float dlt = f - bnd;
+                    const uint32_t code = (uint32_t)base + (dlt > 0.f ? 1u : 0u);
+                    near = near || (fabsf(dlt) < a.code_guard);
+                    const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
+                    w[wi] |= code << sh;
+                    if (sh + BITS > 32) w[wi + 1] |= code >> (32 - sh);
+                    if (PROD) {
+                        const float cent = __shfl_sync(0xffffffffu, lut_cent, (int)code);
+                        const float rho = f - cent;
+                        rs = fmaf(rho, rho, rs);
+                        const float r = rho * kScaleRho;
+                        if (e & 1) {
+                            const __half2 h = __floats2half2_rn(prev_rho, r);
+                            const float2 hf = __half22float2(h);
+                            rhi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                            rlo[e >> 1] = pack_half2(prev_rho - hf.x, r - hf.y);
+                        } else {
+                            prev_rho = r;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < BITS; ++k) code_stage[(ch * BITS + k) * L::kStagePitch + row] = w[k];
+                if (PROD) {
+                    tmem_st16(a_hi + ch * 16, rhi);
+                    tmem_st16(a_hi + kABlock + ch * 16, rlo);
+                }
+            }
+            if (PROD) {
+                tmem_wait_st();
+                if (grow < a.n) a.rnorms[grow] = sqrtf(rs) * (1.f / kAccScale);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(BAR(BAR_ACC_EMPTY + ab));
+                if (PROD) mbar_arrive(BAR(BAR_RHO_FULL + b));
+            }
+            if (PROD) {
+                fail = !mbar_wait(BAR(BAR_ACC2_FULL), (uint32_t)(i & 1), abort_flag);
+                if (bar_or(2, 128, fail)) break;
+                tc_fence_after();
+                const uint32_t acc2 = tmem + lane_addr + kAcc2Col;
+#pragma unroll 1
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(acc2 + ch * 32, v);
+                    tmem_wait_ld();
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float f = __uint_as_float(v[e]);
+                        word |= (f >= 0.f ? 1u : 0u) << e;
+                        near = near || (fabsf(f) < a.sign_guard);
+                    }
+                    sign_stage[ch * L::kStagePitch + row] = word;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(BAR_ACC2_EMPTY));
+            }
+            const uint32_t mask = __ballot_sync(0xffffffffu, near && grow < a.n);
+            if (lane == 0 && tile * kTileRows + quarter * 32 < a.n) a.rowmask[tile * 4 + quarter] = mask;
+            // staged rows -> global, coalesced
+            bar_or(2, 128, false);
+            {
+                constexpr int kGroups = kCodeWords / 4;  // 16-byte pieces per packed row
+                uint4* dst = reinterpret_cast<uint4*>(a.codes + tile * kTileRows * kCodeWords);
+                const int total = (int)rows_valid * kGroups;
+                for (int k = et; k < total; k += 128) {
+                    const int r = k / kGroups, q = k - r * kGroups;
+                    const uint32_t* s0 = code_stage + (4 * q) * L::kStagePitch + r;
+                    dst[k] = make_uint4(s0[0], s0[L::kStagePitch], s0[2 * L::kStagePitch], s0[3 * L::kStagePitch]);
+                }
+                if (PROD) {
+                    static_assert(D / 32 == 4, "sign rows are one 16-byte piece");
+                    uint4* sdst = reinterpret_cast<uint4*>(a.signs + tile * kTileRows * (D / 32));
+                    for (int r = et; r < (int)rows_valid; r += 128) {
+                        const uint32_t* s0 = sign_stage + r;
+                        sdst[r] = make_uint4(s0[0], s0[L::kStagePitch], s0[2 * L::kStagePitch], s0[3 * L::kStagePitch]);
+                    }
+                }
+            }
+            bar_or(2, 128, false);
+        }
+    }
+
+    // ---- teardown -----------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// fp16 bits of a float, round to nearest even (host)
+uint16_t host_half_bits(float f) {
+    const __half h = __float2half_rn(f);
+    uint16_t b;
+    memcpy(&b, &h, 2);
+    return b;
+}
+float host_half_value(uint16_t b) {
+    __half h;
+    memcpy(&h, &b, 2);
+    return __half2float(h);
+}
+
+// Split scale*M[n][k] into hi + lo fp16 and lay both out as 8x8 core matrices, K-major.
+void split_operand(const std::vector<double>& m, int d, double scale, uint16_t* hi, uint16_t* lo) {
+    const size_t sbo = (size_t)(d / 8) * 128, lbo = 128;
+    for (int n = 0; n < d; ++n)
+        for (int k = 0; k < d; ++k) {
+            const float v = (float)(m[(size_t)n * d + k] * scale);
+            const uint16_t h = host_half_bits(v);
+            const uint16_t l = host_half_bits((float)((double)v - (double)host_half_value(h)));
+            const size_t off = ((size_t)(n / 8) * sbo + (size_t)(k / 8) * lbo + (size_t)(n % 8) * 16 + (size_t)(k % 8) * 2) / 2;
+            hi[off] = h;
+            lo[off] = l;
+        }
+}
+
+int host_cell(float v, float scale, float offset) {
+    float u = fmaf(v, scale, offset);
+    u = u < 0.f ? 0.f : (u > 1.f ? 1.f : u);
+    if (!(u == u)) u = 0.f;
+    return (int)floor((double)u * (double)kCellMul);
+}
+
+// Find a 32-cell uniform grid over the (scaled) boundaries such that every cell holds at most one
+// boundary and every boundary keeps its cell within +-margin.  Returns false if none is found.
+bool build_cell_lut(const float* bnd_scaled, int nb, float margin, float* scale, float* offset, float* lut_bnd,
+                    int* lut_base) {
+    const float bmin = bnd_scaled[0], bmax = bnd_scaled[nb - 1];
+    // cells must be much wider than the margin, also when there is a single boundary
+    const float span = fmaxf(bmax - bmin, 1024.f * margin);
+    for (int ta = 1; ta <= 24; ++ta)
+        for (int tb = 1; tb <= 24; ++tb) {
+            const float lo = bmin - span * 0.013f * ta, hi = bmax + span * 0.013f * tb;
+            const float sc = 1.f / (hi - lo), of = -lo * sc;
+            int cells[256];
+            bool ok = true;
+            for (int k = 0; k < nb && ok; ++k) {
+                const int c = host_cell(bnd_scaled[k], sc, of);
+                if (host_cell(bnd_scaled[k] - margin, sc, of) != c || host_cell(bnd_scaled[k] + margin, sc, of) != c) ok = false;
+                if (c <= 0 || c >= kCells - 1) ok = false;  // keep the end cells free of boundaries
+                if (k > 0 && c == cells[k - 1]) ok = false;
+                cells[k] = c;
+            }
+            if (!ok) continue;
+            int k = 0;
+            for (int c = 0; c < kCells; ++c) {
+                lut_base[c] = k;
+                if (k < nb && cells[k] == c) {
+                    lut_bnd[c] = bnd_scaled[k];
+                    ++k;
+                } else {
+                    lut_bnd[c] = INFINITY;
+                }
+            }
+            *scale = sc;
+            *offset = of;
+            return true;
+        }
+    return false;
+}
+
+}  // namespace
+
+struct TensorConsts {
+    void* dev = nullptr;   // one allocation: operand matrices + lookup tables
+    TensorArgs args{};     // pointers into `dev` and the scalar parameters
+};
+
+bool tq_tensor_supported(int d, int bits) { return d == 128 && bits >= 1 && bits <= 4; }
+
+int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection) {
+    const int d = p->dev.d, levels = p->dev.levels, nb = levels - 1;
+    // boundaries exactly as the plan holds them
+    std::vector<float> bnd(nb), bnd_s(nb);
+    for (int k = 0; k < nb; ++k) {
+        volatile float s = codebook[k] + codebook[k + 1];
+        bnd[k] = 0.5f * s;
+        bnd_s[k] = bnd[k] * kAccScale;
+    }
+    for (int k = 1; k < nb; ++k)
+        if (!(bnd_s[k] > bnd_s[k - 1])) return TQ_OK;  // degenerate codebook: leave tensor_ok false
+    for (int k = 0; k < nb; ++k)
+        if (!(fabsf(bnd[k]) < 4.f)) return TQ_OK;
+    float lut_bnd[kCells], lut_cent[kCells], cs = 0.f, co = 0.f;
+    int lut_base[kCells];
+    const float guard = TQ_CODE_GUARD * kAccScale;
+    if (!build_cell_lut(bnd_s.data(), nb, 4.f * guard, &cs, &co, lut_bnd, lut_base)) return TQ_OK;
+    for (int l = 0; l < kCells; ++l) lut_cent[l] = codebook[l % levels] * kAccScale;
+
+    const size_t dd = (size_t)d * d;
+    const int nmat = projection ? 4 : 2;
+    std::vector<uint16_t> mats(dd * nmat, 0);
+    std::vector<double> m(dd);
+    for (size_t i = 0; i < dd; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
+    split_operand(m, d, kScaleB, mats.data(), mats.data() + dd);
+    if (projection) {
+        // B2[n=j][k] = (R S^T)[k][j] = sum_i R[k][i] S[j][i]
+        for (int j = 0; j < d; ++j)
+            for (int k = 0; k < d; ++k) {
+                double acc = 0.0;
+                for (int i = 0; i < d; ++i) acc += (double)rotation[(size_t)k * d + i] * (double)projection[(size_t)j * d + i];
+                m[(size_t)j * d + k] = acc;
+            }
+        split_operand(m, d, kScaleM, mats.data() + 2 * dd, mats.data() + 3 * dd);
+    }
+    const size_t mat_bytes = mats.size() * 2;
+    const size_t total = mat_bytes + 3 * kCells * 4;
+    TensorConsts* t = new TensorConsts();
+    cudaError_t e = cudaMalloc(&t->dev, total);
+    if (e != cudaSuccess) {
+        delete t;
+        return tq_fail(TQ_ERR_CUDA, "cudaMalloc(%zu) failed: %s", total, cudaGetErrorString(e));
+    }
+    unsigned char* base = static_cast<unsigned char*>(t->dev);
+    bool ok = cudaMemcpy(base, mats.data(), mat_bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(base + mat_bytes, lut_bnd, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(base + mat_bytes + kCells * 4, lut_base, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(base + mat_bytes + 2 * kCells * 4, lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    if (!ok || !encode_tiled_fn()) {
+        cudaFree(t->dev);
+        delete t;
+        return tq_fail(TQ_ERR_CUDA, "upload of tensor-path constants failed");
+    }
+    t->args.bmat = reinterpret_cast<const __half*>(base);
+    t->args.lut_bnd = reinterpret_cast<const float*>(base + mat_bytes);
+    t->args.lut_base = reinterpret_cast<const int*>(base + mat_bytes + kCells * 4);
+    t->args.lut_cent = reinterpret_cast<const float*>(base + mat_bytes + 2 * kCells * 4);
+    t->args.cell_scale = cs;
+    t->args.cell_offset = co;
+    t->args.code_guard = guard;
+    // accumulator 2 holds 2^10 * 16 * (residual . S row)
+    t->args.sign_guard = TQ_SIGN_GUARD * 1024.f * kScaleM;
+    p->tensor = t;
+    p->tensor_ok = true;
+    return TQ_OK;
+}
+
+void tq_tensor_plan_free(tq_plan* p) {
+    if (p->tensor) {
+        if (p->tensor->dev) cudaFree(p->tensor->dev);
+        delete p->tensor;
+        p->tensor = nullptr;
+    }
+}
+
+template <int D, int BITS, bool PROD>
+static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
+    const int sm = Smem<D, PROD>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize_kernel<D, BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    tensor_quantize_kernel<D, BITS, PROD><<<grid, kThreads, sm, st>>>(map, args);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
+int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
+                              uint32_t* signs, float* rnorms, float* norms, uint32_t* rowmask, cudaStream_t st) {
+    if (!p->tensor) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for this plan");
+    const int d = p->dev.d;
+    if (n > (int64_t)0x7fffff00) return tq_fail(TQ_ERR_UNSUPPORTED, "n above 2^31 rows per call");
+    TensorArgs args = p->tensor->args;
+    args.n = n;
+    args.ntiles = (n + kTileRows - 1) / kTileRows;
+    args.codes = codes;
+    args.signs = signs;
+    args.norms = norms;
+    args.rnorms = rnorms;
+    args.rowmask = rowmask;
+    args.status = p->counters + 1;
+
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)d, (cuuint64_t)n};
+    const cuuint64_t gstride[1] = {(cuuint64_t)d * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kTileRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), gdim, gstride,
+                                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tq_fail(TQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
+    const int grid = (int)(args.ntiles < sms ? args.ntiles : sms);
+    const int bits = p->dev.bits;
+#define TQ_DISPATCH(B)                                                                        \
+    case B:                                                                                   \
+        return prod ? launch_one<128, B, true>(map, args, grid, st) : launch_one<128, B, false>(map, args, grid, st);
+    switch (bits) {
+        TQ_DISPATCH(1)
+        TQ_DISPATCH(2)
+        TQ_DISPATCH(3)
+        TQ_DISPATCH(4)
+    }
+#undef TQ_DISPATCH
+    return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for bits=%d", bits);
 }

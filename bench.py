@@ -1,0 +1,323 @@
+#!/usr/bin/env python3
+"""Benchmark of the TurboQuant hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (one "step" = one pass of the hot path over one batch, per GPU):
+TurboQuantProd(dimension=128, bits=4, seed=2026) -- quantize 1,048,576 float32 N(0,1) keys, then
+score 32 float32 N(0,1) queries against all of them (32 x 1,048,576 float32 score matrix) with the
+per-query top-100 fused into the same pass.  With N > 1 GPUs every rank owns its own shard of that
+size (weak scaling, no collective on the data path) and the per-shard top-100 candidates are
+all-gathered over NCCL and merged, which is the only exchange the path has.
+
+The JSON line carries: `value` = quantize throughput with inputs resident in HBM (whole job, all
+ranks), `attention_score` = the scoring throughput of the same step, `roofline` for each against
+the measured HBM copy bandwidth, `e2e` = the same quantize metric through the public Python API
+with pinned host buffers (H2D of the keys and D2H of the packed encoding inside the timed
+region), and `cpu_baseline` = the NumPy oracle on this host's cores on a bounded sample.
+
+`--impl reference` times the CPU restatement of the reference's NumPy path (oracle/) on all host
+threads, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, BITS, SEED = 128, 4, 2026
+N_KEYS, N_QUERIES, TOPK = 1 << 20, 32, 100
+B_MSE = max(BITS - 1, 1)
+QUANT_BYTES_PER_VEC = 4 * D + D * B_MSE // 8 + D // 8 + 8            # read fp32 row, write codes+signs+2 norms
+SCORE_BYTES_PER_KEY = D * B_MSE // 8 + D // 8 + 8 + 4 * N_QUERIES    # read packed key, write 32 scores
+METRIC = "quantize Mvec/s & attention_score Gkeys/s; % HBM roofline"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        busy = [s for s in sm if s > 0.5 * max(mx)] if sm else []
+        return {"sm_mhz": statistics.median(busy or sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def oracle_params():
+    from oracle import turboquant_oracle as orc
+    return orc, orc.prod_params(D, BITS, seed=SEED)
+
+
+def time_oracle(n_quant, n_score_keys, n_score_queries, repeats):
+    """Best-of-`repeats` CPU times of the oracle on a bounded sample: (quantize s, score s per query)."""
+    orc, pp = oracle_params()
+    rng = np.random.default_rng(20262)
+    keys = rng.standard_normal((n_quant, D)).astype(np.float32)
+    queries = rng.standard_normal((n_score_queries, D)).astype(np.float32)
+    tq = []
+    enc = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        enc = orc.prod_quantize(pp, keys)
+        tq.append(time.perf_counter() - t0)
+    sub = tuple(a[:n_score_keys] if hasattr(a, "shape") and a.shape[:1] == (n_quant,) else a for a in enc[:4]) + ((n_score_keys,),)
+    ts = []
+    for q in queries:
+        t0 = time.perf_counter()
+        orc.prod_attention_score(pp, q, *sub)
+        ts.append(time.perf_counter() - t0)
+    return min(tq), min(ts)
+
+
+def host_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        n = [i.get("num_threads") for i in threadpool_info() if i.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return len(os.sched_getaffinity(0))
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_sample = 65536  # about half a second of CPU work per step
+    tq_steps, ts_steps = [], []
+    for _ in range(args.warmup):
+        time_oracle(n_sample, n_sample, 1, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        a, b = time_oracle(n_sample, n_sample, 1, 1)
+        tq_steps.append(a)
+        ts_steps.append(b)
+    wall = time.perf_counter() - t0
+    mvec = n_sample / statistics.mean(tq_steps) / 1e6
+    # the reference scores one query per call: 32 queries cost 32 passes over the keys
+    gkeys = n_sample / (statistics.mean(ts_steps) * N_QUERIES) / 1e9
+    cores = host_threads()
+    sample = (f"oracle port of the reference NumPy path, {n_sample} of {N_KEYS} keys per step; scoring timed for 1 of "
+              f"{N_QUERIES} queries and multiplied by {N_QUERIES}")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": mvec, "unit": "Mvec/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * wall / max(args.steps, 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "TurboQuantProd d=128 bits=4 seed=2026: quantize + attention_score, CPU sample", "l2": "n/a"},
+        "attention_score": {"value": gkeys, "unit": "Gkeys/s", "queries": N_QUERIES},
+        "cpu_baseline": {"value": mvec, "unit": "Mvec/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": mvec, "unit": "Mvec/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import project_tensor_b200 as tg
+    from project_tensor_b200 import packed_buffers
+    from project_tensor_b200.sharded import merge_topk_across_ranks
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    quant = tg.TurboQuantProd(D, BITS, seed=SEED)
+    gen = torch.Generator(device=dev).manual_seed(20262 * 1000 + rank)
+    keys = torch.randn((N_KEYS, D), generator=gen, device=dev, dtype=torch.float32)
+    queries = torch.randn((N_QUERIES, D), generator=torch.Generator(device=dev).manual_seed(20272),
+                          device=dev, dtype=torch.float32)
+    idx_base = rank * N_KEYS
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    q_ms, s_ms = [], []
+
+    def step(record):
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        enc = quant.quantize(keys)
+        e1.record()
+        top_s, top_i, scores = quant.attention_scores(queries, enc, topk=TOPK, return_matrix=True,
+                                                      index_base=idx_base)
+        e2.record()
+        if world > 1:
+            top_s, top_i = merge_topk_across_ranks(top_s, top_i)
+        if record is not None:
+            record.append((e0, e1, e2))
+        return top_s, top_i, scores
+
+    for _ in range(args.warmup):
+        step(None)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    recs = []
+    t_start, t_end = ev(), ev()
+    t_start.record()
+    for _ in range(args.steps):
+        out = step(recs)
+    t_end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total_ms = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None
+    for e0, e1, e2 in recs:
+        q_ms.append(e0.elapsed_time(e1))
+        s_ms.append(e1.elapsed_time(e2))
+    mine = torch.tensor([total_ms, statistics.mean(q_ms), statistics.mean(s_ms)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(mine, op=dist.ReduceOp.MAX)
+    total_ms, q_mean, s_mean = (float(v) for v in mine.tolist())
+
+    # ---- end to end through the public API with host buffers (pinned), rank-local -------------------
+    host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
+    host_keys.copy_(keys)
+    host_np = host_keys.numpy()
+    e2e_ms = []
+    d2h = 0
+    for it in range(2 + 3):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        enc = quant.quantize(host_np)                          # H2D inside
+        bufs = packed_buffers(enc)
+        host_out = [bufs[k].cpu() for k in ("codes", "signs", "norms", "residual_norms")]  # D2H of the result
+        torch.cuda.synchronize()
+        if it >= 2:
+            e2e_ms.append(1e3 * (time.perf_counter() - t0))
+        d2h = sum(t.numel() * t.element_size() for t in host_out)
+    e2e = torch.tensor([statistics.mean(e2e_ms)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    e2e_mean = float(e2e.item())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        quant_gbs = QUANT_BYTES_PER_VEC * N_KEYS / (q_mean * 1e-3) / 1e9
+        score_gbs = SCORE_BYTES_PER_KEY * N_KEYS / (s_mean * 1e-3) / 1e9
+        line = {
+            "metric": METRIC,
+            "value": world * N_KEYS / (q_mean * 1e-3) / 1e6,
+            "unit": "Mvec/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (rotation as 3 fp16 tensor-core passes, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"TurboQuantProd d={D} bits={BITS} seed={SEED}: quantize {N_KEYS} keys + attention_score "
+                                   f"{N_QUERIES} queries (matrix + fused top-{TOPK}) per GPU",
+                       "keys_per_gpu": N_KEYS, "queries": N_QUERIES, "parallelism": f"shard{world}",
+                       "l2": "inputs (512 MiB of keys per GPU) are larger than L2; no flush needed"},
+            "attention_score": {
+                "value": world * N_KEYS / (s_mean * 1e-3) / 1e9, "unit": "Gkeys/s", "queries": N_QUERIES,
+                "ms": s_mean,
+                "roofline": {"bound": "hbm", "achieved": score_gbs, "peak": peak, "unit": "GB/s",
+                             "frac": score_gbs / peak, "frac_of_8TBs": score_gbs / 8000.0, "traffic": None,
+                             "bytes_per_key": SCORE_BYTES_PER_KEY, "peak_kind": peak_kind}},
+            "quantize_ms": q_mean,
+            "roofline": {"bound": "hbm", "achieved": quant_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": quant_gbs / peak, "frac_of_8TBs": quant_gbs / 8000.0, "traffic": None,
+                         "bytes_per_vector": QUANT_BYTES_PER_VEC, "peak_kind": peak_kind,
+                         "kernel": "tq_prod_quantize call (tensor-core kernel + exact second stage)"},
+            "e2e": {"value": world * N_KEYS / (e2e_mean * 1e-3) / 1e6, "unit": "Mvec/s",
+                    "h2d_bytes_per_step": N_KEYS * D * 4, "d2h_bytes_per_step": d2h,
+                    "what": "TurboQuantProd.quantize(pinned NumPy keys) + copy of the packed encoding to the host"},
+            "gpu_launches": args.steps * 4,
+            "clocks": clocks,
+        }
+        if world == 1:
+            n_sample = 262144
+            cq, cs = time_oracle(n_sample, n_sample, 2, 3)
+            line["cpu_baseline"] = {
+                "value": n_sample / cq / 1e6, "unit": "Mvec/s", "cores": host_threads(), "kind": "port",
+                "attention_score_Gkeys_per_s": n_sample / (cs * N_QUERIES) / 1e9,
+                "sample": f"NumPy oracle, quantize {n_sample} of {N_KEYS} keys (best of 3); scoring 1 query x {n_sample} "
+                          f"keys (best of 2) multiplied by {N_QUERIES} queries"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,75 @@
+"""Host-side logic of the multi-GPU path, on CPU: shard arithmetic, and the all-gather + merge
+plumbing run as two gloo ranks with the merge kernel replaced by a NumPy stand-in."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from project_tensor_b200.sharded import gather_score_slabs, merge_topk_across_ranks, shard_range
+
+
+def test_shard_range_covers_everything_once():
+    for n in (0, 1, 7, 8, 134217728, 1000003):
+        for world in (1, 2, 4, 8):
+            spans = [shard_range(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_range(10, 2, 2)
+
+
+def numpy_merge(gs, gi):
+    """Stand-in for tq_topk_merge: descending by score, ties to the earlier list / slot."""
+    gs, gi = gs.numpy(), gi.numpy()
+    lists, queries, k = gs.shape
+    out_s = np.full((queries, k), -np.inf, np.float32)
+    out_i = np.full((queries, k), -1, np.int64)
+    for q in range(queries):
+        s = gs[:, q, :].reshape(-1)
+        i = gi[:, q, :].reshape(-1)
+        valid = i >= 0
+        order = np.lexsort((np.arange(s.size), -s))
+        order = [o for o in order if valid[o]][:k]
+        out_s[q, :len(order)] = s[order]
+        out_i[q, :len(order)] = i[order]
+    return torch.from_numpy(out_s), torch.from_numpy(out_i)
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(7)
+        n, q, k = 64, 3, 5
+        scores = rng.standard_normal((q, n)).astype(np.float32)
+        scores[:, 10] = scores[:, 40]                       # a tie across the two shards
+        lo, hi = shard_range(n, rank, world)
+        local = scores[:, lo:hi]
+        order = np.argsort(-local, axis=1, kind="stable")[:, :k]
+        top_s = torch.from_numpy(np.take_along_axis(local, order, axis=1))
+        top_i = torch.from_numpy(order.astype(np.int64) + lo)
+        got_s, got_i = merge_topk_across_ranks(top_s, top_i, merge=numpy_merge)
+        want = np.argsort(-scores, axis=1, kind="stable")[:, :k]
+        assert np.array_equal(got_i.numpy(), want)
+        assert np.array_equal(got_s.numpy(), np.take_along_axis(scores, want, axis=1))
+        slab = gather_score_slabs(torch.from_numpy(local.copy()))
+        assert np.array_equal(slab.numpy(), scores)
+        ret[rank] = True
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gather_and_merge_over_gloo():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert ret.get(0) and ret.get(1)

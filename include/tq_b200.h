@@ -21,8 +21,10 @@
  * Packed layouts (row = one vector / key)
  *   codes : row stride tq_code_row_bytes() = 4*ceil(d*bits/32) bytes; coordinate j occupies bits
  *           [j*bits, (j+1)*bits) of the row read as a little-endian bit stream; padding bits are 0.
- *   signs : row stride tq_sign_row_bytes() = 4*ceil(d/32) bytes; bit j is 1 when the QJL sign of
- *           coordinate j is +1 (the reference stores +1/-1 int8, _quant.py:67-70).
+ *   signs : row stride tq_sign_row_bytes() = 4*ceil(d/32) bytes, one 32-bit word per 32 coordinates;
+ *           inside a word the even coordinates take bits 0..15 and the odd ones bits 16..31
+ *           (coordinate j -> bit ((j%32)>>1) + 16*(j&1)); a bit is 1 when the QJL sign is +1
+ *           (the reference stores +1/-1 int8, _quant.py:67-70).
  */
 #ifndef TQ_B200_H
 #define TQ_B200_H
@@ -76,7 +78,8 @@ int64_t tq_code_row_bytes(const tq_plan* plan);
 int64_t tq_sign_row_bytes(const tq_plan* plan);
 /* Scratch bytes tq_mse_quantize / tq_prod_quantize need for n rows (may be 0). */
 int64_t tq_quantize_scratch_bytes(const tq_plan* plan, int64_t n);
-/* Scratch bytes tq_score_batched needs when topk > 0 (0 when topk == 0). */
+/* Scratch bytes tq_score_batched needs for these sizes (prepared queries, and for topk > 0 the
+ * candidate lists and, when no score matrix is requested, a chunk of scores).  May be > 0 for topk == 0. */
 int64_t tq_topk_scratch_bytes(const tq_plan* plan, int groups, int q_per_group,
                               int64_t keys_per_group, int topk);
 

@@ -290,7 +290,7 @@ int tq_score_broadcast(const tq_plan* p, const float* q, const void* codes, cons
     TQ_TRY(check_encoding(codes, signs, residual_norms, norms));
     TQ_TRY(check_ptr(scores, "scores"));
     DeviceScope scope(p->device);
-    return tq_launch_score_batched(p, q, 1, 1, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
+    return tq_launch_score_general(p, q, 1, 1, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
                                    residual_norms, norms, n, scores, 0, nullptr, nullptr, 0, nullptr, 0,
                                    static_cast<cudaStream_t>(stream));
 }

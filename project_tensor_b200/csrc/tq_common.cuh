@@ -84,6 +84,11 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
                             cudaStream_t st);
+int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                            const uint32_t* signs, const float* rnorms, const float* norms,
+                            int64_t keys_per_group, float* scores, int topk, float* top_scores,
+                            int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
+                            cudaStream_t st);
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk);
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
                          float* out_scores, int64_t* out_idx, cudaStream_t st);
@@ -95,6 +100,21 @@ int tq_launch_unpack_signs(const tq_plan* p, const uint32_t* signs, int64_t n, i
 int tq_launch_pack_signs(const tq_plan* p, const int8_t* in, int64_t n, uint32_t* signs, cudaStream_t st);
 
 // ---- small device helpers ---------------------------------------------------------------------
+// Bit position of coordinate j's QJL sign inside its 32-bit word: the even coordinates of a group of
+// 32 fill bits 0..15 and the odd ones bits 16..31, so coordinates (2i, 2i+1) sit exactly 16 bits
+// apart -- the two halves of one half2 operand of the scoring kernel.
+__host__ __device__ __forceinline__ int tq_sign_bitpos(int j) { return ((j & 31) >> 1) + ((j & 1) << 4); }
+
+// Re-order a word whose bit i belongs to coordinate i (e.g. a ballot) into the stored order above.
+__device__ __forceinline__ uint32_t tq_sign_word_from_natural(uint32_t w) {
+    uint32_t e = w & 0x55555555u, o = (w >> 1) & 0x55555555u;
+    e = (e | (e >> 1)) & 0x33333333u; o = (o | (o >> 1)) & 0x33333333u;
+    e = (e | (e >> 2)) & 0x0f0f0f0fu; o = (o | (o >> 2)) & 0x0f0f0f0fu;
+    e = (e | (e >> 4)) & 0x00ff00ffu; o = (o | (o >> 4)) & 0x00ff00ffu;
+    e = (e | (e >> 8)) & 0x0000ffffu; o = (o | (o >> 8)) & 0x0000ffffu;
+    return e | (o << 16);
+}
+
 // Code of coordinate j in a packed row (little-endian bit stream, `bits` <= 8).
 __device__ __forceinline__ uint32_t tq_get_code(const uint32_t* row, int j, int bits) {
     const int bit = j * bits;

@@ -183,7 +183,7 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
                     for (int c = 0; c < 4; ++c) {
                         const int j = j0 + lane + 32 * c;
                         const uint32_t word = __ballot_sync(0xffffffffu, j < d && acc[c] >= 0.f);
-                        if (lane == 0 && j0 + 32 * c < d) srow[(j0 >> 5) + c] = word;
+                        if (lane == 0 && j0 + 32 * c < d) srow[(j0 >> 5) + c] = tq_sign_word_from_natural(word);
                     }
                 }
             }
@@ -205,7 +205,7 @@ exact_dequantize_kernel(TqDev p, const uint32_t* __restrict__ codes, const uint3
         const uint32_t* crow = codes + row * p.code_words;
         for (int k = lane; k < d; k += 32) {
             wb.a[k] = __ldg(p.codebook + tq_get_code(crow, k, p.bits));
-            if (PROD) wb.b[k] = ((signs[row * p.sign_words + (k >> 5)] >> (k & 31)) & 1u) ? 1.f : -1.f;
+            if (PROD) wb.b[k] = ((signs[row * p.sign_words + (k >> 5)] >> tq_sign_bitpos(k)) & 1u) ? 1.f : -1.f;
         }
         __syncwarp();
         const float nrm = norms[row];
@@ -260,7 +260,7 @@ exact_pairwise_score_kernel(TqDev p, const float* __restrict__ q, const uint32_t
                 float a = 0.f, b = 0.f;
                 if (j < d) {
                     a = __fmul_rn(qa[j], r[c]);
-                    b = ((srow[j >> 5] >> (j & 31)) & 1u) ? s[c] : -s[c];
+                    b = ((srow[j >> 5] >> tq_sign_bitpos(j)) & 1u) ? s[c] : -s[c];
                 }
                 t1[cnt] = a;
                 t2[cnt] = b;

@@ -39,7 +39,7 @@ __global__ void unpack_signs_kernel(const uint32_t* __restrict__ signs, int64_t 
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t row = i / d;
         const int j = (int)(i - row * d);
-        out[i] = ((signs[row * words + (j >> 5)] >> (j & 31)) & 1u) ? (int8_t)1 : (int8_t)-1;
+        out[i] = ((signs[row * words + (j >> 5)] >> tq_sign_bitpos(j)) & 1u) ? (int8_t)1 : (int8_t)-1;
     }
 }
 
@@ -52,7 +52,7 @@ __global__ void pack_signs_kernel(const int8_t* __restrict__ in, int64_t n, int 
         uint32_t v = 0;
         for (int b = 0; b < 32; ++b) {
             const int j = w * 32 + b;
-            if (j < d && in[row * d + j] >= 0) v |= 1u << b;
+            if (j < d && in[row * d + j] >= 0) v |= 1u << tq_sign_bitpos(j);
         }
         signs[i] = v;
     }

@@ -106,7 +106,7 @@ score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __re
                 for (int j = 0; j < d; ++j) {
                     if ((j & 31) == 0) sw = srow[j >> 5];
                     const float c = cb[tq_get_code(crow, j, p.bits)];
-                    const float s = (sw >> (j & 31)) & 1u ? 1.f : -1.f;
+                    const float s = (sw >> tq_sign_bitpos(j)) & 1u ? 1.f : -1.f;
 #pragma unroll
                     for (int t = 0; t < kQT; ++t) {
                         a1[t] = fmaf(c, qs[(t * 2) * d + j], a1[t]);
@@ -258,11 +258,35 @@ ScoreGeometry geometry(int groups, int64_t keys_per_group, int topk) {
 
 }  // namespace
 
-int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk) {
-    (void)p;
+int64_t tq_score_tc_scratch(int groups, int qpg, int64_t keys_per_group, int topk);
+int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                       const uint32_t* signs, const float* rnorms, const float* norms, int64_t keys_per_group,
+                       float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
+                       size_t scratch_bytes, cudaStream_t st);
+
+static bool use_tensor_scoring(const tq_plan* p) {
+    return p->path != TQ_PATH_EXACT && p->has_projection && tq_tensor_supported(p->dev.d, p->dev.bits);
+}
+
+static int64_t general_topk_scratch(int groups, int qpg, int64_t keys_per_group, int topk) {
     if (topk <= 0) return 0;
     const ScoreGeometry s = geometry(groups, keys_per_group, topk);
     return (int64_t)groups * s.nblk * qpg * topk * (int64_t)sizeof(unsigned long long);
+}
+
+int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk) {
+    const int64_t a = general_topk_scratch(groups, qpg, keys_per_group, topk);
+    const int64_t b = tq_tensor_supported(p->dev.d, p->dev.bits) ? tq_score_tc_scratch(groups, qpg, keys_per_group, topk) : 0;
+    return a > b ? a : b;
+}
+
+int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int groups, int topk, int64_t idx_base,
+                         float* top_scores, int64_t* top_idx, cudaStream_t st) {
+    const int k2 = pow2_at_least(topk);
+    merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * k2 * sizeof(unsigned long long), st>>>(part, lists, qpg, topk, k2,
+                                                                                           idx_base, top_scores, top_idx);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
 }
 
 int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
@@ -270,9 +294,21 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
                             cudaStream_t st) {
+    if (use_tensor_scoring(p) && keys_per_group > 0 && groups > 0 && qpg > 0)
+        return tq_launch_score_tc(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, topk, top_scores,
+                                  top_idx, idx_base, scratch, scratch_bytes, st);
+    return tq_launch_score_general(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, topk,
+                                   top_scores, top_idx, idx_base, scratch, scratch_bytes, st);
+}
+
+int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                            const uint32_t* signs, const float* rnorms, const float* norms,
+                            int64_t keys_per_group, float* scores, int topk, float* top_scores,
+                            int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
+                            cudaStream_t st) {
     const ScoreGeometry s = geometry(groups, keys_per_group, topk);
     if (topk > 0) {
-        const int64_t need = tq_score_topk_scratch(p, groups, qpg, keys_per_group, topk);
+        const int64_t need = general_topk_scratch(groups, qpg, keys_per_group, topk);
         if (!scratch || (int64_t)scratch_bytes < need)
             return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "top-k scratch: need %lld bytes, got %zu", (long long)need, scratch_bytes);
     }

@@ -1,0 +1,578 @@
+// Tensor-core scoring of TurboQuantProd keys (d = 128, 1..4 code bits) on B200.
+//
+//   score(q, key) = norm * ( (R q) . codebook[codes]  +  alpha * rnorm * ((S q) . signs) )
+//
+// is a small GEMM per tile of 128 keys: the keys are the M side, the (at most 32) queries the N side
+// and the 128 coordinates the K side.  Per tile:
+//
+//   bulk copy (1 thread)   packed codes and sign words of 128 keys -> smem ring (plain 1-D bulk copies)
+//   expanders (8 warps)    one thread per half key: turn packed codes into fp16 operands and store
+//                          them into tensor memory with tcgen05.st (lane = key).  Two codes at a time
+//                          index a lookup table of (hi pair, lo pair) half2 values -- centroid * 2^10
+//                          split into fp16 hi + lo -- replicated per lane in smem so the lookups are
+//                          free of bank conflicts; two sign bits become one half2 of +-1 with a shift
+//                          and a logic op (the sign layout keeps them 16 bits apart for that).
+//   MMA (1 thread)         D1 = C_hi Q_hi + C_lo Q_hi + C_hi Q_lo,  D2 = Sg P_hi + Sg P_lo  (kind::f16,
+//                          fp32 accumulators in TMEM); Q = R q and P = S q are rotated / projected,
+//                          scaled by a power of two and split into fp16 hi + lo once per call by a
+//                          small preparation kernel, and live in smem as the B operand.
+//   epilogue (4 warps)     one thread per key: tcgen05.ld both accumulators, apply the per-query
+//                          descale, alpha * rnorm and norm, store one coalesced 128-byte line per query.
+//
+// A second kernel selects the per-query top-k from a score matrix with a rising threshold and a
+// bitonic prune (the same scheme as the general kernel in tq_score.cu), one block per row segment.
+#include "tq_common.cuh"
+#include "tq_ptx.cuh"
+
+#include <math.h>
+
+namespace {
+
+using namespace tqptx;
+
+constexpr int D = 128;
+constexpr int kTileKeys = 128;
+constexpr int kThreads = 448;
+constexpr int kFirstExpWarp = 2;
+constexpr int kFirstEpiWarp = 10;
+constexpr int kStages = 8;
+constexpr float kCentScale = 1024.f;
+constexpr int kRowBytesB = D * 2;  // one query row of one fp16 operand matrix
+
+__host__ __device__ constexpr int prep_group_bytes(int qpad) { return 4 * qpad * kRowBytesB + 2 * qpad * 4; }
+
+struct ScoreTcArgs {
+    const uint32_t* codes;
+    const uint32_t* signs;
+    const float* rnorms;
+    const float* norms;
+    const unsigned char* prep;    // [groups][prep_group_bytes]
+    const float* codebook;
+    int64_t keys_per_group;       // rows between the first keys of consecutive groups
+    int64_t key_off;              // first key of every group handled by this launch
+    int64_t key_cnt;              // keys per group handled by this launch
+    int64_t tiles_per_group, total_tiles;
+    int nq;                       // live queries (<= QPAD)
+    int64_t out_group_stride;     // floats between groups in `scores`
+    int64_t out_row_stride;       // floats between query rows
+    float* scores;                // points at (group 0, first query of this pass, key_off)
+    float alpha;
+    unsigned long long* status;
+};
+
+enum {
+    SB_K_FULL = 0,      // [8]
+    SB_K_EMPTY = 8,     // [8]
+    SB_A_FULL = 16,     // [2]
+    SB_A_EMPTY = 18,    // [2]
+    SB_D_FULL = 20,     // [2]
+    SB_D_EMPTY = 22,    // [2]
+    SB_B_FULL = 24,     // [2]
+    SB_B_EMPTY = 26,    // [2]
+    SB_COUNT = 28
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int BITS, int QPAD>
+struct ScoreSmem {
+    static constexpr int kLutEntries = 1 << (2 * BITS);
+    static constexpr int kLutBytes = kLutEntries * 32 * 8;
+    static constexpr int kCodeRowBytes = D * BITS / 8;
+    static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + 16);
+    static constexpr int kBBytes = (prep_group_bytes(QPAD) + 127) & ~127;
+    static constexpr int off_lut = 0;
+    static constexpr int off_b = off_lut + kLutBytes;
+    static constexpr int off_ring = off_b + 2 * kBBytes;
+    static constexpr int off_misc = off_ring + kStages * kStageBytes;
+    static constexpr int total = off_misc + 512 + 128;
+};
+
+template <int BITS, int QPAD>
+__global__ void __launch_bounds__(kThreads, 1)
+score_tc_kernel(const ScoreTcArgs a) {
+    using L = ScoreSmem<BITS, QPAD>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const uint32_t smem_base = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + SB_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) { mbar_init(BAR(SB_K_FULL + i), 1); mbar_init(BAR(SB_K_EMPTY + i), 8); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(SB_A_FULL + i), 8);
+            mbar_init(BAR(SB_A_EMPTY + i), 1);
+            mbar_init(BAR(SB_D_FULL + i), 1);
+            mbar_init(BAR(SB_D_EMPTY + i), 4);
+            mbar_init(BAR(SB_B_FULL + i), 1);
+            mbar_init(BAR(SB_B_EMPTY + i), 5);  // last MMA of the group + the four epilogue warps
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {   // pair lookup table: entry e = (code0 | code1 << BITS) -> (half2 hi(c0), hi(c1)), (half2 lo(c0), lo(c1))
+        uint2* lut = reinterpret_cast<uint2*>(smem + L::off_lut);
+        for (int i = threadIdx.x; i < L::kLutEntries * 32; i += kThreads) {
+            const int e = i >> 5;
+            const float c0 = __ldg(a.codebook + (e & ((1 << BITS) - 1))) * kCentScale;
+            const float c1 = __ldg(a.codebook + (e >> BITS)) * kCentScale;
+            const __half2 h = __floats2half2_rn(c0, c1);
+            const float2 hf = __half22float2(h);
+            uint2 v;
+            v.x = *reinterpret_cast<const uint32_t*>(&h);
+            v.y = pack_half2(c0 - hf.x, c1 - hf.y);
+            lut[i] = v;
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // contiguous tile range of this CTA, so that it rarely changes group
+    const int64_t t0 = a.total_tiles * (int64_t)blockIdx.x / gridDim.x;
+    const int64_t t1 = a.total_tiles * (int64_t)(blockIdx.x + 1) / gridDim.x;
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(QPAD >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
+    constexpr uint32_t kBufCols = 256;
+    constexpr uint32_t kColHi = 0, kColLo = 64, kColSg = 128, kColD1 = 192, kColD2 = 224;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int64_t prev_g = -1, gcount = 0;
+            for (int64_t t = t0; t < t1; ++t) {
+                const int64_t g = t / a.tiles_per_group, kt = t - g * a.tiles_per_group;
+                if (g != prev_g) {
+                    const int bb = (int)(gcount & 1);
+                    if (!mbar_wait(BAR(SB_B_EMPTY + bb), (uint32_t)((gcount >> 1) & 1) ^ 1u, abort_flag)) break;
+                    mbar_arrive_expect_tx(BAR(SB_B_FULL + bb), prep_group_bytes(QPAD));
+                    bulk_load(smem_base + L::off_b + bb * L::kBBytes, a.prep + g * prep_group_bytes(QPAD),
+                              prep_group_bytes(QPAD), BAR(SB_B_FULL + bb));
+                    prev_g = g;
+                    ++gcount;
+                }
+                const int64_t i = t - t0;
+                const int s = (int)(i % kStages);
+                if (!mbar_wait(BAR(SB_K_EMPTY + s), (uint32_t)((i / kStages) & 1) ^ 1u, abort_flag)) break;
+                int64_t valid = a.key_cnt - kt * kTileKeys;
+                if (valid > kTileKeys) valid = kTileKeys;
+                const int64_t row0 = g * a.keys_per_group + a.key_off + kt * kTileKeys;
+                const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes, sb = (uint32_t)valid * 16u;
+                mbar_arrive_expect_tx(BAR(SB_K_FULL + s), cb + sb);
+                const uint32_t dst = smem_base + L::off_ring + s * L::kStageBytes;
+                bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(SB_K_FULL + s));
+                bulk_load(dst + kTileKeys * L::kCodeRowBytes, reinterpret_cast<const unsigned char*>(a.signs) + row0 * 16, sb,
+                          BAR(SB_K_FULL + s));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t lbo = 128, sbo = (D / 8) * 128;
+            int64_t prev_g = -1, gcount = 0;
+            int bb = 0;
+            for (int64_t t = t0; t < t1; ++t) {
+                const int64_t i = t - t0;
+                const int b = (int)(i & 1);
+                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                const int64_t g = t / a.tiles_per_group;
+                if (g != prev_g) {
+                    bb = (int)(gcount & 1);
+                    if (!mbar_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
+                    prev_g = g;
+                    ++gcount;
+                }
+                if (!mbar_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
+                if (!mbar_wait(BAR(SB_D_EMPTY + b), par2 ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t base = tmem + b * kBufCols;
+                const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
+#pragma unroll
+                for (int kb = 0; kb < D / 16; ++kb) {
+                    const uint64_t qh = make_smem_desc(bq + 0 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
+                    const uint64_t ql = make_smem_desc(bq + 1 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
+                    const uint64_t ph = make_smem_desc(bq + 2 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
+                    const uint64_t pl = make_smem_desc(bq + 3 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
+                    mma_ts(base + kColD1, base + kColHi + kb * 8, qh, kIdesc, kb > 0);
+                    mma_ts(base + kColD1, base + kColLo + kb * 8, qh, kIdesc, 1);
+                    mma_ts(base + kColD1, base + kColHi + kb * 8, ql, kIdesc, 1);
+                    mma_ts(base + kColD2, base + kColSg + kb * 8, ph, kIdesc, kb > 0);
+                    mma_ts(base + kColD2, base + kColSg + kb * 8, pl, kIdesc, 1);
+                }
+                mma_commit(BAR(SB_D_FULL + b));
+                mma_commit(BAR(SB_A_EMPTY + b));
+                const bool last_of_group = (t + 1 == t1) || ((t + 1) / a.tiles_per_group != g);
+                if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+            }
+        }
+    } else if (warp < kFirstEpiWarp) {
+        // ---- expanders ----------------------------------------------------------------------------
+        const int half = (warp - kFirstExpWarp) >> 2;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
+        constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
+        constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
+        for (int64_t t = t0; t < t1; ++t) {
+            const int64_t i = t - t0;
+            const int s = (int)(i % kStages);
+            const int b = (int)(i & 1);
+            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+            uint32_t w[kHalfWords + 1], sw[2];
+            {
+                const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
+                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * 16) + half * 2;
+#pragma unroll
+                for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
+                w[kHalfWords] = 0;
+                sw[0] = fail ? 0u : ~sg[0];
+                sw[1] = fail ? 0u : ~sg[1];
+            }
+            __syncwarp();
+            if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
+            if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+            if (bar_or(1, 256, fail)) break;
+            tc_fence_after();
+            const uint32_t abase = tmem + lane_addr + b * kBufCols + half * 32;
+#pragma unroll
+            for (int sb = 0; sb < 2; ++sb) {
+                uint32_t hi[16], lo[16], sg[16];
+#pragma unroll
+                for (int p = 0; p < 16; ++p) {
+                    const int pair = sb * 16 + p;
+                    const int bit = pair * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                    uint32_t e;
+                    if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                    else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                    const uint2 v = lut_lane[e * 32];
+                    hi[p] = v.x;
+                    lo[p] = v.y;
+                    // sign word sb covers coordinates 32*sb .. 32*sb+31 of this half; pair p: bits p, 16+p
+                    sg[p] = ((sw[sb] << (15 - p)) & 0x80008000u) | 0x3c003c00u;
+                }
+                tmem_st16(abase + kColHi + sb * 16, hi);
+                tmem_st16(abase + kColLo + sb * 16, lo);
+                tmem_st16(abase + kColSg + sb * 16, sg);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+        }
+    } else {
+        // ---- epilogue -----------------------------------------------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        int64_t prev_g = -1, gcount = 0;
+        int bb = 0;
+        for (int64_t t = t0; t < t1; ++t) {
+            const int64_t i = t - t0;
+            const int b = (int)(i & 1);
+            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            const int64_t g = t / a.tiles_per_group, kt = t - g * a.tiles_per_group;
+            if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
+            const int64_t key = kt * kTileKeys + row;          // within this launch's key range
+            const bool live = key < a.key_cnt;
+            const int64_t grow = g * a.keys_per_group + a.key_off + key;
+            const float nrm = live ? __ldg(a.norms + grow) : 0.f;
+            const float arn = live ? a.alpha * __ldg(a.rnorms + grow) : 0.f;
+            bool fail = !mbar_wait(BAR(SB_D_FULL + b), par2, abort_flag);
+            if (bar_or(2, 128, fail)) break;
+            tc_fence_after();
+            uint32_t d1[QPAD], d2[QPAD];
+            const uint32_t dbase = tmem + lane_addr + b * kBufCols;
+            if constexpr (QPAD == 32) {
+                tmem_ld32(dbase + kColD1, d1);
+                tmem_ld32(dbase + kColD2, d2);
+            } else {
+                tmem_ld16(dbase + kColD1, d1);
+                tmem_ld16(dbase + kColD2, d2);
+            }
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + b));
+            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB);
+            float* out = a.scores + g * a.out_group_stride + key;
+#pragma unroll
+            for (int qi = 0; qi < QPAD; ++qi) {
+                if (qi < a.nq) {
+                    const float2 sc = ds[qi];  // (descale of D1, descale of D2)
+                    const float v = nrm * fmaf(arn, __uint_as_float(d2[qi]) * sc.y, __uint_as_float(d1[qi]) * sc.x);
+                    if (live) out[qi * a.out_row_stride] = v;
+                }
+            }
+            const bool last_of_group = (t + 1 == t1) || ((t + 1) / a.tiles_per_group != g);
+            if (last_of_group) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(SB_B_EMPTY + bb));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 2ull);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// Rotate / project the queries of one pass and lay them out as fp16 hi/lo B operands.
+// grid (QPAD, groups), block 128 (thread = coordinate).
+__global__ void __launch_bounds__(128)
+score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq, int qpad, unsigned char* __restrict__ prep) {
+    __shared__ float qs[D];
+    __shared__ float red[2][4];
+    const int slot = blockIdx.x, g = blockIdx.y, j = threadIdx.x;
+    unsigned char* base = prep + (size_t)g * prep_group_bytes(qpad);
+    const size_t off = (size_t)(slot / 8) * ((D / 8) * 128) + (size_t)(j / 8) * 128 + (size_t)(slot % 8) * 16 + (size_t)(j % 8) * 2;
+    __half* m0 = reinterpret_cast<__half*>(base + 0 * (size_t)qpad * kRowBytesB + off);
+    __half* m1 = reinterpret_cast<__half*>(base + 1 * (size_t)qpad * kRowBytesB + off);
+    __half* m2 = reinterpret_cast<__half*>(base + 2 * (size_t)qpad * kRowBytesB + off);
+    __half* m3 = reinterpret_cast<__half*>(base + 3 * (size_t)qpad * kRowBytesB + off);
+    float2* ds = reinterpret_cast<float2*>(base + 4 * (size_t)qpad * kRowBytesB);
+    if (slot >= nq) {
+        *m0 = *m1 = *m2 = *m3 = __float2half_rn(0.f);
+        if (j == 0) ds[slot] = make_float2(0.f, 0.f);
+        return;
+    }
+    qs[j] = q[((size_t)g * qpg + q0 + slot) * D + j];
+    __syncthreads();
+    float r = 0.f, s = 0.f;
+    for (int k = 0; k < D; ++k) {
+        r = fmaf(qs[k], __ldg(p.Rt + (size_t)k * D + j), r);
+        s = fmaf(qs[k], __ldg(p.St + (size_t)k * D + j), s);
+    }
+    float mr = fabsf(r), ms = fabsf(s);
+    for (int o = 16; o > 0; o >>= 1) {
+        mr = fmaxf(mr, __shfl_xor_sync(0xffffffffu, mr, o));
+        ms = fmaxf(ms, __shfl_xor_sync(0xffffffffu, ms, o));
+    }
+    if ((j & 31) == 0) { red[0][j >> 5] = mr; red[1][j >> 5] = ms; }
+    __syncthreads();
+    mr = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    ms = fmaxf(fmaxf(red[1][0], red[1][1]), fmaxf(red[1][2], red[1][3]));
+    // power-of-two scales that bring the largest magnitude into [512, 1024): safe in fp16, exact to undo
+    const bool okr = mr > 0.f && mr < 3.0e38f, oks = ms > 0.f && ms < 3.0e38f;
+    const float e1 = okr ? ldexpf(1.f, 9 - ilogbf(mr)) : 1.f;
+    const float e2 = oks ? ldexpf(1.f, 9 - ilogbf(ms)) : 1.f;
+    const float rs = r * e1, ss = s * e2;
+    const __half rh = __float2half_rn(rs), sh = __float2half_rn(ss);
+    *m0 = rh;
+    *m1 = __float2half_rn(rs - __half2float(rh));
+    *m2 = sh;
+    *m3 = __float2half_rn(ss - __half2float(sh));
+    if (j == 0) ds[slot] = make_float2(1.f / (e1 * kCentScale), 1.f / e2);
+}
+
+// ---- top-k from a score matrix -----------------------------------------------------------------
+__device__ __forceinline__ uint32_t ordered_bits(float s) {
+    const uint32_t u = __float_as_uint(s);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long make_key(float s, uint32_t row) {
+    return ((unsigned long long)ordered_bits(s) << 32) | (unsigned long long)(0xffffffffu - row);
+}
+__device__ void block_sort_desc(unsigned long long* a, int n2) {
+    for (int k = 2; k <= n2; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const unsigned long long x = a[i], y = a[l];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (x < y) : (x > y)) { a[i] = y; a[l] = x; }
+                }
+            }
+        }
+    __syncthreads();
+}
+
+constexpr int kSelThreads = 256;
+
+// grid (segments, rows): block scans scores[row][seg*seg_len ...) and writes its k best as sortable keys
+// to part[((group*lists_per_group + list_base + seg) * qpg + qi) * topk ...].
+__global__ void __launch_bounds__(kSelThreads)
+topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t group_stride, int qpg, int64_t n,
+                 int64_t seg_len, int64_t first_row_of_group_stride, int64_t key_off, int topk, int cap2,
+                 int lists_per_group, int list_base, unsigned long long* __restrict__ part) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    unsigned long long* buf = reinterpret_cast<unsigned long long*>(smraw);
+    __shared__ int cnt;
+    __shared__ unsigned long long thr;
+    const int seg = blockIdx.x, r = blockIdx.y, g = r / qpg, qi = r - g * qpg;
+    const float* src = scores + g * group_stride + qi * row_stride;
+    const int64_t k0 = (int64_t)seg * seg_len;
+    int64_t k1 = k0 + seg_len;
+    if (k1 > n) k1 = n;
+    if (threadIdx.x == 0) { cnt = 0; thr = 0ull; }
+    __syncthreads();
+    for (int64_t kb = k0; kb < k1; kb += kSelThreads) {
+        const int64_t key = kb + threadIdx.x;
+        if (key < k1) {
+            const unsigned long long ck = make_key(src[key], (uint32_t)(g * first_row_of_group_stride + key_off + key));
+            if (ck > thr) buf[atomicAdd(&cnt, 1)] = ck;
+        }
+        __syncthreads();
+        if (cnt + kSelThreads > cap2) {
+            const int c = cnt;
+            for (int i = c + threadIdx.x; i < cap2; i += kSelThreads) buf[i] = 0ull;
+            block_sort_desc(buf, cap2);
+            if (threadIdx.x == 0) { cnt = topk; thr = buf[topk - 1]; }
+            __syncthreads();
+        }
+    }
+    __syncthreads();
+    {
+        const int c = cnt;
+        for (int i = c + threadIdx.x; i < cap2; i += kSelThreads) buf[i] = 0ull;
+        block_sort_desc(buf, cap2);
+        unsigned long long* dst = part + (((size_t)g * lists_per_group + list_base + seg) * qpg + qi) * topk;
+        for (int i = threadIdx.x; i < topk; i += kSelThreads) dst[i] = buf[i];
+    }
+}
+
+int pow2_at_least(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+template <int BITS, int QPAD>
+int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
+    const int sm = ScoreSmem<BITS, QPAD>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    score_tc_kernel<BITS, QPAD><<<grid, kThreads, sm, st>>>(args);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
+}  // namespace
+
+// ---- host-side planning ---------------------------------------------------------------------------
+constexpr int64_t kChunkKeys = 1 << 20;     // keys per group scored into scratch at a time when only top-k is wanted
+constexpr int64_t kSegLen = 16384;          // scores per selection block
+
+struct ScoreTcPlan {
+    int64_t chunk, nchunks, segs_per_chunk, lists_per_group;
+    size_t prep_bytes, part_bytes, matrix_bytes, total;
+    size_t off_prep, off_part, off_matrix;
+};
+
+static ScoreTcPlan plan_score(int groups, int qpg, int64_t keys_per_group, int topk, bool need_scratch_matrix) {
+    ScoreTcPlan s{};
+    s.chunk = keys_per_group < kChunkKeys ? keys_per_group : kChunkKeys;
+    if (s.chunk < 1) s.chunk = 1;
+    s.nchunks = (keys_per_group + s.chunk - 1) / s.chunk;
+    if (s.nchunks < 1) s.nchunks = 1;
+    s.segs_per_chunk = (s.chunk + kSegLen - 1) / kSegLen;
+    s.lists_per_group = s.nchunks * s.segs_per_chunk;
+    s.prep_bytes = ((size_t)groups * prep_group_bytes(32) + 255) & ~size_t(255);
+    s.part_bytes = topk > 0 ? (((size_t)groups * s.lists_per_group * qpg * topk * 8) + 255) & ~size_t(255) : 0;
+    s.matrix_bytes = (topk > 0 && need_scratch_matrix) ? (((size_t)groups * qpg * s.chunk * 4) + 255) & ~size_t(255) : 0;
+    s.off_prep = 0;
+    s.off_part = s.prep_bytes;
+    s.off_matrix = s.off_part + s.part_bytes;
+    s.total = s.off_matrix + s.matrix_bytes;
+    return s;
+}
+
+int64_t tq_score_tc_scratch(int groups, int qpg, int64_t keys_per_group, int topk) {
+    return (int64_t)plan_score(groups, qpg, keys_per_group, topk, true).total;
+}
+
+int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int groups, int topk, int64_t idx_base,
+                         float* top_scores, int64_t* top_idx, cudaStream_t st);
+
+int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
+                       const uint32_t* signs, const float* rnorms, const float* norms, int64_t keys_per_group,
+                       float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
+                       size_t scratch_bytes, cudaStream_t st) {
+    const ScoreTcPlan sp = plan_score(groups, qpg, keys_per_group, topk, scores == nullptr);
+    if (!scratch || scratch_bytes < sp.total)
+        return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "score scratch: need %zu bytes, got %zu", sp.total, scratch_bytes);
+    unsigned char* sc = static_cast<unsigned char*>(scratch);
+    unsigned char* prep = sc + sp.off_prep;
+    unsigned long long* part = reinterpret_cast<unsigned long long*>(sc + sp.off_part);
+    float* tmp = reinterpret_cast<float*>(sc + sp.off_matrix);
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
+    const int bits = p->dev.bits;
+
+    if (topk > 0) TQ_CUDA_TRY(cudaMemsetAsync(part, 0, sp.part_bytes, st));  // zero = empty slot
+    const int64_t nchunks = scores ? 1 : sp.nchunks;  // with a caller matrix everything is scored in one go
+    for (int64_t c = 0; c < nchunks; ++c) {
+        const int64_t key_off = scores ? 0 : c * sp.chunk;
+        int64_t key_cnt = scores ? keys_per_group : keys_per_group - key_off;
+        if (!scores && key_cnt > sp.chunk) key_cnt = sp.chunk;
+        float* mat = scores ? scores : tmp;
+        const int64_t row_stride = scores ? keys_per_group : sp.chunk;
+        const int64_t group_stride = (int64_t)qpg * row_stride;
+        for (int q0 = 0; q0 < qpg; q0 += 32) {
+            const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
+            const int qpad = nq <= 16 ? 16 : 32;
+            score_prep_kernel<<<dim3(qpad, groups), 128, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep);
+            TQ_CUDA_TRY(cudaGetLastError());
+            ScoreTcArgs a{};
+            a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
+            a.prep = prep; a.codebook = p->dev.codebook;
+            a.keys_per_group = keys_per_group; a.key_off = key_off; a.key_cnt = key_cnt;
+            a.tiles_per_group = (key_cnt + kTileKeys - 1) / kTileKeys;
+            a.total_tiles = a.tiles_per_group * groups;
+            a.nq = nq;
+            a.out_group_stride = group_stride; a.out_row_stride = row_stride;
+            a.scores = mat + (int64_t)q0 * row_stride;
+            a.alpha = p->dev.alpha;
+            a.status = p->counters + 1;
+            const int grid = (int)(a.total_tiles < sms ? a.total_tiles : sms);
+            int r = TQ_ERR_UNSUPPORTED;
+#define TQ_SC(B)                                                                                             \
+    case B:                                                                                                  \
+        r = qpad == 16 ? launch_score<B, 16>(a, grid, st) : launch_score<B, 32>(a, grid, st);               \
+        break;
+            switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }
+#undef TQ_SC
+            if (r != TQ_OK) return r == TQ_ERR_UNSUPPORTED ? tq_fail(r, "no tensor-core scoring kernel for bits=%d", bits) : r;
+        }
+        if (topk > 0) {
+            const int cap2 = pow2_at_least(topk + kSelThreads);
+            const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
+            // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
+            topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, (size_t)cap2 * 8, st>>>(
+                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, keys_per_group, key_off, topk, cap2,
+                (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part);
+            TQ_CUDA_TRY(cudaGetLastError());
+        }
+    }
+    if (topk > 0)
+        return tq_merge_keys_launch(part, (int)sp.lists_per_group, qpg, groups, topk, idx_base, top_scores, top_idx, st);
+    return TQ_OK;
+}

@@ -489,11 +489,20 @@ class TurboQuantProd:
         torch = _torch()
         lib = _native.load()
         scores = torch.empty((num_codes,), dtype=torch.float32, device=pk.device)
+        handle = self._plans.handle(pk.device)
         with torch.cuda.device(pk.device):
-            fn = lib.tq_score_broadcast if broadcast else lib.tq_score_pairwise
-            _native.check(fn(self._plans.handle(pk.device), _ptr(q), _ptr(pk.codes), _ptr(pk.signs),
-                             _ptr(pk.residual_norms), _ptr(pk.norms), num_codes, _ptr(scores),
-                             _stream_ptr(pk.device)))
+            if broadcast:
+                # one query against all keys is the one-row case of the batched entry point
+                need = int(lib.tq_topk_scratch_bytes(handle, 1, 1, num_codes, 0))
+                scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=pk.device)
+                _native.check(lib.tq_score_batched(handle, _ptr(q), 1, 1, _ptr(pk.codes), _ptr(pk.signs),
+                                                   _ptr(pk.residual_norms), _ptr(pk.norms), num_codes,
+                                                   _ptr(scores), 0, None, None, 0, _ptr(scratch),
+                                                   scratch.numel(), _stream_ptr(pk.device)))
+            else:
+                _native.check(lib.tq_score_pairwise(handle, _ptr(q), _ptr(pk.codes), _ptr(pk.signs),
+                                                    _ptr(pk.residual_norms), _ptr(pk.norms), num_codes,
+                                                    _ptr(scores), _stream_ptr(pk.device)))
         shape = q_prefix if (broadcast or q.shape[0] != 1) else tuple(encoding.prefix_shape)
         return _deliver(scores, staged.kind).reshape(shape)
 

@@ -194,8 +194,8 @@ int64_t tq_sign_row_bytes(const tq_plan* p) { return p ? 4 * (int64_t)p->dev.sig
 
 int64_t tq_quantize_scratch_bytes(const tq_plan* p, int64_t n) {
     if (!p || n < 0) return 0;
-    // one flag bit per row (rows the tensor-core kernel hands to the exact kernel), padded to 16 B
-    return (((n + 31) / 32) * 4 + 15) & ~int64_t(15);
+    // header + list of (row, coordinate) entries + list of rows for the exact second stage
+    return (int64_t)sizeof(TqRecheckHeader) + 8 * (int64_t)tq_recheck_code_cap(n) + 4 * (int64_t)tq_recheck_row_cap(n) + 16;
 }
 
 int64_t tq_topk_scratch_bytes(const tq_plan* p, int groups, int q_per_group, int64_t keys_per_group, int topk) {
@@ -224,12 +224,20 @@ static int quantize_common(const tq_plan* p, bool prod, const float* x, int64_t 
         if (!scratch || (int64_t)scratch_bytes < need)
             return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "quantize scratch: need %lld bytes, got %zu", (long long)need, scratch_bytes);
         TQ_TRY(check_ptr(scratch, "scratch"));
-        uint32_t* mask = static_cast<uint32_t*>(scratch);
+        TqRecheck lists;
+        unsigned char* sc = static_cast<unsigned char*>(scratch);
+        lists.hdr = reinterpret_cast<TqRecheckHeader*>(sc);
+        lists.code_cap = tq_recheck_code_cap(n);
+        lists.row_cap = tq_recheck_row_cap(n);
+        lists.code_entries = reinterpret_cast<unsigned long long*>(sc + sizeof(TqRecheckHeader));
+        lists.row_entries = reinterpret_cast<unsigned int*>(sc + sizeof(TqRecheckHeader) + 8 * (size_t)lists.code_cap);
+        TQ_CUDA_TRY(cudaMemsetAsync(lists.hdr, 0, sizeof(TqRecheckHeader), st));
         TQ_CUDA_TRY(cudaMemsetAsync(p->counters, 0, sizeof(unsigned long long), st));
         TQ_TRY(tq_launch_tensor_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
-                                         rnorms, norms, mask, st));
+                                         rnorms, norms, &lists, st));
+        TQ_TRY(tq_launch_exact_code_check(p, prod, x, n, static_cast<uint32_t*>(codes), &lists, st));
         return tq_launch_exact_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
-                                        rnorms, norms, mask, p->counters, st);
+                                        rnorms, norms, &lists, p->counters, st);
     }
     if (err != TQ_OK) return err;
     return tq_launch_exact_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs), rnorms,
@@ -395,6 +403,16 @@ int tq_plan_last_recheck_rows(const tq_plan* p, void* stream, int64_t* rows) {
     *rows = (int64_t)v[0];
     if (v[1] != 0) return tq_fail(TQ_ERR_CUDA, "a tensor-core kernel gave up on a bounded wait (status %llu)", v[1]);
     return TQ_OK;
+}
+
+// Debug helpers (not part of the public header): raw access to the plan's counter block.
+int tq_debug_read_counters(const tq_plan* p, long long* out, int n) {
+    if (!p || n > 32) return -1;
+    return cudaMemcpy(out, p->counters, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
+}
+int tq_debug_zero_counters(const tq_plan* p) {
+    if (!p) return -1;
+    return cudaMemset(p->counters, 0, 256) == cudaSuccess ? 0 : -3;
 }
 
 }  // extern "C"

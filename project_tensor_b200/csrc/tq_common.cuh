@@ -19,6 +19,26 @@
 // Same idea for the QJL projection, whose sign is taken at zero.
 #define TQ_SIGN_GUARD 4.0e-6f
 
+// Work lists that the tensor-core quantizers leave in the caller's scratch buffer for the exact
+// second stage.  Layout of the scratch: this header (64 bytes), then `code_cap` 64-bit entries
+// (row << 8 | coordinate: a rotated coordinate inside the guard band of a boundary), then `row_cap`
+// 32-bit row numbers (rows to recompute completely).  If a list overflows, `overflow` is set and
+// the second stage recomputes every row instead.
+struct TqRecheckHeader {
+    unsigned int n_codes;    // entries appended to the coordinate list (may exceed code_cap)
+    unsigned int n_rows;     // entries appended to the row list (may exceed row_cap)
+    unsigned int overflow;
+    unsigned int pad[13];
+};
+struct TqRecheck {
+    TqRecheckHeader* hdr;
+    unsigned long long* code_entries;
+    unsigned int* row_entries;
+    unsigned int code_cap, row_cap;
+};
+__host__ __device__ __forceinline__ unsigned int tq_recheck_code_cap(int64_t n) { return (unsigned int)(n / 2 + 4096); }
+__host__ __device__ __forceinline__ unsigned int tq_recheck_row_cap(int64_t n) { return (unsigned int)(n / 8 + 4096); }
+
 // Device-side view of a plan: plain pointers, passed to kernels by value.
 struct TqDev {
     int d;             // vector dimension
@@ -58,11 +78,14 @@ int tq_fail(int code, const char* fmt, ...);
     } while (0)
 
 // ---- launchers implemented in the kernel files -----------------------------------------------
-// Exact (reference-order float32) kernels.  `rowmask` (may be null) restricts the work to rows
-// whose bit is set: bit (i & 31) of word (i >> 5).
+// Exact (reference-order float32) kernels.  With `lists` null every row is computed; otherwise
+// first the listed coordinates are re-decided (tq_launch_exact_code_check), then the listed rows
+// are recomputed.
 int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
-                             uint32_t* signs, float* rnorms, float* norms, const uint32_t* rowmask,
+                             uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists,
                              unsigned long long* redo_counter, cudaStream_t st);
+int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
+                               const TqRecheck* lists, cudaStream_t st);
 int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs,
                                const float* rnorms, const float* norms, int64_t n, float* out,
                                cudaStream_t st);
@@ -75,7 +98,7 @@ bool tq_tensor_supported(int d, int bits);
 int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection);
 void tq_tensor_plan_free(tq_plan* p);
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
-                              uint32_t* signs, float* rnorms, float* norms, uint32_t* rowmask,
+                              uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists,
                               cudaStream_t st);
 
 // Scoring kernels.

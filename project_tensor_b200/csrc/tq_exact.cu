@@ -12,7 +12,7 @@
 //   * every other elementwise step is a separately rounded float32 operation (no contraction).
 //
 // One warp owns one row.  These kernels serve arbitrary (d <= 1024, bits <= 8); they are also the
-// second stage of the tensor-core quantizers, which hand over the rows they flagged (`rowmask`).
+// second stage of the tensor-core quantizers, which hand over lists of coordinates and rows to re-decide.
 #include "tq_common.cuh"
 
 namespace {
@@ -111,84 +111,209 @@ size_t smem_bytes(int d) {
 }
 
 // TurboQuantMSE.quantize / TurboQuantProd.quantize, array part (_quant.py:224-236, 300-308).
+// One block works on kRB rows at a time with one thread per output coordinate, so that every matrix
+// element fetched from L1/L2 feeds kRB chains; the vectors sit in shared memory transposed ([k][row])
+// and are read as broadcast float4s.
+constexpr int kRB = 8;
+
+struct RowsSmem {
+    float* vt;      // [d][kRB]   unit vectors, later residuals (transposed)
+    float* ct;      // [d][kRB]   centroid values (transposed)
+    float* sq;      // [kRB][dp]  squares, row-major for the pairwise sums
+    uint8_t* cs;    // [kRB][dp]  codes
+    float* nrm;     // [kRB]
+};
+__host__ __device__ inline size_t rows_smem_bytes(int d) {
+    const int dp = (d + 31) & ~31;
+    return (size_t)(2 * d * kRB + kRB * dp + kRB) * sizeof(float) + (size_t)kRB * dp + 64;
+}
+
 template <bool PROD>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(1024)
 exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                       uint32_t* __restrict__ signs, float* __restrict__ rnorms, float* __restrict__ norms,
-                      const uint32_t* __restrict__ rowmask, unsigned long long* redo_counter) {
+                      TqRecheck lists, unsigned long long* redo_counter) {
     extern __shared__ float smem[];
-    const int d = p.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const WarpBufs wb = warp_bufs(smem, d, warp);
-    const int64_t nwords = (n + 31) >> 5;
-    const int64_t wstride = (int64_t)gridDim.x * kWarps;
+    const int d = p.d, dp = (d + 31) & ~31;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+    RowsSmem sm;
+    sm.vt = smem;
+    sm.ct = sm.vt + (size_t)d * kRB;
+    sm.sq = sm.ct + (size_t)d * kRB;
+    sm.nrm = sm.sq + (size_t)kRB * dp;
+    sm.cs = reinterpret_cast<uint8_t*>(sm.nrm + kRB);
+    const int tj = t < d ? t : d - 1;  // coordinate this thread computes (threads beyond d mirror the last one)
 
-    for (int64_t wi = (int64_t)blockIdx.x * kWarps + warp; wi < nwords; wi += wstride) {
-        uint32_t m = rowmask ? rowmask[wi] : 0xffffffffu;
-        if (rowmask && m && lane == 0 && redo_counter) atomicAdd(redo_counter, (unsigned long long)__popc(m));
-        while (m) {
-            const int bit = __ffs(m) - 1;
-            m &= m - 1;
-            const int64_t row = wi * 32 + bit;
-            if (row >= n) break;
-            const float* xr = x + row * d;
+    // all rows, or the rows of the list (every row again if a list overflowed)
+    const bool listed = lists.hdr != nullptr && lists.hdr->overflow == 0;
+    const int64_t limit = listed ? (int64_t)min(lists.hdr->n_rows, lists.row_cap) : n;
+    if (lists.hdr != nullptr && redo_counter && blockIdx.x == 0 && t == 0)
+        atomicAdd(redo_counter, (unsigned long long)limit);
 
-            for (int k = lane; k < d; k += 32) {
-                const float v = xr[k];
-                wb.a[k] = v;
-                wb.b[k] = __fmul_rn(v, v);
-            }
-            __syncwarp();
-            const float nrm = __fsqrt_rn(np_pairwise_sum(wb.b, d, lane));
-            const bool ok = nrm > 0.f;
-            for (int k = lane; k < d; k += 32) wb.a[k] = ok ? __fdiv_rn(wb.a[k], nrm) : 0.f;
-            __syncwarp();
-
-            for (int j0 = 0; j0 < d; j0 += 128) {
-                float acc[4];
-                chain4(wb.a, p.Rt, d, j0, lane, acc);
+    for (int64_t g0 = (int64_t)blockIdx.x * kRB; g0 < limit; g0 += (int64_t)gridDim.x * kRB) {
+        int64_t rows[kRB];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int j = j0 + lane + 32 * c;
-                    if (j < d) {
-                        const int code = count_below(p.boundaries, p.levels - 1, acc[c]);
-                        wb.c[j] = (uint8_t)code;
-                        if (PROD) wb.b[j] = __ldg(p.codebook + code);
-                    }
-                }
-            }
-            __syncwarp();
-            store_packed_codes(wb.c, d, p.bits, p.code_words, lane, codes + row * p.code_words);
-            if (lane == 0) norms[row] = nrm;
-
-            if (PROD) {
-                for (int j0 = 0; j0 < d; j0 += 128) {
-                    float acc[4];
-                    chain4(wb.b, p.R, d, j0, lane, acc);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int j = j0 + lane + 32 * c;
-                        if (j < d) wb.a[j] = __fsub_rn(wb.a[j], acc[c]);  // residual replaces unit
-                    }
-                }
-                __syncwarp();
-                for (int k = lane; k < d; k += 32) wb.b[k] = __fmul_rn(wb.a[k], wb.a[k]);
-                __syncwarp();
-                const float rn = __fsqrt_rn(np_pairwise_sum(wb.b, d, lane));
-                if (lane == 0) rnorms[row] = rn;
-                uint32_t* srow = signs + row * p.sign_words;
-                for (int j0 = 0; j0 < d; j0 += 128) {
-                    float acc[4];
-                    chain4(wb.a, p.St, d, j0, lane, acc);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int j = j0 + lane + 32 * c;
-                        const uint32_t word = __ballot_sync(0xffffffffu, j < d && acc[c] >= 0.f);
-                        if (lane == 0 && j0 + 32 * c < d) srow[(j0 >> 5) + c] = tq_sign_word_from_natural(word);
-                    }
-                }
-            }
-            __syncwarp();
+        for (int r = 0; r < kRB; ++r) {
+            const int64_t idx = g0 + r;
+            int64_t row = idx < limit ? (listed ? (int64_t)lists.row_entries[idx] : idx) : -1;
+            if (row >= n) row = -1;
+            rows[r] = row;
         }
+        __syncthreads();  // previous group fully written out
+#pragma unroll
+        for (int r = 0; r < kRB; ++r) {
+            const float v = (rows[r] >= 0 && t < d) ? x[rows[r] * d + t] : 0.f;
+            if (t < dp) sm.sq[r * dp + t] = __fmul_rn(v, v);
+            if (t < d) sm.vt[t * kRB + r] = v;
+        }
+        __syncthreads();
+        for (int r = warp; r < kRB; r += nwarps) {
+            const float nr = __fsqrt_rn(np_pairwise_sum(sm.sq + r * dp, d, lane));
+            if (lane == 0) sm.nrm[r] = nr;
+        }
+        __syncthreads();
+        if (t < d) {
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) {
+                const float nr = sm.nrm[r];
+                sm.vt[t * kRB + r] = nr > 0.f ? __fdiv_rn(sm.vt[t * kRB + r], nr) : 0.f;
+            }
+        }
+        __syncthreads();
+
+        float acc[kRB];
+        // rotated[j] = sum_k unit[k] * R[j][k]
+#pragma unroll
+        for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
+#pragma unroll 16
+        for (int k = 0; k < d; ++k) {
+            const float m = __ldg(p.Rt + (size_t)k * d + tj);
+            const float4 a = *reinterpret_cast<const float4*>(sm.vt + k * kRB);
+            const float4 b = *reinterpret_cast<const float4*>(sm.vt + k * kRB + 4);
+            acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
+            acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
+            acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
+            acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
+        }
+        if (t < d) {
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) {
+                const int code = count_below(p.boundaries, p.levels - 1, acc[r]);
+                sm.cs[r * dp + t] = (uint8_t)code;
+                if (PROD) sm.ct[t * kRB + r] = __ldg(p.codebook + code);
+            }
+        }
+        __syncthreads();
+        for (int r = warp; r < kRB; r += nwarps) {
+            if (rows[r] < 0) continue;
+            store_packed_codes(sm.cs + r * dp, d, p.bits, p.code_words, lane, codes + rows[r] * p.code_words);
+            if (lane == 0) norms[rows[r]] = sm.nrm[r];
+        }
+
+        if (PROD) {
+            // recon[j] = sum_k centroid[k] * R[k][j];  residual = unit - recon
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
+#pragma unroll 16
+            for (int k = 0; k < d; ++k) {
+                const float m = __ldg(p.R + (size_t)k * d + tj);
+                const float4 a = *reinterpret_cast<const float4*>(sm.ct + k * kRB);
+                const float4 b = *reinterpret_cast<const float4*>(sm.ct + k * kRB + 4);
+                acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
+                acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
+                acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
+                acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
+            }
+            __syncthreads();  // nobody reads unit[k] of other coordinates any more
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) {
+                const float res = t < d ? __fsub_rn(sm.vt[t * kRB + r], acc[r]) : 0.f;
+                if (t < d) sm.vt[t * kRB + r] = res;
+                if (t < dp) sm.sq[r * dp + t] = __fmul_rn(res, res);
+            }
+            __syncthreads();
+            for (int r = warp; r < kRB; r += nwarps) {
+                const float rn = __fsqrt_rn(np_pairwise_sum(sm.sq + r * dp, d, lane));
+                if (lane == 0 && rows[r] >= 0) rnorms[rows[r]] = rn;
+            }
+            // projected[j] = sum_k residual[k] * S[j][k]
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
+#pragma unroll 16
+            for (int k = 0; k < d; ++k) {
+                const float m = __ldg(p.St + (size_t)k * d + tj);
+                const float4 a = *reinterpret_cast<const float4*>(sm.vt + k * kRB);
+                const float4 b = *reinterpret_cast<const float4*>(sm.vt + k * kRB + 4);
+                acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
+                acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
+                acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
+                acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
+            }
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) {
+                const uint32_t word = __ballot_sync(0xffffffffu, t < d && acc[r] >= 0.f);
+                if (lane == 0 && rows[r] >= 0 && warp * 32 < d)
+                    signs[rows[r] * p.sign_words + warp] = tq_sign_word_from_natural(word);
+            }
+        }
+    }
+}
+
+
+// Second stage of the tensor-core quantizers, part 1: one warp per listed (row, coordinate).
+// The coordinate's rotated value is recomputed exactly as the reference does (norm by pairwise sum,
+// IEEE division, one FMA per k, k ascending) and its code re-decided.  If the stored code differs it is
+// patched in place (MSE); for TurboQuantProd the residual of the whole row depends on it, so the
+// row goes to the row list instead.
+__global__ void __launch_bounds__(256)
+exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
+                        TqRecheck lists) {
+    extern __shared__ float smem[];
+    if (lists.hdr->overflow) return;  // the row pass will redo everything
+    const unsigned int count = min(lists.hdr->n_codes, lists.code_cap);
+    const int d = p.d, dp = (d + 31) & ~31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    float* xs = smem + (size_t)warp * 3 * dp;   // row, then unit row
+    float* sq = xs + dp;                        // squares
+    float* rs = sq + dp;                        // row j of the rotation
+    for (unsigned int e = blockIdx.x * nwarps + warp; e < count; e += gridDim.x * nwarps) {
+        const unsigned long long ent = lists.code_entries[e];
+        const int64_t row = (int64_t)(ent >> 8);
+        const int j = (int)(ent & 255u);
+        if (row >= n || j >= d) continue;
+        const float* xr = x + row * d;
+        const float* rj = p.R + (size_t)j * d;
+        __syncwarp();
+        for (int k = lane; k < d; k += 32) {
+            const float v = xr[k];
+            xs[k] = v;
+            sq[k] = __fmul_rn(v, v);
+            rs[k] = __ldg(rj + k);
+        }
+        __syncwarp();
+        const float nrm = __fsqrt_rn(np_pairwise_sum(sq, d, lane));
+        const bool ok = nrm > 0.f;
+        for (int k = lane; k < d; k += 32) xs[k] = ok ? __fdiv_rn(xs[k], nrm) : 0.f;
+        __syncwarp();
+        float acc = 0.f;  // every lane runs the same chain on broadcast reads
+#pragma unroll 8
+        for (int k = 0; k < d; ++k) acc = __fmaf_rn(xs[k], rs[k], acc);
+        if (lane != 0) continue;
+        const uint32_t code = (uint32_t)count_below(p.boundaries, p.levels - 1, acc);
+        uint32_t* crow = codes + row * p.code_words;
+        const uint32_t old = tq_get_code(crow, j, p.bits);
+        if (old == code) continue;
+        if (prod) {
+            const unsigned int pos = atomicAdd(&lists.hdr->n_rows, 1u);
+            if (pos < lists.row_cap) lists.row_entries[pos] = (unsigned int)row;
+            else lists.hdr->overflow = 1u;
+        } else {
+            const uint32_t delta = old ^ code;
+            const int bit = j * p.bits, w = bit >> 5, sh = bit & 31;
+            atomicXor(crow + w, delta << sh);
+            if (sh + p.bits > 32) atomicXor(crow + w + 1, delta >> (32 - sh));
+        }
+        atomicAdd(&lists.hdr->pad[0], 1u);  // diagnostic: codes the exact arithmetic decided differently
     }
 }
 
@@ -298,18 +423,31 @@ int grid_for(int64_t work_items, int per_block) {
 
 }  // namespace
 
+int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
+                               const TqRecheck* lists, cudaStream_t st) {
+    if (n == 0) return TQ_OK;
+    const int dp = (p->dev.d + 31) & ~31;
+    exact_code_check_kernel<<<148 * 4, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
 int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
-                             uint32_t* signs, float* rnorms, float* norms, const uint32_t* rowmask,
+                             uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists_in,
                              unsigned long long* redo_counter, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    const size_t sm = smem_bytes(p->dev.d);
-    const int grid = grid_for((n + 31) / 32, kWarps);
+    const size_t sm = rows_smem_bytes(p->dev.d);
+    TqRecheck none{};
+    const TqRecheck lists = lists_in ? *lists_in : none;
+    // the listed pass does not know its size on the host: a fixed grid strides over the list
+    const int grid = lists_in ? 148 * 4 : grid_for(n, kRB);
+    const int threads = (p->dev.d + 31) & ~31;
     if (prod) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<true><<<grid, kWarps * 32, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, rowmask, redo_counter);
+        exact_quantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter);
     } else {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<false><<<grid, kWarps * 32, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, rowmask, redo_counter);
+        exact_quantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter);
     }
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;

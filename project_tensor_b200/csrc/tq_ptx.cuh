@@ -35,6 +35,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the limit ran out or another thread has already given up.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (*abort_flag) return false;  // somebody already gave up: do not block again
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -64,6 +65,11 @@ __device__ __forceinline__ bool bar_or(int id, int count, bool pred) {
         : "r"(id), "r"(count), "r"((uint32_t)pred)
         : "memory");
     return out != 0;
+}
+
+// Plain named barrier over `count` threads (a multiple of 32).
+__device__ __forceinline__ void bar_sync(int id, int count) {
+    asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {

@@ -25,6 +25,7 @@
 #include "tq_ptx.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -58,6 +59,7 @@ struct ScoreTcArgs {
     float* scores;                // points at (group 0, first query of this pass, key_off)
     float alpha;
     unsigned long long* status;
+    long long* prof;              // optional per-role cycle counters (debug), may be null
 };
 
 enum {
@@ -155,15 +157,22 @@ score_tc_kernel(const ScoreTcArgs a) {
     // contiguous tile range of this CTA, so that it rarely changes group
     const int64_t t0 = a.total_tiles * (int64_t)blockIdx.x / gridDim.x;
     const int64_t t1 = a.total_tiles * (int64_t)(blockIdx.x + 1) / gridDim.x;
-    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(QPAD >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
-    constexpr uint32_t kBufCols = 256;
-    constexpr uint32_t kColHi = 0, kColLo = 64, kColSg = 128, kColD1 = 192, kColD2 = 224;
+    // Instruction descriptors for N = QPAD and N = 2*QPAD (hi and lo query halves side by side).
+    constexpr uint32_t kIdesc1 = (1u << 4) | ((uint32_t)(QPAD >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
+    constexpr uint32_t kIdesc2 = (1u << 4) | ((uint32_t)(2 * QPAD >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
+    // TMEM: two A buffers of 192 columns (C_hi | C_lo | Sg), then the accumulators D1 = [C q_hi | C_hi q_lo]
+    // and D2 = [Sg p_hi | Sg p_lo], 2*QPAD columns each; double-buffered when they fit (QPAD = 16).
+    constexpr uint32_t kBufCols = 192;
+    constexpr uint32_t kColHi = 0, kColLo = 64, kColSg = 128;
+    constexpr int kDBufs = QPAD == 16 ? 2 : 1;
+    constexpr uint32_t kColD = 384, kDCols = 4 * QPAD;
 
     if (warp == 0) {
         if (lane == 0) {
             int64_t prev_g = -1, gcount = 0;
-            for (int64_t t = t0; t < t1; ++t) {
-                const int64_t g = t / a.tiles_per_group, kt = t - g * a.tiles_per_group;
+            int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
+            for (int64_t t = t0; t < t1; ++t, ++kt) {
+                if (kt == a.tiles_per_group) { kt = 0; ++g; }
                 if (g != prev_g) {
                     const int bb = (int)(gcount & 1);
                     if (!mbar_wait(BAR(SB_B_EMPTY + bb), (uint32_t)((gcount >> 1) & 1) ^ 1u, abort_flag)) break;
@@ -192,37 +201,47 @@ score_tc_kernel(const ScoreTcArgs a) {
             const uint32_t lbo = 128, sbo = (D / 8) * 128;
             int64_t prev_g = -1, gcount = 0;
             int bb = 0;
-            for (int64_t t = t0; t < t1; ++t) {
+            int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
+            uint64_t dq_hi = 0, dp_hi = 0;
+            for (int64_t t = t0; t < t1; ++t, ++kt) {
+                if (kt == a.tiles_per_group) { kt = 0; ++g; }
                 const int64_t i = t - t0;
                 const int b = (int)(i & 1);
                 const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-                const int64_t g = t / a.tiles_per_group;
                 if (g != prev_g) {
                     bb = (int)(gcount & 1);
                     if (!mbar_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
                     prev_g = g;
                     ++gcount;
+                    const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
+                    dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
+                    dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
                 }
+                long long c0 = clock64();
                 if (!mbar_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
-                if (!mbar_wait(BAR(SB_D_EMPTY + b), par2 ^ 1u, abort_flag)) break;
+                long long c1 = clock64();
+                const int db = kDBufs == 2 ? b : 0;
+                const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
+                if (!mbar_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
                 tc_fence_after();
+                long long c2 = clock64();
+                if (a.prof && blockIdx.x == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
                 const uint32_t base = tmem + b * kBufCols;
-                const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
+                const uint32_t d1 = tmem + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
 #pragma unroll
                 for (int kb = 0; kb < D / 16; ++kb) {
-                    const uint64_t qh = make_smem_desc(bq + 0 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
-                    const uint64_t ql = make_smem_desc(bq + 1 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
-                    const uint64_t ph = make_smem_desc(bq + 2 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
-                    const uint64_t pl = make_smem_desc(bq + 3 * QPAD * kRowBytesB + kb * 2 * lbo, lbo, sbo);
-                    mma_ts(base + kColD1, base + kColHi + kb * 8, qh, kIdesc, kb > 0);
-                    mma_ts(base + kColD1, base + kColLo + kb * 8, qh, kIdesc, 1);
-                    mma_ts(base + kColD1, base + kColHi + kb * 8, ql, kIdesc, 1);
-                    mma_ts(base + kColD2, base + kColSg + kb * 8, ph, kIdesc, kb > 0);
-                    mma_ts(base + kColD2, base + kColSg + kb * 8, pl, kIdesc, 1);
+                    // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                    const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                    const uint64_t qh = dq_hi + step, ph = dp_hi + step;
+                    // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
+                    mma_ts(d1, base + kColHi + kb * 8, qh, kIdesc2, kb > 0);
+                    mma_ts(d1, base + kColLo + kb * 8, qh, kIdesc1, 1);
+                    mma_ts(d2, base + kColSg + kb * 8, ph, kIdesc2, kb > 0);
                 }
-                mma_commit(BAR(SB_D_FULL + b));
+                mma_commit(BAR(SB_D_FULL + db));
                 mma_commit(BAR(SB_A_EMPTY + b));
-                const bool last_of_group = (t + 1 == t1) || ((t + 1) / a.tiles_per_group != g);
+                if (a.prof && blockIdx.x == 0) a.prof[10] += clock64() - c2;
+                const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
                 if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
             }
         }
@@ -235,12 +254,15 @@ score_tc_kernel(const ScoreTcArgs a) {
         const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
         constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
+        long long pc[5] = {0, 0, 0, 0, 0};
         for (int64_t t = t0; t < t1; ++t) {
             const int64_t i = t - t0;
             const int s = (int)(i % kStages);
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            long long c0 = clock64();
             bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+            long long c1 = clock64(); pc[0] += c1 - c0;
             uint32_t w[kHalfWords + 1], sw[2];
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
@@ -254,9 +276,12 @@ score_tc_kernel(const ScoreTcArgs a) {
             }
             __syncwarp();
             if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
+            c0 = clock64(); pc[1] += c0 - c1;
             if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+            c1 = clock64(); pc[2] += c1 - c0;
             if (bar_or(1, 256, fail)) break;
             tc_fence_after();
+            c0 = clock64(); pc[3] += c0 - c1;
             const uint32_t abase = tmem + lane_addr + b * kBufCols + half * 32;
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb) {
@@ -278,10 +303,16 @@ score_tc_kernel(const ScoreTcArgs a) {
                 tmem_st16(abase + kColLo + sb * 16, lo);
                 tmem_st16(abase + kColSg + sb * 16, sg);
             }
+            c1 = clock64(); pc[4] += c1 - c0;
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+            if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
+                for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
+                a.prof[5] = clock64() - c1;  // last st wait
+                a.prof[6] = t1 - t0;
+            }
         }
     } else {
         // ---- epilogue -----------------------------------------------------------------------------
@@ -290,44 +321,61 @@ score_tc_kernel(const ScoreTcArgs a) {
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         int64_t prev_g = -1, gcount = 0;
         int bb = 0;
-        for (int64_t t = t0; t < t1; ++t) {
+        int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
+        for (int64_t t = t0; t < t1; ++t, ++kt) {
+            if (kt == a.tiles_per_group) { kt = 0; ++g; }
             const int64_t i = t - t0;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            const int64_t g = t / a.tiles_per_group, kt = t - g * a.tiles_per_group;
             if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
             const int64_t key = kt * kTileKeys + row;          // within this launch's key range
             const bool live = key < a.key_cnt;
             const int64_t grow = g * a.keys_per_group + a.key_off + key;
             const float nrm = live ? __ldg(a.norms + grow) : 0.f;
             const float arn = live ? a.alpha * __ldg(a.rnorms + grow) : 0.f;
-            bool fail = !mbar_wait(BAR(SB_D_FULL + b), par2, abort_flag);
+            long long c0 = clock64();
+            const int db = kDBufs == 2 ? b : 0;
+            const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
+            bool fail = !mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
             if (bar_or(2, 128, fail)) break;
             tc_fence_after();
-            uint32_t d1[QPAD], d2[QPAD];
-            const uint32_t dbase = tmem + lane_addr + b * kBufCols;
-            if constexpr (QPAD == 32) {
-                tmem_ld32(dbase + kColD1, d1);
-                tmem_ld32(dbase + kColD2, d2);
-            } else {
-                tmem_ld16(dbase + kColD1, d1);
-                tmem_ld16(dbase + kColD2, d2);
-            }
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + b));
+            long long c1 = clock64();
+            const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols;
             const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB);
             float* out = a.scores + g * a.out_group_stride + key;
+            long long c2 = c1;
 #pragma unroll
-            for (int qi = 0; qi < QPAD; ++qi) {
-                if (qi < a.nq) {
-                    const float2 sc = ds[qi];  // (descale of D1, descale of D2)
-                    const float v = nrm * fmaf(arn, __uint_as_float(d2[qi]) * sc.y, __uint_as_float(d1[qi]) * sc.x);
-                    if (live) out[qi * a.out_row_stride] = v;
+            for (int h = 0; h < QPAD / 16; ++h) {
+                uint32_t ua[16], ub[16], va[16], vb[16];
+                tmem_ld16(dbase + h * 16, ua);                  // C q_hi   (+ C_lo q_hi)
+                tmem_ld16(dbase + QPAD + h * 16, ub);           // C_hi q_lo
+                tmem_ld16(dbase + 2 * QPAD + h * 16, va);       // Sg p_hi
+                tmem_ld16(dbase + 3 * QPAD + h * 16, vb);       // Sg p_lo
+                tmem_wait_ld();
+                if (h == QPAD / 16 - 1) {
+                    c2 = clock64();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));
+                }
+                if (live) {
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const int qi = h * 16 + k;
+                        if (qi < a.nq) {
+                            const float2 sc = ds[qi];  // (descale of D1, descale of D2)
+                            const float s1 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * sc.x;
+                            const float s2 = (__uint_as_float(va[k]) + __uint_as_float(vb[k])) * sc.y;
+                            __stcs(out, nrm * fmaf(arn, s2, s1));
+                            out += a.out_row_stride;
+                        }
+                    }
                 }
             }
-            const bool last_of_group = (t + 1 == t1) || ((t + 1) / a.tiles_per_group != g);
+            if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32) {
+                a.prof[12] += c1 - c0; a.prof[13] += c2 - c1; a.prof[14] += clock64() - c2;
+            }
+            const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
             if (last_of_group) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(SB_B_EMPTY + bb));
@@ -552,6 +600,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             a.scores = mat + (int64_t)q0 * row_stride;
             a.alpha = p->dev.alpha;
             a.status = p->counters + 1;
+            a.prof = getenv("TQ_PROF") ? reinterpret_cast<long long*>(p->counters + 8) : nullptr;
             const int grid = (int)(a.total_tiles < sms ? a.total_tiles : sms);
             int r = TQ_ERR_UNSUPPORTED;
 #define TQ_SC(B)                                                                                             \

@@ -29,6 +29,7 @@
 
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -38,7 +39,7 @@ namespace {
 using namespace tqptx;
 
 constexpr int kTileRows = 128;
-constexpr int kThreads = 448;            // 14 warps: TMA, MMA, 8 converters, 4 epilogue
+constexpr int kThreads = 576;            // 18 warps: TMA, MMA, 8 converters, 8 epilogue
 constexpr int kFirstConvWarp = 2;
 constexpr int kFirstEpiWarp = 10;
 constexpr int kBoxBytes = 128 * 128;     // 128 rows x 32 floats
@@ -52,9 +53,9 @@ constexpr float kCellMul = 31.99998f;
 
 struct TensorArgs {
     const __half* bmat;      // [R_hi | R_lo | M_hi | M_lo], each d*d halves in the interleaved layout
-    const float* lut_bnd;    // [32] boundary of each cell (scaled by 2^20) or +inf
-    const int* lut_base;     // [32] number of boundaries in lower cells
-    const float* lut_cent;   // [32] scaled centroids, entry l = centroid (l mod levels)
+    const float4* cell_lut;  // [32] per cell: boundary (x 2^20, +inf if none), 1 + boundaries below the cell
+                             // (as int bits), -centroid below * 2^10, -centroid above * 2^10
+    const float* code_ncent; // [32] entry l: -centroid(l mod levels) * 2^10
     float cell_scale, cell_offset;
     float code_guard, sign_guard;  // in accumulator units
     int64_t n;
@@ -63,8 +64,9 @@ struct TensorArgs {
     uint32_t* signs;
     float* norms;
     float* rnorms;
-    uint32_t* rowmask;
+    TqRecheck lists;
     unsigned long long* status;  // [0]: set to a non-zero code when a wait timed out
+    long long* prof;             // optional cycle counters per role (debug), may be null
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -76,15 +78,10 @@ struct Smem {
     static constexpr int kBBytes = D * D * 2;                       // one fp16 operand matrix
     static constexpr int kNumB = PROD ? 4 : 2;
     static constexpr int kRingBoxes = PROD ? 5 : 8;
-    static constexpr int kStagePitch = kTileRows + 4;               // words; staging is [word][row]
-    static constexpr int kCodeStageBytes = (D * 4 / 32) * kStagePitch * 4;  // up to 4 bits per coordinate
-    static constexpr int kSignStageBytes = PROD ? (D / 32) * kStagePitch * 4 : 0;
     static constexpr int off_b = 0;
     static constexpr int off_ring = off_b + kNumB * kBBytes;
-    static constexpr int off_codes = off_ring + kRingBoxes * kBoxBytes;
-    static constexpr int off_signs = off_codes + kCodeStageBytes;
-    static constexpr int off_misc = off_signs + kSignStageBytes;    // sumsq exchange, force flags, barriers
-    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512;
+    static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
+    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 2 * kTileRows * 4 + kCells * 16;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
 };
 
@@ -102,6 +99,83 @@ enum {
     BAR_COUNT = 28
 };
 
+// Append work for the exact second stage (rare: about one row in a hundred).
+__device__ __noinline__ void push_code_entries(const TqRecheck& l, int64_t row, int first_coord, uint32_t mask) {
+    while (mask) {
+        const int e = __ffs(mask) - 1;
+        mask &= mask - 1;
+        const unsigned int pos = atomicAdd(&l.hdr->n_codes, 1u);
+        if (pos < l.code_cap) l.code_entries[pos] = ((unsigned long long)row << 8) | (unsigned long long)(first_coord + e);
+        else l.hdr->overflow = 1u;
+    }
+}
+// One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
+// and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
+// the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 by cell, lut_ncent by code.
+template <int BITS, bool PROD>
+__device__ __forceinline__ bool process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
+                                              float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
+                                              uint32_t (&rhi)[16], uint32_t (&rlo)[16], float& rs) {
+    bool near_any = false;
+    float prev_rho = 0.f;
+#pragma unroll
+    for (int k = 0; k <= BITS; ++k) w[k] = 0;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        const float f = __uint_as_float(v[e]);
+        const float u = fma_sat(f, cell_scale, cell_offset);
+        const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
+        const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
+        const int base1 = __shfl_sync(0xffffffffu, lut_base1, cell);
+        const float dlt = f - bnd;
+        const uint32_t code = (uint32_t)base1 - (dlt > 0.f ? 0u : 1u);
+        near_any = near_any || (fabsf(dlt) < guard);
+        const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
+        w[wi] += code << sh;
+        if (sh + BITS > 32) w[wi + 1] += code >> (32 - sh);
+        if (PROD) {
+            const float ncent = __shfl_sync(0xffffffffu, lut_ncent, (int)code);
+            const float r = fmaf(f, kScaleRho, ncent);  // 2^10 * (value - centroid)
+            rs = fmaf(r, r, rs);
+            if (e & 1) {
+                const __half2 h = __floats2half2_rn(prev_rho, r);
+                const float2 hf = __half22float2(h);
+                rhi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                rlo[e >> 1] = pack_half2(prev_rho - hf.x, r - hf.y);
+            } else {
+                prev_rho = r;
+            }
+        }
+    }
+    return near_any;
+}
+
+// Rare path: some value of this 32-column chunk lies inside the guard band; find which ones.
+// Entered by the whole warp when any of its rows has such a value (about one chunk in twelve); the
+// values are read again from tensor memory so that the hot path's register arrays never have to be
+// addressable.  `want` says whether this lane's row takes part.
+__device__ __noinline__ void push_near_codes(const TqRecheck& l, bool want, int64_t row, int first_coord, uint32_t taddr,
+                                             float lut_bnd, float cell_scale, float cell_offset, float guard) {
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+    tmem_wait_ld();
+    uint32_t mask = 0;
+#pragma unroll 4
+    for (int e = 0; e < 32; ++e) {
+        const float f = __uint_as_float(v[e]);
+        const float u = fma_sat(f, cell_scale, cell_offset);
+        const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
+        const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
+        if (fabsf(f - bnd) < guard) mask |= 1u << e;
+    }
+    if (want) push_code_entries(l, row, first_coord, mask);
+}
+__device__ __noinline__ void push_row_entry(const TqRecheck& l, int64_t row) {
+    const unsigned int pos = atomicAdd(&l.hdr->n_rows, 1u);
+    if (pos < l.row_cap) l.row_entries[pos] = (unsigned int)row;
+    else l.hdr->overflow = 1u;
+}
+
 template <int D, int BITS, bool PROD>
 __global__ void __launch_bounds__(kThreads, 1)
 tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
@@ -115,6 +189,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     unsigned char* force = smem + L::off_misc + 2 * kTileRows * 4;                      // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 2 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - 2 * kTileRows * 4 - kCells * 16);  // [2][128]
+    float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - kCells * 16);  // [32]
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -128,14 +204,15 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             mbar_init(BAR(BAR_A_FULL + i), 8);
             mbar_init(BAR(BAR_A_EMPTY + i), 1);
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
-            mbar_init(BAR(BAR_ACC_EMPTY + i), 4);
-            mbar_init(BAR(BAR_RHO_FULL + i), 4);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), 8);
+            mbar_init(BAR(BAR_RHO_FULL + i), 8);
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
-        mbar_init(BAR(BAR_ACC2_EMPTY), 4);
+        mbar_init(BAR(BAR_ACC2_EMPTY), 8);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x < kCells) cell_lut[threadIdx.x] = a.cell_lut[threadIdx.x];
     {   // operand matrices: global -> smem, once per CTA
         const uint4* src = reinterpret_cast<const uint4*>(a.bmat);
         uint4* dst = reinterpret_cast<uint4*>(smem + L::off_b);
@@ -183,42 +260,55 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint32_t sbo = (D / 8) * 128, lbo = 128;
             const uint32_t b_rhi = smem_base + L::off_b, b_rlo = b_rhi + L::kBBytes;
             const uint32_t b_mhi = b_rlo + L::kBBytes, b_mlo = b_mhi + L::kBBytes;
+            // descriptors of k-block 0; the start-address field counts 16-byte units, so k-block kb
+            // (two core matrices further) is the same descriptor + kb * 2 * lbo / 16
+            const uint64_t d_rhi = make_smem_desc(b_rhi, lbo, sbo), d_rlo = make_smem_desc(b_rlo, lbo, sbo);
+            const uint64_t d_mhi = make_smem_desc(b_mhi, lbo, sbo), d_mlo = make_smem_desc(b_mlo, lbo, sbo);
+            (void)d_mhi; (void)d_mlo; (void)b_mlo;
             for (int64_t i = 0; i < my_tiles; ++i) {
                 const int b = (int)(i & 1);
                 const uint32_t par2 = (uint32_t)((i >> 1) & 1);
                 const int ab = PROD ? 0 : b;
                 const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
+                const bool pr = a.prof && blockIdx.x == 0;
+                long long c0 = clock64();
                 if (!mbar_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
+                long long c1 = clock64();
                 if (!mbar_wait(BAR(BAR_ACC_EMPTY + ab), acc_par ^ 1u, abort_flag)) break;
                 tc_fence_after();
+                long long c2 = clock64();
+                if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
                 const uint32_t acc = tmem + ACC_COL(ab);
                 const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
 #pragma unroll
                 for (int kb = 0; kb < D / 16; ++kb) {
-                    const uint64_t dh = make_smem_desc(b_rhi + kb * 2 * lbo, lbo, sbo);
-                    const uint64_t dl = make_smem_desc(b_rlo + kb * 2 * lbo, lbo, sbo);
+                    const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
+                    const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
                     mma_ts(acc, a_hi + kb * 8, dh, kIdesc, kb > 0);
                     mma_ts(acc, a_hi + kb * 8, dl, kIdesc, 1);
                     mma_ts(acc, a_lo + kb * 8, dh, kIdesc, 1);
                 }
                 mma_commit(BAR(BAR_ACC_FULL + ab));
+                c0 = clock64(); if (pr) a.prof[10] += c0 - c2;
                 if (!PROD) {
                     mma_commit(BAR(BAR_A_EMPTY + b));
                 } else {
                     if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
                     if (!mbar_wait(BAR(BAR_ACC2_EMPTY), (uint32_t)(i & 1) ^ 1u, abort_flag)) break;
                     tc_fence_after();
+                    c1 = clock64(); if (pr) a.prof[11] += c1 - c0;
                     const uint32_t acc2 = tmem + kAcc2Col;
 #pragma unroll
                     for (int kb = 0; kb < D / 16; ++kb) {
-                        const uint64_t dh = make_smem_desc(b_mhi + kb * 2 * lbo, lbo, sbo);
-                        const uint64_t dl = make_smem_desc(b_mlo + kb * 2 * lbo, lbo, sbo);
+                        const uint64_t dh = d_mhi + (uint64_t)(kb * 2 * lbo >> 4);
+                        const uint64_t dl = d_mlo + (uint64_t)(kb * 2 * lbo >> 4);
                         mma_ts(acc2, a_hi + kb * 8, dh, kIdesc, kb > 0);
                         mma_ts(acc2, a_hi + kb * 8, dl, kIdesc, 1);
                         mma_ts(acc2, a_lo + kb * 8, dh, kIdesc, 1);
                     }
                     mma_commit(BAR(BAR_ACC2_FULL));
                     mma_commit(BAR(BAR_A_EMPTY + b));
+                    if (pr) a.prof[12] += clock64() - c1;
                 }
             }
         }
@@ -236,6 +326,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             float x[64];
             bool fail = false;
+            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32;
+            long long c0 = clock64(), c1;
 #pragma unroll
             for (int bb = 0; bb < 2; ++bb) {
                 const int64_t g = g_base + half * 2 + bb;
@@ -259,7 +351,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 #pragma unroll
             for (int k = 0; k < 64; ++k) ss = fmaf(x[k], x[k], ss);
             ssq[half * kTileRows + row] = ss;
-            if (bar_or(1, 256, fail)) break;
+            c1 = clock64(); if (pr) a.prof[0] += c1 - c0;
+            bar_sync(1 + quarter, 64);  // the two warps that share these 32 rows
+            c0 = clock64(); if (pr) a.prof[1] += c0 - c1;
             const float tot = ssq[row] + ssq[kTileRows + row];
             const float nrm = sqrtf(tot);
             const bool ok = nrm > 0.f;
@@ -273,8 +367,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 force[(i & 3) * kTileRows + row] = odd ? 1 : 0;
             }
             if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
-            if (bar_or(1, 256, fail)) break;
             tc_fence_after();
+            c1 = clock64(); if (pr) a.prof[2] += c1 - c0;
             const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * 32;
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
@@ -291,23 +385,25 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
             }
+            c0 = clock64(); if (pr) a.prof[3] += c0 - c1;
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + b));
+            if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; }
         }
     } else {
-        // ---- epilogue: one thread per row --------------------------------------------------------
+        // ---- epilogue: two threads per row, each owning two 32-column chunks ------------------------
         const int quarter = warp & 3;
+        const int colhalf = (warp - kFirstEpiWarp) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const float lut_bnd = a.lut_bnd[lane];
-        const int lut_base = a.lut_base[lane];
-        const float lut_cent = a.lut_cent[lane];
-        uint32_t* code_stage = reinterpret_cast<uint32_t*>(smem + L::off_codes);
-        uint32_t* sign_stage = reinterpret_cast<uint32_t*>(smem + L::off_signs);
         constexpr int kCodeWords = D * BITS / 32;  // words per packed row
-        const int et = threadIdx.x - kFirstEpiWarp * 32;  // 0..127
+        // lookup tables held in the lanes of the warp: per cell (boundary, 1 + boundaries below), per code
+        // (- centroid * 2^10)
+        const float lut_bnd = cell_lut[lane].x;
+        const int lut_base1 = __float_as_int(cell_lut[lane].y);
+        const float lut_ncent = a.code_ncent[lane];
         for (int64_t i = 0; i < my_tiles; ++i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
@@ -315,55 +411,41 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const int ab = PROD ? 0 : b;
             const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
             const int64_t grow = tile * kTileRows + row;
-            int64_t rows_valid = a.n - tile * kTileRows;
-            if (rows_valid > kTileRows) rows_valid = kTileRows;
-            bool fail = !mbar_wait(BAR(BAR_ACC_FULL + ab), acc_par, abort_flag);
-            if (bar_or(2, 128, fail)) break;
+            const bool live = grow < a.n;
+            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32;
+            long long c0 = clock64(), c1;
+            mbar_wait(BAR(BAR_ACC_FULL + ab), acc_par, abort_flag);
             tc_fence_after();
-            bool near = force[(i & 3) * kTileRows + row] != 0;
+            c1 = clock64(); if (pr) a.prof[16] += c1 - c0;
+            bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
             float rs = 0.f;
             const uint32_t acc = tmem + lane_addr + ACC_COL(ab);
             const uint32_t a_hi = tmem + lane_addr + A_COL(b);
-#pragma unroll 1
-            for (int ch = 0; ch < D / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld32(acc + ch * 32, v);
-                tmem_wait_ld();
-                uint32_t w[BITS + 1];
+            static_assert(D / 64 == 2, "two chunks per thread");
+            uint32_t v0[32], v1[32];
+            tmem_ld32(acc + (colhalf * 2) * 32, v0);
+            tmem_ld32(acc + (colhalf * 2 + 1) * 32, v1);
+            tmem_wait_ld();
+            if (pr) { const long long cx = clock64(); a.prof[20] += cx - c1; }
 #pragma unroll
-                for (int k = 0; k <= BITS; ++k) w[k] = 0;
-                uint32_t rhi[16], rlo[16];
-                float prev_rho = 0.f;
+            for (int cc = 0; cc < 2; ++cc) {
+                const int ch = colhalf * 2 + cc;
+                uint32_t w[BITS + 1], rhi[16], rlo[16];
+                const bool near_any = cc == 0
+                    ? process_chunk<BITS, PROD>(v0, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
+                    : process_chunk<BITS, PROD>(v1, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
+                if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
+                    uint32_t* dst = a.codes + grow * kCodeWords + ch * BITS;
+                    if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                    else {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float f = __uint_as_float(v[e]);
-                    const float u = fma_sat(f, a.cell_scale, a.cell_offset);
-                    const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
-                    const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
-                    const int base = __shfl_sync(0xffffffffu, lut_base, cell);
-                    const float dlt = f - bnd;
-                    const uint32_t code = (uint32_t)base + (dlt > 0.f ? 1u : 0u);
-                    near = near || (fabsf(dlt) < a.code_guard);
-                    const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
-                    w[wi] |= code << sh;
-                    if (sh + BITS > 32) w[wi + 1] |= code >> (32 - sh);
-                    if (PROD) {
-                        const float cent = __shfl_sync(0xffffffffu, lut_cent, (int)code);
-                        const float rho = f - cent;
-                        rs = fmaf(rho, rho, rs);
-                        const float r = rho * kScaleRho;
-                        if (e & 1) {
-                            const __half2 h = __floats2half2_rn(prev_rho, r);
-                            const float2 hf = __half22float2(h);
-                            rhi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                            rlo[e >> 1] = pack_half2(prev_rho - hf.x, r - hf.y);
-                        } else {
-                            prev_rho = r;
-                        }
+                        for (int k = 0; k < BITS; ++k) dst[k] = w[k];
                     }
                 }
-#pragma unroll
-                for (int k = 0; k < BITS; ++k) code_stage[(ch * BITS + k) * L::kStagePitch + row] = w[k];
+                const bool want = near_any && live && !redo_row;
+                if (__any_sync(0xffffffffu, want))
+                    push_near_codes(a.lists, want, grow, ch * 32, acc + ch * 32, lut_bnd, a.cell_scale, a.cell_offset, a.code_guard);
                 if (PROD) {
                     tmem_st16(a_hi + ch * 16, rhi);
                     tmem_st16(a_hi + kABlock + ch * 16, rlo);
@@ -371,7 +453,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             }
             if (PROD) {
                 tmem_wait_st();
-                if (grow < a.n) a.rnorms[grow] = sqrtf(rs) * (1.f / kAccScale);
+                rs_part[colhalf * kTileRows + row] = rs;
             }
             tc_fence_before();
             __syncwarp();
@@ -379,13 +461,18 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 mbar_arrive(BAR(BAR_ACC_EMPTY + ab));
                 if (PROD) mbar_arrive(BAR(BAR_RHO_FULL + b));
             }
+            c0 = clock64(); if (pr) a.prof[17] += c0 - c1;
             if (PROD) {
-                fail = !mbar_wait(BAR(BAR_ACC2_FULL), (uint32_t)(i & 1), abort_flag);
-                if (bar_or(2, 128, fail)) break;
+                mbar_wait(BAR(BAR_ACC2_FULL), (uint32_t)(i & 1), abort_flag);
+                bar_sync(5 + quarter, 64);  // rs_part of both column halves of these 32 rows is written
                 tc_fence_after();
+                c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
+                if (colhalf == 0 && live)
+                    a.rnorms[grow] = sqrtf(rs_part[row] + rs_part[kTileRows + row]) * kScaleRho;  // rs is in 2^10 units
                 const uint32_t acc2 = tmem + lane_addr + kAcc2Col;
 #pragma unroll 1
-                for (int ch = 0; ch < D / 32; ++ch) {
+                for (int cc = 0; cc < D / 64; ++cc) {
+                    const int ch = colhalf * (D / 64) + cc;
                     uint32_t v[32];
                     tmem_ld32(acc2 + ch * 32, v);
                     tmem_wait_ld();
@@ -394,37 +481,16 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     for (int e = 0; e < 32; ++e) {
                         const float f = __uint_as_float(v[e]);
                         word |= (f >= 0.f ? 1u : 0u) << ((e >> 1) + ((e & 1) << 4));
-                        near = near || (fabsf(f) < a.sign_guard);
+                        redo_row = redo_row || (fabsf(f) < a.sign_guard);
                     }
-                    sign_stage[ch * L::kStagePitch + row] = word;
+                    if (live) a.signs[grow * (D / 32) + ch] = word;
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(BAR_ACC2_EMPTY));
+                c0 = clock64(); if (pr) a.prof[19] += c0 - c1;
             }
-            const uint32_t mask = __ballot_sync(0xffffffffu, near && grow < a.n);
-            if (lane == 0 && tile * kTileRows + quarter * 32 < a.n) a.rowmask[tile * 4 + quarter] = mask;
-            // staged rows -> global, coalesced
-            bar_or(2, 128, false);
-            {
-                constexpr int kGroups = kCodeWords / 4;  // 16-byte pieces per packed row
-                uint4* dst = reinterpret_cast<uint4*>(a.codes + tile * kTileRows * kCodeWords);
-                const int total = (int)rows_valid * kGroups;
-                for (int k = et; k < total; k += 128) {
-                    const int r = k / kGroups, q = k - r * kGroups;
-                    const uint32_t* s0 = code_stage + (4 * q) * L::kStagePitch + r;
-                    dst[k] = make_uint4(s0[0], s0[L::kStagePitch], s0[2 * L::kStagePitch], s0[3 * L::kStagePitch]);
-                }
-                if (PROD) {
-                    static_assert(D / 32 == 4, "sign rows are one 16-byte piece");
-                    uint4* sdst = reinterpret_cast<uint4*>(a.signs + tile * kTileRows * (D / 32));
-                    for (int r = et; r < (int)rows_valid; r += 128) {
-                        const uint32_t* s0 = sign_stage + r;
-                        sdst[r] = make_uint4(s0[0], s0[L::kStagePitch], s0[2 * L::kStagePitch], s0[3 * L::kStagePitch]);
-                    }
-                }
-            }
-            bar_or(2, 128, false);
+            if (redo_row && live) push_row_entry(a.lists, grow);
         }
     }
 
@@ -555,7 +621,17 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     int lut_base[kCells];
     const float guard = TQ_CODE_GUARD * kAccScale;
     if (!build_cell_lut(bnd_s.data(), nb, 4.f * guard, &cs, &co, lut_bnd, lut_base)) return TQ_OK;
-    for (int l = 0; l < kCells; ++l) lut_cent[l] = codebook[l % levels] * kAccScale;
+    float lut4[kCells * 4];
+    for (int c = 0; c < kCells; ++c) {
+        const int base = lut_base[c];                     // boundaries in lower cells = code of a value below this cell's boundary
+        const int above = base + 1 < levels ? base + 1 : base;
+        const int base1 = base + 1;
+        lut4[4 * c + 0] = lut_bnd[c];
+        memcpy(&lut4[4 * c + 1], &base1, 4);
+        lut4[4 * c + 2] = -codebook[base] * kScaleA;      // - centroid * 2^10 (the A-operand scale)
+        lut4[4 * c + 3] = -codebook[above] * kScaleA;
+    }
+    for (int l = 0; l < kCells; ++l) lut_cent[l] = -codebook[l % levels] * kScaleA;
 
     const size_t dd = (size_t)d * d;
     const int nmat = projection ? 4 : 2;
@@ -574,7 +650,7 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
         split_operand(m, d, kScaleM, mats.data() + 2 * dd, mats.data() + 3 * dd);
     }
     const size_t mat_bytes = mats.size() * 2;
-    const size_t total = mat_bytes + 3 * kCells * 4;
+    const size_t total = mat_bytes + 5 * kCells * 4;
     TensorConsts* t = new TensorConsts();
     cudaError_t e = cudaMalloc(&t->dev, total);
     if (e != cudaSuccess) {
@@ -583,18 +659,16 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     }
     unsigned char* base = static_cast<unsigned char*>(t->dev);
     bool ok = cudaMemcpy(base, mats.data(), mat_bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
-              cudaMemcpy(base + mat_bytes, lut_bnd, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
-              cudaMemcpy(base + mat_bytes + kCells * 4, lut_base, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
-              cudaMemcpy(base + mat_bytes + 2 * kCells * 4, lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+              cudaMemcpy(base + mat_bytes, lut4, sizeof(lut4), cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(base + mat_bytes + sizeof(lut4), lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
     if (!ok || !encode_tiled_fn()) {
         cudaFree(t->dev);
         delete t;
         return tq_fail(TQ_ERR_CUDA, "upload of tensor-path constants failed");
     }
     t->args.bmat = reinterpret_cast<const __half*>(base);
-    t->args.lut_bnd = reinterpret_cast<const float*>(base + mat_bytes);
-    t->args.lut_base = reinterpret_cast<const int*>(base + mat_bytes + kCells * 4);
-    t->args.lut_cent = reinterpret_cast<const float*>(base + mat_bytes + 2 * kCells * 4);
+    t->args.cell_lut = reinterpret_cast<const float4*>(base + mat_bytes);
+    t->args.code_ncent = reinterpret_cast<const float*>(base + mat_bytes + kCells * 16);
     t->args.cell_scale = cs;
     t->args.cell_offset = co;
     t->args.code_guard = guard;
@@ -623,7 +697,7 @@ static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, 
 }
 
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
-                              uint32_t* signs, float* rnorms, float* norms, uint32_t* rowmask, cudaStream_t st) {
+                              uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists, cudaStream_t st) {
     if (!p->tensor) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for this plan");
     const int d = p->dev.d;
     if (n > (int64_t)0x7fffff00) return tq_fail(TQ_ERR_UNSUPPORTED, "n above 2^31 rows per call");
@@ -634,8 +708,9 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     args.signs = signs;
     args.norms = norms;
     args.rnorms = rnorms;
-    args.rowmask = rowmask;
+    args.lists = *lists;
     args.status = p->counters + 1;
+    args.prof = getenv("TQ_PROF") ? reinterpret_cast<long long*>(p->counters + 8) : nullptr;
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)d, (cuuint64_t)n};

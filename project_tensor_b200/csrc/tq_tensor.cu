@@ -39,7 +39,9 @@ namespace {
 using namespace tqptx;
 
 constexpr int kTileRows = 128;
-constexpr int kThreads = 576;            // 18 warps: TMA, MMA, 8 converters, 8 epilogue
+// Warps: TMA, MMA, 8 converters, then the epilogue: one thread per row for TurboQuantProd (its epilogue
+// needs the registers), two per row (each owning half of the columns) for TurboQuantMSE.
+template <bool PROD> struct Threads { static constexpr int kEpiPerRow = PROD ? 1 : 2; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
 constexpr int kFirstConvWarp = 2;
 constexpr int kFirstEpiWarp = 10;
 constexpr int kBoxBytes = 128 * 128;     // 128 rows x 32 floats
@@ -49,6 +51,7 @@ constexpr float kAccScale = kScaleA * kScaleB;  // accumulator = 2^20 * rotated 
 constexpr float kScaleRho = 1.f / 1024.f;       // accumulator units -> 2^10 * rho for the second A operand
 constexpr float kScaleM = 16.f;                 // R S^T -> second B operand
 constexpr int kCells = 32;
+constexpr int kPendCap = 64;               // second-stage entries staged per epilogue warp and list
 constexpr float kCellMul = 31.99998f;
 
 struct TensorArgs {
@@ -81,7 +84,8 @@ struct Smem {
     static constexpr int off_b = 0;
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
-    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 2 * kTileRows * 4 + kCells * 16;
+    static constexpr int kPendBytes = 8 * kPendCap * (8 + 4);   // per epilogue warp: 64-bit and 32-bit entries
+    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 2 * kTileRows * 4 + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
 };
 
@@ -99,24 +103,57 @@ enum {
     BAR_COUNT = 28
 };
 
-// Append work for the exact second stage (rare: about one row in a hundred).
-__device__ __noinline__ void push_code_entries(const TqRecheck& l, int64_t row, int first_coord, uint32_t mask) {
-    while (mask) {
-        const int e = __ffs(mask) - 1;
-        mask &= mask - 1;
-        const unsigned int pos = atomicAdd(&l.hdr->n_codes, 1u);
-        if (pos < l.code_cap) l.code_entries[pos] = ((unsigned long long)row << 8) | (unsigned long long)(first_coord + e);
+// Work for the exact second stage is rare (about one row in a hundred), but a global atomic per entry
+// would stall the epilogue warp for a memory round trip each time.  Every epilogue warp therefore
+// collects its entries in a private shared-memory buffer and reserves space in the global lists
+// once per batch.
+struct WarpPending {
+    unsigned long long* codes;  // [kPendCap]
+    unsigned int* rows;         // [kPendCap]
+    int n_codes, n_rows;        // warp-uniform
+};
+
+__device__ __noinline__ void flush_pending_codes(const TqRecheck& l, WarpPending& w, int lane) {
+    __syncwarp();
+    unsigned int base = 0;
+    if (lane == 0) base = atomicAdd(&l.hdr->n_codes, (unsigned int)w.n_codes);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < w.n_codes; i += 32) {
+        if (base + i < l.code_cap) l.code_entries[base + i] = w.codes[i];
         else l.hdr->overflow = 1u;
     }
+    __syncwarp();
+    w.n_codes = 0;
 }
+__device__ __noinline__ void flush_pending_rows(const TqRecheck& l, WarpPending& w, int lane) {
+    __syncwarp();
+    unsigned int base = 0;
+    if (lane == 0) base = atomicAdd(&l.hdr->n_rows, (unsigned int)w.n_rows);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < w.n_rows; i += 32) {
+        if (base + i < l.row_cap) l.row_entries[base + i] = w.rows[i];
+        else l.hdr->overflow = 1u;
+    }
+    __syncwarp();
+    w.n_rows = 0;
+}
+// Whole warp: every lane with `want` appends its row.
+__device__ __forceinline__ void pend_rows(const TqRecheck& l, WarpPending& w, bool want, int64_t row, int lane) {
+    const uint32_t votes = __ballot_sync(0xffffffffu, want);
+    if (votes == 0u) return;
+    if (w.n_rows + __popc(votes) > kPendCap) flush_pending_rows(l, w, lane);
+    if (want) w.rows[w.n_rows + __popc(votes & ((1u << lane) - 1u))] = (unsigned int)row;
+    w.n_rows += __popc(votes);
+}
+
 // One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
 // and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
 // the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 by cell, lut_ncent by code.
 template <int BITS, bool PROD>
-__device__ __forceinline__ bool process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
+__device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
                                               float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
                                               uint32_t (&rhi)[16], uint32_t (&rlo)[16], float& rs) {
-    bool near_any = false;
+    uint32_t nearmask = 0;  // bit e: element e lies inside the guard band of its boundary
     float prev_rho = 0.f;
 #pragma unroll
     for (int k = 0; k <= BITS; ++k) w[k] = 0;
@@ -129,7 +166,7 @@ __device__ __forceinline__ bool process_chunk(const uint32_t (&v)[32], float lut
         const int base1 = __shfl_sync(0xffffffffu, lut_base1, cell);
         const float dlt = f - bnd;
         const uint32_t code = (uint32_t)base1 - (dlt > 0.f ? 0u : 1u);
-        near_any = near_any || (fabsf(dlt) < guard);
+        if (fabsf(dlt) < guard) nearmask |= 1u << e;
         const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
         w[wi] += code << sh;
         if (sh + BITS > 32) w[wi + 1] += code >> (32 - sh);
@@ -147,39 +184,33 @@ __device__ __forceinline__ bool process_chunk(const uint32_t (&v)[32], float lut
             }
         }
     }
-    return near_any;
+    return nearmask;
 }
 
-// Rare path: some value of this 32-column chunk lies inside the guard band; find which ones.
-// Entered by the whole warp when any of its rows has such a value (about one chunk in twelve); the
-// values are read again from tensor memory so that the hot path's register arrays never have to be
-// addressable.  `want` says whether this lane's row takes part.
-__device__ __noinline__ void push_near_codes(const TqRecheck& l, bool want, int64_t row, int first_coord, uint32_t taddr,
-                                             float lut_bnd, float cell_scale, float cell_offset, float guard) {
-    uint32_t v[32];
-    tmem_ld32(taddr, v);
-    tmem_wait_ld();
-    uint32_t mask = 0;
-#pragma unroll 4
-    for (int e = 0; e < 32; ++e) {
-        const float f = __uint_as_float(v[e]);
-        const float u = fma_sat(f, cell_scale, cell_offset);
-        const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
-        const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
-        if (fabsf(f - bnd) < guard) mask |= 1u << e;
+// Whole warp: every lane appends one (row, coordinate) entry per bit of its mask.  Called after the
+// accumulator has been handed back, so it never delays the tensor pipe.
+__device__ __noinline__ void pend_codes(const TqRecheck& l, WarpPending& w, uint32_t mask, int64_t row, int first_coord,
+                                        int lane) {
+    for (;;) {
+        const uint32_t votes = __ballot_sync(0xffffffffu, mask != 0u);
+        if (votes == 0u) break;
+        if (w.n_codes + __popc(votes) > kPendCap) flush_pending_codes(l, w, lane);
+        if (mask != 0u) {
+            const int e = __ffs(mask) - 1;
+            mask &= mask - 1;
+            w.codes[w.n_codes + __popc(votes & ((1u << lane) - 1u))] =
+                ((unsigned long long)row << 8) | (unsigned long long)(first_coord + e);
+        }
+        w.n_codes += __popc(votes);
     }
-    if (want) push_code_entries(l, row, first_coord, mask);
-}
-__device__ __noinline__ void push_row_entry(const TqRecheck& l, int64_t row) {
-    const unsigned int pos = atomicAdd(&l.hdr->n_rows, 1u);
-    if (pos < l.row_cap) l.row_entries[pos] = (unsigned int)row;
-    else l.hdr->overflow = 1u;
 }
 
 template <int D, int BITS, bool PROD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Threads<PROD>::kThreads, 1)
 tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
     static_assert(D == 128, "this kernel is written for d = 128");
+    constexpr int kThreads = Threads<PROD>::kThreads;
+    constexpr int kEpiPerRow = Threads<PROD>::kEpiPerRow;
     using L = Smem<D, PROD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -189,8 +220,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     unsigned char* force = smem + L::off_misc + 2 * kTileRows * 4;                      // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 2 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
-    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - 2 * kTileRows * 4 - kCells * 16);  // [2][128]
-    float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - kCells * 16);  // [32]
+    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - 2 * kTileRows * 4 - kCells * 16);  // [2][128]
+    float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
+    unsigned char* pend_base = smem + L::off_misc + L::kMiscBytes - L::kPendBytes;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -204,11 +236,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             mbar_init(BAR(BAR_A_FULL + i), 8);
             mbar_init(BAR(BAR_A_EMPTY + i), 1);
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
-            mbar_init(BAR(BAR_ACC_EMPTY + i), 8);
-            mbar_init(BAR(BAR_RHO_FULL + i), 8);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), 4 * kEpiPerRow);
+            mbar_init(BAR(BAR_RHO_FULL + i), 4 * kEpiPerRow);
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
-        mbar_init(BAR(BAR_ACC2_EMPTY), 8);
+        mbar_init(BAR(BAR_ACC2_EMPTY), 4 * kEpiPerRow);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -393,17 +425,23 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; }
         }
     } else {
-        // ---- epilogue: two threads per row, each owning two 32-column chunks ------------------------
+        // ---- epilogue: one thread per row -----------------------------------------------------------
         const int quarter = warp & 3;
-        const int colhalf = (warp - kFirstEpiWarp) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         constexpr int kCodeWords = D * BITS / 32;  // words per packed row
+        constexpr int kChunks = D / 32 / kEpiPerRow;                 // 32-column chunks per thread
+        const int chunk0 = ((warp - kFirstEpiWarp) >> 2) * kChunks;   // first chunk of this thread
         // lookup tables held in the lanes of the warp: per cell (boundary, 1 + boundaries below), per code
         // (- centroid * 2^10)
         const float lut_bnd = cell_lut[lane].x;
         const int lut_base1 = __float_as_int(cell_lut[lane].y);
         const float lut_ncent = a.code_ncent[lane];
+        WarpPending pend;
+        pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + (warp - kFirstEpiWarp) * kPendCap;
+        pend.rows = reinterpret_cast<unsigned int*>(pend_base + 8 * kPendCap * 8) + (warp - kFirstEpiWarp) * kPendCap;
+        pend.n_codes = 0;
+        pend.n_rows = 0;
         for (int64_t i = 0; i < my_tiles; ++i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
@@ -421,21 +459,23 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             float rs = 0.f;
             const uint32_t acc = tmem + lane_addr + ACC_COL(ab);
             const uint32_t a_hi = tmem + lane_addr + A_COL(b);
-            static_assert(D / 64 == 2, "two chunks per thread");
-            uint32_t v0[32], v1[32];
-            tmem_ld32(acc + (colhalf * 2) * 32, v0);
-            tmem_ld32(acc + (colhalf * 2 + 1) * 32, v1);
+            uint32_t va[32], vb[32];
+            uint32_t nm[kChunks];
+            tmem_ld32(acc + chunk0 * 32, va);
             tmem_wait_ld();
-            if (pr) { const long long cx = clock64(); a.prof[20] += cx - c1; }
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                const int ch = colhalf * 2 + cc;
+            for (int ch = 0; ch < kChunks; ++ch) {
+                // MSE: fetch the next chunk while this one is processed (Prod has no registers to spare)
+                if (!PROD && ch + 1 < kChunks) {
+                    if (ch & 1) tmem_ld32(acc + (chunk0 + ch + 1) * 32, va); else tmem_ld32(acc + (chunk0 + ch + 1) * 32, vb);
+                }
+                if (PROD && ch > 0) { tmem_ld32(acc + (chunk0 + ch) * 32, va); tmem_wait_ld(); }
                 uint32_t w[BITS + 1], rhi[16], rlo[16];
-                const bool near_any = cc == 0
-                    ? process_chunk<BITS, PROD>(v0, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
-                    : process_chunk<BITS, PROD>(v1, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
+                nm[ch] = (!PROD && (ch & 1))
+                    ? process_chunk<BITS, PROD>(vb, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
+                    : process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
                 if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
-                    uint32_t* dst = a.codes + grow * kCodeWords + ch * BITS;
+                    uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
                     if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
                     else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
                     else {
@@ -443,17 +483,15 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                         for (int k = 0; k < BITS; ++k) dst[k] = w[k];
                     }
                 }
-                const bool want = near_any && live && !redo_row;
-                if (__any_sync(0xffffffffu, want))
-                    push_near_codes(a.lists, want, grow, ch * 32, acc + ch * 32, lut_bnd, a.cell_scale, a.cell_offset, a.code_guard);
                 if (PROD) {
-                    tmem_st16(a_hi + ch * 16, rhi);
-                    tmem_st16(a_hi + kABlock + ch * 16, rlo);
+                    tmem_st16(a_hi + (chunk0 + ch) * 16, rhi);
+                    tmem_st16(a_hi + kABlock + (chunk0 + ch) * 16, rlo);
                 }
+                if (!PROD && ch + 1 < kChunks) tmem_wait_ld();
             }
             if (PROD) {
                 tmem_wait_st();
-                rs_part[colhalf * kTileRows + row] = rs;
+                if (live) a.rnorms[grow] = sqrtf(rs) * kScaleRho;  // rs is in 2^10 units
             }
             tc_fence_before();
             __syncwarp();
@@ -461,37 +499,52 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 mbar_arrive(BAR(BAR_ACC_EMPTY + ab));
                 if (PROD) mbar_arrive(BAR(BAR_RHO_FULL + b));
             }
+            // second-stage work is recorded after the accumulator went back to the tensor pipe
+            uint32_t any_nm = 0;
+#pragma unroll
+            for (int ch = 0; ch < kChunks; ++ch) {
+                if (!live || redo_row) nm[ch] = 0;
+                any_nm |= nm[ch];
+            }
+            if (__any_sync(0xffffffffu, any_nm != 0u)) {
+#pragma unroll
+                for (int ch = 0; ch < kChunks; ++ch) pend_codes(a.lists, pend, nm[ch], grow, (chunk0 + ch) * 32, lane);
+            }
             c0 = clock64(); if (pr) a.prof[17] += c0 - c1;
             if (PROD) {
                 mbar_wait(BAR(BAR_ACC2_FULL), (uint32_t)(i & 1), abort_flag);
-                bar_sync(5 + quarter, 64);  // rs_part of both column halves of these 32 rows is written
                 tc_fence_after();
                 c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
-                if (colhalf == 0 && live)
-                    a.rnorms[grow] = sqrtf(rs_part[row] + rs_part[kTileRows + row]) * kScaleRho;  // rs is in 2^10 units
                 const uint32_t acc2 = tmem + lane_addr + kAcc2Col;
-#pragma unroll 1
-                for (int cc = 0; cc < D / 64; ++cc) {
-                    const int ch = colhalf * (D / 64) + cc;
-                    uint32_t v[32];
-                    tmem_ld32(acc2 + ch * 32, v);
-                    tmem_wait_ld();
+                uint32_t sw[kChunks];
+                tmem_ld32(acc2, va);
+                tmem_wait_ld();
+#pragma unroll
+                for (int ch = 0; ch < kChunks; ++ch) {
+                    if (ch > 0) { tmem_ld32(acc2 + ch * 32, va); tmem_wait_ld(); }
                     uint32_t word = 0;
+                    float amin = 3.0e38f;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
-                        const float f = __uint_as_float(v[e]);
-                        word |= (f >= 0.f ? 1u : 0u) << ((e >> 1) + ((e & 1) << 4));
-                        redo_row = redo_row || (fabsf(f) < a.sign_guard);
+                        const uint32_t bits = va[e];
+                        // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
+                        // inside the guard band and recomputed anyway)
+                        word |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
+                        amin = fminf(amin, fabsf(__uint_as_float(bits)));
                     }
-                    if (live) a.signs[grow * (D / 32) + ch] = word;
+                    sw[ch] = word;
+                    redo_row = redo_row || (amin < a.sign_guard);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(BAR_ACC2_EMPTY));
+                if (live) *reinterpret_cast<uint4*>(a.signs + grow * (D / 32)) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
                 c0 = clock64(); if (pr) a.prof[19] += c0 - c1;
             }
-            if (redo_row && live) push_row_entry(a.lists, grow);
+            pend_rows(a.lists, pend, redo_row && live, grow, lane);
         }
+        if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
+        if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
     }
 
     // ---- teardown -----------------------------------------------------------------------------------
@@ -691,7 +744,7 @@ template <int D, int BITS, bool PROD>
 static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
     const int sm = Smem<D, PROD>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize_kernel<D, BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    tensor_quantize_kernel<D, BITS, PROD><<<grid, kThreads, sm, st>>>(map, args);
+    tensor_quantize_kernel<D, BITS, PROD><<<grid, Threads<PROD>::kThreads, sm, st>>>(map, args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -91,6 +91,28 @@ int64_t tq_topk_scratch_bytes(const tq_plan* plan, int groups, int q_per_group,
 int tq_mse_quantize(const tq_plan* plan, const float* x, int64_t n, void* codes, float* norms,
                     void* scratch, size_t scratch_bytes, void* stream);
 
+/*
+ * tq_mse_quantize for callers that must not allocate.  No counterpart in the reference (NumPy/CuPy
+ * allocate freely); it exists for hosts that cannot hand over a scratch buffer at call time: a
+ * serving loop whose device memory was carved up at start-up and is frozen afterwards, a binding
+ * from a runtime that can only pass through buffers it registered in advance, or a region where a
+ * device allocation would stall every stream of the process.  Inputs and outputs are still the
+ * caller's; only the work lists of the second stage live in an array inside the library's device
+ * image (about 1.2 MB, held by every GPU that loads the library until the process exits).
+ *
+ *   - n must not exceed TQ_NOALLOC_MAX_ROWS; larger batches are refused with TQ_ERR_UNSUPPORTED
+ *     (split them, or use tq_mse_quantize).
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
+ *     that first call before any stream capture starts.  No call allocates or frees device memory.
+ *   - All calls on one device share the one array.  Each call resets the list counters itself, so
+ *     calls in sequence on a stream are fine; calls that overlap on the GPU (different streams,
+ *     different threads) race on the lists and may corrupt each other's output.
+ * Same results as tq_mse_quantize.
+ */
+#define TQ_NOALLOC_MAX_ROWS 262144
+int tq_mse_quantize_noalloc(const tq_plan* plan, const float* x, int64_t n, void* codes, float* norms,
+                            void* stream);
+
 /* TurboQuantMSE.dequantize (_quant.py:238-242,251-254): out_i = (codebook[codes_i] R) * norms[i]. */
 int tq_mse_dequantize(const tq_plan* plan, const void* codes, const float* norms, int64_t n,
                       float* out, void* stream);

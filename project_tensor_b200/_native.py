@@ -29,6 +29,7 @@ SIGNATURES = {
     "tq_quantize_scratch_bytes": (c_int64, [c_void_p, c_int64]),
     "tq_topk_scratch_bytes": (c_int64, [c_void_p, c_int, c_int, c_int64, c_int]),
     "tq_mse_quantize": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tq_mse_quantize_noalloc": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "tq_mse_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_prod_quantize": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_size_t, c_void_p]),

@@ -6,11 +6,25 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
 #include <vector>
 
+// Scratch of tq_mse_quantize_noalloc: lives in the library's device image, so every GPU that loads the
+// library holds these bytes until the process exits.  Sized for TQ_NOALLOC_MAX_ROWS rows.
+#define TQ_NOALLOC_SCRATCH_BYTES \
+    (sizeof(TqRecheckHeader) + 8 * (size_t)(TQ_NOALLOC_MAX_ROWS / 2 + 4096) + 4 * (size_t)(TQ_NOALLOC_MAX_ROWS / 8 + 4096) + 16)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TQ_NOALLOC_SCRATCH_BYTES];
+
 namespace {
 thread_local char g_err[512] = "";
+
+// Device address of g_noalloc_scratch per GPU.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use; the address has to be asked for, once per device, with
+// that device current.
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -252,6 +266,32 @@ int tq_mse_quantize(const tq_plan* p, const float* x, int64_t n, void* codes, fl
 int tq_prod_quantize(const tq_plan* p, const float* x, int64_t n, void* codes, void* signs, float* residual_norms,
                      float* norms, void* scratch, size_t scratch_bytes, void* stream) {
     return quantize_common(p, true, x, n, codes, signs, residual_norms, norms, scratch, scratch_bytes, stream);
+}
+
+int tq_mse_quantize_noalloc(const tq_plan* p, const float* x, int64_t n, void* codes, float* norms, void* stream) {
+    TQ_TRY(check_plan(p, false));
+    if (n < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "n is negative");
+    if (n > TQ_NOALLOC_MAX_ROWS)
+        return tq_fail(TQ_ERR_UNSUPPORTED, "tq_mse_quantize_noalloc handles at most %d rows per call, got %lld; "
+                       "split the batch or use tq_mse_quantize with caller scratch", TQ_NOALLOC_MAX_ROWS, (long long)n);
+    if (p->device < 0 || p->device >= kMaxDevices) return tq_fail(TQ_ERR_NO_DEVICE, "device index %d out of range", p->device);
+    void* scratch = nullptr;
+    {
+        DeviceScope scope(p->device);
+        if (!scope.ok) return tq_fail(TQ_ERR_CUDA, "cannot select device %d", p->device);
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ptr[p->device]) {
+            void* ptr = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+            if (e != cudaSuccess || !ptr)
+                return tq_fail(TQ_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed: %s", cudaGetErrorString(e));
+            g_noalloc_ptr[p->device] = ptr;
+        }
+        scratch = g_noalloc_ptr[p->device];
+    }
+    // quantize_common clears the list header at the start of every call (cudaMemsetAsync, no allocation);
+    // the entries behind it are only read up to the counts written by the same call.
+    return quantize_common(p, false, x, n, codes, nullptr, nullptr, norms, scratch, TQ_NOALLOC_SCRATCH_BYTES, stream);
 }
 
 int tq_mse_dequantize(const tq_plan* p, const void* codes, const float* norms, int64_t n, float* out, void* stream) {

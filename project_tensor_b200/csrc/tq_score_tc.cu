@@ -33,7 +33,8 @@ using namespace tqptx;
 
 constexpr int D = 128;
 constexpr int kTileKeys = 128;
-constexpr int kThreads = 448;
+// Warps: bulk copy, MMA, 8 expanders, then 4 epilogue warps per 16 queries of the pass.
+template <int QPAD> struct ScoreThreads { static constexpr int kEpiPerRow = QPAD / 16; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
 constexpr int kFirstExpWarp = 2;
 constexpr int kFirstEpiWarp = 10;
 constexpr int kStages = 8;
@@ -105,9 +106,11 @@ struct ScoreSmem {
 };
 
 template <int BITS, int QPAD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(ScoreThreads<QPAD>::kThreads, 1)
 score_tc_kernel(const ScoreTcArgs a) {
     using L = ScoreSmem<BITS, QPAD>;
+    constexpr int kThreads = ScoreThreads<QPAD>::kThreads;
+    constexpr int kEpiPerRow = ScoreThreads<QPAD>::kEpiPerRow;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const uint32_t smem_base = smem_u32(smem);
@@ -124,9 +127,9 @@ score_tc_kernel(const ScoreTcArgs a) {
             mbar_init(BAR(SB_A_FULL + i), 8);
             mbar_init(BAR(SB_A_EMPTY + i), 1);
             mbar_init(BAR(SB_D_FULL + i), 1);
-            mbar_init(BAR(SB_D_EMPTY + i), 4);
+            mbar_init(BAR(SB_D_EMPTY + i), 4 * kEpiPerRow);
             mbar_init(BAR(SB_B_FULL + i), 1);
-            mbar_init(BAR(SB_B_EMPTY + i), 5);  // last MMA of the group + the four epilogue warps
+            mbar_init(BAR(SB_B_EMPTY + i), 1 + 4 * kEpiPerRow);  // last MMA of the group + every epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -279,7 +282,6 @@ score_tc_kernel(const ScoreTcArgs a) {
             c0 = clock64(); pc[1] += c0 - c1;
             if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
             c1 = clock64(); pc[2] += c1 - c0;
-            if (bar_or(1, 256, fail)) break;
             tc_fence_after();
             c0 = clock64(); pc[3] += c0 - c1;
             const uint32_t abase = tmem + lane_addr + b * kBufCols + half * 32;
@@ -336,39 +338,32 @@ score_tc_kernel(const ScoreTcArgs a) {
             long long c0 = clock64();
             const int db = kDBufs == 2 ? b : 0;
             const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
-            bool fail = !mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
-            if (bar_or(2, 128, fail)) break;
+            mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
             tc_fence_after();
             long long c1 = clock64();
-            const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols;
-            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB);
-            float* out = a.scores + g * a.out_group_stride + key;
-            long long c2 = c1;
+            const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
+            const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
+            uint32_t ua[16], ub[16], va[16], vb[16];
+            tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
+            tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
+            tmem_ld16(dbase + 2 * QPAD, va);       // Sg p_hi
+            tmem_ld16(dbase + 3 * QPAD, vb);       // Sg p_lo
+            tmem_wait_ld();
+            long long c2 = clock64();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
+            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB) + q16;
+            float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
+            if (live) {
 #pragma unroll
-            for (int h = 0; h < QPAD / 16; ++h) {
-                uint32_t ua[16], ub[16], va[16], vb[16];
-                tmem_ld16(dbase + h * 16, ua);                  // C q_hi   (+ C_lo q_hi)
-                tmem_ld16(dbase + QPAD + h * 16, ub);           // C_hi q_lo
-                tmem_ld16(dbase + 2 * QPAD + h * 16, va);       // Sg p_hi
-                tmem_ld16(dbase + 3 * QPAD + h * 16, vb);       // Sg p_lo
-                tmem_wait_ld();
-                if (h == QPAD / 16 - 1) {
-                    c2 = clock64();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));
-                }
-                if (live) {
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        const int qi = h * 16 + k;
-                        if (qi < a.nq) {
-                            const float2 sc = ds[qi];  // (descale of D1, descale of D2)
-                            const float s1 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * sc.x;
-                            const float s2 = (__uint_as_float(va[k]) + __uint_as_float(vb[k])) * sc.y;
-                            __stcs(out, nrm * fmaf(arn, s2, s1));
-                            out += a.out_row_stride;
-                        }
+                for (int k = 0; k < 16; ++k) {
+                    if (q16 + k < a.nq) {
+                        const float2 sc = ds[k];  // (descale of D1, descale of D2)
+                        const float s1 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * sc.x;
+                        const float s2 = (__uint_as_float(va[k]) + __uint_as_float(vb[k])) * sc.y;
+                        __stcs(out, nrm * fmaf(arn, s2, s1));
+                        out += a.out_row_stride;
                     }
                 }
             }
@@ -465,47 +460,120 @@ __device__ void block_sort_desc(unsigned long long* a, int n2) {
 }
 
 constexpr int kSelThreads = 256;
+constexpr int kSelPerThread = 8;
+constexpr int kSelBatch = kSelPerThread * kSelThreads;   // scores examined between two looks at the buffer
+constexpr int kSelCap = 4096;                            // candidate buffer (64-bit keys) per block
+
+// Keep the `k` largest of the `c` distinct keys in buf[0..c) (c <= kSelCap), unsorted, in buf[0..k); returns
+// the k-th largest key.  Radix select, 8 bits per pass from the top, with a 256-bin histogram in shared
+// memory; far cheaper than sorting the buffer.  Whole block; c and k are uniform, k <= c.
+__device__ unsigned long long block_select_topk(unsigned long long* buf, int c, int k, int* hist /*[256]*/,
+                                                int* scratch /*[4]*/) {
+    unsigned long long prefix = 0ull, mask = 0ull;
+    int remaining = k;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < c; i += blockDim.x) {
+            const unsigned long long key = buf[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 255ull)], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // lane l owns bins 255-8l .. 248-8l (descending); find where the running count reaches `remaining`
+            const int lane = threadIdx.x;
+            int mine = 0;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) mine += hist[255 - 8 * lane - b];
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int before = incl - mine;  // keys in strictly higher bins of higher lanes
+            if (before < remaining && incl >= remaining) {
+                int acc = before;
+                for (int b = 0; b < 8; ++b) {
+                    const int bin = 255 - 8 * lane - b;
+                    if (acc + hist[bin] >= remaining) { scratch[0] = bin; scratch[1] = remaining - acc; break; }
+                    acc += hist[bin];
+                }
+            }
+        }
+        __syncthreads();
+        prefix |= (unsigned long long)scratch[0] << shift;
+        mask |= 255ull << shift;
+        remaining = scratch[1];
+        __syncthreads();
+    }
+    // prefix is now the k-th largest key; gather the keys >= prefix (exactly k, keys are distinct)
+    unsigned long long keep[kSelCap / kSelThreads];
+    int nkeep = 0;
+    for (int i = threadIdx.x, j = 0; j < kSelCap / kSelThreads; i += blockDim.x, ++j) {
+        keep[j] = 0ull;
+        if (i < c) { const unsigned long long key = buf[i]; if (key >= prefix) { keep[j] = key; ++nkeep; } }
+    }
+    if (threadIdx.x == 0) scratch[2] = 0;
+    __syncthreads();
+    int pos = nkeep ? atomicAdd(&scratch[2], nkeep) : 0;
+#pragma unroll
+    for (int j = 0; j < kSelCap / kSelThreads; ++j)
+        if (keep[j] != 0ull) buf[pos++] = keep[j];
+    __syncthreads();
+    return prefix;
+}
 
 // grid (segments, rows): block scans scores[row][seg*seg_len ...) and writes its k best as sortable keys
-// to part[((group*lists_per_group + list_base + seg) * qpg + qi) * topk ...].
+// to part[((group*lists_per_group + list_base + seg) * qpg + qi) * topk ...].  Candidates above the
+// running threshold are collected in shared memory; when the buffer could overflow in the next batch
+// it is cut back to the k best, which also raises the threshold.
 __global__ void __launch_bounds__(kSelThreads)
 topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t group_stride, int qpg, int64_t n,
-                 int64_t seg_len, int64_t first_row_of_group_stride, int64_t key_off, int topk, int cap2,
+                 int64_t seg_len, int64_t first_row_of_group_stride, int64_t key_off, int topk, int k2,
                  int lists_per_group, int list_base, unsigned long long* __restrict__ part) {
-    extern __shared__ __align__(16) unsigned char smraw[];
-    unsigned long long* buf = reinterpret_cast<unsigned long long*>(smraw);
+    __shared__ __align__(16) unsigned long long buf[kSelCap];
+    __shared__ int hist[256];
+    __shared__ int scratch[4];
     __shared__ int cnt;
     __shared__ unsigned long long thr;
     const int seg = blockIdx.x, r = blockIdx.y, g = r / qpg, qi = r - g * qpg;
     const float* src = scores + g * group_stride + qi * row_stride;
+    const uint32_t row0 = (uint32_t)(g * first_row_of_group_stride + key_off);
     const int64_t k0 = (int64_t)seg * seg_len;
     int64_t k1 = k0 + seg_len;
     if (k1 > n) k1 = n;
     if (threadIdx.x == 0) { cnt = 0; thr = 0ull; }
     __syncthreads();
-    for (int64_t kb = k0; kb < k1; kb += kSelThreads) {
-        const int64_t key = kb + threadIdx.x;
-        if (key < k1) {
-            const unsigned long long ck = make_key(src[key], (uint32_t)(g * first_row_of_group_stride + key_off + key));
-            if (ck > thr) buf[atomicAdd(&cnt, 1)] = ck;
+    for (int64_t kb = k0; kb < k1; kb += kSelBatch) {
+        float v[kSelPerThread];
+#pragma unroll
+        for (int j = 0; j < kSelPerThread; ++j) {
+            const int64_t key = kb + j * kSelThreads + threadIdx.x;
+            v[j] = key < k1 ? __ldcs(src + key) : 0.f;
+        }
+        const unsigned long long t = thr;
+#pragma unroll
+        for (int j = 0; j < kSelPerThread; ++j) {
+            const int64_t key = kb + j * kSelThreads + threadIdx.x;
+            const unsigned long long ck = make_key(v[j], row0 + (uint32_t)key);
+            if (key < k1 && ck > t) buf[atomicAdd(&cnt, 1)] = ck;
         }
         __syncthreads();
-        if (cnt + kSelThreads > cap2) {
-            const int c = cnt;
-            for (int i = c + threadIdx.x; i < cap2; i += kSelThreads) buf[i] = 0ull;
-            block_sort_desc(buf, cap2);
-            if (threadIdx.x == 0) { cnt = topk; thr = buf[topk - 1]; }
-            __syncthreads();
+        const int c = cnt;  // uniform: nobody appends between the two barriers
+        if (c + kSelBatch > kSelCap && c > topk) {
+            const unsigned long long kth = block_select_topk(buf, c, topk, hist, scratch);
+            if (threadIdx.x == 0) { cnt = topk; thr = kth; }
         }
+        __syncthreads();
     }
+    int c = cnt;
+    if (c > topk) { block_select_topk(buf, c, topk, hist, scratch); c = topk; }
     __syncthreads();
-    {
-        const int c = cnt;
-        for (int i = c + threadIdx.x; i < cap2; i += kSelThreads) buf[i] = 0ull;
-        block_sort_desc(buf, cap2);
-        unsigned long long* dst = part + (((size_t)g * lists_per_group + list_base + seg) * qpg + qi) * topk;
-        for (int i = threadIdx.x; i < topk; i += kSelThreads) dst[i] = buf[i];
-    }
+    for (int i = c + threadIdx.x; i < k2; i += kSelThreads) buf[i] = 0ull;
+    block_sort_desc(buf, k2);
+    unsigned long long* dst = part + (((size_t)g * lists_per_group + list_base + seg) * qpg + qi) * topk;
+    for (int i = threadIdx.x; i < topk; i += kSelThreads) dst[i] = buf[i];
 }
 
 int pow2_at_least(int v) {
@@ -518,7 +586,7 @@ template <int BITS, int QPAD>
 int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
     const int sm = ScoreSmem<BITS, QPAD>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    score_tc_kernel<BITS, QPAD><<<grid, kThreads, sm, st>>>(args);
+    score_tc_kernel<BITS, QPAD><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -527,7 +595,7 @@ int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
 
 // ---- host-side planning ---------------------------------------------------------------------------
 constexpr int64_t kChunkKeys = 1 << 20;     // keys per group scored into scratch at a time when only top-k is wanted
-constexpr int64_t kSegLen = 16384;          // scores per selection block
+constexpr int64_t kSegLen = 65536;          // scores per selection block
 
 struct ScoreTcPlan {
     int64_t chunk, nchunks, segs_per_chunk, lists_per_group;
@@ -612,11 +680,10 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             if (r != TQ_OK) return r == TQ_ERR_UNSUPPORTED ? tq_fail(r, "no tensor-core scoring kernel for bits=%d", bits) : r;
         }
         if (topk > 0) {
-            const int cap2 = pow2_at_least(topk + kSelThreads);
             const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
             // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
-            topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, (size_t)cap2 * 8, st>>>(
-                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, keys_per_group, key_off, topk, cap2,
+            topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, 0, st>>>(
+                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, keys_per_group, key_off, topk, pow2_at_least(topk),
                 (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part);
             TQ_CUDA_TRY(cudaGetLastError());
         }

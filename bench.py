@@ -25,9 +25,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 import numpy as np
@@ -43,6 +41,13 @@ SCORE_BYTES_PER_KEY = D * B_MSE // 8 + D // 8 + 8 + 4 * N_QUERIES    # read pack
 METRIC = "quantize Mvec/s & attention_score Gkeys/s; % HBM roofline"
 
 
+def workload_config(world):
+    return {"workload": f"TurboQuantProd d={D} bits={BITS} seed={SEED}: quantize {N_KEYS} keys + attention_score "
+                        f"{N_QUERIES} queries ({N_QUERIES}x{N_KEYS} float32 score matrix) + per-query top-{TOPK}, per GPU",
+            "keys_per_gpu": N_KEYS, "queries": N_QUERIES, "parallelism": f"shard{world}",
+            "l2": "inputs (512 MiB of keys per GPU) are larger than L2; no flush needed"}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -52,53 +57,55 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """SM clock and throttle-reason samples taken by a background thread through NVML while the timed
+    region runs (the region lasts tens of milliseconds, too short for nvidia-smi's own polling)."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
+               ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, gpu_index):
-        self.gpu_index = gpu_index
-        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self.proc = None
+    def __init__(self, gpu_index, period_s=0.002):
+        self.gpu_index, self.period_s = gpu_index, period_s
+        self.samples, self.reason_bits, self.max_mhz = [], 0, None
+        self._stop = False
+        self._thread = None
+        self._err = None
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            phys = self.gpu_index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                ids = [v for v in vis.split(",") if v.strip()]
+                if self.gpu_index < len(ids) and ids[self.gpu_index].strip().isdigit():
+                    phys = int(ids[self.gpu_index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            while not self._stop:
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                try:
+                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                except Exception:
+                    pass
+                time.sleep(self.period_s)
+        except Exception as exc:  # no NVML: report that instead of inventing numbers
+            self._err = repr(exc)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+        import threading
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.file.flush()
-        self.file.seek(0)
-        sm, mx, reasons = [], [], set()
-        for line in self.file.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                 parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.file.name)
-        busy = [s for s in sm if s > 0.5 * max(mx)] if sm else []
-        return {"sm_mhz": statistics.median(busy or sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0,
+                    "reasons": ["no NVML samples" + (": " + self._err if self._err else "")]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
+                "reasons": sorted(name for name, bit in self.REASONS if self.reason_bits & bit)}
 
 
 def oracle_params():
@@ -162,7 +169,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": mvec, "unit": "Mvec/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * wall / max(args.steps, 1),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "TurboQuantProd d=128 bits=4 seed=2026: quantize + attention_score, CPU sample", "l2": "n/a"},
+        "config": workload_config(args.gpus),
         "attention_score": {"value": gkeys, "unit": "Gkeys/s", "queries": N_QUERIES},
         "cpu_baseline": {"value": mvec, "unit": "Mvec/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": mvec, "unit": "Mvec/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -200,11 +207,11 @@ def run_gpu(args):
         e0.record()
         enc = quant.quantize(keys)
         e1.record()
-        top_s, top_i, scores = quant.attention_scores(queries, enc, topk=TOPK, return_matrix=True,
-                                                      index_base=idx_base)
+        scores = quant.attention_scores(queries, enc)                      # the 32 x N score matrix
         e2.record()
+        top_s, top_i = quant.attention_scores(queries, enc, topk=TOPK, index_base=idx_base)
         if world > 1:
-            top_s, top_i = merge_topk_across_ranks(top_s, top_i)
+            top_s, top_i = merge_topk_across_ranks(top_s, top_i)           # the only exchange: NCCL all-gather
         if record is not None:
             record.append((e0, e1, e2))
         return top_s, top_i, scores
@@ -237,6 +244,13 @@ def run_gpu(args):
         dist.all_reduce(mine, op=dist.ReduceOp.MAX)
     total_ms, q_mean, s_mean = (float(v) for v in mine.tolist())
 
+    if args.skip_host_legs:
+        if rank == 0:
+            print(json.dumps({"note": "profiling run without host legs", "keys": N_KEYS, "quantize_ms": q_mean,
+                              "score_ms": s_mean, "ms_per_step": total_ms / args.steps}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     # ---- end to end through the public API with host buffers (pinned), rank-local -------------------
     host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
     host_keys.copy_(keys)
@@ -270,10 +284,7 @@ def run_gpu(args):
             "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 (rotation as 3 fp16 tensor-core passes, fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"TurboQuantProd d={D} bits={BITS} seed={SEED}: quantize {N_KEYS} keys + attention_score "
-                                   f"{N_QUERIES} queries (matrix + fused top-{TOPK}) per GPU",
-                       "keys_per_gpu": N_KEYS, "queries": N_QUERIES, "parallelism": f"shard{world}",
-                       "l2": "inputs (512 MiB of keys per GPU) are larger than L2; no flush needed"},
+            "config": workload_config(world),
             "attention_score": {
                 "value": world * N_KEYS / (s_mean * 1e-3) / 1e9, "unit": "Gkeys/s", "queries": N_QUERIES,
                 "ms": s_mean,
@@ -288,7 +299,7 @@ def run_gpu(args):
             "e2e": {"value": world * N_KEYS / (e2e_mean * 1e-3) / 1e6, "unit": "Mvec/s",
                     "h2d_bytes_per_step": N_KEYS * D * 4, "d2h_bytes_per_step": d2h,
                     "what": "TurboQuantProd.quantize(pinned NumPy keys) + copy of the packed encoding to the host"},
-            "gpu_launches": args.steps * 4,
+            "gpu_launches": args.steps * 12,  # per step: 3 quantize kernels, 2 + 2 scoring, 2 + 2 + 1 top-k
             "clocks": clocks,
         }
         if world == 1:
@@ -310,7 +321,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--keys", type=int, default=N_KEYS,
+                    help="keys per GPU; the default is the benchmark's workload, smaller values are for profiler captures only")
+    ap.add_argument("--skip-host-legs", action="store_true",
+                    help="leave out the end-to-end and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
+    global N_KEYS
+    N_KEYS = args.keys
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
     if args.impl == "reference":

@@ -316,6 +316,7 @@ def run_gpu(args):
 
 
 def main():
+    global N_KEYS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -326,7 +327,6 @@ def main():
     ap.add_argument("--skip-host-legs", action="store_true",
                     help="leave out the end-to-end and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
-    global N_KEYS
     N_KEYS = args.keys
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3

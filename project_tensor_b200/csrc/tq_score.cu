@@ -11,6 +11,7 @@
 // memory with a rising threshold, prunes it with a bitonic sort when it fills, and writes its k
 // best (score, row) pairs as 64-bit sortable keys; a second kernel merges the per-block lists.
 #include "tq_common.cuh"
+#include "tq_topk.cuh"
 
 #include <math.h>
 
@@ -19,35 +20,7 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kQT = 8;  // queries scored together per pass over a block's keys
 
-__device__ __forceinline__ uint32_t ordered_bits(float s) {
-    const uint32_t u = __float_as_uint(s);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float unordered_bits(uint32_t o) {
-    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
-}
-// Larger key = better candidate: higher score first, then lower row index.
-__device__ __forceinline__ unsigned long long make_key(float s, uint32_t row) {
-    return ((unsigned long long)ordered_bits(s) << 32) | (unsigned long long)(0xffffffffu - row);
-}
-
-// In-place descending bitonic sort of `n2` (power of two) keys in shared memory by the whole block.
-__device__ void block_sort_desc(unsigned long long* a, int n2) {
-    for (int k = 2; k <= n2; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-                const int l = i ^ j;
-                if (l > i) {
-                    const unsigned long long x = a[i], y = a[l];
-                    const bool desc = (i & k) == 0;
-                    if (desc ? (x < y) : (x > y)) { a[i] = y; a[l] = x; }
-                }
-            }
-        }
-    }
-    __syncthreads();
-}
+using namespace tqtopk;
 
 __global__ void __launch_bounds__(kThreads)
 score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __restrict__ codes,
@@ -164,21 +137,41 @@ score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __re
     }
 }
 
-// Merge `lists` sorted-or-not lists of `topk` sortable keys per query into the final top-k.
-// part: [groups][lists][qpg][topk]; one block per (query, group).
+// Merge `lists` lists of `topk` sortable keys per query into the final top-k.
+// part: [groups][lists][qpg][topk]; one block per (query, group).  Lists are loaded in batches into a
+// shared buffer that is cut back to the k best by radix select whenever it fills; one final sort.
 __global__ void __launch_bounds__(256)
 merge_keys_kernel(const unsigned long long* __restrict__ part, int lists, int qpg, int topk, int k2,
                   int64_t idx_base, float* __restrict__ top_scores, int64_t* __restrict__ top_idx) {
-    extern __shared__ __align__(16) unsigned char smraw[];
-    unsigned long long* a = reinterpret_cast<unsigned long long*>(smraw);  // [2*k2]
+    __shared__ __align__(16) unsigned long long a[kSelCap];
+    __shared__ int hist[256];
+    __shared__ int scratch[4];
+    __shared__ int count;
     const int qi = blockIdx.x, g = blockIdx.y;
-    for (int i = threadIdx.x; i < 2 * k2; i += blockDim.x) a[i] = 0ull;
+    if (threadIdx.x == 0) count = 0;
     __syncthreads();
     for (int l = 0; l < lists; ++l) {
+        if (count + topk > kSelCap) {  // uniform: count only changes between barriers
+            const int c = count;
+            __syncthreads();
+            block_select_topk(a, c, topk, hist, scratch);
+            if (threadIdx.x == 0) count = topk;
+            __syncthreads();
+        }
         const unsigned long long* src = part + (((size_t)g * lists + l) * qpg + qi) * topk;
-        for (int i = threadIdx.x; i < k2; i += blockDim.x) a[k2 + i] = i < topk ? src[i] : 0ull;
-        block_sort_desc(a, 2 * k2);
+        // empty slots (0) are left out, so every key in the buffer is distinct
+        for (int i = threadIdx.x; i < topk; i += blockDim.x) {
+            const unsigned long long v = src[i];
+            if (v != 0ull) a[atomicAdd(&count, 1)] = v;
+        }
+        __syncthreads();
     }
+    const int c = count;
+    const int keep = c < topk ? c : topk;
+    if (keep < c) block_select_topk(a, c, keep, hist, scratch);
+    __syncthreads();
+    for (int i = keep + threadIdx.x; i < k2; i += blockDim.x) a[i] = 0ull;
+    block_sort_desc(a, k2);
     for (int i = threadIdx.x; i < topk; i += blockDim.x) {
         const unsigned long long ck = a[i];
         const size_t o = ((size_t)g * qpg + qi) * topk + i;
@@ -283,7 +276,7 @@ int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t key
 int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int groups, int topk, int64_t idx_base,
                          float* top_scores, int64_t* top_idx, cudaStream_t st) {
     const int k2 = pow2_at_least(topk);
-    merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * k2 * sizeof(unsigned long long), st>>>(part, lists, qpg, topk, k2,
+    merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(part, lists, qpg, topk, k2,
                                                                                            idx_base, top_scores, top_idx);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
@@ -317,7 +310,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
             // no keys: every slot is empty
             const size_t cnt = (size_t)groups * qpg * topk;
             TQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, cnt * sizeof(unsigned long long), st));
-            merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * pow2_at_least(topk) * sizeof(unsigned long long), st>>>(
+            merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(
                 static_cast<unsigned long long*>(scratch), 1, qpg, topk, pow2_at_least(topk), idx_base, top_scores, top_idx);
             TQ_CUDA_TRY(cudaGetLastError());
         }
@@ -333,7 +326,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
     TQ_CUDA_TRY(cudaGetLastError());
     if (topk > 0) {
         const int k2 = pow2_at_least(topk);
-        merge_keys_kernel<<<dim3(qpg, groups), 256, 2 * k2 * sizeof(unsigned long long), st>>>(
+        merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(
             static_cast<unsigned long long*>(scratch), s.nblk, qpg, topk, k2, idx_base, top_scores, top_idx);
         TQ_CUDA_TRY(cudaGetLastError());
     }

@@ -23,6 +23,7 @@
 // bitonic prune (the same scheme as the general kernel in tq_score.cu), one block per row segment.
 #include "tq_common.cuh"
 #include "tq_ptx.cuh"
+#include "tq_topk.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -409,6 +410,7 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     qs[j] = q[((size_t)g * qpg + q0 + slot) * D + j];
     __syncthreads();
     float r = 0.f, s = 0.f;
+#pragma unroll 32
     for (int k = 0; k < D; ++k) {
         r = fmaf(qs[k], __ldg(p.Rt + (size_t)k * D + j), r);
         s = fmaf(qs[k], __ldg(p.St + (size_t)k * D + j), s);
@@ -435,94 +437,7 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     if (j == 0) ds[slot] = make_float2(1.f / (e1 * kCentScale), 1.f / e2);
 }
 
-// ---- top-k from a score matrix -----------------------------------------------------------------
-__device__ __forceinline__ uint32_t ordered_bits(float s) {
-    const uint32_t u = __float_as_uint(s);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ unsigned long long make_key(float s, uint32_t row) {
-    return ((unsigned long long)ordered_bits(s) << 32) | (unsigned long long)(0xffffffffu - row);
-}
-__device__ void block_sort_desc(unsigned long long* a, int n2) {
-    for (int k = 2; k <= n2; k <<= 1)
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-                const int l = i ^ j;
-                if (l > i) {
-                    const unsigned long long x = a[i], y = a[l];
-                    const bool desc = (i & k) == 0;
-                    if (desc ? (x < y) : (x > y)) { a[i] = y; a[l] = x; }
-                }
-            }
-        }
-    __syncthreads();
-}
-
-constexpr int kSelThreads = 256;
-constexpr int kSelPerThread = 8;
-constexpr int kSelBatch = kSelPerThread * kSelThreads;   // scores examined between two looks at the buffer
-constexpr int kSelCap = 4096;                            // candidate buffer (64-bit keys) per block
-
-// Keep the `k` largest of the `c` distinct keys in buf[0..c) (c <= kSelCap), unsorted, in buf[0..k); returns
-// the k-th largest key.  Radix select, 8 bits per pass from the top, with a 256-bin histogram in shared
-// memory; far cheaper than sorting the buffer.  Whole block; c and k are uniform, k <= c.
-__device__ unsigned long long block_select_topk(unsigned long long* buf, int c, int k, int* hist /*[256]*/,
-                                                int* scratch /*[4]*/) {
-    unsigned long long prefix = 0ull, mask = 0ull;
-    int remaining = k;
-    for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-        __syncthreads();
-        for (int i = threadIdx.x; i < c; i += blockDim.x) {
-            const unsigned long long key = buf[i];
-            if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 255ull)], 1);
-        }
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            // lane l owns bins 255-8l .. 248-8l (descending); find where the running count reaches `remaining`
-            const int lane = threadIdx.x;
-            int mine = 0;
-#pragma unroll
-            for (int b = 0; b < 8; ++b) mine += hist[255 - 8 * lane - b];
-            int incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            const int before = incl - mine;  // keys in strictly higher bins of higher lanes
-            if (before < remaining && incl >= remaining) {
-                int acc = before;
-                for (int b = 0; b < 8; ++b) {
-                    const int bin = 255 - 8 * lane - b;
-                    if (acc + hist[bin] >= remaining) { scratch[0] = bin; scratch[1] = remaining - acc; break; }
-                    acc += hist[bin];
-                }
-            }
-        }
-        __syncthreads();
-        prefix |= (unsigned long long)scratch[0] << shift;
-        mask |= 255ull << shift;
-        remaining = scratch[1];
-        __syncthreads();
-    }
-    // prefix is now the k-th largest key; gather the keys >= prefix (exactly k, keys are distinct)
-    unsigned long long keep[kSelCap / kSelThreads];
-    int nkeep = 0;
-    for (int i = threadIdx.x, j = 0; j < kSelCap / kSelThreads; i += blockDim.x, ++j) {
-        keep[j] = 0ull;
-        if (i < c) { const unsigned long long key = buf[i]; if (key >= prefix) { keep[j] = key; ++nkeep; } }
-    }
-    if (threadIdx.x == 0) scratch[2] = 0;
-    __syncthreads();
-    int pos = nkeep ? atomicAdd(&scratch[2], nkeep) : 0;
-#pragma unroll
-    for (int j = 0; j < kSelCap / kSelThreads; ++j)
-        if (keep[j] != 0ull) buf[pos++] = keep[j];
-    __syncthreads();
-    return prefix;
-}
+using namespace tqtopk;
 
 // grid (segments, rows): block scans scores[row][seg*seg_len ...) and writes its k best as sortable keys
 // to part[((group*lists_per_group + list_base + seg) * qpg + qi) * topk ...].  Candidates above the

@@ -318,38 +318,66 @@ exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t
 }
 
 // TurboQuantMSE.dequantize / TurboQuantProd.dequantize (_quant.py:238-242,251-254,317-332).
+// Same block shape as the quantizer above: kRB rows per pass, one thread per output coordinate.
 template <bool PROD>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(1024)
 exact_dequantize_kernel(TqDev p, const uint32_t* __restrict__ codes, const uint32_t* __restrict__ signs,
                         const float* __restrict__ rnorms, const float* __restrict__ norms, int64_t n,
                         float* __restrict__ out) {
     extern __shared__ float smem[];
-    const int d = p.d, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const WarpBufs wb = warp_bufs(smem, d, warp);
-    for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < n; row += (int64_t)gridDim.x * kWarps) {
-        const uint32_t* crow = codes + row * p.code_words;
-        for (int k = lane; k < d; k += 32) {
-            wb.a[k] = __ldg(p.codebook + tq_get_code(crow, k, p.bits));
-            if (PROD) wb.b[k] = ((signs[row * p.sign_words + (k >> 5)] >> tq_sign_bitpos(k)) & 1u) ? 1.f : -1.f;
-        }
-        __syncwarp();
-        const float nrm = norms[row];
-        const float rn = PROD ? rnorms[row] : 0.f;
-        for (int j0 = 0; j0 < d; j0 += 128) {
-            float r[4], s[4];
-            chain4(wb.a, p.R, d, j0, lane, r);
-            if (PROD) chain4(wb.b, p.S, d, j0, lane, s);
+    const int d = p.d, t = threadIdx.x;
+    float* ct = smem;                        // [d][kRB] centroid values (transposed)
+    float* st = ct + (size_t)d * kRB;        // [d][kRB] +-1 signs (transposed), Prod only
+    const int tj = t < d ? t : d - 1;
+    for (int64_t g0 = (int64_t)blockIdx.x * kRB; g0 < n; g0 += (int64_t)gridDim.x * kRB) {
+        __syncthreads();
+        if (t < d) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int j = j0 + lane + 32 * c;
-                if (j < d) {
-                    float u = r[c];
-                    if (PROD) u = __fadd_rn(u, __fmul_rn(__fmul_rn(s[c], p.alpha), rn));
-                    out[row * d + j] = __fmul_rn(u, nrm);
+            for (int r = 0; r < kRB; ++r) {
+                const int64_t row = g0 + r;
+                float c = 0.f, sg = 0.f;
+                if (row < n) {
+                    c = __ldg(p.codebook + tq_get_code(codes + row * p.code_words, t, p.bits));
+                    if (PROD) sg = ((signs[row * p.sign_words + (t >> 5)] >> tq_sign_bitpos(t)) & 1u) ? 1.f : -1.f;
+                }
+                ct[t * kRB + r] = c;
+                if (PROD) st[t * kRB + r] = sg;
+            }
+        }
+        __syncthreads();
+        float acc[kRB], acs[kRB];
+#pragma unroll
+        for (int r = 0; r < kRB; ++r) { acc[r] = 0.f; acs[r] = 0.f; }
+#pragma unroll 8
+        for (int k = 0; k < d; ++k) {
+            const float m = __ldg(p.R + (size_t)k * d + tj);
+            const float4 a = *reinterpret_cast<const float4*>(ct + k * kRB);
+            const float4 b = *reinterpret_cast<const float4*>(ct + k * kRB + 4);
+            acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
+            acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
+            acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
+            acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
+            if (PROD) {
+                const float ms = __ldg(p.S + (size_t)k * d + tj);
+                const float4 e = *reinterpret_cast<const float4*>(st + k * kRB);
+                const float4 f = *reinterpret_cast<const float4*>(st + k * kRB + 4);
+                acs[0] = __fmaf_rn(e.x, ms, acs[0]); acs[1] = __fmaf_rn(e.y, ms, acs[1]);
+                acs[2] = __fmaf_rn(e.z, ms, acs[2]); acs[3] = __fmaf_rn(e.w, ms, acs[3]);
+                acs[4] = __fmaf_rn(f.x, ms, acs[4]); acs[5] = __fmaf_rn(f.y, ms, acs[5]);
+                acs[6] = __fmaf_rn(f.z, ms, acs[6]); acs[7] = __fmaf_rn(f.w, ms, acs[7]);
+            }
+        }
+        if (t < d) {
+#pragma unroll
+            for (int r = 0; r < kRB; ++r) {
+                const int64_t row = g0 + r;
+                if (row < n) {
+                    float u = acc[r];
+                    if (PROD) u = __fadd_rn(u, __fmul_rn(__fmul_rn(acs[r], p.alpha), rnorms[row]));
+                    out[row * d + t] = __fmul_rn(u, norms[row]);
                 }
             }
         }
-        __syncwarp();
     }
 }
 
@@ -457,14 +485,16 @@ int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* code
                                const float* rnorms, const float* norms, int64_t n, float* out,
                                cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    const size_t sm = smem_bytes(p->dev.d);
-    const int grid = grid_for(n, kWarps);
+    const int d = p->dev.d;
+    const size_t sm = (size_t)2 * d * kRB * sizeof(float);
+    const int grid = grid_for(n, kRB);
+    const int threads = (d + 31) & ~31;
     if (prod) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_dequantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_dequantize_kernel<true><<<grid, kWarps * 32, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
+        exact_dequantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
     } else {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_dequantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_dequantize_kernel<false><<<grid, kWarps * 32, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
+        exact_dequantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
     }
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;

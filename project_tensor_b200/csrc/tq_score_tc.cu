@@ -410,10 +410,18 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     qs[j] = q[((size_t)g * qpg + q0 + slot) * D + j];
     __syncthreads();
     float r = 0.f, s = 0.f;
-#pragma unroll 32
-    for (int k = 0; k < D; ++k) {
-        r = fmaf(qs[k], __ldg(p.Rt + (size_t)k * D + j), r);
-        s = fmaf(qs[k], __ldg(p.St + (size_t)k * D + j), s);
+    for (int k0 = 0; k0 < D; k0 += 16) {
+        float mr16[16], ms16[16];  // fetch a batch of matrix elements first, then run the two chains
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            mr16[u] = __ldg(p.Rt + (size_t)(k0 + u) * D + j);
+            ms16[u] = __ldg(p.St + (size_t)(k0 + u) * D + j);
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            r = fmaf(qs[k0 + u], mr16[u], r);
+            s = fmaf(qs[k0 + u], ms16[u], s);
+        }
     }
     float mr = fabsf(r), ms = fabsf(s);
     for (int o = 16; o > 0; o >>= 1) {

@@ -39,9 +39,8 @@ namespace {
 using namespace tqptx;
 
 constexpr int kTileRows = 128;
-// Warps: TMA, MMA, 8 converters, then the epilogue: one thread per row for TurboQuantProd (its epilogue
-// needs the registers), two per row (each owning half of the columns) for TurboQuantMSE.
-template <bool PROD> struct Threads { static constexpr int kEpiPerRow = PROD ? 1 : 2; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
+// Warps: TMA, MMA, 8 converters, then 8 epilogue warps: two threads per row, each owning half of the columns.
+template <bool PROD> struct Threads { static constexpr int kEpiPerRow = 2; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
 constexpr int kFirstConvWarp = 2;
 constexpr int kFirstEpiWarp = 10;
 constexpr int kBoxBytes = 128 * 128;     // 128 rows x 32 floats
@@ -85,7 +84,7 @@ struct Smem {
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
     static constexpr int kPendBytes = 8 * kPendCap * (8 + 4);   // per epilogue warp: 64-bit and 32-bit entries
-    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 2 * kTileRows * 4 + kCells * 16 + kPendBytes;
+    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 4 * kTileRows * 4 + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
 };
 
@@ -98,8 +97,7 @@ enum {
     BAR_ACC_FULL = 20,            // [2]
     BAR_ACC_EMPTY = 22,           // [2]
     BAR_RHO_FULL = 24,            // [2]
-    BAR_ACC2_FULL = 26,           // [1]
-    BAR_ACC2_EMPTY = 27,          // [1]
+    BAR_ACC2_FULL = 26,           // [2]
     BAR_COUNT = 28
 };
 
@@ -220,7 +218,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     unsigned char* force = smem + L::off_misc + 2 * kTileRows * 4;                      // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 2 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
-    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - 2 * kTileRows * 4 - kCells * 16);  // [2][128]
+    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - 4 * kTileRows * 4 - kCells * 16);  // [2 tiles][2 halves][128]
     float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
     unsigned char* pend_base = smem + L::off_misc + L::kMiscBytes - L::kPendBytes;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -234,13 +232,13 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         for (int i = 0; i < 8; ++i) { mbar_init(BAR(BAR_FULL + i), 1); mbar_init(BAR(BAR_EMPTY + i), 4); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(BAR_A_FULL + i), 8);
-            mbar_init(BAR(BAR_A_EMPTY + i), 1);
+            mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kEpiPerRow : 1);    // Prod: freed by the sign epilogue
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
-            mbar_init(BAR(BAR_ACC_EMPTY + i), 4 * kEpiPerRow);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kEpiPerRow);  // Prod: freed when MMA 2 has read rho
             mbar_init(BAR(BAR_RHO_FULL + i), 4 * kEpiPerRow);
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
-        mbar_init(BAR(BAR_ACC2_EMPTY), 4 * kEpiPerRow);
+        mbar_init(BAR(BAR_ACC2_FULL + 1), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -265,8 +263,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     constexpr int kABlock = D / 2;  // TMEM columns of one fp16 A block (two halves per column)
     // TMEM column map
     auto A_COL = [&](int b) { return (uint32_t)(b * 2 * kABlock); };
-    auto ACC_COL = [&](int b) { return (uint32_t)(4 * kABlock + (PROD ? 0 : b * D)); };
-    const uint32_t kAcc2Col = 4 * kABlock + D;
+    // TMEM: two tile buffers, each an A block (x split; for Prod later the second accumulator) and an
+    // accumulator block (for Prod later rho, split and stored in place chunk by chunk)
+    auto ACC_COL = [&](int b) { return (uint32_t)(4 * kABlock + b * D); };
 
     if (warp == 0) {
         // ---- TMA producer ----------------------------------------------------------------------
@@ -297,49 +296,56 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint64_t d_rhi = make_smem_desc(b_rhi, lbo, sbo), d_rlo = make_smem_desc(b_rlo, lbo, sbo);
             const uint64_t d_mhi = make_smem_desc(b_mhi, lbo, sbo), d_mlo = make_smem_desc(b_mlo, lbo, sbo);
             (void)d_mhi; (void)d_mlo; (void)b_mlo;
-            for (int64_t i = 0; i < my_tiles; ++i) {
-                const int b = (int)(i & 1);
-                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-                const int ab = PROD ? 0 : b;
-                const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
+            // Prod runs one tile ahead with the first contraction: MMA1(i), then MMA2(i-1), so that the
+            // residual epilogue of a tile overlaps tensor work of its neighbour.
+            const int64_t iters = PROD ? my_tiles + 1 : my_tiles;
+            for (int64_t i = 0; i < iters; ++i) {
                 const bool pr = a.prof && blockIdx.x == 0;
-                long long c0 = clock64();
-                if (!mbar_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
-                long long c1 = clock64();
-                if (!mbar_wait(BAR(BAR_ACC_EMPTY + ab), acc_par ^ 1u, abort_flag)) break;
-                tc_fence_after();
-                long long c2 = clock64();
-                if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
-                const uint32_t acc = tmem + ACC_COL(ab);
-                const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
-#pragma unroll
-                for (int kb = 0; kb < D / 16; ++kb) {
-                    const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
-                    const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
-                    mma_ts(acc, a_hi + kb * 8, dh, kIdesc, kb > 0);
-                    mma_ts(acc, a_hi + kb * 8, dl, kIdesc, 1);
-                    mma_ts(acc, a_lo + kb * 8, dh, kIdesc, 1);
-                }
-                mma_commit(BAR(BAR_ACC_FULL + ab));
-                c0 = clock64(); if (pr) a.prof[10] += c0 - c2;
-                if (!PROD) {
-                    mma_commit(BAR(BAR_A_EMPTY + b));
-                } else {
-                    if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
-                    if (!mbar_wait(BAR(BAR_ACC2_EMPTY), (uint32_t)(i & 1) ^ 1u, abort_flag)) break;
+                if (i < my_tiles) {
+                    const int b = (int)(i & 1);
+                    const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                    long long c0 = clock64();
+                    if (!mbar_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
+                    long long c1 = clock64();
+                    if (!mbar_wait(BAR(BAR_ACC_EMPTY + b), par2 ^ 1u, abort_flag)) break;
                     tc_fence_after();
-                    c1 = clock64(); if (pr) a.prof[11] += c1 - c0;
-                    const uint32_t acc2 = tmem + kAcc2Col;
+                    long long c2 = clock64();
+                    if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
+                    const uint32_t acc = tmem + ACC_COL(b);
+                    const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
+#pragma unroll
+                    for (int kb = 0; kb < D / 16; ++kb) {
+                        const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
+                        const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
+                        mma_ts(acc, a_hi + kb * 8, dh, kIdesc, kb > 0);
+                        mma_ts(acc, a_hi + kb * 8, dl, kIdesc, 1);
+                        mma_ts(acc, a_lo + kb * 8, dh, kIdesc, 1);
+                    }
+                    mma_commit(BAR(BAR_ACC_FULL + b));
+                    if (!PROD) mma_commit(BAR(BAR_A_EMPTY + b));
+                    if (pr) a.prof[10] += clock64() - c2;
+                }
+                if (PROD && i >= 1) {
+                    const int64_t j = i - 1;
+                    const int b = (int)(j & 1);
+                    const uint32_t par2 = (uint32_t)((j >> 1) & 1);
+                    long long c0 = clock64();
+                    if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
+                    tc_fence_after();
+                    long long c1 = clock64(); if (pr) a.prof[11] += c1 - c0;
+                    const uint32_t acc2 = tmem + A_COL(b);      // the tile's A block is free: MMA 1 has read it
+                    const uint32_t rho = tmem + ACC_COL(b);     // rho hi / lo pairs, 16 + 16 columns per 32 coordinates
 #pragma unroll
                     for (int kb = 0; kb < D / 16; ++kb) {
                         const uint64_t dh = d_mhi + (uint64_t)(kb * 2 * lbo >> 4);
                         const uint64_t dl = d_mlo + (uint64_t)(kb * 2 * lbo >> 4);
-                        mma_ts(acc2, a_hi + kb * 8, dh, kIdesc, kb > 0);
-                        mma_ts(acc2, a_hi + kb * 8, dl, kIdesc, 1);
-                        mma_ts(acc2, a_lo + kb * 8, dh, kIdesc, 1);
+                        const uint32_t r_hi = rho + (kb >> 1) * 32 + (kb & 1) * 8, r_lo = r_hi + 16;
+                        mma_ts(acc2, r_hi, dh, kIdesc, kb > 0);
+                        mma_ts(acc2, r_hi, dl, kIdesc, 1);
+                        mma_ts(acc2, r_lo, dh, kIdesc, 1);
                     }
-                    mma_commit(BAR(BAR_ACC2_FULL));
-                    mma_commit(BAR(BAR_A_EMPTY + b));
+                    mma_commit(BAR(BAR_ACC2_FULL + b));
+                    mma_commit(BAR(BAR_ACC_EMPTY + b));         // rho has been read: the accumulator block is free
                     if (pr) a.prof[12] += clock64() - c1;
                 }
             }
@@ -442,23 +448,21 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         pend.rows = reinterpret_cast<unsigned int*>(pend_base + 8 * kPendCap * 8) + (warp - kFirstEpiWarp) * kPendCap;
         pend.n_codes = 0;
         pend.n_rows = 0;
-        for (int64_t i = 0; i < my_tiles; ++i) {
+        // first-accumulator epilogue of tile i: codes (+ rho for Prod)
+        auto epilogue1 = [&](int64_t i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            const int ab = PROD ? 0 : b;
-            const uint32_t acc_par = PROD ? (uint32_t)(i & 1) : par2;
             const int64_t grow = tile * kTileRows + row;
             const bool live = grow < a.n;
             const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32;
             long long c0 = clock64(), c1;
-            mbar_wait(BAR(BAR_ACC_FULL + ab), acc_par, abort_flag);
+            mbar_wait(BAR(BAR_ACC_FULL + b), par2, abort_flag);
             tc_fence_after();
             c1 = clock64(); if (pr) a.prof[16] += c1 - c0;
-            bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
+            const bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
             float rs = 0.f;
-            const uint32_t acc = tmem + lane_addr + ACC_COL(ab);
-            const uint32_t a_hi = tmem + lane_addr + A_COL(b);
+            const uint32_t acc = tmem + lane_addr + ACC_COL(b);
             uint32_t va[32], vb[32];
             uint32_t nm[kChunks];
             tmem_ld32(acc + chunk0 * 32, va);
@@ -483,22 +487,21 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                         for (int k = 0; k < BITS; ++k) dst[k] = w[k];
                     }
                 }
-                if (PROD) {
-                    tmem_st16(a_hi + (chunk0 + ch) * 16, rhi);
-                    tmem_st16(a_hi + kABlock + (chunk0 + ch) * 16, rlo);
+                if (PROD) {  // rho replaces the chunk it was computed from: 16 columns of hi pairs, 16 of lo pairs
+                    tmem_st16(acc + (chunk0 + ch) * 32, rhi);
+                    tmem_st16(acc + (chunk0 + ch) * 32 + 16, rlo);
                 }
                 if (!PROD && ch + 1 < kChunks) tmem_wait_ld();
             }
             if (PROD) {
                 tmem_wait_st();
-                if (live) a.rnorms[grow] = sqrtf(rs) * kScaleRho;  // rs is in 2^10 units
+                // this thread's share of |rho|^2; summed in the sign epilogue of the same tile, which every
+                // epilogue warp reaches only after all of them have arrived on RHO_FULL below
+                rs_part[(b * 2 + (chunk0 ? 1 : 0)) * kTileRows + row] = rs;
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(BAR(BAR_ACC_EMPTY + ab));
-                if (PROD) mbar_arrive(BAR(BAR_RHO_FULL + b));
-            }
+            if (lane == 0) mbar_arrive(BAR(PROD ? BAR_RHO_FULL + b : BAR_ACC_EMPTY + b));
             // second-stage work is recorded after the accumulator went back to the tensor pipe
             uint32_t any_nm = 0;
 #pragma unroll
@@ -510,38 +513,59 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 #pragma unroll
                 for (int ch = 0; ch < kChunks; ++ch) pend_codes(a.lists, pend, nm[ch], grow, (chunk0 + ch) * 32, lane);
             }
-            c0 = clock64(); if (pr) a.prof[17] += c0 - c1;
-            if (PROD) {
-                mbar_wait(BAR(BAR_ACC2_FULL), (uint32_t)(i & 1), abort_flag);
-                tc_fence_after();
-                c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
-                const uint32_t acc2 = tmem + lane_addr + kAcc2Col;
-                uint32_t sw[kChunks];
-                tmem_ld32(acc2, va);
+            if (!PROD) pend_rows(a.lists, pend, redo_row && live, grow, lane);
+            if (pr) a.prof[17] += clock64() - c1;
+        };
+        // second-accumulator epilogue of tile j (Prod): sign bits, guard test, release of the tile's A block
+        auto epilogue2 = [&](int64_t j) {
+            const int64_t tile = blockIdx.x + j * gridDim.x;
+            const int b = (int)(j & 1);
+            const uint32_t par2 = (uint32_t)((j >> 1) & 1);
+            const int64_t grow = tile * kTileRows + row;
+            const bool live = grow < a.n;
+            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32;
+            bool redo_row = force[(j & 3) * kTileRows + row] != 0;
+            long long c0 = clock64(), c1;
+            mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag);
+            tc_fence_after();
+            c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
+            const uint32_t acc2 = tmem + lane_addr + A_COL(b);
+            if (chunk0 == 0 && live)   // rs is in 2^10 units
+                a.rnorms[grow] = sqrtf(rs_part[(b * 2) * kTileRows + row] + rs_part[(b * 2 + 1) * kTileRows + row]) * kScaleRho;
+            uint32_t sw[kChunks];
+            uint32_t va[32];
+#pragma unroll
+            for (int ch = 0; ch < kChunks; ++ch) {
+                tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
                 tmem_wait_ld();
+                uint32_t word = 0;
+                float amin = 3.0e38f;
 #pragma unroll
-                for (int ch = 0; ch < kChunks; ++ch) {
-                    if (ch > 0) { tmem_ld32(acc2 + ch * 32, va); tmem_wait_ld(); }
-                    uint32_t word = 0;
-                    float amin = 3.0e38f;
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const uint32_t bits = va[e];
-                        // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
-                        // inside the guard band and recomputed anyway)
-                        word |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
-                        amin = fminf(amin, fabsf(__uint_as_float(bits)));
-                    }
-                    sw[ch] = word;
-                    redo_row = redo_row || (amin < a.sign_guard);
+                for (int e = 0; e < 32; ++e) {
+                    const uint32_t bits = va[e];
+                    // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
+                    // inside the guard band and recomputed anyway)
+                    word |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
+                    amin = fminf(amin, fabsf(__uint_as_float(bits)));
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(BAR_ACC2_EMPTY));
-                if (live) *reinterpret_cast<uint4*>(a.signs + grow * (D / 32)) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
-                c0 = clock64(); if (pr) a.prof[19] += c0 - c1;
+                sw[ch] = word;
+                redo_row = redo_row || (amin < a.sign_guard);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + b));  // the converters may refill this tile buffer
+            if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw[0], sw[1]);
             pend_rows(a.lists, pend, redo_row && live, grow, lane);
+            if (pr) a.prof[19] += clock64() - c1;
+        };
+        if (PROD) {
+            static_assert(kChunks == 2, "the sign store writes two words per thread");
+            for (int64_t i = 0; i <= my_tiles; ++i) {
+                if (i < my_tiles) epilogue1(i);
+                if (i >= 1) epilogue2(i - 1);
+            }
+        } else {
+            for (int64_t i = 0; i < my_tiles; ++i) epilogue1(i);
         }
         if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
         if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);

@@ -41,6 +41,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-Xcompiler", "-fPIC", "-shared"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("TQ_NVCC_FLAGS", "").split()   # extra compiler flags, e.g. -DTQ_PROF for experiments
     cmd += [os.path.join(SRC_DIR, s) for s in SOURCES]
     cmd += ["-o", LIB_PATH]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -147,38 +147,59 @@ __device__ __forceinline__ void pend_rows(const TqRecheck& l, WarpPending& w, bo
 // One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
 // and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
 // the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 by cell, lut_ncent by code.
+__device__ long long g_dbg_blocks[160 * 4];
+
 template <int BITS, bool PROD>
 __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
                                               float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
                                               uint32_t (&rhi)[16], uint32_t (&rlo)[16], float& rs) {
+    // Elements go through the steps in groups of kGroup, step by step, so that the shuffles of a group
+    // are in flight together instead of one element's chain after the other.
+    constexpr int kGroup = 8;
     uint32_t nearmask = 0;  // bit e: element e lies inside the guard band of its boundary
-    float prev_rho = 0.f;
 #pragma unroll
     for (int k = 0; k <= BITS; ++k) w[k] = 0;
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-        const float f = __uint_as_float(v[e]);
-        const float u = fma_sat(f, cell_scale, cell_offset);
-        const int cell = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
-        const float bnd = __shfl_sync(0xffffffffu, lut_bnd, cell);
-        const int base1 = __shfl_sync(0xffffffffu, lut_base1, cell);
-        const float dlt = f - bnd;
-        const uint32_t code = (uint32_t)base1 - (dlt > 0.f ? 0u : 1u);
-        if (fabsf(dlt) < guard) nearmask |= 1u << e;
-        const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
-        w[wi] += code << sh;
-        if (sh + BITS > 32) w[wi + 1] += code >> (32 - sh);
+    for (int g = 0; g < 32; g += kGroup) {
+        int cell[kGroup];
+        float bnd[kGroup];
+        int base1[kGroup];
+        uint32_t code[kGroup];
+#pragma unroll
+        for (int t = 0; t < kGroup; ++t) {
+            const float u = fma_sat(__uint_as_float(v[g + t]), cell_scale, cell_offset);
+            cell[t] = __float_as_int(fma_rm(u, kCellMul, 8388608.f));
+        }
+#pragma unroll
+        for (int t = 0; t < kGroup; ++t) {
+            bnd[t] = __shfl_sync(0xffffffffu, lut_bnd, cell[t]);
+            base1[t] = __shfl_sync(0xffffffffu, lut_base1, cell[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < kGroup; ++t) {
+            const int e = g + t;
+            const float dlt = __uint_as_float(v[e]) - bnd[t];
+            code[t] = (uint32_t)base1[t] - (dlt > 0.f ? 0u : 1u);
+            if (fabsf(dlt) < guard) nearmask |= 1u << e;
+            const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
+            w[wi] += code[t] << sh;
+            if (sh + BITS > 32) w[wi + 1] += code[t] >> (32 - sh);
+        }
         if (PROD) {
-            const float ncent = __shfl_sync(0xffffffffu, lut_ncent, (int)code);
-            const float r = fmaf(f, kScaleRho, ncent);  // 2^10 * (value - centroid)
-            rs = fmaf(r, r, rs);
-            if (e & 1) {
-                const __half2 h = __floats2half2_rn(prev_rho, r);
+            float r[kGroup];
+#pragma unroll
+            for (int t = 0; t < kGroup; ++t) {
+                const float ncent = __shfl_sync(0xffffffffu, lut_ncent, (int)code[t]);
+                r[t] = fmaf(__uint_as_float(v[g + t]), kScaleRho, ncent);  // 2^10 * (value - centroid)
+            }
+#pragma unroll
+            for (int t = 0; t < kGroup; t += 2) {
+                rs = fmaf(r[t], r[t], rs);
+                rs = fmaf(r[t + 1], r[t + 1], rs);
+                const __half2 h = __floats2half2_rn(r[t], r[t + 1]);
                 const float2 hf = __half22float2(h);
-                rhi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                rlo[e >> 1] = pack_half2(prev_rho - hf.x, r - hf.y);
-            } else {
-                prev_rho = r;
+                rhi[(g + t) >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                rlo[(g + t) >> 1] = pack_half2(r[t] - hf.x, r[t + 1] - hf.y);
             }
         }
     }
@@ -226,6 +247,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long prof_t0 = clock64();
 
     // ---- one-time set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
@@ -257,6 +279,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    const long long prof_t1 = clock64();
 
     const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
     constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
@@ -313,7 +336,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
                     const uint32_t acc = tmem + ACC_COL(b);
                     const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
-#pragma unroll
+#pragma unroll 1
                     for (int kb = 0; kb < D / 16; ++kb) {
                         const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
                         const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
@@ -333,9 +356,16 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
                     tc_fence_after();
                     long long c1 = clock64(); if (pr) a.prof[11] += c1 - c0;
-                    const uint32_t acc2 = tmem + A_COL(b);      // the tile's A block is free: MMA 1 has read it
+                    // The second accumulator goes to the A block of the OTHER buffer: MMA 1 of tile j + 1, issued
+                    // above, was its last reader, and using it (rather than this tile's own A block) lets the
+                    // converters refill a block one tile earlier.  The last tile has no successor whose
+                    // converter waited for the previous sign epilogue to leave that block, so wait here.
+                    if (i == my_tiles && j >= 1 &&
+                        !mbar_wait(BAR(BAR_A_EMPTY + (b ^ 1)), (uint32_t)((((j + 1) >> 1) & 1) ^ 1), abort_flag))
+                        break;
+                    const uint32_t acc2 = tmem + A_COL(b ^ 1);
                     const uint32_t rho = tmem + ACC_COL(b);     // rho hi / lo pairs, 16 + 16 columns per 32 coordinates
-#pragma unroll
+#pragma unroll 1
                     for (int kb = 0; kb < D / 16; ++kb) {
                         const uint64_t dh = d_mhi + (uint64_t)(kb * 2 * lbo >> 4);
                         const uint64_t dl = d_mlo + (uint64_t)(kb * 2 * lbo >> 4);
@@ -371,7 +401,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 const int64_t g = g_base + half * 2 + bb;
                 const int slot = (int)(g % L::kRingBoxes);
                 const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
+                long long cw0 = clock64();
                 if (!fail && !mbar_wait(BAR(BAR_FULL + slot), par, abort_flag)) fail = true;
+                if (pr) a.prof[6] += clock64() - cw0;
                 const unsigned char* box = smem + L::off_ring + slot * kBoxBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -415,10 +447,14 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 for (int p = 0; p < 16; ++p) {
                     const float u0 = (ok && !odd) ? x[s * 32 + 2 * p] * sc : 0.f;
                     const float u1 = (ok && !odd) ? x[s * 32 + 2 * p + 1] * sc : 0.f;
+#ifdef TQ_EXP_SKIP_CONV
+                    hi[p] = __float_as_uint(u0); lo[p] = __float_as_uint(u1);
+#else
                     const __half2 h = __floats2half2_rn(u0, u1);
                     const float2 hf = __half22float2(h);
                     hi[p] = *reinterpret_cast<const uint32_t*>(&h);
                     lo[p] = pack_half2(u0 - hf.x, u1 - hf.y);
+#endif
                 }
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
@@ -463,35 +499,60 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
             float rs = 0.f;
             const uint32_t acc = tmem + lane_addr + ACC_COL(b);
-            uint32_t va[32], vb[32];
             uint32_t nm[kChunks];
-            tmem_ld32(acc + chunk0 * 32, va);
-            tmem_wait_ld();
+            if (PROD) {
+                // a real loop over the chunks: half the code of the unrolled form, which matters for the
+                // instruction cache more than the loop overhead does
+                uint32_t nm0 = 0, nm1 = 0;
+#pragma unroll 1
+                for (int ch = 0; ch < kChunks; ++ch) {
+                    uint32_t va[32];
+                    tmem_ld32(acc + (chunk0 + ch) * 32, va);
+                    tmem_wait_ld();
+                    uint32_t w[BITS + 1], rhi[16], rlo[16];
+                    const uint32_t m = process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset,
+                                                                 a.code_guard, w, rhi, rlo, rs);
+                    if (ch == 0) nm0 = m; else nm1 = m;
+                    if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
+                        uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
+                        if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                        else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                        else {
 #pragma unroll
-            for (int ch = 0; ch < kChunks; ++ch) {
-                // MSE: fetch the next chunk while this one is processed (Prod has no registers to spare)
-                if (!PROD && ch + 1 < kChunks) {
-                    if (ch & 1) tmem_ld32(acc + (chunk0 + ch + 1) * 32, va); else tmem_ld32(acc + (chunk0 + ch + 1) * 32, vb);
-                }
-                if (PROD && ch > 0) { tmem_ld32(acc + (chunk0 + ch) * 32, va); tmem_wait_ld(); }
-                uint32_t w[BITS + 1], rhi[16], rlo[16];
-                nm[ch] = (!PROD && (ch & 1))
-                    ? process_chunk<BITS, PROD>(vb, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
-                    : process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
-                if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
-                    uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
-                    if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                    else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-                    else {
-#pragma unroll
-                        for (int k = 0; k < BITS; ++k) dst[k] = w[k];
+                            for (int k = 0; k < BITS; ++k) dst[k] = w[k];
+                        }
                     }
-                }
-                if (PROD) {  // rho replaces the chunk it was computed from: 16 columns of hi pairs, 16 of lo pairs
+                    // rho replaces the chunk it was computed from: 16 columns of hi pairs, 16 of lo pairs
                     tmem_st16(acc + (chunk0 + ch) * 32, rhi);
                     tmem_st16(acc + (chunk0 + ch) * 32 + 16, rlo);
                 }
-                if (!PROD && ch + 1 < kChunks) tmem_wait_ld();
+                nm[0] = nm0;
+                nm[kChunks - 1] = nm1;
+            } else {
+                uint32_t va[32], vb[32];
+                tmem_ld32(acc + chunk0 * 32, va);
+                tmem_wait_ld();
+#pragma unroll
+                for (int ch = 0; ch < kChunks; ++ch) {
+                    // fetch the next chunk while this one is processed
+                    if (ch + 1 < kChunks) {
+                        if (ch & 1) tmem_ld32(acc + (chunk0 + ch + 1) * 32, va); else tmem_ld32(acc + (chunk0 + ch + 1) * 32, vb);
+                    }
+                    uint32_t w[BITS + 1], rhi[16], rlo[16];
+                    nm[ch] = (ch & 1)
+                        ? process_chunk<BITS, PROD>(vb, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
+                        : process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
+                    if (live) {
+                        uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
+                        if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                        else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                        else {
+#pragma unroll
+                            for (int k = 0; k < BITS; ++k) dst[k] = w[k];
+                        }
+                    }
+                    if (ch + 1 < kChunks) tmem_wait_ld();
+                }
             }
             if (PROD) {
                 tmem_wait_st();
@@ -529,12 +590,13 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag);
             tc_fence_after();
             c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
-            const uint32_t acc2 = tmem + lane_addr + A_COL(b);
+            const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
             if (chunk0 == 0 && live)   // rs is in 2^10 units
                 a.rnorms[grow] = sqrtf(rs_part[(b * 2) * kTileRows + row] + rs_part[(b * 2 + 1) * kTileRows + row]) * kScaleRho;
             uint32_t sw[kChunks];
             uint32_t va[32];
-#pragma unroll
+            uint32_t sw0 = 0, sw1 = 0;
+#pragma unroll 1
             for (int ch = 0; ch < kChunks; ++ch) {
                 tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
                 tmem_wait_ld();
@@ -548,12 +610,14 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     word |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
                     amin = fminf(amin, fabsf(__uint_as_float(bits)));
                 }
-                sw[ch] = word;
+                if (ch == 0) sw0 = word; else sw1 = word;
                 redo_row = redo_row || (amin < a.sign_guard);
             }
+            sw[0] = sw0;
+            sw[kChunks - 1] = sw1;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + b));  // the converters may refill this tile buffer
+            if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + (b ^ 1)));  // the converters may refill that A block
             if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw[0], sw[1]);
             pend_rows(a.lists, pend, redo_row && live, grow, lane);
             if (pr) a.prof[19] += clock64() - c1;
@@ -563,6 +627,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             for (int64_t i = 0; i <= my_tiles; ++i) {
                 if (i < my_tiles) epilogue1(i);
                 if (i >= 1) epilogue2(i - 1);
+                // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 has read it
+                else if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
             }
         } else {
             for (int64_t i = 0; i < my_tiles; ++i) epilogue1(i);
@@ -575,6 +641,16 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
+    if (a.prof && threadIdx.x == 0) {
+        const long long t2 = clock64();
+        atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 21), (unsigned long long)(t2 - prof_t0));
+        atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 22), (unsigned long long)(prof_t1 - prof_t0));
+        if (blockIdx.x == 0) a.prof[23] = t2 - prof_t0;
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        if (blockIdx.x < 160) { g_dbg_blocks[blockIdx.x * 4] = t2 - prof_t0; g_dbg_blocks[blockIdx.x * 4 + 1] = smid;
+                                g_dbg_blocks[blockIdx.x * 4 + 2] = (long long)gt; g_dbg_blocks[blockIdx.x * 4 + 3] = my_tiles; }
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
@@ -678,6 +754,8 @@ struct TensorConsts {
     void* dev = nullptr;   // one allocation: operand matrices + lookup tables
     TensorArgs args{};     // pointers into `dev` and the scalar parameters
 };
+
+extern "C" int tq_debug_read_blocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_dbg_blocks, sizeof(long long) * 640); }
 
 bool tq_tensor_supported(int d, int bits) { return d == 128 && bits >= 1 && bits <= 4; }
 

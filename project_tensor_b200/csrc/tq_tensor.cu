@@ -147,8 +147,6 @@ __device__ __forceinline__ void pend_rows(const TqRecheck& l, WarpPending& w, bo
 // One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
 // and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
 // the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 by cell, lut_ncent by code.
-__device__ long long g_dbg_blocks[160 * 4];
-
 template <int BITS, bool PROD>
 __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
                                               float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
@@ -417,9 +415,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(BAR_EMPTY + slot));
             }
-            float ss = 0.f;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int k = 0; k < 64; ++k) ss = fmaf(x[k], x[k], ss);
+            for (int k = 0; k < 64; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
+            const float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
             ssq[half * kTileRows + row] = ss;
             c1 = clock64(); if (pr) a.prof[0] += c1 - c0;
             bar_sync(1 + quarter, 64);  // the two warps that share these 32 rows
@@ -447,14 +446,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 for (int p = 0; p < 16; ++p) {
                     const float u0 = (ok && !odd) ? x[s * 32 + 2 * p] * sc : 0.f;
                     const float u1 = (ok && !odd) ? x[s * 32 + 2 * p + 1] * sc : 0.f;
-#ifdef TQ_EXP_SKIP_CONV
-                    hi[p] = __float_as_uint(u0); lo[p] = __float_as_uint(u1);
-#else
                     const __half2 h = __floats2half2_rn(u0, u1);
                     const float2 hf = __half22float2(h);
                     hi[p] = *reinterpret_cast<const uint32_t*>(&h);
                     lo[p] = pack_half2(u0 - hf.x, u1 - hf.y);
-#endif
                 }
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
@@ -600,16 +595,18 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             for (int ch = 0; ch < kChunks; ++ch) {
                 tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
                 tmem_wait_ld();
-                uint32_t word = 0;
-                float amin = 3.0e38f;
+                uint32_t wd[4] = {0u, 0u, 0u, 0u};                    // four partial chains instead of one long one
+                float am[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const uint32_t bits = va[e];
                     // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
                     // inside the guard band and recomputed anyway)
-                    word |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
-                    amin = fminf(amin, fabsf(__uint_as_float(bits)));
+                    wd[e & 3] |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
+                    am[e & 3] = fminf(am[e & 3], fabsf(__uint_as_float(bits)));
                 }
+                const uint32_t word = (wd[0] | wd[1]) | (wd[2] | wd[3]);
+                const float amin = fminf(fminf(am[0], am[1]), fminf(am[2], am[3]));
                 if (ch == 0) sw0 = word; else sw1 = word;
                 redo_row = redo_row || (amin < a.sign_guard);
             }
@@ -646,10 +643,6 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 21), (unsigned long long)(t2 - prof_t0));
         atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 22), (unsigned long long)(prof_t1 - prof_t0));
         if (blockIdx.x == 0) a.prof[23] = t2 - prof_t0;
-        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        if (blockIdx.x < 160) { g_dbg_blocks[blockIdx.x * 4] = t2 - prof_t0; g_dbg_blocks[blockIdx.x * 4 + 1] = smid;
-                                g_dbg_blocks[blockIdx.x * 4 + 2] = (long long)gt; g_dbg_blocks[blockIdx.x * 4 + 3] = my_tiles; }
     }
     if (warp == 1) {
         tc_fence_after();
@@ -754,8 +747,6 @@ struct TensorConsts {
     void* dev = nullptr;   // one allocation: operand matrices + lookup tables
     TensorArgs args{};     // pointers into `dev` and the scalar parameters
 };
-
-extern "C" int tq_debug_read_blocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_dbg_blocks, sizeof(long long) * 640); }
 
 bool tq_tensor_supported(int d, int bits) { return d == 128 && bits >= 1 && bits <= 4; }
 

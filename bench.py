@@ -63,14 +63,18 @@ class ClockSampler:
     REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
                ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, gpu_index, period_s=0.002):
+    def __init__(self, gpu_index, period_s=0.001):
         self.gpu_index, self.period_s = gpu_index, period_s
         self.samples, self.reason_bits, self.max_mhz = [], 0, None
         self._stop = False
         self._thread = None
         self._err = None
+        self._nvml = None
+        self._handle = None
 
-    def _run(self):
+    def _open(self):
+        """NVML is opened on the caller's thread, before the timed region: opening it takes longer than
+        the region lasts."""
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -80,20 +84,32 @@ class ClockSampler:
                 ids = [v for v in vis.split(",") if v.strip()]
                 if self.gpu_index < len(ids) and ids[self.gpu_index].strip().isdigit():
                     phys = int(ids[self.gpu_index])
-            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
-            while not self._stop:
-                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
-                try:
-                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                except Exception:
-                    pass
-                time.sleep(self.period_s)
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
         except Exception as exc:  # no NVML: report that instead of inventing numbers
             self._err = repr(exc)
 
+    def sample_now(self):
+        """One sample on the caller's thread (called between launches while the GPU is busy)."""
+        if self._nvml is None:
+            return
+        try:
+            self.samples.append(float(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM)))
+            self.reason_bits |= int(self._nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        except Exception as exc:
+            self._err = repr(exc)
+
+    def _run(self):
+        while not self._stop:
+            self.sample_now()
+            time.sleep(self.period_s)
+
     def start(self):
         import threading
+        self._open()
+        if self._nvml is None:
+            return
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
 
@@ -181,7 +197,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
     import project_tensor_b200 as tg
-    from project_tensor_b200 import packed_buffers
+    from project_tensor_b200 import packed_to_host
     from project_tensor_b200.sharded import merge_topk_across_ranks
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -228,8 +244,10 @@ def run_gpu(args):
     recs = []
     t_start, t_end = ev(), ev()
     t_start.record()
-    for _ in range(args.steps):
+    for it in range(args.steps):
         out = step(recs)
+        if rank == 0 and it % 4 == 1:
+            sampler.sample_now()   # the GPU is still working through the launches queued above
     t_end.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -263,16 +281,16 @@ def run_gpu(args):
     host_np = host_keys.numpy()
     e2e_ms = []
     d2h = 0
+    host_out = None
     for it in range(2 + 3):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         enc = quant.quantize(host_np)                          # H2D inside
-        bufs = packed_buffers(enc)
-        host_out = [bufs[k].cpu() for k in ("codes", "signs", "norms", "residual_norms")]  # D2H of the result
+        host_out = packed_to_host(enc, out=host_out)           # D2H of the result into reused pinned buffers
         torch.cuda.synchronize()
         if it >= 2:
             e2e_ms.append(1e3 * (time.perf_counter() - t0))
-        d2h = sum(t.numel() * t.element_size() for t in host_out)
+        d2h = sum(t.numel() * t.element_size() for t in host_out.values() if t is not None)
     e2e = torch.tensor([statistics.mean(e2e_ms)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
@@ -304,7 +322,7 @@ def run_gpu(args):
                          "kernel": "tq_prod_quantize call (tensor-core kernel + exact second stage)"},
             "e2e": {"value": world * N_KEYS / (e2e_mean * 1e-3) / 1e6, "unit": "Mvec/s",
                     "h2d_bytes_per_step": N_KEYS * D * 4, "d2h_bytes_per_step": d2h,
-                    "what": "TurboQuantProd.quantize(pinned NumPy keys) + copy of the packed encoding to the host"},
+                    "what": "TurboQuantProd.quantize(pinned NumPy keys) + packed_to_host(encoding) into reused pinned buffers"},
             "gpu_launches": args.steps * 12,  # per step: 3 quantize kernels, 2 + 2 scoring, 2 + 2 + 1 top-k
             "clocks": clocks,
         }

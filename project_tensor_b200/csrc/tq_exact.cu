@@ -89,27 +89,6 @@ __device__ __forceinline__ void store_packed_codes(const uint8_t* cs, int d, int
     }
 }
 
-struct WarpBufs {
-    float* a;
-    float* b;
-    uint8_t* c;
-};
-
-__device__ __forceinline__ WarpBufs warp_bufs(float* smem, int d, int warp) {
-    const int dp = (d + 31) & ~31;
-    float* base = smem + (size_t)warp * (2 * dp + dp / 4);
-    WarpBufs w;
-    w.a = base;
-    w.b = base + dp;
-    w.c = reinterpret_cast<uint8_t*>(base + 2 * dp);
-    return w;
-}
-
-size_t smem_bytes(int d) {
-    const int dp = (d + 31) & ~31;
-    return (size_t)kWarps * (2 * dp + dp / 4) * sizeof(float);
-}
-
 // TurboQuantMSE.quantize / TurboQuantProd.quantize, array part (_quant.py:224-236, 300-308).
 // One block works on kRB rows at a time with one thread per output coordinate, so that every matrix
 // element fetched from L1/L2 feeds kRB chains; the vectors sit in shared memory transposed ([k][row])

@@ -41,6 +41,7 @@ constexpr int kFirstEpiWarp = 10;
 constexpr int kStages = 8;
 constexpr float kCentScale = 1024.f;
 constexpr int kRowBytesB = D * 2;  // one query row of one fp16 operand matrix
+constexpr int kPrepSmemBytes = 2 * D * D * 4;  // rotation and projection matrices staged by the preparation kernel
 
 __host__ __device__ constexpr int prep_group_bytes(int qpad) { return 4 * qpad * kRowBytesB + 2 * qpad * 4; }
 
@@ -325,6 +326,17 @@ score_tc_kernel(const ScoreTcArgs a) {
         int64_t prev_g = -1, gcount = 0;
         int bb = 0;
         int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
+        // norm and residual norm of this thread's key, fetched one tile ahead of their use (a load issued
+        // in the tile that needs it would stall the stores for a full trip to memory)
+        auto fetch_norms = [&](int64_t gg, int64_t kk, float& n_out, float& r_out) {
+            const int64_t key_n = kk * kTileKeys + row;
+            const bool live_n = key_n < a.key_cnt;
+            const int64_t grow_n = gg * a.keys_per_group + a.key_off + key_n;
+            n_out = live_n ? __ldg(a.norms + grow_n) : 0.f;
+            r_out = live_n ? __ldg(a.rnorms + grow_n) : 0.f;
+        };
+        float nrm_next = 0.f, rn_next = 0.f;
+        if (t0 < t1) fetch_norms(g, kt, nrm_next, rn_next);
         for (int64_t t = t0; t < t1; ++t, ++kt) {
             if (kt == a.tiles_per_group) { kt = 0; ++g; }
             const int64_t i = t - t0;
@@ -333,9 +345,12 @@ score_tc_kernel(const ScoreTcArgs a) {
             if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
             const int64_t key = kt * kTileKeys + row;          // within this launch's key range
             const bool live = key < a.key_cnt;
-            const int64_t grow = g * a.keys_per_group + a.key_off + key;
-            const float nrm = live ? __ldg(a.norms + grow) : 0.f;
-            const float arn = live ? a.alpha * __ldg(a.rnorms + grow) : 0.f;
+            const float nrm = nrm_next;
+            const float arn = a.alpha * rn_next;
+            if (t + 1 < t1) {
+                const bool wrap = kt + 1 == a.tiles_per_group;
+                fetch_norms(wrap ? g + 1 : g, wrap ? 0 : kt + 1, nrm_next, rn_next);
+            }
             long long c0 = clock64();
             const int db = kDBufs == 2 ? b : 0;
             const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
@@ -410,18 +425,27 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     qs[j] = q[((size_t)g * qpg + q0 + slot) * D + j];
     __syncthreads();
     float r = 0.f, s = 0.f;
-    for (int k0 = 0; k0 < D; k0 += 16) {
-        float mr16[16], ms16[16];  // fetch a batch of matrix elements first, then run the two chains
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            mr16[u] = __ldg(p.Rt + (size_t)(k0 + u) * D + j);
-            ms16[u] = __ldg(p.St + (size_t)(k0 + u) * D + j);
+    // The matrices are usually cold (the keys streamed through L2 since the last call), so the time would
+    // go into memory latency if the loads trickled in between the arithmetic: bring both matrices into
+    // shared memory with all copies in flight at once, then run the two chains in order from there.
+    extern __shared__ __align__(16) float mats[];   // [2][D][D]: R^T, S^T
+    {
+        const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(mats);
+        constexpr int kChunks = D * D / 4;          // 16-byte chunks per matrix
+        for (int c = j; c < kChunks; c += 128) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + c * 16), "l"(p.Rt + (size_t)c * 4) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + (kChunks + c) * 16), "l"(p.St + (size_t)c * 4) : "memory");
         }
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            r = fmaf(qs[k0 + u], mr16[u], r);
-            s = fmaf(qs[k0 + u], ms16[u], s);
-        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
+    const float* Rs = mats;
+    const float* Ss = mats + D * D;
+#pragma unroll 16
+    for (int k = 0; k < D; ++k) {
+        r = fmaf(qs[k], Rs[k * D + j], r);
+        s = fmaf(qs[k], Ss[k * D + j], s);
     }
     float mr = fabsf(r), ms = fabsf(s);
     for (int o = 16; o > 0; o >>= 1) {
@@ -578,7 +602,8 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
         for (int q0 = 0; q0 < qpg; q0 += 32) {
             const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
             const int qpad = nq <= 16 ? 16 : 32;
-            score_prep_kernel<<<dim3(qpad, groups), 128, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep);
+            TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
+            score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep);
             TQ_CUDA_TRY(cudaGetLastError());
             ScoreTcArgs a{};
             a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;

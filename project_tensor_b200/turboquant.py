@@ -298,6 +298,29 @@ def packed_buffers(encoding) -> Dict[str, Any]:
     return {"codes": pk.codes, "signs": pk.signs, "norms": pk.norms, "residual_norms": pk.residual_norms}
 
 
+def packed_to_host(encoding, out: Optional[Dict[str, Any]] = None, wait: bool = True) -> Dict[str, Any]:
+    """Copy the packed buffers of an encoding into page-locked host tensors (same keys as
+    ``packed_buffers``).  ``out`` may be the dict returned by an earlier call for an encoding of the
+    same shape; its tensors are reused, which avoids allocating (and faulting in) fresh host memory for
+    every batch -- a device-to-host copy into new pageable memory runs far below the link rate.  The
+    copies are enqueued on the current stream; with ``wait=False`` the caller synchronises."""
+    torch = _require_cuda()
+    bufs = packed_buffers(encoding)
+    host: Dict[str, Any] = {} if out is None else out
+    for name, dev_t in bufs.items():
+        if dev_t is None:
+            host[name] = None
+            continue
+        dst = host.get(name)
+        if dst is None or dst.shape != dev_t.shape or dst.dtype != dev_t.dtype or not dst.is_pinned():
+            dst = torch.empty(dev_t.shape, dtype=dev_t.dtype, pin_memory=True)
+            host[name] = dst
+        dst.copy_(dev_t, non_blocking=True)
+    if wait:
+        torch.cuda.current_stream().synchronize()
+    return host
+
+
 def _as_packed(encoding, plans: _PlanSet, need_signs: bool) -> _Packed:
     """Packed device form of ``encoding``: its own buffers when it came from this quantizer's
     geometry, else packed now from the reference-style array fields."""

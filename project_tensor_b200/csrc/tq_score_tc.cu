@@ -492,12 +492,24 @@ topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t g
     if (k1 > n) k1 = n;
     if (threadIdx.x == 0) { cnt = 0; thr = 0ull; }
     __syncthreads();
+    // The scores of the next batch are already on their way while this one is filtered, and the common
+    // case (nothing to prune) costs one barrier per batch.
+    float nxt[kSelPerThread];
+#pragma unroll
+    for (int j = 0; j < kSelPerThread; ++j) {
+        const int64_t key = k0 + j * kSelThreads + threadIdx.x;
+        nxt[j] = key < k1 ? __ldcs(src + key) : 0.f;
+    }
     for (int64_t kb = k0; kb < k1; kb += kSelBatch) {
         float v[kSelPerThread];
 #pragma unroll
-        for (int j = 0; j < kSelPerThread; ++j) {
-            const int64_t key = kb + j * kSelThreads + threadIdx.x;
-            v[j] = key < k1 ? __ldcs(src + key) : 0.f;
+        for (int j = 0; j < kSelPerThread; ++j) v[j] = nxt[j];
+        if (kb + kSelBatch < k1) {
+#pragma unroll
+            for (int j = 0; j < kSelPerThread; ++j) {
+                const int64_t key = kb + kSelBatch + j * kSelThreads + threadIdx.x;
+                nxt[j] = key < k1 ? __ldcs(src + key) : 0.f;
+            }
         }
         const unsigned long long t = thr;
 #pragma unroll
@@ -506,14 +518,18 @@ topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t g
             const unsigned long long ck = make_key(v[j], row0 + (uint32_t)key);
             if (key < k1 && ck > t) buf[atomicAdd(&cnt, 1)] = ck;
         }
-        __syncthreads();
-        const int c = cnt;  // uniform: nobody appends between the two barriers
-        if (c + kSelBatch > kSelCap && c > topk) {
-            const unsigned long long kth = block_select_topk(buf, c, topk, hist, scratch);
-            if (threadIdx.x == 0) { cnt = topk; thr = kth; }
+        // Each thread tests the count it sees after its own appends; the thread that appended last sees the
+        // final count, so the OR over the block is the test on the final count and is the same for everyone.
+        if (__syncthreads_or(cnt + kSelBatch > kSelCap)) {
+            const int c = cnt;  // stable: every thread is in this branch
+            if (c > topk) {
+                const unsigned long long kth = block_select_topk(buf, c, topk, hist, scratch);
+                if (threadIdx.x == 0) { cnt = topk; thr = kth; }
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
+    __syncthreads();
     int c = cnt;
     if (c > topk) { block_select_topk(buf, c, topk, hist, scratch); c = topk; }
     __syncthreads();
@@ -542,7 +558,7 @@ int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
 
 // ---- host-side planning ---------------------------------------------------------------------------
 constexpr int64_t kChunkKeys = 1 << 20;     // keys per group scored into scratch at a time when only top-k is wanted
-constexpr int64_t kSegLen = 65536;          // scores per selection block
+constexpr int64_t kSegLen = 65536;          // scores per selection block (smaller segments cost more in per-block selection than they gain)
 
 struct ScoreTcPlan {
     int64_t chunk, nchunks, segs_per_chunk, lists_per_group;

@@ -180,6 +180,15 @@ int tq_plan_create(int d, int bits_mse, const float* rotation, const float* code
         }
         p->tensor_ok = p->tensor != nullptr;
     }
+    if (p->tensor_ok && tq_dequant_tc_supported(d, bits_mse, projection != nullptr)) {
+        const int r = tq_dequant_tc_plan_init(p, rotation, projection);
+        if (r != TQ_OK) {
+            tq_tensor_plan_free(p);
+            cudaFree(p->slab);
+            delete p;
+            return r;
+        }
+    }
     *out = p;
     return TQ_OK;
 }
@@ -188,6 +197,7 @@ void tq_plan_destroy(tq_plan* p) {
     if (!p) return;
     DeviceScope scope(p->device);
     tq_tensor_plan_free(p);
+    tq_dequant_tc_plan_free(p);
     if (p->slab) cudaFree(p->slab);
     delete p;
 }
@@ -302,6 +312,11 @@ int tq_mse_dequantize(const tq_plan* p, const void* codes, const float* norms, i
     TQ_TRY(check_ptr(norms, "norms"));
     TQ_TRY(check_ptr(out, "out"));
     DeviceScope scope(p->device);
+    // the tensor-core kernel when the plan has one (within ~1e-7 relative of the reference arithmetic); the
+    // exact kernel reproduces the reference bit for bit and serves every other geometry and the EXACT path
+    if (p->path != TQ_PATH_EXACT && p->dequant)
+        return tq_launch_dequant_tc(p, false, static_cast<const uint32_t*>(codes), nullptr, nullptr, norms, n, out,
+                                    static_cast<cudaStream_t>(stream));
     return tq_launch_exact_dequantize(p, false, static_cast<const uint32_t*>(codes), nullptr, nullptr, norms, n, out,
                                       static_cast<cudaStream_t>(stream));
 }
@@ -317,6 +332,9 @@ int tq_prod_dequantize(const tq_plan* p, const void* codes, const void* signs, c
     TQ_TRY(check_ptr(norms, "norms"));
     TQ_TRY(check_ptr(out, "out"));
     DeviceScope scope(p->device);
+    if (p->path != TQ_PATH_EXACT && p->dequant)
+        return tq_launch_dequant_tc(p, true, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
+                                    residual_norms, norms, n, out, static_cast<cudaStream_t>(stream));
     return tq_launch_exact_dequantize(p, true, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
                                       residual_norms, norms, n, out, static_cast<cudaStream_t>(stream));
 }

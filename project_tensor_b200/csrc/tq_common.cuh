@@ -56,6 +56,7 @@ struct TqDev {
 };
 
 struct TensorConsts;  // defined in tq_tensor.cu
+struct DequantConsts; // defined in tq_dequant_tc.cu
 
 struct tq_plan {
     TqDev dev;
@@ -65,6 +66,7 @@ struct tq_plan {
     bool tensor_ok;          // tensor-core kernels cover this (d, bits)
     void* slab;              // one device allocation holding every constant
     TensorConsts* tensor;    // host-side bookkeeping for the tensor-core kernels (may be null)
+    DequantConsts* dequant;  // operand matrices of the tensor-core dequantize kernels (may be null)
     unsigned long long* counters;  // device: [0] rows re-done by the exact kernel in the last quantize
 };
 
@@ -100,6 +102,13 @@ void tq_tensor_plan_free(tq_plan* p);
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                               uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists,
                               cudaStream_t st);
+
+// Tensor-core dequantize (d = 128): operand matrices per plan, then one launch per call.
+bool tq_dequant_tc_supported(int d, int bits_mse, bool prod);
+int tq_dequant_tc_plan_init(tq_plan* p, const float* rotation, const float* projection);
+void tq_dequant_tc_plan_free(tq_plan* p);
+int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
+                         const float* norms, int64_t n, float* out, cudaStream_t st);
 
 // Scoring kernels.
 int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,

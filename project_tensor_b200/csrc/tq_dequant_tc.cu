@@ -1,0 +1,468 @@
+// Tensor-core dequantize for d = 128 on B200: TurboQuantMSE.dequantize and TurboQuantProd.dequantize
+// (_quant.py:238-242,251-254 and 317-332).
+//
+//   MSE :  x~ = norm * ( codebook[codes] . R )
+//   Prod:  x~ = norm * ( codebook[codes] . R  +  alpha * rnorm * (signs . S) ),  alpha = sqrt(pi/2) / d
+//
+// Both are contractions over the 128 coordinates with the 128 keys of a tile on the M side and the 128
+// output coordinates on the N side.  Operands are fp16 hi + lo pairs (three products per contraction, fp32
+// accumulate), which keeps the result within about 1e-7 relative of the float32 reference arithmetic.
+// For Prod the per-key factor alpha * rnorm is folded into the sign operand (+-beta, split hi/lo, exact),
+// so that both contractions add into one accumulator.  Per tile:
+//
+//   bulk copy (1 thread)   packed codes (and sign words) of 128 keys -> smem ring
+//   expanders (8 warps)    one thread per half key: codes -> (hi, lo) half2 pairs through a lane-replicated
+//                          pair lookup table, signs -> +-beta pairs; tcgen05.st into a ring of four
+//                          64-column operand slots in tensor memory (C_hi, C_lo [, B_hi, B_lo] of
+//                          successive tiles)
+//   MMA (1 thread)         operand by operand: C_hi x (Rt_hi, Rt_lo), C_lo x Rt_hi [, B_hi x (St_hi, St_lo),
+//                          B_lo x St_hi], N = 128, accumulators double-buffered
+//   epilogue (8 warps)     two threads per key: tcgen05.ld, times norm * 2^-20, 16-byte streaming stores
+//
+// Every wait is bounded; a wait that runs out sets the plan's status word and the kernel drains.
+#include "tq_common.cuh"
+#include "tq_ptx.cuh"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <vector>
+
+namespace {
+
+using namespace tqptx;
+
+constexpr int D = 128;
+constexpr int kTileKeys = 128;
+constexpr int kFirstExpWarp = 2;
+constexpr int kFirstEpiWarp = 10;
+constexpr int kThreads = 18 * 32;
+constexpr int kSlots = 4;
+constexpr float kCentScale = 1024.f;   // centroids  -> A operand
+constexpr float kRotScale = 1024.f;    // rotation   -> B operand
+constexpr float kBetaScale = 65536.f;  // alpha * rnorm -> A operand
+constexpr float kProjScale = 16.f;     // projection -> B operand (kBetaScale * kProjScale = kCentScale * kRotScale)
+constexpr float kOutScale = 1.f / (kCentScale * kRotScale);
+constexpr int kMatBytes = D * D * 2;   // one fp16 operand matrix
+
+struct DequantArgs {
+    const uint32_t* codes;
+    const uint32_t* signs;
+    const float* rnorms;
+    const float* norms;
+    const unsigned char* bmat;   // [Rt_hi | Rt_lo | St_hi | St_lo], interleaved core-matrix layout
+    const float* codebook;
+    float alpha;
+    int64_t n, ntiles;
+    float* out;
+    unsigned long long* status;
+};
+
+enum {
+    DB_K_FULL = 0,     // [8]
+    DB_K_EMPTY = 8,    // [8]
+    DB_A_FULL = 16,    // [4]
+    DB_A_EMPTY = 20,   // [4]
+    DB_D_FULL = 24,    // [2]
+    DB_D_EMPTY = 26,   // [2]
+    DB_COUNT = 28
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32_(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld32(taddr, v); }
+
+template <int BITS, bool PROD>
+struct DqSmem {
+    static constexpr int kLutEntries = 1 << (2 * BITS);
+    static constexpr int kLutBytes = kLutEntries * 32 * 8;
+    static constexpr int kCodeRowBytes = D * BITS / 8;
+    static constexpr int kRowExtra = PROD ? 16 : 0;              // sign words
+    static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + kRowExtra);
+    static constexpr int kNumB = PROD ? 4 : 2;
+    static constexpr int kStages = PROD ? 6 : 8;
+    static constexpr int off_lut = 0;
+    static constexpr int off_b = off_lut + kLutBytes;
+    static constexpr int off_ring = off_b + kNumB * kMatBytes;
+    static constexpr int off_misc = off_ring + kStages * kStageBytes;
+    static constexpr int total = off_misc + 512 + 128;
+    static_assert(total <= 227 * 1024, "shared memory plan");
+};
+
+template <int BITS, bool PROD>
+__global__ void __launch_bounds__(kThreads, 1)
+dequant_tc_kernel(const DequantArgs a) {
+    using L = DqSmem<BITS, PROD>;
+    constexpr int kStages = L::kStages;
+    constexpr int kOps = PROD ? 4 : 2;   // operands per tile: C_hi, C_lo [, B_hi, B_lo]
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const uint32_t smem_base = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DB_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8; ++i) { mbar_init(BAR(DB_K_FULL + i), 1); mbar_init(BAR(DB_K_EMPTY + i), 8); }
+        for (int i = 0; i < kSlots; ++i) { mbar_init(BAR(DB_A_FULL + i), 8); mbar_init(BAR(DB_A_EMPTY + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(BAR(DB_D_FULL + i), 1); mbar_init(BAR(DB_D_EMPTY + i), 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {   // pair lookup table: entry e = (code0 | code1 << BITS) -> (half2 hi(c0), hi(c1)), (half2 lo(c0), lo(c1)),
+        // one copy per lane so that the lookups of a warp never collide on a bank
+        uint2* lut = reinterpret_cast<uint2*>(smem + L::off_lut);
+        for (int i = threadIdx.x; i < L::kLutEntries * 32; i += kThreads) {
+            const int e = i >> 5;
+            const float c0 = __ldg(a.codebook + (e & ((1 << BITS) - 1))) * kCentScale;
+            const float c1 = __ldg(a.codebook + (e >> BITS)) * kCentScale;
+            const __half2 h = __floats2half2_rn(c0, c1);
+            const float2 hf = __half22float2(h);
+            uint2 v;
+            v.x = *reinterpret_cast<const uint32_t*>(&h);
+            v.y = pack_half2(c0 - hf.x, c1 - hf.y);
+            lut[i] = v;
+        }
+    }
+    {   // operand matrices: global -> smem, once per CTA
+        const uint4* src = reinterpret_cast<const uint4*>(a.bmat);
+        uint4* dst = reinterpret_cast<uint4*>(smem + L::off_b);
+        for (int i = threadIdx.x; i < L::kNumB * kMatBytes / 16; i += kThreads) dst[i] = __ldg(src + i);
+        fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
+    constexpr uint32_t kSlotCols = 64;
+    constexpr uint32_t kColD = kSlots * kSlotCols;   // two accumulators of 128 columns behind the operand ring
+
+    if (warp == 0) {
+        // ---- bulk-copy producer -----------------------------------------------------------------
+        if (lane == 0) {
+            for (int64_t i = 0; i < my_tiles; ++i) {
+                const int64_t tile = blockIdx.x + i * gridDim.x;
+                const int s = (int)(i % kStages);
+                if (!mbar_wait(BAR(DB_K_EMPTY + s), (uint32_t)((i / kStages) & 1) ^ 1u, abort_flag)) break;
+                int64_t valid = a.n - tile * kTileKeys;
+                if (valid > kTileKeys) valid = kTileKeys;
+                const int64_t row0 = tile * kTileKeys;
+                const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes;
+                const uint32_t dst = smem_base + L::off_ring + s * L::kStageBytes;
+                if (PROD) {
+                    const uint32_t sb = (uint32_t)valid * 16u;
+                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb + sb);
+                    bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(DB_K_FULL + s));
+                    bulk_load(dst + kTileKeys * L::kCodeRowBytes, reinterpret_cast<const unsigned char*>(a.signs) + row0 * 16, sb,
+                              BAR(DB_K_FULL + s));
+                } else {
+                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb);
+                    bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(DB_K_FULL + s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer --------------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t lbo = 128, sbo = (D / 8) * 128;
+            const uint32_t b0 = smem_base + L::off_b;
+            const uint64_t d_rhi = make_smem_desc(b0, lbo, sbo), d_rlo = make_smem_desc(b0 + kMatBytes, lbo, sbo);
+            const uint64_t d_shi = make_smem_desc(b0 + 2 * kMatBytes, lbo, sbo), d_slo = make_smem_desc(b0 + 3 * kMatBytes, lbo, sbo);
+            (void)d_shi; (void)d_slo;
+            for (int64_t i = 0; i < my_tiles; ++i) {
+                const int b = (int)(i & 1);
+                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                if (!mbar_wait(BAR(DB_D_EMPTY + b), par2 ^ 1u, abort_flag)) break;
+                const uint32_t acc = tmem + kColD + b * D;
+                bool ok = true;
+#pragma unroll
+                for (int op = 0; op < kOps; ++op) {              // 0: C_hi, 1: C_lo, 2: B_hi, 3: B_lo
+                    const int64_t n = (int64_t)kOps * i + op;
+                    const int slot = (int)(n & (kSlots - 1));
+                    if (!mbar_wait(BAR(DB_A_FULL + slot), (uint32_t)((n / kSlots) & 1), abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t aop = tmem + slot * kSlotCols;
+                    const uint64_t bh = op < 2 ? d_rhi : d_shi, bl = op < 2 ? d_rlo : d_slo;
+#pragma unroll 1
+                    for (int kb = 0; kb < D / 16; ++kb) {
+                        // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                        const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                        mma_ts(acc, aop + kb * 8, bh + step, kIdesc, (op > 0 || kb > 0) ? 1u : 0u);
+                        if ((op & 1) == 0) mma_ts(acc, aop + kb * 8, bl + step, kIdesc, 1u);   // hi operand also meets the lo matrix
+                    }
+                    mma_commit(BAR(DB_A_EMPTY + slot));
+                }
+                if (!ok) break;
+                mma_commit(BAR(DB_D_FULL + b));
+            }
+        }
+    } else if (warp < kFirstEpiWarp) {
+        // ---- expanders ----------------------------------------------------------------------------
+        const int half = (warp - kFirstExpWarp) >> 2;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
+        constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
+        constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
+        // residual norm of this thread's key, fetched a tile ahead of its use (Prod)
+        float rn_next = 0.f;
+        if (PROD && my_tiles > 0) {
+            const int64_t r0 = (int64_t)blockIdx.x * kTileKeys + row;
+            rn_next = r0 < a.n ? __ldg(a.rnorms + r0) : 0.f;
+        }
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            const int s = (int)(i % kStages);
+            const float rn = rn_next;
+            if (PROD && i + 1 < my_tiles) {
+                const int64_t r1 = (blockIdx.x + (i + 1) * gridDim.x) * kTileKeys + row;
+                rn_next = r1 < a.n ? __ldg(a.rnorms + r1) : 0.f;
+            }
+            bool fail = !mbar_wait(BAR(DB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+            uint32_t w[kHalfWords + 1], sw[2] = {0u, 0u};
+            {
+                const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
+#pragma unroll
+                for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
+                w[kHalfWords] = 0;
+                if (PROD) {
+                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * 16) + half * 2;
+                    sw[0] = fail ? 0u : ~sg[0];   // a set bit now means a negative sign
+                    sw[1] = fail ? 0u : ~sg[1];
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && !fail) mbar_arrive(BAR(DB_K_EMPTY + s));
+            uint32_t hi[2][16], lo[2][16];
+#pragma unroll
+            for (int sb = 0; sb < 2; ++sb)
+#pragma unroll
+                for (int p = 0; p < 16; ++p) {
+                    const int pair = sb * 16 + p;
+                    const int bit = pair * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                    uint32_t e;
+                    if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                    else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                    const uint2 v = lut_lane[e * 32];
+                    hi[sb][p] = v.x;
+                    lo[sb][p] = v.y;
+                }
+            // beta = alpha * rnorm as fp16 hi + lo, both halves of a pair alike; the signs flip bit 15 / 31
+            uint32_t bh2 = 0u, bl2 = 0u;
+            if (PROD) {
+                const float beta = a.alpha * rn * kBetaScale;
+                const __half bh = __float2half_rn(beta);
+                const __half bl = __float2half_rn(beta - __half2float(bh));
+                const uint32_t bhu = (uint32_t)__half_as_ushort(bh), blu = (uint32_t)__half_as_ushort(bl);
+                bh2 = bhu | (bhu << 16);
+                bl2 = blu | (blu << 16);
+            }
+#pragma unroll
+            for (int op = 0; op < kOps; ++op) {
+                const int64_t n = (int64_t)kOps * i + op;
+                const int slot = (int)(n & (kSlots - 1));
+                if (!mbar_wait(BAR(DB_A_EMPTY + slot), (uint32_t)((n / kSlots) & 1) ^ 1u, abort_flag)) fail = true;
+                tc_fence_after();
+                const uint32_t abase = tmem + lane_addr + slot * kSlotCols + half * 32;
+#pragma unroll
+                for (int sb = 0; sb < 2; ++sb) {
+                    if (op == 0) tmem_st16(abase + sb * 16, hi[sb]);
+                    else if (op == 1) tmem_st16(abase + sb * 16, lo[sb]);
+                    else {
+                        // sign word sb covers coordinates 32*sb .. 32*sb+31 of this half; pair p: bits p, 16+p
+                        uint32_t sg[16];
+                        const uint32_t pat = op == 2 ? bh2 : bl2;
+#pragma unroll
+                        for (int p = 0; p < 16; ++p) sg[p] = pat ^ ((sw[sb] << (15 - p)) & 0x80008000u);
+                        tmem_st16(abase + sb * 16, sg);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(DB_A_FULL + slot));
+            }
+        }
+    } else {
+        // ---- epilogue: two threads per key, each one half of the output coordinates -----------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int colhalf = (warp - kFirstEpiWarp) >> 2;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float nrm_next = 0.f;
+        if (my_tiles > 0) {
+            const int64_t r0 = (int64_t)blockIdx.x * kTileKeys + row;
+            nrm_next = r0 < a.n ? __ldg(a.norms + r0) : 0.f;
+        }
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            const int64_t tile = blockIdx.x + i * gridDim.x;
+            const int b = (int)(i & 1);
+            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+            const int64_t grow = tile * kTileKeys + row;
+            const bool live = grow < a.n;
+            const float sc = nrm_next * kOutScale;
+            if (i + 1 < my_tiles) {   // the norm of the next tile's key is fetched a tile ahead of its use
+                const int64_t rn = (tile + gridDim.x) * kTileKeys + row;
+                nrm_next = rn < a.n ? __ldg(a.norms + rn) : 0.f;
+            }
+            mbar_wait(BAR(DB_D_FULL + b), par2, abort_flag);
+            tc_fence_after();
+            const uint32_t acc = tmem + lane_addr + kColD + b * D + colhalf * 64;
+            uint32_t va[32], vb[32];
+            tmem_ld32_(acc, va);
+            tmem_ld32_(acc + 32, vb);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(DB_D_EMPTY + b));   // the accumulator is free again
+            if (live) {
+                float4* dst = reinterpret_cast<float4*>(a.out + grow * D + colhalf * 64);
+#pragma unroll
+                for (int m = 0; m < 8; ++m)
+                    __stcs(dst + m, make_float4(__uint_as_float(va[4 * m]) * sc, __uint_as_float(va[4 * m + 1]) * sc,
+                                                __uint_as_float(va[4 * m + 2]) * sc, __uint_as_float(va[4 * m + 3]) * sc));
+#pragma unroll
+                for (int m = 0; m < 8; ++m)
+                    __stcs(dst + 8 + m, make_float4(__uint_as_float(vb[4 * m]) * sc, __uint_as_float(vb[4 * m + 1]) * sc,
+                                                    __uint_as_float(vb[4 * m + 2]) * sc, __uint_as_float(vb[4 * m + 3]) * sc));
+            }
+        }
+    }
+
+    // ---- teardown ---------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 3ull);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+uint16_t half_bits(float v) {
+    const __half h = __float2half_rn(v);
+    uint16_t b;
+    memcpy(&b, &h, 2);
+    return b;
+}
+float half_value(uint16_t b) {
+    __half h;
+    memcpy(&h, &b, 2);
+    return __half2float(h);
+}
+
+// B[n][k] = m[k][n] * scale as fp16 hi + lo in the K-major 8x8 core-matrix layout the tensor core reads.
+void split_transposed(const float* m, int d, float scale, uint16_t* hi, uint16_t* lo) {
+    const size_t sbo = (size_t)(d / 8) * 128, lbo = 128;
+    for (int n = 0; n < d; ++n)
+        for (int k = 0; k < d; ++k) {
+            const float v = m[(size_t)k * d + n] * scale;
+            const uint16_t h = half_bits(v);
+            const uint16_t l = half_bits(v - half_value(h));
+            const size_t off = ((size_t)(n / 8) * sbo + (size_t)(k / 8) * lbo + (size_t)(n % 8) * 16 + (size_t)(k % 8) * 2) / 2;
+            hi[off] = h;
+            lo[off] = l;
+        }
+}
+
+template <int BITS, bool PROD>
+int launch_one(const DequantArgs& args, int grid, cudaStream_t st) {
+    const int sm = DqSmem<BITS, PROD>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    dequant_tc_kernel<BITS, PROD><<<grid, kThreads, sm, st>>>(args);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
+}  // namespace
+
+struct DequantConsts {
+    void* dev = nullptr;   // [Rt_hi | Rt_lo | St_hi | St_lo]
+};
+
+bool tq_dequant_tc_supported(int d, int bits_mse, bool prod) {
+    // the pair lookup table of a 4-bit code and four operand matrices do not fit side by side
+    return d == 128 && bits_mse >= 1 && bits_mse <= (prod ? 3 : 4);
+}
+
+int tq_dequant_tc_plan_init(tq_plan* p, const float* rotation, const float* projection) {
+    const int d = p->dev.d;
+    if (d != 128) return TQ_OK;
+    const size_t dd = (size_t)d * d;
+    const int nmat = projection ? 4 : 2;
+    std::vector<uint16_t> mats(dd * nmat, 0);
+    split_transposed(rotation, d, kRotScale, mats.data(), mats.data() + dd);
+    if (projection) split_transposed(projection, d, kProjScale, mats.data() + 2 * dd, mats.data() + 3 * dd);
+    DequantConsts* c = new DequantConsts();
+    cudaError_t e = cudaMalloc(&c->dev, mats.size() * 2);
+    if (e == cudaSuccess) e = cudaMemcpy(c->dev, mats.data(), mats.size() * 2, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (c->dev) cudaFree(c->dev);
+        delete c;
+        return tq_fail(TQ_ERR_CUDA, "upload of dequantize operand matrices failed: %s", cudaGetErrorString(e));
+    }
+    p->dequant = c;
+    return TQ_OK;
+}
+
+void tq_dequant_tc_plan_free(tq_plan* p) {
+    if (p->dequant) {
+        if (p->dequant->dev) cudaFree(p->dequant->dev);
+        delete p->dequant;
+        p->dequant = nullptr;
+    }
+}
+
+int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
+                         const float* norms, int64_t n, float* out, cudaStream_t st) {
+    if (n == 0) return TQ_OK;
+    if (!p->dequant) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core dequantize constants in this plan");
+    DequantArgs a{};
+    a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
+    a.bmat = static_cast<const unsigned char*>(p->dequant->dev);
+    a.codebook = p->dev.codebook;
+    a.alpha = p->dev.alpha;
+    a.n = n;
+    a.ntiles = (n + kTileKeys - 1) / kTileKeys;
+    a.out = out;
+    a.status = p->counters + 1;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
+    const int grid = (int)(a.ntiles < sms ? a.ntiles : sms);
+    const int bits = p->dev.bits;
+    int r = TQ_ERR_UNSUPPORTED;
+    if (prod) {
+        switch (bits) {
+            case 1: r = launch_one<1, true>(a, grid, st); break;
+            case 2: r = launch_one<2, true>(a, grid, st); break;
+            case 3: r = launch_one<3, true>(a, grid, st); break;
+            default: break;
+        }
+    } else {
+        switch (bits) {
+            case 1: r = launch_one<1, false>(a, grid, st); break;
+            case 2: r = launch_one<2, false>(a, grid, st); break;
+            case 3: r = launch_one<3, false>(a, grid, st); break;
+            case 4: r = launch_one<4, false>(a, grid, st); break;
+            default: break;
+        }
+    }
+    if (r == TQ_ERR_UNSUPPORTED) return tq_fail(r, "no tensor-core dequantize kernel for bits=%d", bits);
+    return r;
+}

@@ -434,7 +434,7 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
                                const TqRecheck* lists, cudaStream_t st) {
     if (n == 0) return TQ_OK;
     const int dp = (p->dev.d + 31) & ~31;
-    exact_code_check_kernel<<<148 * 4, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists);
+    exact_code_check_kernel<<<148 * 8, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -286,3 +286,28 @@ def test_round_trip_properties_at_scale(tg):
     again = packed_buffers(prod.quantize(x))
     first = packed_buffers(enc)
     assert torch.equal(first["codes"], again["codes"]) and torch.equal(first["signs"], again["signs"])
+
+
+@pytest.mark.parametrize("cls_name,bits", [("TurboQuantMSE", 4), ("TurboQuantMSE", 3), ("TurboQuantMSE", 1),
+                                           ("TurboQuantProd", 4), ("TurboQuantProd", 2)])
+@pytest.mark.parametrize("n", [1, 127, 129, 40000])
+def test_tensor_dequantize_matches_exact_dequantize(tg, cls_name, bits, n):
+    """The tensor-core dequantize kernel against the exact kernel (which reproduces the reference's float32
+    arithmetic bit for bit) on ragged sizes, with a zero row and rows of very different norms."""
+    import torch
+    d = 128
+    gen = torch.Generator(device="cuda").manual_seed(20290 + n)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    x *= torch.logspace(-6, 6, n, device="cuda")[:, None]
+    if n > 3:
+        x[3] = 0
+    quant = getattr(tg, cls_name)(d, bits, seed=2026)
+    enc = quant.quantize(x)
+    quant.set_kernel_path("exact")
+    ref = quant.dequantize(enc).cpu().numpy()
+    quant.set_kernel_path("tensor")
+    got = quant.dequantize(enc).cpu().numpy()
+    assert got.shape == ref.shape == (n, d)
+    assert parity.max_rel_rows(got, ref) <= REL_RECON
+    if n > 3:
+        assert not got[3].any()

@@ -17,7 +17,8 @@
 //                          successive tiles)
 //   MMA (1 thread)         operand by operand: C_hi x (Rt_hi, Rt_lo), C_lo x Rt_hi [, B_hi x (St_hi, St_lo),
 //                          B_lo x St_hi], N = 128, accumulators double-buffered
-//   epilogue (8 warps)     two threads per key: tcgen05.ld, times norm * 2^-20, 16-byte streaming stores
+//   epilogue (8 warps)     two threads per key: tcgen05.ld, times norm * 2^-20, then through a staging block in
+//                          shared memory so that every global store instruction writes whole 128-byte lines
 //
 // Every wait is bounded; a wait that runs out sets the plan's status word and the kernel drains.
 #include "tq_common.cuh"
@@ -84,11 +85,14 @@ struct DqSmem {
     static constexpr int kRowExtra = PROD ? 16 : 0;              // sign words
     static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + kRowExtra);
     static constexpr int kNumB = PROD ? 4 : 2;
-    static constexpr int kStages = PROD ? 6 : 8;
+    static constexpr int kStages = PROD ? 4 : 6;
+    static constexpr int kOutRowBytes = 36 * 4;                   // 32 floats of a row + padding against bank conflicts
+    static constexpr int kOutWarpBytes = 32 * kOutRowBytes;       // staging block of one epilogue warp
     static constexpr int off_lut = 0;
     static constexpr int off_b = off_lut + kLutBytes;
     static constexpr int off_ring = off_b + kNumB * kMatBytes;
-    static constexpr int off_misc = off_ring + kStages * kStageBytes;
+    static constexpr int off_out = off_ring + kStages * kStageBytes;
+    static constexpr int off_misc = off_out + 8 * kOutWarpBytes;
     static constexpr int total = off_misc + 512 + 128;
     static_assert(total <= 227 * 1024, "shared memory plan");
 };
@@ -313,8 +317,6 @@ dequant_tc_kernel(const DequantArgs a) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            const int64_t grow = tile * kTileKeys + row;
-            const bool live = grow < a.n;
             const float sc = nrm_next * kOutScale;
             if (i + 1 < my_tiles) {   // the norm of the next tile's key is fetched a tile ahead of its use
                 const int64_t rn = (tile + gridDim.x) * kTileKeys + row;
@@ -330,16 +332,28 @@ dequant_tc_kernel(const DequantArgs a) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(DB_D_EMPTY + b));   // the accumulator is free again
-            if (live) {
-                float4* dst = reinterpret_cast<float4*>(a.out + grow * D + colhalf * 64);
+            // Through a per-warp staging block in shared memory, so that the global stores of a warp cover
+            // whole 128-byte lines (four rows x 32 floats per instruction) instead of 16 bytes of 32 rows.
+            unsigned char* stg = smem + L::off_out + (warp - kFirstEpiWarp) * L::kOutWarpBytes;
+            const int64_t row0 = tile * kTileKeys + quarter * 32;
 #pragma unroll
-                for (int m = 0; m < 8; ++m)
-                    __stcs(dst + m, make_float4(__uint_as_float(va[4 * m]) * sc, __uint_as_float(va[4 * m + 1]) * sc,
-                                                __uint_as_float(va[4 * m + 2]) * sc, __uint_as_float(va[4 * m + 3]) * sc));
+            for (int ch = 0; ch < 2; ++ch) {
+                float4* mine = reinterpret_cast<float4*>(stg + lane * L::kOutRowBytes);
 #pragma unroll
-                for (int m = 0; m < 8; ++m)
-                    __stcs(dst + 8 + m, make_float4(__uint_as_float(vb[4 * m]) * sc, __uint_as_float(vb[4 * m + 1]) * sc,
-                                                    __uint_as_float(vb[4 * m + 2]) * sc, __uint_as_float(vb[4 * m + 3]) * sc));
+                for (int m = 0; m < 8; ++m) {
+                    const uint32_t* v = ch == 0 ? va : vb;
+                    mine[m] = make_float4(__uint_as_float(v[4 * m]) * sc, __uint_as_float(v[4 * m + 1]) * sc,
+                                          __uint_as_float(v[4 * m + 2]) * sc, __uint_as_float(v[4 * m + 3]) * sc);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int r = it * 4 + (lane >> 3), c4 = lane & 7;
+                    const float4 val = *reinterpret_cast<const float4*>(stg + r * L::kOutRowBytes + c4 * 16);
+                    if (row0 + r < a.n)
+                        __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * D + colhalf * 64 + ch * 32) + c4, val);
+                }
+                __syncwarp();
             }
         }
     }

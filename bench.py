@@ -246,9 +246,9 @@ def run_gpu(args):
     t_start.record()
     for it in range(args.steps):
         out = step(recs)
-        if rank == 0 and it % 4 == 1:
-            sampler.sample_now()   # the GPU is still working through the launches queued above
     t_end.record()
+    if rank == 0:
+        sampler.sample_now()       # the GPU is still working through the launches queued above
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -275,6 +275,41 @@ def run_gpu(args):
         if world > 1:
             dist.destroy_process_group()
         return
+    # ---- the other calls of the path, each timed alone with CUDA events (median of 10), rank 0 only --------
+    other = {}
+    if rank == 0:
+        def timed(fn, reps=10):
+            for _ in range(3):
+                fn()
+            ms = []
+            for _ in range(reps):
+                a_, b_ = ev(), ev()
+                a_.record()
+                fn()
+                b_.record()
+                torch.cuda.synchronize()
+                ms.append(a_.elapsed_time(b_))
+            return statistics.median(ms)
+
+        mse = tg.TurboQuantMSE(D, BITS, seed=SEED)
+        enc_m = mse.quantize(keys)
+        enc_p = quant.quantize(keys)
+        mse_bytes = 4 * D + D * BITS // 8 + 4
+        rows = (
+            ("mse_quantize", lambda: mse.quantize(keys), mse_bytes, "B/vector: fp32 row in, packed codes + norm out"),
+            ("mse_dequantize", lambda: mse.dequantize(enc_m), mse_bytes, "B/vector: packed codes + norm in, fp32 row out"),
+            ("prod_dequantize", lambda: quant.dequantize(enc_p), QUANT_BYTES_PER_VEC, "B/vector: packed encoding in, fp32 row out"),
+            ("attention_score_top%d_no_matrix" % TOPK,
+             lambda: quant.attention_scores(queries, enc_p, topk=TOPK, index_base=idx_base),
+             D * B_MSE // 8 + D // 8 + 8, "B/key: packed key in; scores stay in scratch"),
+        )
+        peak_o, _ = measured_peaks()
+        for name, fn, nbytes, what in rows:
+            ms = timed(fn)
+            gbs = nbytes * N_KEYS / (ms * 1e-3) / 1e9
+            other[name] = {"ms": ms, "M_per_s": N_KEYS / (ms * 1e-3) / 1e6, "bytes_per_unit": nbytes, "bytes": what,
+                           "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_o}
+        del enc_m, enc_p
     # ---- end to end through the public API with host buffers (pinned), rank-local -------------------
     host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
     host_keys.copy_(keys)
@@ -325,6 +360,7 @@ def run_gpu(args):
                     "what": "TurboQuantProd.quantize(pinned NumPy keys) + packed_to_host(encoding) into reused pinned buffers"},
             "gpu_launches": args.steps * 12,  # per step: 3 quantize kernels, 2 + 2 scoring, 2 + 2 + 1 top-k
             "clocks": clocks,
+            "other_calls": other,
         }
         if world == 1:
             n_sample = 262144

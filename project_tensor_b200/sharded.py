@@ -54,10 +54,16 @@ def merge_topk_across_ranks(top_scores, top_idx, group=None, merge: Optional[Cal
     if world == 1:
         gathered_s, gathered_i = top_scores[None], top_idx[None]
     else:
-        gathered_s = torch.empty((world,) + tuple(top_scores.shape), dtype=top_scores.dtype, device=top_scores.device)
-        gathered_i = torch.empty((world,) + tuple(top_idx.shape), dtype=top_idx.dtype, device=top_idx.device)
-        dist.all_gather(list(gathered_s.unbind(0)), top_scores, group=group)
-        dist.all_gather(list(gathered_i.unbind(0)), top_idx, group=group)
+        # one collective for both arrays: the score bits ride in an int64 beside the indices
+        k = top_scores.shape[-1]
+        packed = torch.cat((top_scores.view(torch.int32).to(torch.int64), top_idx), dim=-1)
+        gathered = torch.empty((world,) + tuple(packed.shape), dtype=torch.int64, device=packed.device)
+        if packed.is_cuda:
+            dist.all_gather_into_tensor(gathered, packed, group=group)
+        else:  # gloo
+            dist.all_gather(list(gathered.unbind(0)), packed, group=group)
+        gathered_s = gathered[..., :k].to(torch.int32).view(torch.float32).contiguous()
+        gathered_i = gathered[..., k:].contiguous()
     return (merge or _merge_on_gpu)(gathered_s, gathered_i)
 
 

@@ -9,11 +9,13 @@ array operation in hand-written sm_100a CUDA kernels.
 The six public names of the reference module are exported unchanged.
 """
 from .turboquant import (Tensor, TurboQuantMSE, TurboQuantMSEEncoding, TurboQuantProd,
-                         TurboQuantProdEncoding, packed_buffers, packed_to_host, turboquant_mse, turboquant_prod)
+                         TurboQuantProdEncoding, packed_buffers, packed_to_host, quantize_to_host, turboquant_mse,
+                         turboquant_prod)
 from .codebook import _build_lloyd_max_codebook  # used by the reference's own tests
 
 __all__ = ["Tensor", "TurboQuantMSE", "TurboQuantMSEEncoding", "TurboQuantProd",
-           "TurboQuantProdEncoding", "packed_buffers", "packed_to_host", "turboquant_mse", "turboquant_prod"]
+           "TurboQuantProdEncoding", "packed_buffers", "packed_to_host", "quantize_to_host", "turboquant_mse",
+           "turboquant_prod"]
 
 
 def set_device(device: str) -> None:

@@ -321,6 +321,74 @@ def packed_to_host(encoding, out: Optional[Dict[str, Any]] = None, wait: bool = 
     return host
 
 
+def quantize_to_host(quantizer, keys, chunk_rows: int = 131072, out: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+    """Quantize host-resident keys and leave the packed encoding in page-locked host tensors, for key sets
+    that do not stay on the GPU (``quantizer`` is a TurboQuantMSE or TurboQuantProd, ``keys`` a NumPy
+    array of shape (..., d), best page-locked).  The keys go up in chunks of ``chunk_rows`` on one stream
+    while the previous chunk is quantized on a second and the chunk before that is copied back on a third,
+    so the call takes about as long as the host-to-device copy alone.  Returns the dict described under
+    ``packed_buffers`` (``out`` may be the dict of an earlier call of the same size: its tensors are
+    reused)."""
+    torch = _require_cuda()
+    prod = isinstance(quantizer, TurboQuantProd)
+    mseq = quantizer.mse if prod else quantizer
+    plans = quantizer._plans
+    d = quantizer.dimension
+    array = _to_array(keys)
+    if not isinstance(array, np.ndarray):
+        raise TypeError("quantize_to_host expects host (NumPy) keys; use quantize() for device arrays")
+    _ensure_last_dim(array, d)
+    flat = torch.from_numpy(np.ascontiguousarray(array.reshape(-1, d), dtype=np.float32))
+    n = flat.shape[0]
+    device = torch.device("cuda", torch.cuda.current_device())
+    code_bytes, sign_bytes = plans.row_bytes()
+    shapes = {"codes": ((n, code_bytes), torch.uint8), "norms": ((n,), torch.float32)}
+    if prod:
+        shapes.update({"signs": ((n, sign_bytes), torch.uint8), "residual_norms": ((n,), torch.float32)})
+    host: Dict[str, Any] = {} if out is None else out
+    for name, (shape, dtype) in shapes.items():
+        t = host.get(name)
+        if t is None or tuple(t.shape) != shape or t.dtype != dtype or not t.is_pinned():
+            host[name] = torch.empty(shape, dtype=dtype, pin_memory=True)
+    if not prod:
+        host["signs"] = host["residual_norms"] = None
+    if n == 0:
+        return host
+    chunk_rows = max(1, min(int(chunk_rows), n))
+    with torch.cuda.device(device):
+        s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        for s_ in (s_in, s_run, s_out):
+            s_.wait_stream(torch.cuda.current_stream())
+        bufs = [torch.empty((chunk_rows, d), dtype=torch.float32, device=device) for _ in range(2)]
+        ran = [None, None]          # event: the kernels that read bufs[b] have finished
+        alive = []                  # chunk results stay allocated until the copies back are done
+        for i, start in enumerate(range(0, n, chunk_rows)):
+            m = min(chunk_rows, n - start)
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if ran[b] is not None:
+                    s_in.wait_event(ran[b])
+                bufs[b][:m].copy_(flat[start:start + m], non_blocking=True)
+                up = torch.cuda.Event()
+                up.record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(up)
+                pk = mseq._quantize_staged(_Staged(bufs[b][:m], (m,), "torch", device), plans, prod)
+                ran[b] = torch.cuda.Event()
+                ran[b].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ran[b])
+                host["codes"][start:start + m].copy_(pk.codes, non_blocking=True)
+                host["norms"][start:start + m].copy_(pk.norms, non_blocking=True)
+                if prod:
+                    host["signs"][start:start + m].copy_(pk.signs, non_blocking=True)
+                    host["residual_norms"][start:start + m].copy_(pk.residual_norms, non_blocking=True)
+            alive.append(pk)
+        s_out.synchronize()
+        torch.cuda.current_stream().wait_stream(s_run)
+    return host
+
+
 def _as_packed(encoding, plans: _PlanSet, need_signs: bool) -> _Packed:
     """Packed device form of ``encoding``: its own buffers when it came from this quantizer's
     geometry, else packed now from the reference-style array fields."""

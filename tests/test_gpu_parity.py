@@ -311,3 +311,24 @@ def test_tensor_dequantize_matches_exact_dequantize(tg, cls_name, bits, n):
     assert parity.max_rel_rows(got, ref) <= REL_RECON
     if n > 3:
         assert not got[3].any()
+
+
+@pytest.mark.parametrize("cls_name", ["TurboQuantMSE", "TurboQuantProd"])
+def test_quantize_to_host_equals_quantize(tg, cls_name):
+    """The chunked host-to-host path gives the same packed bytes as one device call, for a size that is not
+    a multiple of the chunk, with pageable and with page-locked input, and when its output is reused."""
+    import torch
+    from project_tensor_b200 import packed_buffers, quantize_to_host
+    d, n = 128, 70001
+    x = np.random.default_rng(20291).standard_normal((n, d)).astype(np.float32)
+    quant = getattr(tg, cls_name)(d, 4, seed=2026)
+    ref = packed_buffers(quant.quantize(torch.from_numpy(x).cuda()))
+    pinned = torch.from_numpy(x).pin_memory().numpy()
+    out = None
+    for keys in (x, pinned, pinned):
+        out = quantize_to_host(quant, keys, chunk_rows=16384, out=out)
+        for name, dev_t in ref.items():
+            if dev_t is None:
+                assert out[name] is None
+            else:
+                assert torch.equal(out[name], dev_t.cpu()), name

@@ -147,22 +147,31 @@ merge_keys_kernel(const unsigned long long* __restrict__ part, int lists, int qp
     __shared__ int hist[256];
     __shared__ int scratch[4];
     __shared__ int count;
+    __shared__ unsigned long long thr;   // keys at or below it cannot be among the k best any more
     const int qi = blockIdx.x, g = blockIdx.y;
-    if (threadIdx.x == 0) count = 0;
+    if (threadIdx.x == 0) { count = 0; thr = 0ull; }
     __syncthreads();
-    for (int l = 0; l < lists; ++l) {
-        if (count + topk > kSelCap) {  // uniform: count only changes between barriers
+    // all slots of all lists in batches, whatever the number of lists (some callers bring hundreds of short
+    // ones, mostly empty)
+    const int total = lists * topk;
+    constexpr int kBatch = 2048;
+    for (int base = 0; base < total; base += kBatch) {
+        if (count + kBatch > kSelCap) {  // uniform: count only changes between barriers
             const int c = count;
             __syncthreads();
-            block_select_topk(a, c, topk, hist, scratch);
-            if (threadIdx.x == 0) count = topk;
+            if (c > topk) {
+                const unsigned long long kth = block_select_topk(a, c, topk, hist, scratch);
+                if (threadIdx.x == 0) { count = topk; thr = kth; }
+            }
             __syncthreads();
         }
-        const unsigned long long* src = part + (((size_t)g * lists + l) * qpg + qi) * topk;
+        const unsigned long long t = thr;
+        const int end = base + kBatch < total ? base + kBatch : total;
         // empty slots (0) are left out, so every key in the buffer is distinct
-        for (int i = threadIdx.x; i < topk; i += blockDim.x) {
-            const unsigned long long v = src[i];
-            if (v != 0ull) a[atomicAdd(&count, 1)] = v;
+        for (int i = base + threadIdx.x; i < end; i += blockDim.x) {
+            const int l = i / topk, j = i - l * topk;
+            const unsigned long long v = part[(((size_t)g * lists + l) * qpg + qi) * topk + j];
+            if (v > t) a[atomicAdd(&count, 1)] = v;   // also drops the empty slots
         }
         __syncthreads();
     }

@@ -1,0 +1,107 @@
+"""GPU suite for batched scoring: query groups (one block of queries per block of keys, as the heads of a KV
+cache), per-query top-k, index offsets, key sets that span several scratch chunks.  The oracle scores one
+query at a time, exactly as the reference's callers do (validate_turboquant.py:92-95)."""
+import numpy as np
+import pytest
+
+from oracle import turboquant_oracle as orc
+import parity
+
+pytestmark = pytest.mark.gpu
+
+REL_SCORE = 1e-4
+
+
+@pytest.fixture(scope="module")
+def tg(lib_built):
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import project_tensor_b200 as tg
+    return tg
+
+
+def _oracle_params(prod):
+    d, bits = prod.dimension, prod.bits
+    return orc.ProdParams(d, bits, orc.mse_params(d, max(bits - 1, 1), rotation=prod.mse.rotation,
+                                                  codebook=prod.mse.codebook), prod.projection)
+
+
+@pytest.mark.parametrize("path", ["exact", "tensor"])
+def test_grouped_queries_with_outlier_channels_against_oracle(tg, path):
+    """Six key groups (KV heads) of 4096 keys with four channels per head scaled by 10, four queries per
+    group, TurboQuantProd(128, 3): every query meets the keys of its own group only."""
+    d, bits, groups, kpg, qpg = 128, 3, 6, 4096, 4
+    rng = np.random.default_rng(20263)
+    keys = rng.standard_normal((groups, kpg, d)).astype(np.float32)
+    for h in range(groups):
+        keys[h][:, np.random.default_rng(20280 + h).choice(d, 4, replace=False)] *= 10.0
+    queries = np.random.default_rng(20273).standard_normal((groups, qpg, d)).astype(np.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    prod.set_kernel_path(path)
+    pp = _oracle_params(prod)
+    flat = keys.reshape(-1, d)
+    want = orc.prod_quantize(pp, flat)
+    ref_enc = tg.TurboQuantProdEncoding(indices=want[0], qjl=want[1], residual_norms=want[2], norms=want[3],
+                                        prefix_shape=(groups * kpg,))
+    got = prod.attention_scores(queries.reshape(-1, d), ref_enc, groups=groups)
+    assert got.shape == (groups * qpg, kpg)
+    for g in range(groups):
+        sl = slice(g * kpg, (g + 1) * kpg)
+        part = (want[0][sl], want[1][sl], want[2][sl], want[3][sl], (kpg,))
+        ref = np.stack([orc.prod_attention_score(pp, q, *part) for q in queries[g]])
+        err = parity.max_score_err(got[g * qpg:(g + 1) * qpg], ref, np.linalg.norm(queries[g], axis=1)[:, None],
+                                   want[3][sl][None, :], d)
+        assert err <= REL_SCORE, (g, err)
+    # top-k of the same call: global key indices, descending scores, equal to the matrix they come from
+    k = 10
+    top_s, top_i, mat = prod.attention_scores(queries.reshape(-1, d), ref_enc, groups=groups, topk=k, return_matrix=True,
+                                              index_base=1000)
+    assert np.array_equal(mat, got)
+    for r in range(groups * qpg):
+        g = r // qpg
+        order = np.argsort(-got[r], kind="stable")[:k]
+        assert np.array_equal(top_s[r], got[r][order])
+        assert np.array_equal(top_i[r], order + g * kpg + 1000)
+
+
+@pytest.mark.parametrize("path", ["exact", "tensor"])
+@pytest.mark.parametrize("n,nq,k", [(1000, 4, 10), (70000, 40, 100), (38405, 32, 300), (257, 3, 500)])
+def test_topk_equals_sorted_matrix(tg, path, n, nq, k):
+    """Per-query top-k, with and without the matrix, against a stable sort of the matrix of the same kernels:
+    ragged key counts, more than 32 queries (two passes), k above 128 and k above the number of keys."""
+    import torch
+    d = 128
+    gen = torch.Generator(device="cuda").manual_seed(20264 + n)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, 4, seed=2026)
+    prod.set_kernel_path(path)
+    enc = prod.quantize(x)
+    mat = prod.attention_scores(q, enc)
+    top_s, top_i = prod.attention_scores(q, enc, topk=k)
+    top_s2, top_i2, mat2 = prod.attention_scores(q, enc, topk=k, return_matrix=True)
+    assert torch.equal(mat, mat2) and torch.equal(top_s, top_s2) and torch.equal(top_i, top_i2)
+    kk = min(k, n)
+    srt = torch.sort(mat, dim=1, descending=True, stable=True)
+    assert torch.equal(top_s[:, :kk], srt.values[:, :kk])
+    assert torch.equal(top_i[:, :kk], srt.indices[:, :kk])
+    if k > n:   # the slots beyond the last key are marked empty
+        assert bool((top_i[:, n:] == -1).all()) and bool(torch.isinf(top_s[:, n:]).all())
+
+
+def test_topk_over_several_scratch_chunks(tg):
+    """2,500,000 keys: without a matrix from the caller the scores pass through scratch in chunks of 2^20
+    keys; the per-chunk candidates must merge into the same top-100 as a sort of the full matrix."""
+    import torch
+    d, n, nq, k = 128, 2_500_000, 8, 100
+    gen = torch.Generator(device="cuda").manual_seed(20265)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, 4, seed=2026)
+    enc = prod.quantize(x)
+    del x
+    mat = prod.attention_scores(q, enc)
+    top_s, top_i = prod.attention_scores(q, enc, topk=k, index_base=7)
+    srt = torch.sort(mat, dim=1, descending=True, stable=True)
+    assert torch.equal(top_s, srt.values[:, :k])
+    assert torch.equal(top_i, srt.indices[:, :k] + 7)

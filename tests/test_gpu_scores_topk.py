@@ -105,3 +105,34 @@ def test_topk_over_several_scratch_chunks(tg):
     srt = torch.sort(mat, dim=1, descending=True, stable=True)
     assert torch.equal(top_s, srt.values[:, :k])
     assert torch.equal(top_i, srt.indices[:, :k] + 7)
+
+
+def test_sharded_index_matches_single_index(tg):
+    """ShardedKeyIndex filled chunk by chunk (device and host chunks) and searched, and two shards of the same
+    keys searched one after the other and merged with tq_topk_merge as the ranks of a job would after the
+    all-gather: both give the top-k of one index over all keys."""
+    import torch
+    from project_tensor_b200.sharded import ShardedKeyIndex, _merge_on_gpu, shard_range
+    d, n, nq, k = 128, 150_001, 5, 50
+    gen = torch.Generator(device="cuda").manual_seed(20266)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, 4, seed=2026)
+    whole = ShardedKeyIndex(prod, n, rank=0, world=1)
+    whole.add(x[:60_000])
+    whole.add(x[60_000:60_007].cpu().numpy())
+    whole.add(x[60_007:])
+    with pytest.raises(ValueError):
+        whole.add(x[:1])
+    ref_s, ref_i = prod.attention_scores(q, prod.quantize(x), topk=k)
+    got_s, got_i = whole.search(q, k)
+    assert torch.equal(got_s, ref_s) and torch.equal(got_i, ref_i)
+    parts = []
+    for rank in range(2):
+        lo, hi = shard_range(n, rank, 2)
+        shard = ShardedKeyIndex(prod, n, rank=rank, world=2)
+        shard.add(x[lo:hi])
+        assert (shard.start, shard.stop) == (lo, hi)
+        parts.append(prod.attention_scores(q, shard.encoding(), topk=k, index_base=lo))
+    merged_s, merged_i = _merge_on_gpu(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]))
+    assert torch.equal(merged_s, ref_s) and torch.equal(merged_i, ref_i)

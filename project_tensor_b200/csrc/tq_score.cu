@@ -267,7 +267,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
                        size_t scratch_bytes, cudaStream_t st);
 
 static bool use_tensor_scoring(const tq_plan* p) {
-    return p->path != TQ_PATH_EXACT && p->has_projection && tq_tensor_supported(p->dev.d, p->dev.bits);
+    return p->path != TQ_PATH_EXACT && p->has_projection && p->dev.d == 128 && tq_tensor_supported(p->dev.d, p->dev.bits);
 }
 
 static int64_t general_topk_scratch(int groups, int qpg, int64_t keys_per_group, int topk) {
@@ -278,7 +278,7 @@ static int64_t general_topk_scratch(int groups, int qpg, int64_t keys_per_group,
 
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk) {
     const int64_t a = general_topk_scratch(groups, qpg, keys_per_group, topk);
-    const int64_t b = tq_tensor_supported(p->dev.d, p->dev.bits) ? tq_score_tc_scratch(groups, qpg, keys_per_group, topk) : 0;
+    const int64_t b = (p->dev.d == 128 && tq_tensor_supported(p->dev.d, p->dev.bits)) ? tq_score_tc_scratch(groups, qpg, keys_per_group, topk) : 0;
     return a > b ? a : b;
 }
 

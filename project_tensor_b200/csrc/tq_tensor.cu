@@ -74,10 +74,11 @@ struct TensorArgs {
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan
 // ---------------------------------------------------------------------------------------------
+constexpr int kW = 128;   // width of the operand layouts in tensor and shared memory; d = 64 is zero-padded to it
 template <int D, bool PROD>
 struct Smem {
     static constexpr int kBoxesPerTile = D / 32;
-    static constexpr int kBBytes = D * D * 2;                       // one fp16 operand matrix
+    static constexpr int kBBytes = kW * kW * 2;                     // one fp16 operand matrix (padded)
     static constexpr int kNumB = PROD ? 4 : 2;
     static constexpr int kRingBoxes = PROD ? 5 : 8;
     static constexpr int off_b = 0;
@@ -225,7 +226,11 @@ __device__ __noinline__ void pend_codes(const TqRecheck& l, WarpPending& w, uint
 template <int D, int BITS, bool PROD>
 __global__ void __launch_bounds__(Threads<PROD>::kThreads, 1)
 tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
-    static_assert(D == 128, "this kernel is written for d = 128");
+    static_assert(D == 128 || D == 64, "this kernel is written for d = 128 and d = 64");
+    // d = 64 runs in the layouts of d = 128 with the upper half of every row absent: the converter warps
+    // and the epilogue warps of that half stay idle, the contractions stop after d / 16 k-blocks and cover
+    // N = d output coordinates.
+    constexpr int kHalves = D / 64;
     constexpr int kThreads = Threads<PROD>::kThreads;
     constexpr int kEpiPerRow = Threads<PROD>::kEpiPerRow;
     using L = Smem<D, PROD>;
@@ -251,11 +256,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8; ++i) { mbar_init(BAR(BAR_FULL + i), 1); mbar_init(BAR(BAR_EMPTY + i), 4); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(BAR_A_FULL + i), 8);
-            mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kEpiPerRow : 1);    // Prod: freed by the sign epilogue
+            mbar_init(BAR(BAR_A_FULL + i), 4 * kHalves);                   // the converter warps that have data
+            mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kHalves : 1);       // Prod: freed by the sign epilogue
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
-            mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kEpiPerRow);  // Prod: freed when MMA 2 has read rho
-            mbar_init(BAR(BAR_RHO_FULL + i), 4 * kEpiPerRow);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kHalves);     // Prod: freed when MMA 2 has read rho
+            mbar_init(BAR(BAR_RHO_FULL + i), 4 * kHalves);
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
         mbar_init(BAR(BAR_ACC2_FULL + 1), 1);
@@ -281,12 +286,12 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 
     const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
     constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
-    constexpr int kABlock = D / 2;  // TMEM columns of one fp16 A block (two halves per column)
+    constexpr int kABlock = kW / 2;  // TMEM columns of one fp16 A block (two halves per column)
     // TMEM column map
     auto A_COL = [&](int b) { return (uint32_t)(b * 2 * kABlock); };
     // TMEM: two tile buffers, each an A block (x split; for Prod later the second accumulator) and an
     // accumulator block (for Prod later rho, split and stored in place chunk by chunk)
-    auto ACC_COL = [&](int b) { return (uint32_t)(4 * kABlock + b * D); };
+    auto ACC_COL = [&](int b) { return (uint32_t)(4 * kABlock + b * kW); };
 
     if (warp == 0) {
         // ---- TMA producer ----------------------------------------------------------------------
@@ -309,7 +314,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     } else if (warp == 1) {
         // ---- MMA issuer ------------------------------------------------------------------------
         if (lane == 0) {
-            const uint32_t sbo = (D / 8) * 128, lbo = 128;
+            const uint32_t sbo = (kW / 8) * 128, lbo = 128;
             const uint32_t b_rhi = smem_base + L::off_b, b_rlo = b_rhi + L::kBBytes;
             const uint32_t b_mhi = b_rlo + L::kBBytes, b_mlo = b_mhi + L::kBBytes;
             // descriptors of k-block 0; the start-address field counts 16-byte units, so k-block kb
@@ -386,7 +391,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         int64_t g_base = 0;
-        for (int64_t i = 0; i < my_tiles; ++i, g_base += L::kBoxesPerTile) {
+        for (int64_t i = 0; i < (half < kHalves ? my_tiles : 0); ++i, g_base += L::kBoxesPerTile) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
@@ -421,9 +426,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
             ssq[half * kTileRows + row] = ss;
             c1 = clock64(); if (pr) a.prof[0] += c1 - c0;
-            bar_sync(1 + quarter, 64);  // the two warps that share these 32 rows
+            if (kHalves == 2) bar_sync(1 + quarter, 64);  // the two warps that share these 32 rows
+            else __syncwarp();
             c0 = clock64(); if (pr) a.prof[1] += c0 - c1;
-            const float tot = ssq[row] + ssq[kTileRows + row];
+            const float tot = kHalves == 2 ? ssq[row] + ssq[kTileRows + row] : ssq[row];
             const float nrm = sqrtf(tot);
             const bool ok = nrm > 0.f;
             // rows the tensor-core pass cannot represent go to the exact kernel: overflowed or
@@ -467,8 +473,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         constexpr int kCodeWords = D * BITS / 32;  // words per packed row
-        constexpr int kChunks = D / 32 / kEpiPerRow;                 // 32-column chunks per thread
-        const int chunk0 = ((warp - kFirstEpiWarp) >> 2) * kChunks;   // first chunk of this thread
+        constexpr int kChunks = 2;                                    // 32-column chunks per thread
+        const int colgroup = (warp - kFirstEpiWarp) >> 2;             // which 64 columns of the row
+        const int chunk0 = colgroup * kChunks;                        // first chunk of this thread
+        const int64_t epi_tiles = colgroup < kHalves ? my_tiles : 0;  // with d = 64 the warps of the upper half idle
         // lookup tables held in the lanes of the warp: per cell (boundary, 1 + boundaries below), per code
         // (- centroid * 2^10)
         const float lut_bnd = cell_lut[lane].x;
@@ -586,8 +594,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             tc_fence_after();
             c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
             const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
-            if (chunk0 == 0 && live)   // rs is in 2^10 units
-                a.rnorms[grow] = sqrtf(rs_part[(b * 2) * kTileRows + row] + rs_part[(b * 2 + 1) * kTileRows + row]) * kScaleRho;
+            if (chunk0 == 0 && live) {   // rs is in 2^10 units
+                const float rs_all = kHalves == 2 ? rs_part[(b * 2) * kTileRows + row] + rs_part[(b * 2 + 1) * kTileRows + row]
+                                                  : rs_part[(b * 2) * kTileRows + row];
+                a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
+            }
             uint32_t sw[kChunks];
             uint32_t va[32];
             uint32_t sw0 = 0, sw1 = 0;
@@ -621,14 +632,14 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         };
         if (PROD) {
             static_assert(kChunks == 2, "the sign store writes two words per thread");
-            for (int64_t i = 0; i <= my_tiles; ++i) {
-                if (i < my_tiles) epilogue1(i);
+            for (int64_t i = 0; i <= epi_tiles && epi_tiles > 0; ++i) {
+                if (i < epi_tiles) epilogue1(i);
                 if (i >= 1) epilogue2(i - 1);
                 // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 has read it
                 else if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
             }
         } else {
-            for (int64_t i = 0; i < my_tiles; ++i) epilogue1(i);
+            for (int64_t i = 0; i < epi_tiles; ++i) epilogue1(i);
         }
         if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
         if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
@@ -683,8 +694,9 @@ float host_half_value(uint16_t b) {
 }
 
 // Split scale*M[n][k] into hi + lo fp16 and lay both out as 8x8 core matrices, K-major.
+// m is d x d; the operand is laid out kW x kW (the caller zero-fills hi / lo, so d < kW is padded with zeros)
 void split_operand(const std::vector<double>& m, int d, double scale, uint16_t* hi, uint16_t* lo) {
-    const size_t sbo = (size_t)(d / 8) * 128, lbo = 128;
+    const size_t sbo = (size_t)(kW / 8) * 128, lbo = 128;
     for (int n = 0; n < d; ++n)
         for (int k = 0; k < d; ++k) {
             const float v = (float)(m[(size_t)n * d + k] * scale);
@@ -748,7 +760,7 @@ struct TensorConsts {
     TensorArgs args{};     // pointers into `dev` and the scalar parameters
 };
 
-bool tq_tensor_supported(int d, int bits) { return d == 128 && bits >= 1 && bits <= 4; }
+bool tq_tensor_supported(int d, int bits) { return (d == 128 || d == 64) && bits >= 1 && bits <= 4; }
 
 int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection) {
     const int d = p->dev.d, levels = p->dev.levels, nb = levels - 1;
@@ -779,11 +791,11 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     }
     for (int l = 0; l < kCells; ++l) lut_cent[l] = -codebook[l % levels] * kScaleA;
 
-    const size_t dd = (size_t)d * d;
+    const size_t dd = (size_t)kW * kW;   // operand matrices are stored padded to kW x kW
     const int nmat = projection ? 4 : 2;
     std::vector<uint16_t> mats(dd * nmat, 0);
-    std::vector<double> m(dd);
-    for (size_t i = 0; i < dd; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
+    std::vector<double> m((size_t)d * d);
+    for (size_t i = 0; i < (size_t)d * d; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
     split_operand(m, d, kScaleB, mats.data(), mats.data() + dd);
     if (projection) {
         // B2[n=j][k] = (R S^T)[k][j] = sum_i R[k][i] S[j][i]
@@ -872,8 +884,9 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     const int grid = (int)(args.ntiles < sms ? args.ntiles : sms);
     const int bits = p->dev.bits;
-#define TQ_DISPATCH(B)                                                                        \
-    case B:                                                                                   \
+#define TQ_DISPATCH(B)                                                                                     \
+    case B:                                                                                                \
+        if (d == 64) return prod ? launch_one<64, B, true>(map, args, grid, st) : launch_one<64, B, false>(map, args, grid, st); \
         return prod ? launch_one<128, B, true>(map, args, grid, st) : launch_one<128, B, false>(map, args, grid, st);
     switch (bits) {
         TQ_DISPATCH(1)

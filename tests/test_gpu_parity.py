@@ -164,7 +164,14 @@ def test_special_rows(tg):
         mse.set_kernel_path(path)
         enc = mse.quantize(x)
         assert np.array_equal(enc.indices, codes)
-        assert np.array_equal(enc.norms, norms, equal_nan=True)
+        got = np.asarray(enc.norms)
+        if path == "exact":
+            assert np.array_equal(got, norms, equal_nan=True)
+        else:   # the tensor-core path sums the squares in another order: within 1e-5, special values alike
+            assert np.array_equal(np.isnan(got), np.isnan(norms)) and np.array_equal(np.isinf(got), np.isinf(norms))
+            fin = np.isfinite(norms)
+            assert np.array_equal(got[fin] == 0, norms[fin] == 0)
+            assert parity.max_rel_scalar(got[fin], norms[fin]) <= REL_RECON
         assert np.all(enc.indices[1] == np.searchsorted(mse.boundaries, 0.0, side="left"))
 
 

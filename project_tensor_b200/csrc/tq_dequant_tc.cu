@@ -33,7 +33,7 @@ namespace {
 
 using namespace tqptx;
 
-constexpr int D = 128;
+constexpr int D = 128;   // width of the operand layouts; vectors of d = 64 use their lower half
 constexpr int kTileKeys = 128;
 constexpr int kFirstExpWarp = 2;
 constexpr int kFirstEpiWarp = 10;
@@ -77,12 +77,13 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 __device__ __forceinline__ void tmem_ld32_(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld32(taddr, v); }
 
-template <int BITS, bool PROD>
+template <int BITS, bool PROD, int DR>
 struct DqSmem {
     static constexpr int kLutEntries = 1 << (2 * BITS);
     static constexpr int kLutBytes = kLutEntries * 32 * 8;
-    static constexpr int kCodeRowBytes = D * BITS / 8;
-    static constexpr int kRowExtra = PROD ? 16 : 0;              // sign words
+    static constexpr int kCodeRowBytes = DR * BITS / 8;
+    static constexpr int kSignRowBytes = DR / 8;
+    static constexpr int kRowExtra = PROD ? kSignRowBytes : 0;   // sign words
     static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + kRowExtra);
     static constexpr int kNumB = PROD ? 4 : 2;
     static constexpr int kStages = PROD ? 4 : 6;
@@ -97,10 +98,14 @@ struct DqSmem {
     static_assert(total <= 227 * 1024, "shared memory plan");
 };
 
-template <int BITS, bool PROD>
+template <int BITS, bool PROD, int DR>
 __global__ void __launch_bounds__(kThreads, 1)
 dequant_tc_kernel(const DequantArgs a) {
-    using L = DqSmem<BITS, PROD>;
+    static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
+    // d = 64: the expander warps and the epilogue warps of the upper half idle, the contractions stop after
+    // DR / 16 k-blocks and cover N = DR output coordinates
+    constexpr int kHalves = DR / 64;
+    using L = DqSmem<BITS, PROD, DR>;
     constexpr int kStages = L::kStages;
     constexpr int kOps = PROD ? 4 : 2;   // operands per tile: C_hi, C_lo [, B_hi, B_lo]
     extern __shared__ unsigned char smem_raw[];
@@ -114,9 +119,9 @@ dequant_tc_kernel(const DequantArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 8; ++i) { mbar_init(BAR(DB_K_FULL + i), 1); mbar_init(BAR(DB_K_EMPTY + i), 8); }
-        for (int i = 0; i < kSlots; ++i) { mbar_init(BAR(DB_A_FULL + i), 8); mbar_init(BAR(DB_A_EMPTY + i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(BAR(DB_D_FULL + i), 1); mbar_init(BAR(DB_D_EMPTY + i), 8); }
+        for (int i = 0; i < 8; ++i) { mbar_init(BAR(DB_K_FULL + i), 1); mbar_init(BAR(DB_K_EMPTY + i), 4 * kHalves); }
+        for (int i = 0; i < kSlots; ++i) { mbar_init(BAR(DB_A_FULL + i), 4 * kHalves); mbar_init(BAR(DB_A_EMPTY + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(BAR(DB_D_FULL + i), 1); mbar_init(BAR(DB_D_EMPTY + i), 4 * kHalves); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -151,7 +156,7 @@ dequant_tc_kernel(const DequantArgs a) {
     const uint32_t tmem = *tmem_slot;
 
     const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
-    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(DR >> 3) << 17) | ((uint32_t)(kTileKeys >> 4) << 24);
     constexpr uint32_t kSlotCols = 64;
     constexpr uint32_t kColD = kSlots * kSlotCols;   // two accumulators of 128 columns behind the operand ring
 
@@ -167,15 +172,21 @@ dequant_tc_kernel(const DequantArgs a) {
                 const int64_t row0 = tile * kTileKeys;
                 const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes;
                 const uint32_t dst = smem_base + L::off_ring + s * L::kStageBytes;
+                unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes;
+                // a ragged last tile of 8- or 24-byte rows need not end on a 16-byte multiple: the bulk copies take
+                // the multiple, plain loads the few bytes behind it
+                copy_tail_words(stage, csrc, cb);
                 if (PROD) {
-                    const uint32_t sb = (uint32_t)valid * 16u;
-                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb + sb);
-                    bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(DB_K_FULL + s));
-                    bulk_load(dst + kTileKeys * L::kCodeRowBytes, reinterpret_cast<const unsigned char*>(a.signs) + row0 * 16, sb,
-                              BAR(DB_K_FULL + s));
+                    const uint32_t sb = (uint32_t)valid * L::kSignRowBytes;
+                    const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(a.signs) + row0 * L::kSignRowBytes;
+                    copy_tail_words(stage + kTileKeys * L::kCodeRowBytes, ssrc, sb);
+                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), (cb & ~15u) + (sb & ~15u));
+                    if (cb & ~15u) bulk_load(dst, csrc, cb & ~15u, BAR(DB_K_FULL + s));
+                    if (sb & ~15u) bulk_load(dst + kTileKeys * L::kCodeRowBytes, ssrc, sb & ~15u, BAR(DB_K_FULL + s));
                 } else {
-                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb);
-                    bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(DB_K_FULL + s));
+                    mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb & ~15u);
+                    if (cb & ~15u) bulk_load(dst, csrc, cb & ~15u, BAR(DB_K_FULL + s));
                 }
             }
         }
@@ -202,7 +213,7 @@ dequant_tc_kernel(const DequantArgs a) {
                     const uint32_t aop = tmem + slot * kSlotCols;
                     const uint64_t bh = op < 2 ? d_rhi : d_shi, bl = op < 2 ? d_rlo : d_slo;
 #pragma unroll 1
-                    for (int kb = 0; kb < D / 16; ++kb) {
+                    for (int kb = 0; kb < DR / 16; ++kb) {
                         // the start-address field counts 16-byte units: one k-block (two core matrices) further
                         const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
                         mma_ts(acc, aop + kb * 8, bh + step, kIdesc, (op > 0 || kb > 0) ? 1u : 0u);
@@ -229,7 +240,7 @@ dequant_tc_kernel(const DequantArgs a) {
             const int64_t r0 = (int64_t)blockIdx.x * kTileKeys + row;
             rn_next = r0 < a.n ? __ldg(a.rnorms + r0) : 0.f;
         }
-        for (int64_t i = 0; i < my_tiles; ++i) {
+        for (int64_t i = 0; i < (half < kHalves ? my_tiles : 0); ++i) {
             const int s = (int)(i % kStages);
             const float rn = rn_next;
             if (PROD && i + 1 < my_tiles) {
@@ -245,7 +256,7 @@ dequant_tc_kernel(const DequantArgs a) {
                 for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
                 w[kHalfWords] = 0;
                 if (PROD) {
-                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * 16) + half * 2;
+                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + half * 2;
                     sw[0] = fail ? 0u : ~sg[0];   // a set bit now means a negative sign
                     sw[1] = fail ? 0u : ~sg[1];
                 }
@@ -313,7 +324,7 @@ dequant_tc_kernel(const DequantArgs a) {
             const int64_t r0 = (int64_t)blockIdx.x * kTileKeys + row;
             nrm_next = r0 < a.n ? __ldg(a.norms + r0) : 0.f;
         }
-        for (int64_t i = 0; i < my_tiles; ++i) {
+        for (int64_t i = 0; i < (colhalf < kHalves ? my_tiles : 0); ++i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
@@ -351,7 +362,7 @@ dequant_tc_kernel(const DequantArgs a) {
                     const int r = it * 4 + (lane >> 3), c4 = lane & 7;
                     const float4 val = *reinterpret_cast<const float4*>(stg + r * L::kOutRowBytes + c4 * 16);
                     if (row0 + r < a.n)
-                        __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * D + colhalf * 64 + ch * 32) + c4, val);
+                        __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * DR + colhalf * 64 + ch * 32) + c4, val);
                 }
                 __syncwarp();
             }
@@ -383,7 +394,7 @@ float half_value(uint16_t b) {
 
 // B[n][k] = m[k][n] * scale as fp16 hi + lo in the K-major 8x8 core-matrix layout the tensor core reads.
 void split_transposed(const float* m, int d, float scale, uint16_t* hi, uint16_t* lo) {
-    const size_t sbo = (size_t)(d / 8) * 128, lbo = 128;
+    const size_t sbo = (size_t)(D / 8) * 128, lbo = 128;   // laid out D x D; the caller zero-fills, so d < D is padded
     for (int n = 0; n < d; ++n)
         for (int k = 0; k < d; ++k) {
             const float v = m[(size_t)k * d + n] * scale;
@@ -395,11 +406,11 @@ void split_transposed(const float* m, int d, float scale, uint16_t* hi, uint16_t
         }
 }
 
-template <int BITS, bool PROD>
+template <int BITS, bool PROD, int DR>
 int launch_one(const DequantArgs& args, int grid, cudaStream_t st) {
-    const int sm = DqSmem<BITS, PROD>::total;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    dequant_tc_kernel<BITS, PROD><<<grid, kThreads, sm, st>>>(args);
+    const int sm = DqSmem<BITS, PROD, DR>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    dequant_tc_kernel<BITS, PROD, DR><<<grid, kThreads, sm, st>>>(args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -412,13 +423,13 @@ struct DequantConsts {
 
 bool tq_dequant_tc_supported(int d, int bits_mse, bool prod) {
     // the pair lookup table of a 4-bit code and four operand matrices do not fit side by side
-    return d == 128 && bits_mse >= 1 && bits_mse <= (prod ? 3 : 4);
+    return (d == 128 || d == 64) && bits_mse >= 1 && bits_mse <= (prod ? 3 : 4);
 }
 
 int tq_dequant_tc_plan_init(tq_plan* p, const float* rotation, const float* projection) {
     const int d = p->dev.d;
-    if (d != 128) return TQ_OK;
-    const size_t dd = (size_t)d * d;
+    if (d != 128 && d != 64) return TQ_OK;
+    const size_t dd = (size_t)D * D;
     const int nmat = projection ? 4 : 2;
     std::vector<uint16_t> mats(dd * nmat, 0);
     split_transposed(rotation, d, kRotScale, mats.data(), mats.data() + dd);
@@ -461,22 +472,16 @@ int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, con
     const int grid = (int)(a.ntiles < sms ? a.ntiles : sms);
     const int bits = p->dev.bits;
     int r = TQ_ERR_UNSUPPORTED;
+#define TQ_DQ(B, P)                                                                                  \
+    case B:                                                                                          \
+        r = p->dev.d == 64 ? launch_one<B, P, 64>(a, grid, st) : launch_one<B, P, 128>(a, grid, st); \
+        break;
     if (prod) {
-        switch (bits) {
-            case 1: r = launch_one<1, true>(a, grid, st); break;
-            case 2: r = launch_one<2, true>(a, grid, st); break;
-            case 3: r = launch_one<3, true>(a, grid, st); break;
-            default: break;
-        }
+        switch (bits) { TQ_DQ(1, true) TQ_DQ(2, true) TQ_DQ(3, true) default: break; }
     } else {
-        switch (bits) {
-            case 1: r = launch_one<1, false>(a, grid, st); break;
-            case 2: r = launch_one<2, false>(a, grid, st); break;
-            case 3: r = launch_one<3, false>(a, grid, st); break;
-            case 4: r = launch_one<4, false>(a, grid, st); break;
-            default: break;
-        }
+        switch (bits) { TQ_DQ(1, false) TQ_DQ(2, false) TQ_DQ(3, false) TQ_DQ(4, false) default: break; }
     }
+#undef TQ_DQ
     if (r == TQ_ERR_UNSUPPORTED) return tq_fail(r, "no tensor-core dequantize kernel for bits=%d", bits);
     return r;
 }

@@ -66,6 +66,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return mbar_wait_slow(bar, parity, abort_flag);
 }
 
+// Bytes of a row block that a bulk copy may not take (it moves multiples of 16 bytes): the last `bytes % 16`
+// bytes, copied here with plain 4-byte loads by the calling thread.  Call before the arrive on the mbarrier
+// that publishes the block, so that its release covers these stores.  `bytes` is a multiple of 4.
+__device__ __forceinline__ void copy_tail_words(unsigned char* dst, const unsigned char* src, uint32_t bytes) {
+    const uint32_t bulk = bytes & ~15u;
+    for (uint32_t o = bulk; o < bytes; o += 4)
+        *reinterpret_cast<uint32_t*>(dst + o) = __ldg(reinterpret_cast<const uint32_t*>(src + o));
+}
+
 // Named barrier over `count` threads that also ORs a predicate across them.
 __device__ __forceinline__ bool bar_or(int id, int count, bool pred) {
     uint32_t out;

@@ -93,12 +93,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "memory");
 }
 
-template <int BITS, int QPAD>
+// DR is the dimension of the vectors (128 or 64); the operand layouts are those of d = 128 in both cases, with the
+// upper half of every key absent for d = 64 (its expander warps idle, the contractions stop after DR / 16 k-blocks).
+template <int BITS, int QPAD, int DR>
 struct ScoreSmem {
     static constexpr int kLutEntries = 1 << (2 * BITS);
     static constexpr int kLutBytes = kLutEntries * 32 * 8;
-    static constexpr int kCodeRowBytes = D * BITS / 8;
-    static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + 16);
+    static constexpr int kCodeRowBytes = DR * BITS / 8;
+    static constexpr int kSignRowBytes = DR / 8;
+    static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + kSignRowBytes);
     static constexpr int kBBytes = (prep_group_bytes(QPAD) + 127) & ~127;
     static constexpr int off_lut = 0;
     static constexpr int off_b = off_lut + kLutBytes;
@@ -107,10 +110,12 @@ struct ScoreSmem {
     static constexpr int total = off_misc + 512 + 128;
 };
 
-template <int BITS, int QPAD>
+template <int BITS, int QPAD, int DR>
 __global__ void __launch_bounds__(ScoreThreads<QPAD>::kThreads, 1)
 score_tc_kernel(const ScoreTcArgs a) {
-    using L = ScoreSmem<BITS, QPAD>;
+    static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
+    constexpr int kHalves = DR / 64;
+    using L = ScoreSmem<BITS, QPAD, DR>;
     constexpr int kThreads = ScoreThreads<QPAD>::kThreads;
     constexpr int kEpiPerRow = ScoreThreads<QPAD>::kEpiPerRow;
     extern __shared__ unsigned char smem_raw[];
@@ -124,9 +129,9 @@ score_tc_kernel(const ScoreTcArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) { mbar_init(BAR(SB_K_FULL + i), 1); mbar_init(BAR(SB_K_EMPTY + i), 8); }
+        for (int i = 0; i < kStages; ++i) { mbar_init(BAR(SB_K_FULL + i), 1); mbar_init(BAR(SB_K_EMPTY + i), 4 * kHalves); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(SB_A_FULL + i), 8);
+            mbar_init(BAR(SB_A_FULL + i), 4 * kHalves);
             mbar_init(BAR(SB_A_EMPTY + i), 1);
             mbar_init(BAR(SB_D_FULL + i), 1);
             mbar_init(BAR(SB_D_EMPTY + i), 4 * kEpiPerRow);
@@ -193,12 +198,18 @@ score_tc_kernel(const ScoreTcArgs a) {
                 int64_t valid = a.key_cnt - kt * kTileKeys;
                 if (valid > kTileKeys) valid = kTileKeys;
                 const int64_t row0 = g * a.keys_per_group + a.key_off + kt * kTileKeys;
-                const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes, sb = (uint32_t)valid * 16u;
-                mbar_arrive_expect_tx(BAR(SB_K_FULL + s), cb + sb);
+                const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes, sb = (uint32_t)valid * L::kSignRowBytes;
+                const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes;
+                const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(a.signs) + row0 * L::kSignRowBytes;
+                unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                // a ragged last tile of 8- or 24-byte rows need not end on a 16-byte multiple: the bulk copies take
+                // the multiple, plain loads the few bytes behind it
+                copy_tail_words(stage, csrc, cb);
+                copy_tail_words(stage + kTileKeys * L::kCodeRowBytes, ssrc, sb);
+                mbar_arrive_expect_tx(BAR(SB_K_FULL + s), (cb & ~15u) + (sb & ~15u));
                 const uint32_t dst = smem_base + L::off_ring + s * L::kStageBytes;
-                bulk_load(dst, reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes, cb, BAR(SB_K_FULL + s));
-                bulk_load(dst + kTileKeys * L::kCodeRowBytes, reinterpret_cast<const unsigned char*>(a.signs) + row0 * 16, sb,
-                          BAR(SB_K_FULL + s));
+                if (cb & ~15u) bulk_load(dst, csrc, cb & ~15u, BAR(SB_K_FULL + s));
+                if (sb & ~15u) bulk_load(dst + kTileKeys * L::kCodeRowBytes, ssrc, sb & ~15u, BAR(SB_K_FULL + s));
             }
         }
     } else if (warp == 1) {
@@ -234,7 +245,7 @@ score_tc_kernel(const ScoreTcArgs a) {
                 const uint32_t base = tmem + b * kBufCols;
                 const uint32_t d1 = tmem + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
 #pragma unroll
-                for (int kb = 0; kb < D / 16; ++kb) {
+                for (int kb = 0; kb < DR / 16; ++kb) {
                     // the start-address field counts 16-byte units: one k-block (two core matrices) further
                     const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
                     const uint64_t qh = dq_hi + step, ph = dp_hi + step;
@@ -260,7 +271,7 @@ score_tc_kernel(const ScoreTcArgs a) {
         constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
         long long pc[5] = {0, 0, 0, 0, 0};
-        for (int64_t t = t0; t < t1; ++t) {
+        for (int64_t t = t0; t < (half < kHalves ? t1 : t0); ++t) {
             const int64_t i = t - t0;
             const int s = (int)(i % kStages);
             const int b = (int)(i & 1);
@@ -272,7 +283,7 @@ score_tc_kernel(const ScoreTcArgs a) {
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
                 const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
-                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * 16) + half * 2;
+                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + half * 2;
 #pragma unroll
                 for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
                 w[kHalfWords] = 0;
@@ -422,7 +433,8 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
         if (j == 0) ds[slot] = make_float2(0.f, 0.f);
         return;
     }
-    qs[j] = q[((size_t)g * qpg + q0 + slot) * D + j];
+    const int d = p.d;   // 128, or 64 with the upper half of every operand row left unused
+    qs[j] = j < d ? q[((size_t)g * qpg + q0 + slot) * d + j] : 0.f;
     __syncthreads();
     float r = 0.f, s = 0.f;
     // The matrices are usually cold (the keys streamed through L2 since the last call), so the time would
@@ -431,7 +443,7 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     extern __shared__ __align__(16) float mats[];   // [2][D][D]: R^T, S^T
     {
         const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(mats);
-        constexpr int kChunks = D * D / 4;          // 16-byte chunks per matrix
+        const int kChunks = d * d / 4;              // 16-byte chunks per matrix
         for (int c = j; c < kChunks; c += 128) {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + c * 16), "l"(p.Rt + (size_t)c * 4) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + (kChunks + c) * 16), "l"(p.St + (size_t)c * 4) : "memory");
@@ -441,11 +453,13 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
         __syncthreads();
     }
     const float* Rs = mats;
-    const float* Ss = mats + D * D;
+    const float* Ss = mats + d * d;
+    if (j < d) {
 #pragma unroll 16
-    for (int k = 0; k < D; ++k) {
-        r = fmaf(qs[k], Rs[k * D + j], r);
-        s = fmaf(qs[k], Ss[k * D + j], s);
+        for (int k = 0; k < d; ++k) {
+            r = fmaf(qs[k], Rs[k * d + j], r);
+            s = fmaf(qs[k], Ss[k * d + j], s);
+        }
     }
     float mr = fabsf(r), ms = fabsf(s);
     for (int o = 16; o > 0; o >>= 1) {
@@ -545,11 +559,11 @@ int pow2_at_least(int v) {
     return p;
 }
 
-template <int BITS, int QPAD>
+template <int BITS, int QPAD, int DR>
 int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
-    const int sm = ScoreSmem<BITS, QPAD>::total;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    score_tc_kernel<BITS, QPAD><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(args);
+    const int sm = ScoreSmem<BITS, QPAD, DR>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -637,7 +651,8 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             int r = TQ_ERR_UNSUPPORTED;
 #define TQ_SC(B)                                                                                             \
     case B:                                                                                                  \
-        r = qpad == 16 ? launch_score<B, 16>(a, grid, st) : launch_score<B, 32>(a, grid, st);               \
+        if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(a, grid, st) : launch_score<B, 32, 64>(a, grid, st);   \
+        else r = qpad == 16 ? launch_score<B, 16, 128>(a, grid, st) : launch_score<B, 32, 128>(a, grid, st);                \
         break;
             switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }
 #undef TQ_SC

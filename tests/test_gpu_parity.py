@@ -339,3 +339,38 @@ def test_quantize_to_host_equals_quantize(tg, cls_name):
                 assert out[name] is None
             else:
                 assert torch.equal(out[name], dev_t.cpu()), name
+
+
+@pytest.mark.parametrize("bits", [4, 3, 1])
+@pytest.mark.parametrize("n", [1, 129, 38405])
+def test_d64_tensor_paths_match_exact_paths(tg, bits, n):
+    """d = 64 runs on the tensor-core kernels in the layouts of d = 128 with the upper half absent.  Packed
+    codes and sign bits must equal the exact kernels', norms, reconstructions and scores agree within the
+    bounds, for odd and ragged sizes too (rows of 8 and 24 bytes end a tile off a 16-byte boundary)."""
+    import torch
+    from project_tensor_b200 import packed_buffers
+    d = 64
+    gen = torch.Generator(device="cuda").manual_seed(20292 + n + bits)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    x *= torch.logspace(-3, 3, n, device="cuda")[:, None]
+    q = torch.randn((5, d), generator=gen, device="cuda", dtype=torch.float32)
+    for cls_name in ("TurboQuantMSE", "TurboQuantProd"):
+        quant = getattr(tg, cls_name)(d, bits, seed=2026)
+        quant.set_kernel_path("exact")
+        ref = quant.quantize(x)
+        ref_bufs = packed_buffers(ref)
+        ref_recon = quant.dequantize(ref).cpu().numpy()
+        quant.set_kernel_path("tensor")
+        got_bufs = packed_buffers(quant.quantize(x))
+        assert torch.equal(got_bufs["codes"], ref_bufs["codes"])
+        assert parity.max_rel_scalar(got_bufs["norms"].cpu().numpy(), ref_bufs["norms"].cpu().numpy()) <= REL_RECON
+        assert parity.max_rel_rows(quant.dequantize(ref).cpu().numpy(), ref_recon) <= REL_RECON
+        if cls_name == "TurboQuantProd":
+            assert torch.equal(got_bufs["signs"], ref_bufs["signs"])
+            assert parity.max_rel_scalar(got_bufs["residual_norms"].cpu().numpy(),
+                                         ref_bufs["residual_norms"].cpu().numpy()) <= REL_RECON
+            got_s = quant.attention_scores(q, ref).cpu().numpy()
+            quant.set_kernel_path("exact")
+            ref_s = quant.attention_scores(q, ref).cpu().numpy()
+            scale = np.linalg.norm(q.cpu().numpy(), axis=1)[:, None]
+            assert parity.max_score_err(got_s, ref_s, scale, ref_bufs["norms"].cpu().numpy()[None, :], d) <= REL_SCORE

@@ -136,3 +136,36 @@ def test_sharded_index_matches_single_index(tg):
         parts.append(prod.attention_scores(q, shard.encoding(), topk=k, index_base=lo))
     merged_s, merged_i = _merge_on_gpu(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]))
     assert torch.equal(merged_s, ref_s) and torch.equal(merged_i, ref_i)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("bits", [2, 4, 5])
+def test_one_and_two_queries_on_every_path(tg, d, bits):
+    """The reference's own call -- one query broadcast over all keys -- runs on a streaming lookup-table kernel
+    by default; it, the tensor-core kernel and the exact kernel must agree within the score bound, for one
+    query, for two, and for one query per group of keys; and the default path must match the oracle."""
+    import torch
+    n = 30_006
+    rng = np.random.default_rng(20267 + d + bits)
+    x = rng.standard_normal((n, d)).astype(np.float32) * rng.uniform(0.2, 5.0, (n, 1)).astype(np.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    pp = _oracle_params(prod)
+    want = orc.prod_quantize(pp, x)
+    enc = tg.TurboQuantProdEncoding(indices=want[0], qjl=want[1], residual_norms=want[2], norms=want[3], prefix_shape=(n,))
+    for nq, groups in ((1, 1), (2, 1), (6, 6), (12, 6)):
+        q = rng.standard_normal((nq, d)).astype(np.float32)
+        res = {}
+        for path in ("exact", "tensor", "auto"):
+            prod.set_kernel_path(path)
+            res[path] = np.asarray(prod.attention_scores(q, enc, groups=groups))
+        kpg = n // groups
+        qn = np.linalg.norm(q, axis=1)[:, None]
+        kn = want[3].reshape(groups, kpg).repeat(nq // groups, axis=0)
+        for path in ("tensor", "auto"):
+            assert parity.max_score_err(res[path], res["exact"], qn, kn, d) <= REL_SCORE, (path, nq, groups)
+    prod.set_kernel_path("auto")
+    q1 = rng.standard_normal((d,)).astype(np.float32)
+    got = prod.attention_score(q1, enc)
+    ref = orc.prod_attention_score(pp, q1, *want)
+    assert got.shape == ref.shape == (n,)
+    assert parity.max_score_err(got[None, :], ref[None, :], np.linalg.norm(q1), want[3][None, :], d) <= REL_SCORE

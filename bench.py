@@ -299,6 +299,8 @@ def run_gpu(args):
             ("mse_quantize", lambda: mse.quantize(keys), mse_bytes, "B/vector: fp32 row in, packed codes + norm out"),
             ("mse_dequantize", lambda: mse.dequantize(enc_m), mse_bytes, "B/vector: packed codes + norm in, fp32 row out"),
             ("prod_dequantize", lambda: quant.dequantize(enc_p), QUANT_BYTES_PER_VEC, "B/vector: packed encoding in, fp32 row out"),
+            ("attention_score_one_query", lambda: quant.attention_score(queries[0], enc_p),
+             D * B_MSE // 8 + D // 8 + 8 + 4, "B/key: packed key in, one score out (the reference's own call)"),
             ("attention_score_top%d_no_matrix" % TOPK,
              lambda: quant.attention_scores(queries, enc_p, topk=TOPK, index_base=idx_base),
              D * B_MSE // 8 + D // 8 + 8, "B/key: packed key in; scores stay in scratch"),

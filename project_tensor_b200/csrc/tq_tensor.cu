@@ -40,9 +40,16 @@ using namespace tqptx;
 
 constexpr int kTileRows = 128;
 // Warps: TMA, MMA, 8 converters, then 8 epilogue warps: two threads per row, each owning half of the columns.
-template <bool PROD> struct Threads { static constexpr int kEpiPerRow = 2; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
+// Warp roles: TMA, MMA, the converter warps, then 8 epilogue warps.  TurboQuantMSE has 16 converter warps (a
+// thread converts 32 values of a row), TurboQuantProd 8 (64 values): the converters' per-tile chain bounds the
+// MSE kernel, while the Prod epilogue needs the registers that more warps would take away.
+template <bool PROD> struct Threads {
+    static constexpr int kEpiPerRow = 2;
+    static constexpr int kConvWarps = PROD ? 8 : 16;
+    static constexpr int kFirstEpiWarp = 2 + kConvWarps;
+    static constexpr int kThreads = (2 + kConvWarps + 4 * kEpiPerRow) * 32;
+};
 constexpr int kFirstConvWarp = 2;
-constexpr int kFirstEpiWarp = 10;
 constexpr int kBoxBytes = 128 * 128;     // 128 rows x 32 floats
 constexpr float kScaleA = 1024.f;        // unit vector -> A operand
 constexpr float kScaleB = 1024.f;        // rotation    -> B operand
@@ -85,8 +92,9 @@ struct Smem {
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
     static constexpr int kPendBytes = 8 * kPendCap * (8 + 4);   // per epilogue warp: 64-bit and 32-bit entries
-    static constexpr int kMiscBytes = 2 * kTileRows * 4 + 4 * kTileRows + 512 + 4 * kTileRows * 4 + kCells * 16 + kPendBytes;
+    static constexpr int kMiscBytes = 8 * kTileRows * 4 + 4 * kTileRows + 512 + 4 * kTileRows * 4 + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
+    static_assert(total <= 227 * 1024, "shared memory plan");
 };
 
 // barrier indices inside the barrier block
@@ -233,14 +241,18 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     constexpr int kHalves = D / 64;
     constexpr int kThreads = Threads<PROD>::kThreads;
     constexpr int kEpiPerRow = Threads<PROD>::kEpiPerRow;
+    constexpr int kFirstEpiWarp = Threads<PROD>::kFirstEpiWarp;
+    constexpr int kConvParts = Threads<PROD>::kConvWarps / 4;   // converter threads per row
+    constexpr int kXs = kW / kConvParts;                        // values a converter thread handles (64 or 32)
+    constexpr int kActiveParts = D / kXs;                       // parts that have data (d = 64: half of them)
     using L = Smem<D, PROD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t smem_base = smem_u32(smem);
 
-    float* ssq = reinterpret_cast<float*>(smem + L::off_misc);                          // [2][128]
-    unsigned char* force = smem + L::off_misc + 2 * kTileRows * 4;                      // [4][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 2 * kTileRows * 4 + 4 * kTileRows);
+    float* ssq_all = reinterpret_cast<float*>(smem + L::off_misc);                      // [2 tiles][4 parts][128]
+    unsigned char* force = smem + L::off_misc + 8 * kTileRows * 4;                      // [4][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 8 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
     float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - 4 * kTileRows * 4 - kCells * 16);  // [2 tiles][2 halves][128]
     float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
@@ -256,7 +268,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8; ++i) { mbar_init(BAR(BAR_FULL + i), 1); mbar_init(BAR(BAR_EMPTY + i), 4); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(BAR_A_FULL + i), 4 * kHalves);                   // the converter warps that have data
+            mbar_init(BAR(BAR_A_FULL + i), 4 * kActiveParts);              // the converter warps that have data
             mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kHalves : 1);       // Prod: freed by the sign epilogue
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
             mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kHalves);     // Prod: freed when MMA 2 has read rho
@@ -385,23 +397,23 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         }
     } else if (warp < kFirstEpiWarp) {
         // ---- converters: fp32 rows -> unit length, fp16 hi/lo, into tensor memory ----------------
-        const int cw = warp - kFirstConvWarp;      // 0..7
-        const int half = cw >> 2;                  // which 64 floats of the row
+        const int cw = warp - kFirstConvWarp;      // 0 .. kConvWarps-1
+        const int half = cw >> 2;                  // which kXs floats of the row
         const int quarter = warp & 3;              // TMEM lane quarter this warp may touch
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         int64_t g_base = 0;
-        for (int64_t i = 0; i < (half < kHalves ? my_tiles : 0); ++i, g_base += L::kBoxesPerTile) {
+        for (int64_t i = 0; i < (half < kActiveParts ? my_tiles : 0); ++i, g_base += L::kBoxesPerTile) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            float x[64];
+            float x[kXs];
             bool fail = false;
             const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32;
             long long c0 = clock64(), c1;
 #pragma unroll
-            for (int bb = 0; bb < 2; ++bb) {
-                const int64_t g = g_base + half * 2 + bb;
+            for (int bb = 0; bb < kXs / 32; ++bb) {
+                const int64_t g = g_base + half * (kXs / 32) + bb;
                 const int slot = (int)(g % L::kRingBoxes);
                 const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
                 long long cw0 = clock64();
@@ -422,14 +434,19 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             }
             float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int k = 0; k < 64; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
+            for (int k = 0; k < kXs; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
             const float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            // partial sums of a tile go to the buffer of its parity: a fast warp writes the next tile's sums
+            // before the barrier of that tile, while a slow partner may still be reading this tile's
+            float* ssq = ssq_all + b * 4 * kTileRows;
             ssq[half * kTileRows + row] = ss;
             c1 = clock64(); if (pr) a.prof[0] += c1 - c0;
-            if (kHalves == 2) bar_sync(1 + quarter, 64);  // the two warps that share these 32 rows
+            if (kActiveParts > 1) bar_sync(1 + quarter, 32 * kActiveParts);  // the warps that share these 32 rows
             else __syncwarp();
             c0 = clock64(); if (pr) a.prof[1] += c0 - c1;
-            const float tot = kHalves == 2 ? ssq[row] + ssq[kTileRows + row] : ssq[row];
+            float tot = ssq[row];
+#pragma unroll
+            for (int pt = 1; pt < kActiveParts; ++pt) tot += ssq[pt * kTileRows + row];
             const float nrm = sqrtf(tot);
             const bool ok = nrm > 0.f;
             // rows the tensor-core pass cannot represent go to the exact kernel: overflowed or
@@ -444,9 +461,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
             tc_fence_after();
             c1 = clock64(); if (pr) a.prof[2] += c1 - c0;
-            const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * 32;
+            const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * (kXs / 2);
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
+            for (int s = 0; s < kXs / 32; ++s) {
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int p = 0; p < 16; ++p) {

@@ -110,6 +110,9 @@ void tq_dequant_tc_plan_free(tq_plan* p);
 int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
                          const float* norms, int64_t n, float* out, cudaStream_t st);
 
+int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
+                          const float* norms, int64_t n, float* scores, cudaStream_t st);
+
 // Streaming scoring kernel for one or two queries per group (d = 128 / 64, 1..4 code bits).
 bool tq_score_few_supported(const tq_plan* p, int qpg);
 size_t tq_score_few_scratch(const tq_plan* p, int groups, int qpg);

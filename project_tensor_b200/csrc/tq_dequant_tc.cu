@@ -55,7 +55,8 @@ struct DequantArgs {
     const float* codebook;
     float alpha;
     int64_t n, ntiles;
-    float* out;
+    float* out;                  // reconstructions [n][d]; or, in pair mode, scores [n]
+    const float* pair_q;         // pair mode: one query row per key, [n][d]
     unsigned long long* status;
 };
 
@@ -94,11 +95,14 @@ struct DqSmem {
     static constexpr int off_ring = off_b + kNumB * kMatBytes;
     static constexpr int off_out = off_ring + kStages * kStageBytes;
     static constexpr int off_misc = off_out + 8 * kOutWarpBytes;
-    static constexpr int total = off_misc + 512 + 128;
+    static constexpr int off_pair = off_misc + 512 + 128;           // pair mode: partial dot products [2 tiles][128]
+    static constexpr int total = off_pair + 2 * kTileKeys * 4;
     static_assert(total <= 227 * 1024, "shared memory plan");
 };
 
-template <int BITS, bool PROD, int DR>
+// PAIR: instead of storing the reconstruction, every key's row is multiplied with the query row of the same
+// index and summed: attention_score with one query per key (_quant.py:342-358), which equals q . dequantize(key).
+template <int BITS, bool PROD, int DR, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 dequant_tc_kernel(const DequantArgs a) {
     static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
@@ -333,6 +337,20 @@ dequant_tc_kernel(const DequantArgs a) {
                 const int64_t rn = (tile + gridDim.x) * kTileKeys + row;
                 nrm_next = rn < a.n ? __ldg(a.norms + rn) : 0.f;
             }
+            unsigned char* stg = smem + L::off_out + (warp - kFirstEpiWarp) * L::kOutWarpBytes;
+            const int64_t row0 = tile * kTileKeys + quarter * 32;
+            // pair mode: the warp's 32 x 32 block of query values, four rows x 128 bytes per load instruction;
+            // the first block is requested before the wait for the accumulator
+            float4 qv[8];
+            auto fetch_q = [&](int ch) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int r = it * 4 + (lane >> 3), c4 = lane & 7;
+                    qv[it] = row0 + r < a.n ? __ldg(reinterpret_cast<const float4*>(a.pair_q + (row0 + r) * DR + colhalf * 64 + ch * 32) + c4)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            };
+            if (PAIR) fetch_q(0);
             mbar_wait(BAR(DB_D_FULL + b), par2, abort_flag);
             tc_fence_after();
             const uint32_t acc = tmem + lane_addr + kColD + b * D + colhalf * 64;
@@ -343,10 +361,42 @@ dequant_tc_kernel(const DequantArgs a) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(DB_D_EMPTY + b));   // the accumulator is free again
+            if (PAIR) {
+                float dot = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + (lane >> 3), c4 = lane & 7;
+                        *reinterpret_cast<float4*>(stg + r * L::kOutRowBytes + c4 * 16) = qv[it];
+                    }
+                    __syncwarp();
+                    if (ch == 0) fetch_q(1);
+                    const float4* mine = reinterpret_cast<const float4*>(stg + lane * L::kOutRowBytes);
+                    const uint32_t* v = ch == 0 ? va : vb;
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        const float4 qq = mine[m];
+                        dot = fmaf(__uint_as_float(v[4 * m]), qq.x, dot);
+                        dot = fmaf(__uint_as_float(v[4 * m + 1]), qq.y, dot);
+                        dot = fmaf(__uint_as_float(v[4 * m + 2]), qq.z, dot);
+                        dot = fmaf(__uint_as_float(v[4 * m + 3]), qq.w, dot);
+                    }
+                    __syncwarp();
+                }
+                // the two threads of a row add their halves through shared memory (buffer by tile parity)
+                float* part = reinterpret_cast<float*>(smem + L::off_pair) + b * kTileKeys;
+                if (kHalves == 2) {
+                    if (colhalf == 1) part[row] = dot;
+                    bar_sync(1 + quarter, 64);
+                    if (colhalf == 0) dot += part[row];
+                }
+                const int64_t grow = tile * kTileKeys + row;
+                if (colhalf == 0 && grow < a.n) a.out[grow] = dot * sc;
+                continue;
+            }
             // Through a per-warp staging block in shared memory, so that the global stores of a warp cover
             // whole 128-byte lines (four rows x 32 floats per instruction) instead of 16 bytes of 32 rows.
-            unsigned char* stg = smem + L::off_out + (warp - kFirstEpiWarp) * L::kOutWarpBytes;
-            const int64_t row0 = tile * kTileKeys + quarter * 32;
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
                 float4* mine = reinterpret_cast<float4*>(stg + lane * L::kOutRowBytes);
@@ -406,11 +456,11 @@ void split_transposed(const float* m, int d, float scale, uint16_t* hi, uint16_t
         }
 }
 
-template <int BITS, bool PROD, int DR>
+template <int BITS, bool PROD, int DR, bool PAIR = false>
 int launch_one(const DequantArgs& args, int grid, cudaStream_t st) {
     const int sm = DqSmem<BITS, PROD, DR>::total;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    dequant_tc_kernel<BITS, PROD, DR><<<grid, kThreads, sm, st>>>(args);
+    TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD, DR, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    dequant_tc_kernel<BITS, PROD, DR, PAIR><<<grid, kThreads, sm, st>>>(args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -483,5 +533,34 @@ int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, con
     }
 #undef TQ_DQ
     if (r == TQ_ERR_UNSUPPORTED) return tq_fail(r, "no tensor-core dequantize kernel for bits=%d", bits);
+    return r;
+}
+
+// attention_score with one query row per key on the dequantize kernel: scores[i] = q[i] . dequantize(key i).
+int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
+                          const float* norms, int64_t n, float* scores, cudaStream_t st) {
+    if (n == 0) return TQ_OK;
+    if (!p->dequant || !p->has_projection) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core dequantize constants in this plan");
+    DequantArgs a{};
+    a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
+    a.bmat = static_cast<const unsigned char*>(p->dequant->dev);
+    a.codebook = p->dev.codebook;
+    a.alpha = p->dev.alpha;
+    a.n = n;
+    a.ntiles = (n + kTileKeys - 1) / kTileKeys;
+    a.out = scores;
+    a.pair_q = q;
+    a.status = p->counters + 1;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
+    const int grid = (int)(a.ntiles < sms ? a.ntiles : sms);
+    int r = TQ_ERR_UNSUPPORTED;
+#define TQ_PW(B)                                                                                                   \
+    case B:                                                                                                        \
+        r = p->dev.d == 64 ? launch_one<B, true, 64, true>(a, grid, st) : launch_one<B, true, 128, true>(a, grid, st); \
+        break;
+    switch (p->dev.bits) { TQ_PW(1) TQ_PW(2) TQ_PW(3) default: break; }
+#undef TQ_PW
+    if (r == TQ_ERR_UNSUPPORTED) return tq_fail(r, "no tensor-core pairwise kernel for bits=%d", p->dev.bits);
     return r;
 }

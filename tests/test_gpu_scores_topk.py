@@ -169,3 +169,25 @@ def test_one_and_two_queries_on_every_path(tg, d, bits):
     ref = orc.prod_attention_score(pp, q1, *want)
     assert got.shape == ref.shape == (n,)
     assert parity.max_score_err(got[None, :], ref[None, :], np.linalg.norm(q1), want[3][None, :], d) <= REL_SCORE
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("n", [1, 129, 20_003])
+def test_one_query_per_key_on_both_paths(tg, d, bits, n):
+    """attention_score with a query row per key (_quant.py:342-358): the tensor-core kernel (the dequantize
+    contraction with a dot product in its epilogue) against the exact kernel and against the oracle."""
+    rng = np.random.default_rng(20268 + d + bits + n)
+    x = rng.standard_normal((n, d)).astype(np.float32) * rng.uniform(0.2, 5.0, (n, 1)).astype(np.float32)
+    q = rng.standard_normal((n, d)).astype(np.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    pp = _oracle_params(prod)
+    want = orc.prod_quantize(pp, x)
+    enc = tg.TurboQuantProdEncoding(indices=want[0], qjl=want[1], residual_norms=want[2], norms=want[3], prefix_shape=(n,))
+    ref = orc.prod_attention_score(pp, q, *want)
+    qn = np.linalg.norm(q, axis=1)
+    for path in ("exact", "tensor"):
+        prod.set_kernel_path(path)
+        got = np.asarray(prod.attention_score(q, enc))
+        assert got.shape == (n,)
+        assert parity.max_score_err(got, ref, qn, want[3], d) <= REL_SCORE, path

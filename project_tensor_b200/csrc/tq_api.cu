@@ -356,6 +356,9 @@ int tq_score_broadcast(const tq_plan* p, const float* q, const void* codes, cons
     TQ_TRY(check_encoding(codes, signs, residual_norms, norms));
     TQ_TRY(check_ptr(scores, "scores"));
     DeviceScope scope(p->device);
+    if (p->path == TQ_PATH_AUTO && tq_score_few_supported(p, 1))
+        return tq_launch_score_few(p, q, 1, 1, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
+                                   residual_norms, norms, n, scores, static_cast<cudaStream_t>(stream));
     return tq_launch_score_general(p, q, 1, 1, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
                                    residual_norms, norms, n, scores, 0, nullptr, nullptr, 0, nullptr, 0,
                                    static_cast<cudaStream_t>(stream));

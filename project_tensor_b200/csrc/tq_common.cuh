@@ -115,10 +115,8 @@ int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* code
 
 // Streaming scoring kernel for one or two queries per group (d = 128 / 64, 1..4 code bits).
 bool tq_score_few_supported(const tq_plan* p, int qpg);
-size_t tq_score_few_scratch(const tq_plan* p, int groups, int qpg);
 int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
-                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, void* scratch,
-                        cudaStream_t st);
+                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st);
 
 // Scoring kernels.
 int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,

@@ -297,11 +297,8 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
                             cudaStream_t st) {
     // One or two queries per group and the matrix wanted (the reference's own call): the streaming kernel.
-    // Groups must start on an 8-byte boundary of the packed rows for its vector loads.
-    if (p->path == TQ_PATH_AUTO && topk == 0 && scores && tq_score_few_supported(p, qpg) && keys_per_group > 0 && groups > 0 &&
-        (groups == 1 || p->dev.d == 128 || keys_per_group % 2 == 0) && scratch &&
-        scratch_bytes >= tq_score_few_scratch(p, groups, qpg))
-        return tq_launch_score_few(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, scratch, st);
+    if (p->path == TQ_PATH_AUTO && topk == 0 && scores && tq_score_few_supported(p, qpg) && keys_per_group > 0 && groups > 0)
+        return tq_launch_score_few(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st);
     // d = 64 has 8-byte sign rows (and 8- or 24-byte code rows): a group must start on a 16-byte boundary
     // for the bulk copies of the tensor-core kernel
     const bool aligned_groups = p->dev.d == 128 || groups == 1 || keys_per_group % 2 == 0;

@@ -22,35 +22,10 @@ namespace {
 
 constexpr int kFewThreads = 256;
 
-// rotated[j] = sum_k q[k] R[j][k], projected[j] = sum_k q[k] S[j][k], one FMA per k, k ascending (the order of
-// the reference's matrix products).  grid (queries), block d threads; out: [queries][2][d].
-__global__ void few_prep_kernel(TqDev p, const float* __restrict__ q, float* __restrict__ out) {
-    extern __shared__ float qs[];
-    const int d = p.d, j = threadIdx.x, qi = blockIdx.x;
-    qs[j] = q[(size_t)qi * d + j];
-    __syncthreads();
-    float r = 0.f, s = 0.f;
-    for (int k0 = 0; k0 < d; k0 += 16) {
-        float mr[16], ms[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            mr[u] = __ldg(p.Rt + (size_t)(k0 + u) * d + j);
-            ms[u] = __ldg(p.St + (size_t)(k0 + u) * d + j);
-        }
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            r = fmaf(qs[k0 + u], mr[u], r);
-            s = fmaf(qs[k0 + u], ms[u], s);
-        }
-    }
-    out[((size_t)qi * 2 + 0) * d + j] = r;
-    out[((size_t)qi * 2 + 1) * d + j] = s;
-}
-
 // grid (blocks over keys, queries per group, groups)
 template <int BITS, int DR>
 __global__ void __launch_bounds__(kFewThreads)
-score_few_kernel(TqDev p, const float* __restrict__ prep, const uint32_t* __restrict__ codes,
+score_few_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restrict__ codes,
                  const uint32_t* __restrict__ signs, const float* __restrict__ rnorms, const float* __restrict__ norms,
                  int64_t keys_per_group, int qpg, float* __restrict__ scores) {
     constexpr int kPairs = DR / 2, kEntries = 1 << (2 * BITS), kBytes = DR / 8;
@@ -60,12 +35,36 @@ score_few_kernel(TqDev p, const float* __restrict__ prep, const uint32_t* __rest
     float* pair_t = tables;                       // [kPairs][kEntries]
     float* byte_t = tables + kPairs * kEntries;   // [kBytes][256]
     const int g = blockIdx.z, qi = blockIdx.y;
-    const float* qr = prep + ((size_t)(g * qpg + qi) * 2 + 0) * DR;
-    const float* ps = prep + ((size_t)(g * qpg + qi) * 2 + 1) * DR;
+    // Every block rotates and projects its query itself (2 d^2 FMAs, the matrices come from L2): rotated[j] =
+    // sum_k q[k] R[j][k], projected[j] = sum_k q[k] S[j][k], one FMA per k, k ascending as in the reference's
+    // matrix products.  That costs a few microseconds per block and saves a launch and a scratch buffer.
+    __shared__ float qs[DR], qr[DR], ps[DR];
+    if (threadIdx.x < DR) qs[threadIdx.x] = __ldg(q + ((size_t)g * qpg + qi) * DR + threadIdx.x);
+    __syncthreads();
+    if (threadIdx.x < DR) {
+        const int j = threadIdx.x;
+        float r = 0.f, sacc = 0.f;
+        for (int k0 = 0; k0 < DR; k0 += 16) {
+            float mr[16], ms[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                mr[u] = __ldg(p.Rt + (size_t)(k0 + u) * DR + j);
+                ms[u] = __ldg(p.St + (size_t)(k0 + u) * DR + j);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                r = fmaf(qs[k0 + u], mr[u], r);
+                sacc = fmaf(qs[k0 + u], ms[u], sacc);
+            }
+        }
+        qr[j] = r;
+        ps[j] = sacc;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < kPairs * kEntries; i += kFewThreads) {
         const int pp = i / kEntries, e = i - pp * kEntries;
         const float c0 = __ldg(p.codebook + (e & ((1 << BITS) - 1))), c1 = __ldg(p.codebook + (e >> BITS));
-        pair_t[i] = fmaf(c1, __ldg(qr + 2 * pp + 1), c0 * __ldg(qr + 2 * pp));
+        pair_t[i] = fmaf(c1, qr[2 * pp + 1], c0 * qr[2 * pp]);
     }
     for (int i = threadIdx.x; i < kBytes * 256; i += kFewThreads) {
         const int pos = i >> 8, v = i & 255, w = pos >> 2, b = pos & 3;
@@ -75,7 +74,7 @@ score_few_kernel(TqDev p, const float* __restrict__ prep, const uint32_t* __rest
             // stored order of the sign words: even coordinates in bits 0..15, odd ones in bits 16..31
             const int bp = 8 * b + bit;
             const int coord = 32 * w + (bp < 16 ? 2 * bp : 2 * (bp - 16) + 1);
-            const float x = __ldg(ps + coord);
+            const float x = ps[coord];
             acc += (v >> bit) & 1 ? x : -x;
         }
         byte_t[i] = acc;
@@ -127,7 +126,7 @@ score_few_kernel(TqDev p, const float* __restrict__ prep, const uint32_t* __rest
 }
 
 template <int BITS, int DR>
-int launch_few(const tq_plan* p, const float* prep, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
+int launch_few(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
                const float* norms, int64_t keys_per_group, int groups, int qpg, float* scores, cudaStream_t st) {
     const int sm = ((DR / 2) * (1 << (2 * BITS)) + (DR / 8) * 256) * 4;
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_few_kernel<BITS, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
@@ -137,7 +136,7 @@ int launch_few(const tq_plan* p, const float* prep, const uint32_t* codes, const
     const int64_t cap = (int64_t)sms * 4;   // the tables cost a few microseconds per block: a few blocks per SM, grid-stride
     if (blocks > cap) blocks = cap;
     score_few_kernel<BITS, DR><<<dim3((unsigned)blocks, (unsigned)qpg, (unsigned)groups), kFewThreads, sm, st>>>(
-        p->dev, prep, codes, signs, rnorms, norms, keys_per_group, qpg, scores);
+        p->dev, q, codes, signs, rnorms, norms, keys_per_group, qpg, scores);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -148,21 +147,15 @@ bool tq_score_few_supported(const tq_plan* p, int qpg) {
     return p->has_projection && (p->dev.d == 128 || p->dev.d == 64) && p->dev.bits >= 1 && p->dev.bits <= 4 && qpg >= 1 && qpg <= 2;
 }
 
-size_t tq_score_few_scratch(const tq_plan* p, int groups, int qpg) { return (size_t)groups * qpg * 2 * p->dev.d * sizeof(float); }
-
-// scores: [groups][qpg][keys_per_group]; scratch holds the rotated / projected queries
+// scores: [groups][qpg][keys_per_group]
 int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
-                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, void* scratch,
-                        cudaStream_t st) {
+                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st) {
     const int d = p->dev.d, bits = p->dev.bits;
-    float* prep = static_cast<float*>(scratch);
-    few_prep_kernel<<<groups * qpg, d, d * sizeof(float), st>>>(p->dev, q, prep);
-    TQ_CUDA_TRY(cudaGetLastError());
     int r = TQ_ERR_UNSUPPORTED;
-#define TQ_FEW(B)                                                                                                           \
-    case B:                                                                                                                \
-        r = d == 64 ? launch_few<B, 64>(p, prep, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st)     \
-                    : launch_few<B, 128>(p, prep, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st);   \
+#define TQ_FEW(B)                                                                                                        \
+    case B:                                                                                                             \
+        r = d == 64 ? launch_few<B, 64>(p, q, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st)     \
+                    : launch_few<B, 128>(p, q, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st);   \
         break;
     switch (bits) { TQ_FEW(1) TQ_FEW(2) TQ_FEW(3) TQ_FEW(4) }
 #undef TQ_FEW

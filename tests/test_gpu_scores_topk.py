@@ -191,3 +191,27 @@ def test_one_query_per_key_on_both_paths(tg, d, bits, n):
         got = np.asarray(prod.attention_score(q, enc))
         assert got.shape == (n,)
         assert parity.max_score_err(got, ref, qn, want[3], d) <= REL_SCORE, path
+
+
+@pytest.mark.parametrize("d,bits", [(128, 4), (64, 3), (256, 4)])
+def test_c_abi_broadcast_entry_point(tg, d, bits):
+    """tq_score_broadcast called directly (no scratch argument): one query against all keys, equal to the
+    batched entry point the Python class uses, on the tensor geometries and on one without tensor kernels."""
+    import torch
+    from project_tensor_b200 import _native, packed_buffers
+    lib = _native.load()
+    n = 10_007
+    gen = torch.Generator(device="cuda").manual_seed(20269 + d)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((d,), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    enc = prod.quantize(x)
+    bufs = packed_buffers(enc)
+    want = prod.attention_score(q, enc)
+    out = torch.empty((n,), dtype=torch.float32, device="cuda")
+    handle = prod._plans.handle(torch.device("cuda", torch.cuda.current_device()))
+    _native.check(lib.tq_score_broadcast(handle, q.data_ptr(), bufs["codes"].data_ptr(), bufs["signs"].data_ptr(),
+                                         bufs["residual_norms"].data_ptr(), bufs["norms"].data_ptr(), n, out.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)

@@ -582,9 +582,14 @@ class TurboQuantProd:
         scores = torch.empty((num_codes,), dtype=torch.float32, device=pk.device)
         handle = self._plans.handle(pk.device)
         with torch.cuda.device(pk.device):
-            if broadcast:
-                # one query against all keys is the one-row case of the batched entry point
-                need = int(lib.tq_topk_scratch_bytes(handle, 1, 1, num_codes, 0))
+            if broadcast and self._plans._path == _native.TQ_PATH_AUTO:
+                # one query against all keys: the entry point that needs no scratch buffer
+                _native.check(lib.tq_score_broadcast(handle, _ptr(q), _ptr(pk.codes), _ptr(pk.signs),
+                                                     _ptr(pk.residual_norms), _ptr(pk.norms), num_codes,
+                                                     _ptr(scores), _stream_ptr(pk.device)))
+            elif broadcast:
+                # a forced kernel path: the one-row case of the batched entry point
+                need =int(lib.tq_topk_scratch_bytes(handle, 1, 1, num_codes, 0))
                 scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=pk.device)
                 _native.check(lib.tq_score_batched(handle, _ptr(q), 1, 1, _ptr(pk.codes), _ptr(pk.signs),
                                                    _ptr(pk.residual_norms), _ptr(pk.norms), num_codes,

@@ -349,11 +349,13 @@ def run_gpu(args):
                 "value": world * N_KEYS / (s_mean * 1e-3) / 1e9, "unit": "Gkeys/s", "queries": N_QUERIES,
                 "ms": s_mean,
                 "roofline": {"bound": "hbm", "achieved": score_gbs, "peak": peak, "unit": "GB/s",
-                             "frac": score_gbs / peak, "frac_of_8TBs": score_gbs / 8000.0, "traffic": None,
+                             "frac": score_gbs / peak, "frac_of_8TBs": score_gbs / 8000.0,
+                             "traffic": traffic_bytes(18.95e6, 33.5e6),
                              "bytes_per_key": SCORE_BYTES_PER_KEY, "peak_kind": peak_kind}},
             "quantize_ms": q_mean,
             "roofline": {"bound": "hbm", "achieved": quant_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": quant_gbs / peak, "frac_of_8TBs": quant_gbs / 8000.0, "traffic": None,
+                         "frac": quant_gbs / peak, "frac_of_8TBs": quant_gbs / 8000.0,
+                         "traffic": traffic_bytes(135.7e6, 19.3e6),
                          "bytes_per_vector": QUANT_BYTES_PER_VEC, "peak_kind": peak_kind,
                          "kernel": "tq_prod_quantize call (tensor-core kernel + exact second stage)"},
             "e2e": {"value": world * N_KEYS / (e2e_mean * 1e-3) / 1e6, "unit": "Mvec/s",
@@ -374,6 +376,16 @@ def run_gpu(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def traffic_bytes(read_262144, write_262144):
+    """DRAM bytes of one launch of the dominant kernel at this run's size.  ncu counted dram__bytes_read.sum and
+    dram__bytes_write.sum for a launch over 262,144 keys (the capture summarised in profiles/); both grow in
+    proportion to the keys, so they are scaled.  A write that was still in L2 when the capture ended is taken
+    at its algorithmic size.  None for a workload other than the captured one (d = 128, bits = 4, 32 queries)."""
+    if D != 128 or BITS != 4 or N_QUERIES != 32:
+        return None
+    return (read_262144 + write_262144) * N_KEYS / 262144.0
 
 
 def main():

@@ -167,6 +167,37 @@ int tq_score_batched(const tq_plan* plan, const float* q, int groups, int q_per_
                      size_t scratch_bytes, void* stream);
 
 /*
+ * tq_score_batched over a cache whose groups are `group_rows` rows apart in the key arrays and hold
+ * keys_per_group <= group_rows keys each (the layout tq_prod_append fills: group_rows = capacity,
+ * keys_per_group = current length).  scores stays dense, float32[groups][q_per_group][keys_per_group];
+ * top_idx = idx_base + row within the key arrays (group * group_rows + position).  The scratch size is
+ * that of tq_topk_scratch_bytes for the same groups, q_per_group, keys_per_group and topk.
+ * No reference counterpart: the reference has no cache type (its encodings are immutable dataclasses,
+ * _quant.py:156-169).
+ */
+int tq_score_cache(const tq_plan* plan, const float* q, int groups, int q_per_group, const void* codes,
+                   const void* signs, const float* residual_norms, const float* norms,
+                   int64_t keys_per_group, int64_t group_rows, float* scores, int topk, float* top_scores,
+                   int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Append path: quantize `tokens` new vectors for each of `groups` sequences/heads straight into a packed
+ * cache.  x: float32[groups][tokens][d].  The cache arrays hold `capacity` rows per group; every group
+ * holds the same number of rows already, kept in DEVICE memory at `length` (one int64), so the call needs
+ * no host-side length and a CUDA graph that captured it stays valid as the cache grows.  Token j of
+ * group g is written to row g * capacity + *length + j, with the same numbers tq_*_quantize gives
+ * (the arithmetic of _quant.py:224-236, 300-308 in the reference's order of operations); rows that would
+ * land beyond `capacity` are dropped.  advance != 0: afterwards *length = min(*length + tokens, capacity),
+ * in stream order.  One kernel launch (two with advance), no scratch, any d and bits.
+ * No reference counterpart (TurboQuantProd.quantize, _quant.py:297-315, always builds a new encoding).
+ */
+int tq_mse_append(const tq_plan* plan, const float* x, int groups, int tokens, void* codes, float* norms,
+                  int64_t capacity, int64_t* length, int advance, void* stream);
+int tq_prod_append(const tq_plan* plan, const float* x, int groups, int tokens, void* codes, void* signs,
+                   float* residual_norms, float* norms, int64_t capacity, int64_t* length, int advance,
+                   void* stream);
+
+/*
  * Merge `lists` candidate lists per query (e.g. one per GPU after an all-gather) into one
  * descending top-k.  in_scores/in_idx: [lists][queries][topk]; out: [queries][topk].
  * No reference counterpart (the reference is single-device).

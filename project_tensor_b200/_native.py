@@ -41,6 +41,13 @@ SIGNATURES = {
     "tq_score_batched": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
                                  c_void_p]),
+    "tq_score_cache": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
+                               c_void_p]),
+    "tq_mse_append": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int,
+                              c_void_p]),
+    "tq_prod_append": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                               c_void_p, c_int, c_void_p]),
     "tq_topk_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "tq_unpack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_pack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),

@@ -278,6 +278,44 @@ int tq_prod_quantize(const tq_plan* p, const float* x, int64_t n, void* codes, v
     return quantize_common(p, true, x, n, codes, signs, residual_norms, norms, scratch, scratch_bytes, stream);
 }
 
+// Append path: groups * tokens new vectors go behind the `*length` rows every group of a cache already holds.
+// One launch of the reference-order kernel (any d, any bits; the batches are small: one or a few tokens per
+// sequence and head), no scratch, no host knowledge of the length.
+static int append_common(const tq_plan* p, bool prod, const float* x, int groups, int tokens, void* codes, void* signs,
+                         float* rnorms, float* norms, int64_t capacity, int64_t* length, int advance, void* stream) {
+    TQ_TRY(check_plan(p, prod));
+    if (groups < 0 || tokens < 0 || capacity < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "negative size");
+    if (tokens > capacity) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "tokens (%d) exceed the capacity (%lld)", tokens, (long long)capacity);
+    if ((double)groups * (double)capacity >= 4294967296.0)
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups * capacity must stay below 2^32");
+    if (groups == 0 || tokens == 0) return TQ_OK;
+    TQ_TRY(check_ptr(x, "x"));
+    TQ_TRY(check_ptr(codes, "codes"));
+    TQ_TRY(check_ptr(norms, "norms"));
+    TQ_TRY(check_ptr(length, "length"));
+    if (prod) {
+        TQ_TRY(check_ptr(signs, "signs"));
+        TQ_TRY(check_ptr(rnorms, "residual_norms"));
+    }
+    DeviceScope scope(p->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const TqRowMap map{tokens, capacity, length};
+    TQ_TRY(tq_launch_exact_quantize(p, prod, x, (int64_t)groups * tokens, static_cast<uint32_t*>(codes),
+                                    static_cast<uint32_t*>(signs), rnorms, norms, nullptr, nullptr, st, &map));
+    if (advance) TQ_TRY(tq_launch_append_advance(length, tokens, capacity, st));
+    return TQ_OK;
+}
+
+int tq_mse_append(const tq_plan* p, const float* x, int groups, int tokens, void* codes, float* norms, int64_t capacity,
+                  int64_t* length, int advance, void* stream) {
+    return append_common(p, false, x, groups, tokens, codes, nullptr, nullptr, norms, capacity, length, advance, stream);
+}
+
+int tq_prod_append(const tq_plan* p, const float* x, int groups, int tokens, void* codes, void* signs,
+                   float* residual_norms, float* norms, int64_t capacity, int64_t* length, int advance, void* stream) {
+    return append_common(p, true, x, groups, tokens, codes, signs, residual_norms, norms, capacity, length, advance, stream);
+}
+
 int tq_mse_quantize_noalloc(const tq_plan* p, const float* x, int64_t n, void* codes, float* norms, void* stream) {
     TQ_TRY(check_plan(p, false));
     if (n < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "n is negative");
@@ -386,10 +424,19 @@ int tq_score_batched(const tq_plan* p, const float* q, int groups, int q_per_gro
                      const void* signs, const float* residual_norms, const float* norms, int64_t keys_per_group,
                      float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
                      size_t scratch_bytes, void* stream) {
+    return tq_score_cache(p, q, groups, q_per_group, codes, signs, residual_norms, norms, keys_per_group, keys_per_group,
+                          scores, topk, top_scores, top_idx, idx_base, scratch, scratch_bytes, stream);
+}
+
+int tq_score_cache(const tq_plan* p, const float* q, int groups, int q_per_group, const void* codes,
+                   const void* signs, const float* residual_norms, const float* norms, int64_t keys_per_group,
+                   int64_t group_rows, float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base,
+                   void* scratch, size_t scratch_bytes, void* stream) {
     TQ_TRY(check_plan(p, true));
     if (groups < 0 || q_per_group < 0 || keys_per_group < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "negative size");
+    if (group_rows < keys_per_group) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "group_rows is smaller than keys_per_group");
     if (groups > 65535) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups > 65535");
-    if ((double)groups * (double)keys_per_group >= 4294967296.0)
+    if ((double)groups * (double)group_rows >= 4294967296.0)
         return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups * keys_per_group must stay below 2^32");
     if (topk < 0 || topk > TQ_MAX_TOPK) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "topk outside [0, %d]", TQ_MAX_TOPK);
     if (!scores && topk == 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "nothing to compute: scores is null and topk is 0");
@@ -405,7 +452,7 @@ int tq_score_batched(const tq_plan* p, const float* q, int groups, int q_per_gro
     return tq_launch_score_batched(p, q, groups, q_per_group, static_cast<const uint32_t*>(codes),
                                    static_cast<const uint32_t*>(signs), residual_norms, norms, keys_per_group, scores,
                                    topk, top_scores, top_idx, idx_base, scratch, scratch_bytes,
-                                   static_cast<cudaStream_t>(stream));
+                                   static_cast<cudaStream_t>(stream), group_rows);
 }
 
 int tq_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk, float* out_scores,

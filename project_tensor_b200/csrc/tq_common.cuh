@@ -36,6 +36,14 @@ struct TqRecheck {
     unsigned int* row_entries;
     unsigned int code_cap, row_cap;
 };
+// Where the rows of a quantize call land when they are appended to a cache of `capacity` rows per group:
+// input row r is token r % tokens of group r / tokens and goes to row group * capacity + *length + token.
+// `length` lives on the device (one value for all groups), so a captured launch stays valid while the cache
+// grows.  tokens == 0: output row = input row.
+struct TqRowMap {
+    int64_t tokens, capacity;
+    const int64_t* length;
+};
 __host__ __device__ __forceinline__ unsigned int tq_recheck_code_cap(int64_t n) { return (unsigned int)(n / 2 + 4096); }
 __host__ __device__ __forceinline__ unsigned int tq_recheck_row_cap(int64_t n) { return (unsigned int)(n / 8 + 4096); }
 
@@ -85,7 +93,8 @@ int tq_fail(int code, const char* fmt, ...);
 // are recomputed.
 int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                              uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists,
-                             unsigned long long* redo_counter, cudaStream_t st);
+                             unsigned long long* redo_counter, cudaStream_t st, const TqRowMap* map = nullptr);
+int tq_launch_append_advance(int64_t* length, int64_t tokens, int64_t capacity, cudaStream_t st);
 int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                                const TqRecheck* lists, cudaStream_t st);
 int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs,
@@ -116,19 +125,21 @@ int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* code
 // Streaming scoring kernel for one or two queries per group (d = 128 / 64, 1..4 code bits).
 bool tq_score_few_supported(const tq_plan* p, int qpg);
 int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
-                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st);
+                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st,
+                        int64_t group_rows = 0);
 
-// Scoring kernels.
+// Scoring kernels.  `group_rows`: rows between the first keys of consecutive groups in the key arrays (0 = the
+// groups follow one another, keys_per_group rows each); top-k indices count rows of the arrays.
 int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
                             const uint32_t* signs, const float* rnorms, const float* norms,
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
-                            cudaStream_t st);
+                            cudaStream_t st, int64_t group_rows = 0);
 int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
                             const uint32_t* signs, const float* rnorms, const float* norms,
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
-                            cudaStream_t st);
+                            cudaStream_t st, int64_t group_rows = 0);
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk);
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
                          float* out_scores, int64_t* out_idx, cudaStream_t st);

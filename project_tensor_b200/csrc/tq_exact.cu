@@ -111,9 +111,10 @@ template <bool PROD>
 __global__ void __launch_bounds__(1024)
 exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                       uint32_t* __restrict__ signs, float* __restrict__ rnorms, float* __restrict__ norms,
-                      TqRecheck lists, unsigned long long* redo_counter) {
+                      TqRecheck lists, unsigned long long* redo_counter, TqRowMap map) {
     extern __shared__ float smem[];
     const int d = p.d, dp = (d + 31) & ~31;
+    const int64_t len0 = map.tokens > 0 ? *map.length : 0;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
     RowsSmem sm;
     sm.vt = smem;
@@ -130,13 +131,18 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
         atomicAdd(redo_counter, (unsigned long long)limit);
 
     for (int64_t g0 = (int64_t)blockIdx.x * kRB; g0 < limit; g0 += (int64_t)gridDim.x * kRB) {
-        int64_t rows[kRB];
+        int64_t rows[kRB], orow[kRB];   // input row and the row its results go to (-1: none)
 #pragma unroll
         for (int r = 0; r < kRB; ++r) {
             const int64_t idx = g0 + r;
             int64_t row = idx < limit ? (listed ? (int64_t)lists.row_entries[idx] : idx) : -1;
             if (row >= n) row = -1;
             rows[r] = row;
+            orow[r] = row;
+            if (map.tokens > 0 && row >= 0) {
+                const int64_t grp = row / map.tokens, pos = len0 + (row - grp * map.tokens);
+                orow[r] = pos < map.capacity ? grp * map.capacity + pos : -1;   // a full cache takes no more rows
+            }
         }
         __syncthreads();  // previous group fully written out
 #pragma unroll
@@ -184,9 +190,9 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
         }
         __syncthreads();
         for (int r = warp; r < kRB; r += nwarps) {
-            if (rows[r] < 0) continue;
-            store_packed_codes(sm.cs + r * dp, d, p.bits, p.code_words, lane, codes + rows[r] * p.code_words);
-            if (lane == 0) norms[rows[r]] = sm.nrm[r];
+            if (orow[r] < 0) continue;
+            store_packed_codes(sm.cs + r * dp, d, p.bits, p.code_words, lane, codes + orow[r] * p.code_words);
+            if (lane == 0) norms[orow[r]] = sm.nrm[r];
         }
 
         if (PROD) {
@@ -213,7 +219,7 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
             __syncthreads();
             for (int r = warp; r < kRB; r += nwarps) {
                 const float rn = __fsqrt_rn(np_pairwise_sum(sm.sq + r * dp, d, lane));
-                if (lane == 0 && rows[r] >= 0) rnorms[rows[r]] = rn;
+                if (lane == 0 && orow[r] >= 0) rnorms[orow[r]] = rn;
             }
             // projected[j] = sum_k residual[k] * S[j][k]
 #pragma unroll
@@ -231,8 +237,8 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
 #pragma unroll
             for (int r = 0; r < kRB; ++r) {
                 const uint32_t word = __ballot_sync(0xffffffffu, t < d && acc[r] >= 0.f);
-                if (lane == 0 && rows[r] >= 0 && warp * 32 < d)
-                    signs[rows[r] * p.sign_words + warp] = tq_sign_word_from_natural(word);
+                if (lane == 0 && orow[r] >= 0 && warp * 32 < d)
+                    signs[orow[r] * p.sign_words + warp] = tq_sign_word_from_natural(word);
             }
         }
     }
@@ -441,9 +447,10 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
 
 int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                              uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists_in,
-                             unsigned long long* redo_counter, cudaStream_t st) {
+                             unsigned long long* redo_counter, cudaStream_t st, const TqRowMap* map_in) {
     if (n == 0) return TQ_OK;
     const size_t sm = rows_smem_bytes(p->dev.d);
+    const TqRowMap map = map_in ? *map_in : TqRowMap{0, 0, nullptr};
     TqRecheck none{};
     const TqRecheck lists = lists_in ? *lists_in : none;
     // the listed pass does not know its size on the host: a fixed grid strides over the list
@@ -451,11 +458,22 @@ int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_
     const int threads = (p->dev.d + 31) & ~31;
     if (prod) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter);
+        exact_quantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map);
     } else {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter);
+        exact_quantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map);
     }
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
+__global__ void append_advance_kernel(int64_t* length, int64_t tokens, int64_t capacity) {
+    const int64_t v = *length + tokens;
+    *length = v < capacity ? v : capacity;
+}
+
+int tq_launch_append_advance(int64_t* length, int64_t tokens, int64_t capacity, cudaStream_t st) {
+    append_advance_kernel<<<1, 1, 0, st>>>(length, tokens, capacity);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -25,7 +25,7 @@ using namespace tqtopk;
 __global__ void __launch_bounds__(kThreads)
 score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __restrict__ codes,
              const uint32_t* __restrict__ signs, const float* __restrict__ rnorms,
-             const float* __restrict__ norms, int64_t keys_per_group, int64_t keys_per_block,
+             const float* __restrict__ norms, int64_t keys_per_group, int64_t group_rows, int64_t keys_per_block,
              float* __restrict__ scores, int topk, int cap2, unsigned long long* __restrict__ part) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int d = p.d;
@@ -41,7 +41,7 @@ score_kernel(TqDev p, const float* __restrict__ q, int qpg, const uint32_t* __re
     const int64_t k0 = (int64_t)blockIdx.x * keys_per_block;
     int64_t k1 = k0 + keys_per_block;
     if (k1 > keys_per_group) k1 = keys_per_group;
-    const int64_t gbase = (int64_t)g * keys_per_group;  // first row of this group in the key arrays
+    const int64_t gbase = (int64_t)g * group_rows;  // first row of this group in the key arrays
 
     for (int i = threadIdx.x; i < 256; i += kThreads) cb[i] = i < p.levels ? p.codebook[i] : 0.f;
 
@@ -264,7 +264,7 @@ int64_t tq_score_tc_scratch(int groups, int qpg, int64_t keys_per_group, int top
 int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
                        const uint32_t* signs, const float* rnorms, const float* norms, int64_t keys_per_group,
                        float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
-                       size_t scratch_bytes, cudaStream_t st);
+                       size_t scratch_bytes, cudaStream_t st, int64_t group_rows);
 
 static bool use_tensor_scoring(const tq_plan* p) {
     return p->path != TQ_PATH_EXACT && p->has_projection && tq_tensor_supported(p->dev.d, p->dev.bits);
@@ -295,25 +295,27 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
                             const uint32_t* signs, const float* rnorms, const float* norms,
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
-                            cudaStream_t st) {
+                            cudaStream_t st, int64_t group_rows) {
+    if (group_rows <= 0) group_rows = keys_per_group;
     // One or two queries per group and the matrix wanted (the reference's own call): the streaming kernel.
     if (p->path == TQ_PATH_AUTO && topk == 0 && scores && tq_score_few_supported(p, qpg) && keys_per_group > 0 && groups > 0)
-        return tq_launch_score_few(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st);
+        return tq_launch_score_few(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st, group_rows);
     // d = 64 has 8-byte sign rows (and 8- or 24-byte code rows): a group must start on a 16-byte boundary
     // for the bulk copies of the tensor-core kernel
-    const bool aligned_groups = p->dev.d == 128 || groups == 1 || keys_per_group % 2 == 0;
+    const bool aligned_groups = p->dev.d == 128 || groups == 1 || group_rows % 2 == 0;
     if (use_tensor_scoring(p) && aligned_groups && keys_per_group > 0 && groups > 0 && qpg > 0)
         return tq_launch_score_tc(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, topk, top_scores,
-                                  top_idx, idx_base, scratch, scratch_bytes, st);
+                                  top_idx, idx_base, scratch, scratch_bytes, st, group_rows);
     return tq_launch_score_general(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, topk,
-                                   top_scores, top_idx, idx_base, scratch, scratch_bytes, st);
+                                   top_scores, top_idx, idx_base, scratch, scratch_bytes, st, group_rows);
 }
 
 int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
                             const uint32_t* signs, const float* rnorms, const float* norms,
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
-                            cudaStream_t st) {
+                            cudaStream_t st, int64_t group_rows) {
+    if (group_rows <= 0) group_rows = keys_per_group;
     const ScoreGeometry s = geometry(groups, keys_per_group, topk);
     if (topk > 0) {
         const int64_t need = general_topk_scratch(groups, qpg, keys_per_group, topk);
@@ -336,7 +338,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
     if (sm > 200 * 1024) return tq_fail(TQ_ERR_UNSUPPORTED, "score kernel needs %zu bytes of shared memory", sm);
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     score_kernel<<<dim3(s.nblk, groups), kThreads, sm, st>>>(p->dev, q, qpg, codes, signs, rnorms, norms,
-                                                             keys_per_group, s.keys_per_block, scores, topk, s.cap2,
+                                                             keys_per_group, group_rows, s.keys_per_block, scores, topk, s.cap2,
                                                              static_cast<unsigned long long*>(scratch));
     TQ_CUDA_TRY(cudaGetLastError());
     if (topk > 0) {

@@ -27,7 +27,7 @@ template <int BITS, int DR>
 __global__ void __launch_bounds__(kFewThreads)
 score_few_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restrict__ codes,
                  const uint32_t* __restrict__ signs, const float* __restrict__ rnorms, const float* __restrict__ norms,
-                 int64_t keys_per_group, int qpg, float* __restrict__ scores) {
+                 int64_t keys_per_group, int64_t group_rows, int qpg, float* __restrict__ scores) {
     constexpr int kPairs = DR / 2, kEntries = 1 << (2 * BITS), kBytes = DR / 8;
     constexpr int kCodeWords = DR * BITS / 32, kSignWords = DR / 32;
     constexpr uint32_t kMask = kEntries - 1;
@@ -85,7 +85,7 @@ score_few_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
     float* out = scores + ((size_t)g * qpg + qi) * keys_per_group;
     for (int64_t key = (int64_t)blockIdx.x * kFewThreads + threadIdx.x; key < keys_per_group;
          key += (int64_t)gridDim.x * kFewThreads) {
-        const int64_t row = (int64_t)g * keys_per_group + key;
+        const int64_t row = (int64_t)g * group_rows + key;
         uint32_t cw[kCodeWords + 1], sw[kSignWords];
         const uint32_t* crow = codes + row * kCodeWords;
         const uint32_t* srow = signs + row * kSignWords;
@@ -127,7 +127,8 @@ score_few_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
 
 template <int BITS, int DR>
 int launch_few(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
-               const float* norms, int64_t keys_per_group, int groups, int qpg, float* scores, cudaStream_t st) {
+               const float* norms, int64_t keys_per_group, int64_t group_rows, int groups, int qpg, float* scores,
+               cudaStream_t st) {
     const int sm = ((DR / 2) * (1 << (2 * BITS)) + (DR / 8) * 256) * 4;
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_few_kernel<BITS, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
     int sms = 148;
@@ -136,7 +137,7 @@ int launch_few(const tq_plan* p, const float* q, const uint32_t* codes, const ui
     const int64_t cap = (int64_t)sms * 4;   // the tables cost a few microseconds per block: a few blocks per SM, grid-stride
     if (blocks > cap) blocks = cap;
     score_few_kernel<BITS, DR><<<dim3((unsigned)blocks, (unsigned)qpg, (unsigned)groups), kFewThreads, sm, st>>>(
-        p->dev, q, codes, signs, rnorms, norms, keys_per_group, qpg, scores);
+        p->dev, q, codes, signs, rnorms, norms, keys_per_group, group_rows, qpg, scores);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -149,13 +150,15 @@ bool tq_score_few_supported(const tq_plan* p, int qpg) {
 
 // scores: [groups][qpg][keys_per_group]
 int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
-                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st) {
+                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st,
+                        int64_t group_rows) {
+    if (group_rows <= 0) group_rows = keys_per_group;
     const int d = p->dev.d, bits = p->dev.bits;
     int r = TQ_ERR_UNSUPPORTED;
 #define TQ_FEW(B)                                                                                                        \
     case B:                                                                                                             \
-        r = d == 64 ? launch_few<B, 64>(p, q, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st)     \
-                    : launch_few<B, 128>(p, q, codes, signs, rnorms, norms, keys_per_group, groups, qpg, scores, st);   \
+        r = d == 64 ? launch_few<B, 64>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st)     \
+                    : launch_few<B, 128>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st);   \
         break;
     switch (bits) { TQ_FEW(1) TQ_FEW(2) TQ_FEW(3) TQ_FEW(4) }
 #undef TQ_FEW

@@ -608,7 +608,8 @@ int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int
 int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,
                        const uint32_t* signs, const float* rnorms, const float* norms, int64_t keys_per_group,
                        float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
-                       size_t scratch_bytes, cudaStream_t st) {
+                       size_t scratch_bytes, cudaStream_t st, int64_t group_rows) {
+    if (group_rows <= 0) group_rows = keys_per_group;
     const ScoreTcPlan sp = plan_score(groups, qpg, keys_per_group, topk, scores == nullptr);
     if (!scratch || scratch_bytes < sp.total)
         return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "score scratch: need %zu bytes, got %zu", sp.total, scratch_bytes);
@@ -638,7 +639,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             ScoreTcArgs a{};
             a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
             a.prep = prep; a.codebook = p->dev.codebook;
-            a.keys_per_group = keys_per_group; a.key_off = key_off; a.key_cnt = key_cnt;
+            a.keys_per_group = group_rows; a.key_off = key_off; a.key_cnt = key_cnt;
             a.tiles_per_group = (key_cnt + kTileKeys - 1) / kTileKeys;
             a.total_tiles = a.tiles_per_group * groups;
             a.nq = nq;
@@ -662,7 +663,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
             // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
             topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, 0, st>>>(
-                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, keys_per_group, key_off, topk, pow2_at_least(topk),
+                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, group_rows, key_off, topk, pow2_at_least(topk),
                 (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part);
             TQ_CUDA_TRY(cudaGetLastError());
         }

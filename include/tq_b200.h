@@ -198,6 +198,31 @@ int tq_prod_append(const tq_plan* plan, const float* x, int groups, int tokens, 
                    void* stream);
 
 /*
+ * Decode attention over a quantized key/value cache, without writing scores or dequantized values:
+ *
+ *   out[g][a][:] = sum_i softmax_i( scale * score(q[g][a], key[g][i]) ) * value[g][i][:]
+ *
+ * score = TurboQuantProd.attention_score (_quant.py:334-358) on keys packed by tq_prod_quantize / tq_prod_append
+ * with `kplan`; value = TurboQuantMSE.dequantize (_quant.py:238-254) of rows packed by tq_mse_quantize /
+ * tq_mse_append with `vplan` (an MSE plan of the same d; its rotation and codebook may differ from the keys').
+ * Scale, softmax and the weighted sum follow scaled_dot_product_attention (_core.py:1606-1683) without mask or
+ * dropout; scale == 0 selects d^-1/2 as `scale or D ** -0.5` does there.
+ * q: float32[groups][q_per_group][d]; out: the same shape.  Keys and values of group g occupy rows
+ * [g * group_rows, g * group_rows + keys_per_group) of their arrays (group_rows >= keys_per_group).
+ * length: null, or a device pointer to one int64 holding the number of keys per group (the counter
+ * tq_prod_append advances); the kernel then attends over min(*length, keys_per_group) keys, so a captured
+ * launch keeps working while the cache grows up to keys_per_group.  No keys: out = 0.
+ * d = 64 or 128, 1..4 code bits for keys and values, else TQ_ERR_UNSUPPORTED.
+ * scratch: tq_decode_attention_scratch_bytes(kplan, groups, q_per_group, keys_per_group) bytes, 16-byte aligned.
+ */
+int64_t tq_decode_attention_scratch_bytes(const tq_plan* kplan, int groups, int q_per_group, int64_t keys_per_group);
+int tq_decode_attention(const tq_plan* kplan, const tq_plan* vplan, const float* q, int groups, int q_per_group,
+                        const void* k_codes, const void* k_signs, const float* k_residual_norms, const float* k_norms,
+                        const void* v_codes, const float* v_norms, int64_t keys_per_group, int64_t group_rows,
+                        const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes,
+                        void* stream);
+
+/*
  * Merge `lists` candidate lists per query (e.g. one per GPU after an all-gather) into one
  * descending top-k.  in_scores/in_idx: [lists][queries][topk]; out: [queries][topk].
  * No reference counterpart (the reference is single-device).

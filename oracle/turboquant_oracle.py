@@ -227,3 +227,30 @@ def prod_attention_score(p: ProdParams, query, codes, qjl, residual_norms, norms
     s2 = _ALPHA_NUM / p.d * residual_norms * np.sum((q @ p.projection.T) * qjl, axis=1)
     out = norms * (s1 + s2)
     return out.reshape(tuple(q_prefix) if q.shape[0] != 1 else tuple(prefix))
+
+
+# --------------------------------------------------------------------------
+# caller side of attention_score: scale -> softmax -> weighted sum of values
+# --------------------------------------------------------------------------
+def softmax_rows(x: np.ndarray) -> np.ndarray:
+    """``Tensor.softmax`` over the last axis (_core.py:1286-1291)."""
+    shifted = x - np.max(x, axis=-1, keepdims=True)
+    e = np.exp(shifted)
+    return e / np.sum(e, axis=-1, keepdims=True)
+
+
+def decode_attention(kp: ProdParams, vp: MSEParams, queries, key_encoding, value_codes, value_norms,
+                     scale: Optional[float] = None) -> np.ndarray:
+    """``scaled_dot_product_attention`` (_core.py:1606-1683; no mask, no dropout) for one group of keys, with
+    ``query @ key.T`` replaced by ``TurboQuantProd.attention_score`` over the packed keys (one broadcast call
+    per query, as the reference's users loop it) and ``value`` by ``TurboQuantMSE.dequantize`` of the packed
+    values.  queries: (Q, d); key_encoding: (codes, qjl, residual_norms, norms) of N keys; returns (Q, d)."""
+    codes, qjl, rn, norms = key_encoding
+    q = np.asarray(queries, dtype=np.float32).reshape(-1, kp.d)
+    n = codes.shape[0]
+    scale = scale or (kp.d ** -0.5)
+    scores = np.stack([prod_attention_score(kp, q[a], codes, qjl, rn, norms, (n,)) for a in range(q.shape[0])])
+    scores = scores * np.float32(scale)
+    weights = softmax_rows(scores)
+    values = mse_dequantize(vp, value_codes, value_norms, (n,))
+    return weights @ values

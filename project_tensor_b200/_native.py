@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p, POINTER
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libtq_sm100.so"
@@ -48,6 +48,10 @@ SIGNATURES = {
                               c_void_p]),
     "tq_prod_append": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_void_p, c_int, c_void_p]),
+    "tq_decode_attention_scratch_bytes": (c_int64, [c_void_p, c_int, c_int, c_int64]),
+    "tq_decode_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_float, c_void_p, c_void_p, c_size_t,
+                                    c_void_p]),
     "tq_topk_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "tq_unpack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_pack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),

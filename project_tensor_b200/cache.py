@@ -165,3 +165,110 @@ class PackedKeyCache:
         pk = _tq._Packed(self.codes[lo:lo + n], self.signs[lo:lo + n], self.norms[lo:lo + n],
                          self.residual_norms[lo:lo + n], n, "torch", self.device, self._plans)
         return _tq._encoding_from_packed(_tq.TurboQuantProdEncoding, pk, (n,))
+
+
+class PackedKVCache:
+    """Packed keys (TurboQuantProd) and values (TurboQuantMSE) of ``groups`` sequences/heads, ``capacity`` rows
+    each, and decode attention over them without materialising scores or dequantized values.
+
+    ``attend(queries)`` returns ``softmax(scale * attention_score(q, keys)) @ dequantize(values)`` per group --
+    the reference's ``scaled_dot_product_attention`` (tensor_gpu_v2/_core.py:1606-1683, no mask, no dropout)
+    with the key product replaced by ``TurboQuantProd.attention_score`` (_quant.py:334-358) and the values by
+    ``TurboQuantMSE.dequantize`` (_quant.py:251-254) -- computed by ``tq_decode_attention`` in one pass over
+    the packed rows (d = 64 or 128, at most 4 code bits for keys and values)."""
+
+    def __init__(self, key_quantizer: "_tq.TurboQuantProd", value_quantizer: "_tq.TurboQuantMSE", groups: int,
+                 capacity: int, device: Any = None):
+        if not isinstance(value_quantizer, _tq.TurboQuantMSE):
+            raise TypeError("PackedKVCache holds TurboQuantMSE values")
+        if value_quantizer.dimension != key_quantizer.dimension:
+            raise ValueError(f"keys have dimension {key_quantizer.dimension}, values {value_quantizer.dimension}")
+        self.keys = PackedKeyCache(key_quantizer, groups, capacity, device)
+        torch = _tq._torch()
+        self.value_quantizer = value_quantizer
+        self.groups, self.capacity, self.device = self.keys.groups, self.keys.capacity, self.keys.device
+        self._vplans = value_quantizer._plans
+        rows = self.groups * self.capacity
+        self.value_codes = torch.zeros((rows, self._vplans.row_bytes()[0]), dtype=torch.uint8, device=self.device)
+        self.value_norms = torch.zeros((rows,), dtype=torch.float32, device=self.device)
+
+    def __len__(self) -> int:
+        return len(self.keys)
+
+    def sync_length(self) -> int:
+        return self.keys.sync_length()
+
+    def reset(self) -> None:
+        self.keys.reset()
+
+    def append(self, keys: Any, values: Any) -> None:
+        """Add one key and one value per token: both of shape (groups, tokens, d) or (groups, d).  The values
+        are written at the position the keys take; the shared length advances once."""
+        torch = _tq._torch()
+        d = self.value_quantizer.dimension
+        karr, varr = _tq._to_array(keys), _tq._to_array(values)
+        _tq._ensure_last_dim(varr, d)
+        if tuple(karr.shape) != tuple(varr.shape):
+            raise ValueError(f"keys {tuple(karr.shape)} and values {tuple(varr.shape)} differ in shape")
+        if varr.ndim not in (2, 3) or int(varr.shape[0]) != self.groups:
+            raise ValueError(f"expected values of shape ({self.groups}, tokens, {d}) or ({self.groups}, {d}), "
+                             f"got {tuple(varr.shape)}")
+        tokens = 1 if varr.ndim == 2 else int(varr.shape[1])
+        lo = len(self.keys)
+        if lo + tokens > self.capacity:
+            raise ValueError(f"cache is full: {lo} + {tokens} rows exceed the capacity {self.capacity}")
+        if tokens == 0:
+            return
+        staged = _tq._stage(values, d, device=self.device)
+        with torch.cuda.device(self.device):
+            if self.groups * tokens <= PackedKeyCache.SMALL_APPEND_ROWS:
+                # the values first, without advancing: the key append that follows reads the same length
+                _native.check(_native.load().tq_mse_append(
+                    self._vplans.handle(self.device), staged.tensor.data_ptr(), self.groups, tokens,
+                    self.value_codes.data_ptr(), self.value_norms.data_ptr(), self.capacity,
+                    self.keys.length_device.data_ptr(), 0, _tq._stream_ptr(self.device)))
+            else:
+                pk = self.value_quantizer._quantize_staged(staged, self._vplans, False)
+                g, c = self.groups, self.capacity
+                self.value_codes.view(g, c, -1)[:, lo:lo + tokens] = pk.codes.view(g, tokens, -1)
+                self.value_norms.view(g, c)[:, lo:lo + tokens] = pk.norms.view(g, tokens)
+        self.keys.append(keys)
+
+    def attend(self, queries: Any, *, scale: Optional[float] = None, use_device_length: bool = False):
+        """``queries`` of shape (groups, q_per_group, d) or (groups, d) -> attention output of the same shape.
+        ``scale`` defaults to d ** -0.5.  ``use_device_length=True`` makes the kernel read the number of keys from
+        the device-side counter (up to the capacity) instead of the host's mirror, for a step that is replayed from
+        a CUDA graph while the cache grows."""
+        torch = _tq._torch()
+        d = self.value_quantizer.dimension
+        array = _tq._to_array(queries)
+        _tq._ensure_last_dim(array, d)
+        if array.ndim not in (2, 3) or int(array.shape[0]) != self.groups:
+            raise ValueError(f"expected queries of shape ({self.groups}, q_per_group, {d}), got {tuple(array.shape)}")
+        qpg = 1 if array.ndim == 2 else int(array.shape[1])
+        staged = _tq._stage(queries, d, device=self.device)
+        n = self.capacity if use_device_length else len(self.keys)
+        lib = _native.load()
+        kc, dev = self.keys, self.device
+        kh, vh = kc._plans.handle(dev), self._vplans.handle(dev)
+        with torch.cuda.device(dev):
+            out = torch.empty((self.groups, qpg, d), dtype=torch.float32, device=dev)
+            need = int(lib.tq_decode_attention_scratch_bytes(kh, self.groups, qpg, n))
+            scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=dev)
+            _native.check(lib.tq_decode_attention(
+                kh, vh, staged.tensor.data_ptr(), self.groups, qpg, kc.codes.data_ptr(), kc.signs.data_ptr(),
+                kc.residual_norms.data_ptr(), kc.norms.data_ptr(), self.value_codes.data_ptr(),
+                self.value_norms.data_ptr(), n, self.capacity,
+                kc.length_device.data_ptr() if use_device_length else None, float(scale or 0.0), out.data_ptr(),
+                scratch.data_ptr(), scratch.numel(), _tq._stream_ptr(dev)))
+        out = _tq._deliver(out, staged.kind)
+        return out.reshape(tuple(array.shape))
+
+    def value_encoding(self, group: int):
+        """The filled value rows of one group as a TurboQuantMSEEncoding (a view of the cache)."""
+        if not 0 <= group < self.groups:
+            raise IndexError(f"group {group} outside [0, {self.groups})")
+        lo, n = group * self.capacity, len(self.keys)
+        pk = _tq._Packed(self.value_codes[lo:lo + n], None, self.value_norms[lo:lo + n], None, n, "torch", self.device,
+                         self._vplans)
+        return _tq._encoding_from_packed(_tq.TurboQuantMSEEncoding, pk, (n,))

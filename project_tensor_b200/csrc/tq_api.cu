@@ -455,6 +455,43 @@ int tq_score_cache(const tq_plan* p, const float* q, int groups, int q_per_group
                                    static_cast<cudaStream_t>(stream), group_rows);
 }
 
+int64_t tq_decode_attention_scratch_bytes(const tq_plan* kp, int groups, int q_per_group, int64_t keys_per_group) {
+    if (!kp || groups < 0 || q_per_group < 0 || keys_per_group < 0) return 0;
+    return tq_decode_attention_scratch(kp, groups, q_per_group, keys_per_group);
+}
+
+int tq_decode_attention(const tq_plan* kp, const tq_plan* vp, const float* q, int groups, int q_per_group,
+                        const void* k_codes, const void* k_signs, const float* k_residual_norms, const float* k_norms,
+                        const void* v_codes, const float* v_norms, int64_t keys_per_group, int64_t group_rows,
+                        const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes, void* stream) {
+    TQ_TRY(check_plan(kp, true));
+    TQ_TRY(check_plan(vp, false));
+    if (kp->device != vp->device) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "key and value plans live on different devices");
+    if (!tq_decode_attention_supported(kp, vp))
+        return tq_fail(TQ_ERR_UNSUPPORTED, "decode attention covers d = 64 or 128 (same for keys and values) and 1..4 code bits; "
+                       "got d = %d / %d, key code bits %d, value bits %d", kp->dev.d, vp->dev.d, kp->dev.bits, vp->dev.bits);
+    if (groups < 0 || q_per_group < 0 || keys_per_group < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "negative size");
+    if (group_rows < keys_per_group) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "group_rows is smaller than keys_per_group");
+    if (groups > 65535) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups > 65535");
+    if ((double)groups * (double)group_rows >= 4294967296.0)
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups * group_rows must stay below 2^32");
+    if (!(scale == scale) || scale < 0.f) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "scale must be a number >= 0 (0 selects d^-1/2)");
+    if (groups == 0 || q_per_group == 0) return TQ_OK;
+    TQ_TRY(check_ptr(q, "q"));
+    TQ_TRY(check_ptr(out, "out"));
+    if (keys_per_group > 0) {
+        TQ_TRY(check_encoding(k_codes, k_signs, k_residual_norms, k_norms));
+        TQ_TRY(check_ptr(v_codes, "v_codes"));
+        TQ_TRY(check_ptr(v_norms, "v_norms"));
+    }
+    if (scale == 0.f) scale = 1.0f / sqrtf((float)kp->dev.d);   // `scale or D ** -0.5`, _core.py:1652
+    DeviceScope scope(kp->device);
+    return tq_launch_decode_attention(kp, vp, q, groups, q_per_group, static_cast<const uint32_t*>(k_codes),
+                                      static_cast<const uint32_t*>(k_signs), k_residual_norms, k_norms,
+                                      static_cast<const uint32_t*>(v_codes), v_norms, keys_per_group, group_rows, length,
+                                      scale, out, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int tq_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk, float* out_scores,
                   int64_t* out_idx, void* stream) {
     if (lists < 1 || queries < 0 || topk < 1 || topk > TQ_MAX_TOPK)

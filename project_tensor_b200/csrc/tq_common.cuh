@@ -140,6 +140,14 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
                             cudaStream_t st, int64_t group_rows = 0);
+// Decode attention over packed keys (Prod plan) and packed values (MSE plan), tq_decode_attn.cu.
+bool tq_decode_attention_supported(const tq_plan* kp, const tq_plan* vp);
+int64_t tq_decode_attention_scratch(const tq_plan* kp, int groups, int qpg, int64_t keys_per_group);
+int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float* q, int groups, int qpg,
+                               const uint32_t* kcodes, const uint32_t* ksigns, const float* krnorms, const float* knorms,
+                               const uint32_t* vcodes, const float* vnorms, int64_t keys_per_group, int64_t group_rows,
+                               const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes,
+                               cudaStream_t st);
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk);
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
                          float* out_scores, int64_t* out_idx, cudaStream_t st);

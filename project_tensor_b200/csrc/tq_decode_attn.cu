@@ -1,0 +1,436 @@
+// Decode attention over a quantized key/value cache, d = 128 or 64:
+//
+//   out[g][a] = softmax_i( scale * score(q[g][a], key[g][i]) ) . value[g][i]
+//
+// with keys held as TurboQuantProd encodings (score = TurboQuantProd.attention_score, _quant.py:334-358) and
+// values as TurboQuantMSE encodings (value = TurboQuantMSE.dequantize, _quant.py:238-254).  It is the caller
+// side of attention_score -- scale, softmax, weighted sum of values: scaled_dot_product_attention,
+// _core.py:1606-1683 -- done without ever writing the scores or the dequantized values to memory: per key
+// the kernel reads the packed key (d*b/8 + d/8 + 8 bytes) and the packed value (d*b/8 + 4 bytes) once.
+//
+// Two facts shape it:
+//   * scores for a few queries per group come from lookup tables (as in tq_score_few.cu): per query a pair
+//     table [d/2][4^bits] and a byte table [d/8][256], here interleaved by query so that one vector load
+//     serves all queries of a pass;
+//   * dequantize is linear after the centroid gather: sum_i p_i * norm_i * (c[idx_i] R) = (sum_i p_i norm_i
+//     c[idx_i]) R, so the block accumulates in the rotated domain (one multiply-add per coordinate, key and
+//     query) and the d x d rotation is applied once per query in the combine kernel.
+//
+// A block of 512 threads walks tiles of 512 keys of one group: thread t scores key t of the tile for the QP
+// queries of the pass, the block agrees on the running maximum (online softmax), then the same threads
+// regroup as (coordinate j = t mod d, slice = t / d) and add the tile's values, staged in shared memory by
+// cp.async, into their accumulators.  Key ranges are split over blocks; every block leaves (max, sum,
+// accumulator) per query in scratch and decode_combine_kernel merges the splits and rotates.
+#include "tq_common.cuh"
+
+#include <math_constants.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kTile = 512;
+constexpr int kMaxSplits = 64;
+constexpr int kWarps = kThreads / 32;
+
+struct DecodeArgs {
+    const float* q;              // [groups][qpg][d]
+    const uint32_t* kcodes;
+    const uint32_t* ksigns;
+    const float* krnorms;
+    const float* knorms;
+    const uint32_t* vcodes;
+    const float* vnorms;
+    const float* vcodebook;      // codebook of the value quantizer
+    int vbits, vwords;           // bits per value code, 32-bit words per packed value row
+    int qpg;
+    int64_t keys_per_group, group_rows;
+    const int64_t* length;       // optional device-side number of keys per group (capped by keys_per_group)
+    float scale_log2e;           // scale * log2(e): the softmax runs in base 2
+    int splits;
+    float* part;                 // [groups][qpg][splits][d + 2]: accumulator, running max, running sum
+};
+
+template <int QP>
+__device__ __forceinline__ void ld_vec(const float* p, float (&v)[QP]) {
+    if constexpr (QP == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else if constexpr (QP == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+        v[0] = *p;
+    }
+}
+template <int QP>
+__device__ __forceinline__ void st_vec(float* p, const float (&v)[QP]) {
+    if constexpr (QP == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else if constexpr (QP == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    else *p = v[0];
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int KB, int DR, int QP>
+constexpr size_t decode_smem_floats() {
+    return (size_t)((DR / 2) * (1 << (2 * KB)) + (DR / 8) * 256 + kTile) * QP + 3 * QP * DR + kWarps * QP + 8 + 16;
+}
+
+// grid (splits, passes over the queries of a group, groups)
+template <int KB, int DR, int QP>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_partial_kernel(TqDev kp, DecodeArgs a) {
+    constexpr int kPairs = DR / 2, kEntries = 1 << (2 * KB), kBytes = DR / 8;
+    constexpr int kCodeWords = DR * KB / 32, kSignWords = DR / 32;
+    constexpr uint32_t kMask = kEntries - 1;
+    constexpr int kSlices = kThreads / DR, kSliceKeys = kTile / kSlices;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    float* pair_t = reinterpret_cast<float*>(smraw);   // [kPairs * kEntries][QP]
+    float* byte_t = pair_t + kPairs * kEntries * QP;    // [kBytes * 256][QP]
+    float* pbuf = byte_t + kBytes * 256 * QP;           // [kTile][QP] weight * value norm; at the end [kSlices][QP][DR]
+    float* qin = pbuf + kTile * QP;                     // [QP][DR]
+    float* qr = qin + QP * DR;                          // rotated queries
+    float* ps = qr + QP * DR;                           // projected queries
+    float* red = ps + QP * DR;                          // [kWarps][QP]
+    float* sm_m = red + kWarps * QP;                    // [4] running maximum per query
+    float* sm_f = sm_m + 4;                             // [4] factor that brings older sums to the new maximum
+    float* vcb = sm_f + 4;                              // [16] value codebook
+    uint32_t* vt = reinterpret_cast<uint32_t*>(vcb + 16);   // [kTile][vwords] packed value rows of the tile
+
+    const int g = blockIdx.z, q0 = blockIdx.y * QP, split = blockIdx.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    int64_t n = a.keys_per_group;
+    if (a.length) {
+        const int64_t len = *a.length;
+        n = len < n ? len : n;
+        if (n < 0) n = 0;
+    }
+
+    for (int i = t; i < QP * DR; i += kThreads) {
+        const int qq = i / DR, k = i - qq * DR;
+        qin[i] = q0 + qq < a.qpg ? __ldg(a.q + ((size_t)g * a.qpg + q0 + qq) * DR + k) : 0.f;
+    }
+    if (t < 16) vcb[t] = t < (1 << a.vbits) ? __ldg(a.vcodebook + t) : 0.f;
+    if (t < 4) sm_m[t] = -CUDART_INF_F;
+    __syncthreads();
+    // rotated[j] = sum_k q[k] R[j][k], projected[j] = sum_k q[k] S[j][k]: one FMA per k, k ascending, as in
+    // the reference's matrix products
+    for (int i = t; i < QP * DR; i += kThreads) {
+        const int qq = i / DR, j = i - qq * DR;
+        const float* qv = qin + qq * DR;
+        float r = 0.f, sacc = 0.f;
+        for (int k0 = 0; k0 < DR; k0 += 16) {
+            float mr[16], ms[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                mr[u] = __ldg(kp.Rt + (size_t)(k0 + u) * DR + j);
+                ms[u] = __ldg(kp.St + (size_t)(k0 + u) * DR + j);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                r = fmaf(qv[k0 + u], mr[u], r);
+                sacc = fmaf(qv[k0 + u], ms[u], sacc);
+            }
+        }
+        qr[i] = r;
+        ps[i] = sacc;
+    }
+    __syncthreads();
+    for (int i = t; i < kPairs * kEntries; i += kThreads) {
+        const int pp = i / kEntries, e = i - pp * kEntries;
+        const float c0 = __ldg(kp.codebook + (e & ((1 << KB) - 1))), c1 = __ldg(kp.codebook + (e >> KB));
+#pragma unroll
+        for (int qq = 0; qq < QP; ++qq) pair_t[i * QP + qq] = fmaf(c1, qr[qq * DR + 2 * pp + 1], c0 * qr[qq * DR + 2 * pp]);
+    }
+    for (int i = t; i < kBytes * 256; i += kThreads) {
+        const int pos = i >> 8, v = i & 255, w = pos >> 2, b = pos & 3;
+#pragma unroll
+        for (int qq = 0; qq < QP; ++qq) {
+            float acc = 0.f;
+#pragma unroll
+            for (int bit = 0; bit < 8; ++bit) {
+                // stored order of the sign words: even coordinates in bits 0..15, odd ones in bits 16..31
+                const int bp = 8 * b + bit;
+                const int coord = 32 * w + (bp < 16 ? 2 * bp : 2 * (bp - 16) + 1);
+                const float x = ps[qq * DR + coord];
+                acc += (v >> bit) & 1 ? x : -x;
+            }
+            byte_t[i * QP + qq] = acc;
+        }
+    }
+
+    const int64_t tiles_total = (n + kTile - 1) / kTile;
+    const int64_t tps = (tiles_total + a.splits - 1) / a.splits;
+    const int64_t tile0 = (int64_t)split * tps;
+    int64_t tile1 = tile0 + tps;
+    if (tile1 > tiles_total) tile1 = tiles_total;
+
+    // this thread's share of the value phase: coordinate j of the keys of one slice of the tile
+    const int j = t & (DR - 1), slice = t / DR;
+    const int vbit = j * a.vbits, vw = vbit >> 5, vsh = vbit & 31;
+    const int vw2 = vw + 1 < a.vwords ? vw + 1 : vw;     // a code that straddles two words never sits in the last one
+    const uint32_t vmask = (1u << a.vbits) - 1u;
+    const int vwords = a.vwords;
+    const float alpha = kp.alpha;
+
+    float l_part[QP], acc[QP];
+#pragma unroll
+    for (int qq = 0; qq < QP; ++qq) { l_part[qq] = 0.f; acc[qq] = 0.f; }
+    __syncthreads();   // tables complete
+
+    for (int64_t tile = tile0; tile < tile1; ++tile) {
+        const int64_t k0 = tile * kTile, key = k0 + t;
+        const int64_t row = (int64_t)g * a.group_rows + key;
+        float s[QP], vn = 0.f;
+        if (key < n) {
+            uint32_t cw[kCodeWords + 1], sw[kSignWords];
+            const uint32_t* crow = a.kcodes + row * kCodeWords;
+            const uint32_t* srow = a.ksigns + row * kSignWords;
+            if (kCodeWords % 4 == 0) {
+#pragma unroll
+                for (int k = 0; k < kCodeWords; k += 4) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(crow + k));
+                    cw[k] = v.x; cw[k + 1] = v.y; cw[k + 2] = v.z; cw[k + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < kCodeWords; k += 2) {
+                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(crow + k));
+                    cw[k] = v.x; cw[k + 1] = v.y;
+                }
+            }
+            cw[kCodeWords] = 0u;
+#pragma unroll
+            for (int k = 0; k < kSignWords; k += 2) {
+                const uint2 v = __ldg(reinterpret_cast<const uint2*>(srow + k));
+                sw[k] = v.x; sw[k + 1] = v.y;
+            }
+            const float nrm = __ldg(a.knorms + row), rn = __ldg(a.krnorms + row);
+            vn = __ldg(a.vnorms + row);
+            float a1[2][QP], a2[QP];
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq) { a1[0][qq] = 0.f; a1[1][qq] = 0.f; a2[qq] = 0.f; }
+#pragma unroll
+            for (int pp = 0; pp < kPairs; ++pp) {
+                const int bit = pp * 2 * KB, wi = bit >> 5, sh = bit & 31;
+                uint32_t e;
+                if (sh + 2 * KB <= 32) e = (cw[wi] >> sh) & kMask;
+                else e = __funnelshift_r(cw[wi], cw[wi + 1], sh) & kMask;
+                float v[QP];
+                ld_vec<QP>(pair_t + (pp * kEntries + e) * QP, v);
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) a1[pp & 1][qq] += v[qq];
+            }
+#pragma unroll
+            for (int pos = 0; pos < kBytes; ++pos) {
+                float v[QP];
+                ld_vec<QP>(byte_t + (pos * 256 + ((sw[pos >> 2] >> (8 * (pos & 3))) & 255u)) * QP, v);
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) a2[qq] += v[qq];
+            }
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq)
+                s[qq] = nrm * fmaf(alpha * rn, a2[qq], a1[0][qq] + a1[1][qq]) * a.scale_log2e;
+        } else {
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq) s[qq] = -CUDART_INF_F;
+        }
+#pragma unroll
+        for (int qq = 0; qq < QP; ++qq) {
+            float m = s[qq];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) red[warp * QP + qq] = m;
+        }
+        __syncthreads();   // tile maxima visible; the value phase of the previous tile is over
+        {
+            // packed value rows of this tile -> shared memory (rows beyond n are not read from memory; what
+            // shared memory holds for them meets a weight of zero)
+            int64_t rows = n - k0;
+            if (rows > kTile) rows = kTile;
+            const int nwords = (int)rows * vwords;
+            const uint32_t* src = a.vcodes + ((int64_t)g * a.group_rows + k0) * vwords;   // first row of the tile
+            if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+                const int n16 = nwords >> 2;
+                for (int i = t; i < n16; i += kThreads) cp_async16(vt + 4 * i, src + 4 * i);
+                for (int i = 4 * n16 + t; i < nwords; i += kThreads) cp_async4(vt + i, src + i);
+            } else {
+                for (int i = t; i < nwords; i += kThreads) cp_async4(vt + i, src + i);
+            }
+            cp_async_commit();
+        }
+        if (t < QP) {
+            float mt = red[t];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) mt = fmaxf(mt, red[w * QP + t]);
+            const float mo = sm_m[t], mn = fmaxf(mo, mt);
+            sm_f[t] = mn == -CUDART_INF_F ? 1.f : exp2f(mo - mn);
+            sm_m[t] = mn;
+        }
+        __syncthreads();
+        {
+            float pv[QP];
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq) {
+                const float mn = sm_m[qq], f = sm_f[qq];
+                const float p = exp2f(s[qq] - (mn == -CUDART_INF_F ? 0.f : mn));   // masked keys: exp2(-inf) = 0
+                l_part[qq] = fmaf(l_part[qq], f, p);
+                acc[qq] *= f;
+                pv[qq] = p * vn;
+            }
+            st_vec<QP>(pbuf + t * QP, pv);
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        {
+            const uint32_t* vrow = vt + (size_t)slice * kSliceKeys * vwords;
+            const float* prow = pbuf + slice * kSliceKeys * QP;
+#pragma unroll 8
+            for (int kk = 0; kk < kSliceKeys; ++kk) {
+                const uint32_t lo = vrow[kk * vwords + vw], hi = vrow[kk * vwords + vw2];
+                const float c = vcb[__funnelshift_r(lo, hi, vsh) & vmask];
+                float pq[QP];
+                ld_vec<QP>(prow + kk * QP, pq);
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) acc[qq] = fmaf(pq[qq], c, acc[qq]);
+            }
+        }
+    }
+
+    __syncthreads();   // last value phase over: pbuf and red are free
+#pragma unroll
+    for (int qq = 0; qq < QP; ++qq) {
+        float v = l_part[qq];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) red[warp * QP + qq] = v;
+        pbuf[(slice * QP + qq) * DR + j] = acc[qq];
+    }
+    __syncthreads();
+    if (t < QP * DR) {
+        const int qq = t / DR, jj = t - qq * DR;
+        if (q0 + qq < a.qpg) {
+            float sum = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < kSlices; ++sl) sum += pbuf[(sl * QP + qq) * DR + jj];
+            float* dst = a.part + (((size_t)g * a.qpg + q0 + qq) * a.splits + split) * (DR + 2);
+            dst[jj] = sum;
+            if (jj == 0) {
+                float l = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) l += red[w * QP + qq];
+                dst[DR] = sm_m[qq];
+                dst[DR + 1] = l;
+            }
+        }
+    }
+}
+
+// One block per (group, query): merge the splits (weights 2^(m_s - M)), divide by the sum, and apply the value
+// quantizer's rotation: out[j] = sum_k a[k] R[k][j] (the `@ self.rotation` of _quant.py:241).
+__global__ void decode_combine_kernel(const float* __restrict__ part, int splits, int d, const float* __restrict__ Rv,
+                                      float* __restrict__ out) {
+    extern __shared__ float avec[];
+    const int t = threadIdx.x;
+    const float* pr = part + (size_t)blockIdx.x * splits * (d + 2);
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, pr[(size_t)s * (d + 2) + d]);
+    float L = 0.f, av = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = pr[(size_t)s * (d + 2) + d];
+        const float w = m == -CUDART_INF_F ? 0.f : exp2f(m - M);
+        L = fmaf(w, pr[(size_t)s * (d + 2) + d + 1], L);
+        if (t < d) av = fmaf(w, pr[(size_t)s * (d + 2) + t], av);
+    }
+    if (t < d) avec[t] = L > 0.f ? av / L : 0.f;   // no keys at all: zeros
+    __syncthreads();
+    if (t < d) {
+        float o = 0.f;
+        for (int k = 0; k < d; ++k) o = fmaf(avec[k], __ldg(Rv + (size_t)k * d + t), o);
+        out[(size_t)blockIdx.x * d + t] = o;
+    }
+}
+
+int queries_per_pass(int kbits, int qpg) { return qpg == 1 ? 1 : (kbits <= 3 ? 4 : 2); }
+
+int splits_for(int groups, int passes, int64_t keys_per_group) {
+    const int64_t tiles = (keys_per_group + kTile - 1) / kTile;
+    const int64_t gq = (int64_t)groups * passes;
+    int64_t s = (2 * 148 + gq - 1) / gq;   // about two blocks per SM in all, one resident at a time
+    if (s > tiles) s = tiles;
+    if (s > kMaxSplits) s = kMaxSplits;
+    if (s < 1) s = 1;
+    return (int)s;
+}
+
+template <int KB, int DR, int QP>
+int launch_partial(const tq_plan* kp, const DecodeArgs& a, int groups, int passes, cudaStream_t st) {
+    const size_t sm = decode_smem_floats<KB, DR, QP>() * 4 + (size_t)kTile * a.vwords * 4;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    decode_partial_kernel<KB, DR, QP><<<dim3((unsigned)a.splits, (unsigned)passes, (unsigned)groups), kThreads, sm, st>>>(kp->dev, a);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
+template <int KB, int DR>
+int launch_partial_qp(const tq_plan* kp, const DecodeArgs& a, int groups, int passes, int qp, cudaStream_t st) {
+    if (qp == 1) return launch_partial<KB, DR, 1>(kp, a, groups, passes, st);
+    if constexpr (KB <= 3) return launch_partial<KB, DR, 4>(kp, a, groups, passes, st);
+    else return launch_partial<KB, DR, 2>(kp, a, groups, passes, st);
+}
+
+}  // namespace
+
+bool tq_decode_attention_supported(const tq_plan* kp, const tq_plan* vp) {
+    const int d = kp->dev.d;
+    return kp->has_projection && vp->dev.d == d && (d == 128 || d == 64) && kp->dev.bits >= 1 && kp->dev.bits <= 4 &&
+           vp->dev.bits >= 1 && vp->dev.bits <= 4;
+}
+
+int64_t tq_decode_attention_scratch(const tq_plan* kp, int groups, int qpg, int64_t keys_per_group) {
+    const int qp = queries_per_pass(kp->dev.bits, qpg);
+    const int passes = (qpg + qp - 1) / qp;
+    const int splits = splits_for(groups, passes, keys_per_group);
+    return (int64_t)groups * qpg * splits * (kp->dev.d + 2) * (int64_t)sizeof(float);
+}
+
+int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float* q, int groups, int qpg,
+                               const uint32_t* kcodes, const uint32_t* ksigns, const float* krnorms, const float* knorms,
+                               const uint32_t* vcodes, const float* vnorms, int64_t keys_per_group, int64_t group_rows,
+                               const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes,
+                               cudaStream_t st) {
+    const int d = kp->dev.d, kb = kp->dev.bits;
+    const int qp = queries_per_pass(kb, qpg);
+    const int passes = (qpg + qp - 1) / qp;
+    DecodeArgs a{};
+    a.q = q; a.kcodes = kcodes; a.ksigns = ksigns; a.krnorms = krnorms; a.knorms = knorms;
+    a.vcodes = vcodes; a.vnorms = vnorms; a.vcodebook = vp->dev.codebook;
+    a.vbits = vp->dev.bits; a.vwords = vp->dev.code_words;
+    a.qpg = qpg; a.keys_per_group = keys_per_group; a.group_rows = group_rows; a.length = length;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    a.splits = splits_for(groups, passes, keys_per_group);
+    a.part = static_cast<float*>(scratch);
+    const size_t need = (size_t)groups * qpg * a.splits * (d + 2) * sizeof(float);
+    if (!scratch || scratch_bytes < need)
+        return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "decode attention scratch: need %zu bytes, got %zu", need, scratch_bytes);
+    int r = TQ_ERR_UNSUPPORTED;
+#define TQ_DEC(B)                                                                                     \
+    case B:                                                                                           \
+        r = d == 64 ? launch_partial_qp<B, 64>(kp, a, groups, passes, qp, st)                          \
+                    : launch_partial_qp<B, 128>(kp, a, groups, passes, qp, st);                        \
+        break;
+    switch (kb) { TQ_DEC(1) TQ_DEC(2) TQ_DEC(3) TQ_DEC(4) }
+#undef TQ_DEC
+    if (r != TQ_OK) return r;
+    decode_combine_kernel<<<(unsigned)(groups * qpg), (d + 31) & ~31, d * sizeof(float), st>>>(a.part, a.splits, d, vp->dev.R, out);
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}

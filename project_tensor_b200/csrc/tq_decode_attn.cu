@@ -18,8 +18,9 @@
 //
 // A block of 512 threads walks tiles of 512 keys of one group: thread t scores key t of the tile for the QP
 // queries of the pass, the block agrees on the running maximum (online softmax), then the same threads
-// regroup as (coordinate j = t mod d, slice = t / d) and add the tile's values, staged in shared memory by
-// cp.async, into their accumulators.  Key ranges are split over blocks; every block leaves (max, sum,
+// regroup as (8 consecutive coordinates, key t / (d/8) of every batch of 512 / (d/8) keys) and add the tile's
+// values, staged in shared memory by cp.async, into their 8 x QP accumulators: one load of packed codes, one
+// of the weights and eight codebook lookups feed 8 x QP multiply-adds.  Key ranges are split over blocks; every block leaves (max, sum,
 // accumulator) per query in scratch and decode_combine_kernel merges the splits and rotates.
 #include "tq_common.cuh"
 
@@ -79,24 +80,29 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+template <int DR, int QP>
+__host__ __device__ constexpr int pbuf_floats() { return kTile * QP > kWarps * DR ? kTile * QP : kWarps * DR; }
+
 template <int KB, int DR, int QP>
 constexpr size_t decode_smem_floats() {
-    return (size_t)((DR / 2) * (1 << (2 * KB)) + (DR / 8) * 256 + kTile) * QP + 3 * QP * DR + kWarps * QP + 8 + 16;
+    return (size_t)((DR / 2) * (1 << (2 * KB)) + (DR / 8) * 256) * QP + pbuf_floats<DR, QP>() + 3 * QP * DR + kWarps * QP + 8 + 16;
 }
 
 // grid (splits, passes over the queries of a group, groups)
-template <int KB, int DR, int QP>
+// VSTRADDLE: the 8 codes of a thread may lie across two 32-bit words (3-bit values only)
+template <int KB, int DR, int QP, bool VSTRADDLE>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_partial_kernel(TqDev kp, DecodeArgs a) {
     constexpr int kPairs = DR / 2, kEntries = 1 << (2 * KB), kBytes = DR / 8;
     constexpr int kCodeWords = DR * KB / 32, kSignWords = DR / 32;
     constexpr uint32_t kMask = kEntries - 1;
-    constexpr int kSlices = kThreads / DR, kSliceKeys = kTile / kSlices;
+    constexpr int kCT = DR / 8;                     // threads that share a key in the value phase, 8 coordinates each
+    constexpr int kIterKeys = kThreads / kCT;       // keys the block takes per step of the value phase
     extern __shared__ __align__(16) unsigned char smraw[];
     float* pair_t = reinterpret_cast<float*>(smraw);   // [kPairs * kEntries][QP]
     float* byte_t = pair_t + kPairs * kEntries * QP;    // [kBytes * 256][QP]
-    float* pbuf = byte_t + kBytes * 256 * QP;           // [kTile][QP] weight * value norm; at the end [kSlices][QP][DR]
-    float* qin = pbuf + kTile * QP;                     // [QP][DR]
+    float* pbuf = byte_t + kBytes * 256 * QP;           // [kTile][QP] weight * value norm; at the end [kWarps][DR]
+    float* qin = pbuf + pbuf_floats<DR, QP>();                    // [QP][DR]
     float* qr = qin + QP * DR;                          // rotated queries
     float* ps = qr + QP * DR;                           // projected queries
     float* red = ps + QP * DR;                          // [kWarps][QP]
@@ -173,17 +179,23 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     int64_t tile1 = tile0 + tps;
     if (tile1 > tiles_total) tile1 = tiles_total;
 
-    // this thread's share of the value phase: coordinate j of the keys of one slice of the tile
-    const int j = t & (DR - 1), slice = t / DR;
-    const int vbit = j * a.vbits, vw = vbit >> 5, vsh = vbit & 31;
-    const int vw2 = vw + 1 < a.vwords ? vw + 1 : vw;     // a code that straddles two words never sits in the last one
+    // this thread's share of the value phase: coordinates 8c .. 8c+7 of key `ksub` of every batch of kIterKeys keys;
+    // their codes are the 8 * vbits bits that start at byte vbits * c of the packed row
+    const int c = t & (kCT - 1), ksub = t / kCT;
+    const int vbyte = a.vbits * c, vw = vbyte >> 2, vsh = (vbyte & 3) * 8;
+    const int vw2 = vw + 1 < a.vwords ? vw + 1 : vw;
+    const int vbits = a.vbits;
     const uint32_t vmask = (1u << a.vbits) - 1u;
     const int vwords = a.vwords;
     const float alpha = kp.alpha;
 
-    float l_part[QP], acc[QP];
+    float l_part[QP], acc[QP][8];
 #pragma unroll
-    for (int qq = 0; qq < QP; ++qq) { l_part[qq] = 0.f; acc[qq] = 0.f; }
+    for (int qq = 0; qq < QP; ++qq) {
+        l_part[qq] = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[qq][u] = 0.f;
+    }
     __syncthreads();   // tables complete
 
     for (int64_t tile = tile0; tile < tile1; ++tile) {
@@ -283,24 +295,28 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 const float mn = sm_m[qq], f = sm_f[qq];
                 const float p = exp2f(s[qq] - (mn == -CUDART_INF_F ? 0.f : mn));   // masked keys: exp2(-inf) = 0
                 l_part[qq] = fmaf(l_part[qq], f, p);
-                acc[qq] *= f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc[qq][u] *= f;
                 pv[qq] = p * vn;
             }
             st_vec<QP>(pbuf + t * QP, pv);
         }
         cp_async_wait_all();
         __syncthreads();
-        {
-            const uint32_t* vrow = vt + (size_t)slice * kSliceKeys * vwords;
-            const float* prow = pbuf + slice * kSliceKeys * QP;
-#pragma unroll 8
-            for (int kk = 0; kk < kSliceKeys; ++kk) {
-                const uint32_t lo = vrow[kk * vwords + vw], hi = vrow[kk * vwords + vw2];
-                const float c = vcb[__funnelshift_r(lo, hi, vsh) & vmask];
-                float pq[QP];
-                ld_vec<QP>(prow + kk * QP, pq);
+#pragma unroll 4
+        for (int it = 0; it < kTile / kIterKeys; ++it) {
+            const int kk = it * kIterKeys + ksub;
+            uint32_t cbits = vt[kk * vwords + vw];
+            if (VSTRADDLE) cbits = __funnelshift_r(cbits, vt[kk * vwords + vw2], vsh);
+            else cbits >>= vsh;
+            float pq[QP];
+            ld_vec<QP>(pbuf + kk * QP, pq);
 #pragma unroll
-                for (int qq = 0; qq < QP; ++qq) acc[qq] = fmaf(pq[qq], c, acc[qq]);
+            for (int u = 0; u < 8; ++u) {
+                const float cv = vcb[cbits & vmask];
+                cbits >>= vbits;
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) acc[qq][u] = fmaf(pq[qq], cv, acc[qq][u]);
             }
         }
     }
@@ -312,18 +328,34 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         if (lane == 0) red[warp * QP + qq] = v;
-        pbuf[(slice * QP + qq) * DR + j] = acc[qq];
     }
-    __syncthreads();
-    if (t < QP * DR) {
-        const int qq = t / DR, jj = t - qq * DR;
-        if (q0 + qq < a.qpg) {
-            float sum = 0.f;
+    // accumulators: lanes c, c + kCT, ... of a warp hold the same coordinates; warps are added through pbuf
+    float res[QP];
 #pragma unroll
-            for (int sl = 0; sl < kSlices; ++sl) sum += pbuf[(sl * QP + qq) * DR + jj];
+    for (int qq = 0; qq < QP; ++qq) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float v = acc[qq][u];
+#pragma unroll
+            for (int o = kCT; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane < kCT) pbuf[warp * DR + lane * 8 + u] = v;
+        }
+        __syncthreads();
+        float sum = 0.f;
+        if (t < DR) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) sum += pbuf[w * DR + t];
+        }
+        res[qq] = sum;
+        __syncthreads();
+    }
+    if (t < DR) {
+#pragma unroll
+        for (int qq = 0; qq < QP; ++qq) {
+            if (q0 + qq >= a.qpg) continue;
             float* dst = a.part + (((size_t)g * a.qpg + q0 + qq) * a.splits + split) * (DR + 2);
-            dst[jj] = sum;
-            if (jj == 0) {
+            dst[t] = res[qq];
+            if (t == 0) {
                 float l = 0.f;
 #pragma unroll
                 for (int w = 0; w < kWarps; ++w) l += red[w * QP + qq];
@@ -361,21 +393,42 @@ __global__ void decode_combine_kernel(const float* __restrict__ part, int splits
 
 int queries_per_pass(int kbits, int qpg) { return qpg == 1 ? 1 : (kbits <= 3 ? 4 : 2); }
 
-int splits_for(int groups, int passes, int64_t keys_per_group) {
+// One block is resident per SM, so blocks run in waves of `sms`.  Among the split counts that fill 1..4 waves,
+// take the one with the fewest tile times per SM (a block's set-up counted as one tile).
+int splits_for(int sms, int groups, int passes, int64_t keys_per_group) {
     const int64_t tiles = (keys_per_group + kTile - 1) / kTile;
     const int64_t gq = (int64_t)groups * passes;
-    int64_t s = (2 * 148 + gq - 1) / gq;   // about two blocks per SM in all, one resident at a time
-    if (s > tiles) s = tiles;
-    if (s > kMaxSplits) s = kMaxSplits;
-    if (s < 1) s = 1;
-    return (int)s;
+    if (tiles <= 1 || gq <= 0) return 1;
+    int64_t best = 1, best_cost = -1;
+    for (int w = 1; w <= 4; ++w) {
+        int64_t s = (int64_t)sms * w / gq;
+        if (s < 1) s = 1;
+        if (s > tiles) s = tiles;
+        if (s > kMaxSplits) s = kMaxSplits;
+        const int64_t waves = (gq * s + sms - 1) / sms;
+        const int64_t cost = waves * ((tiles + s - 1) / s + 1);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return (int)best;
+}
+
+int sm_count(int device) {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return sms > 0 ? sms : 148;
 }
 
 template <int KB, int DR, int QP>
 int launch_partial(const tq_plan* kp, const DecodeArgs& a, int groups, int passes, cudaStream_t st) {
     const size_t sm = decode_smem_floats<KB, DR, QP>() * 4 + (size_t)kTile * a.vwords * 4;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-    decode_partial_kernel<KB, DR, QP><<<dim3((unsigned)a.splits, (unsigned)passes, (unsigned)groups), kThreads, sm, st>>>(kp->dev, a);
+    const dim3 grid((unsigned)a.splits, (unsigned)passes, (unsigned)groups);
+    if (a.vbits == 3) {
+        TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+        decode_partial_kernel<KB, DR, QP, true><<<grid, kThreads, sm, st>>>(kp->dev, a);
+    } else {
+        TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+        decode_partial_kernel<KB, DR, QP, false><<<grid, kThreads, sm, st>>>(kp->dev, a);
+    }
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -398,7 +451,7 @@ bool tq_decode_attention_supported(const tq_plan* kp, const tq_plan* vp) {
 int64_t tq_decode_attention_scratch(const tq_plan* kp, int groups, int qpg, int64_t keys_per_group) {
     const int qp = queries_per_pass(kp->dev.bits, qpg);
     const int passes = (qpg + qp - 1) / qp;
-    const int splits = splits_for(groups, passes, keys_per_group);
+    const int splits = splits_for(sm_count(kp->device), groups, passes, keys_per_group);
     return (int64_t)groups * qpg * splits * (kp->dev.d + 2) * (int64_t)sizeof(float);
 }
 
@@ -416,7 +469,7 @@ int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float
     a.vbits = vp->dev.bits; a.vwords = vp->dev.code_words;
     a.qpg = qpg; a.keys_per_group = keys_per_group; a.group_rows = group_rows; a.length = length;
     a.scale_log2e = scale * 1.4426950408889634f;
-    a.splits = splits_for(groups, passes, keys_per_group);
+    a.splits = splits_for(sm_count(kp->device), groups, passes, keys_per_group);
     a.part = static_cast<float*>(scratch);
     const size_t need = (size_t)groups * qpg * a.splits * (d + 2) * sizeof(float);
     if (!scratch || scratch_bytes < need)

@@ -38,7 +38,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB_PATH
     cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-Xcompiler", "-fPIC", "-shared"]
+           "-Xcompiler", "-fPIC", "-shared", "--threads", "0"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += os.environ.get("TQ_NVCC_FLAGS", "").split()   # extra compiler flags, e.g. -DTQ_PROF for experiments

@@ -230,6 +230,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
             float a1[2][QP], a2[QP];
 #pragma unroll
             for (int qq = 0; qq < QP; ++qq) { a1[0][qq] = 0.f; a1[1][qq] = 0.f; a2[qq] = 0.f; }
+#ifndef TQ_DEC_NOSCORE   // measurement switch: leave the table walk out
 #pragma unroll
             for (int pp = 0; pp < kPairs; ++pp) {
                 const int bit = pp * 2 * KB, wi = bit >> 5, sh = bit & 31;
@@ -248,6 +249,9 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
 #pragma unroll
                 for (int qq = 0; qq < QP; ++qq) a2[qq] += v[qq];
             }
+#else
+            a2[0] = __uint_as_float((cw[0] ^ sw[0]) & 0x3fffffffu) * 1e-30f;
+#endif
 #pragma unroll
             for (int qq = 0; qq < QP; ++qq)
                 s[qq] = nrm * fmaf(alpha * rn, a2[qq], a1[0][qq] + a1[1][qq]) * a.scale_log2e;
@@ -303,6 +307,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
         }
         cp_async_wait_all();
         __syncthreads();
+#ifndef TQ_DEC_NOVALUE   // measurement switch: leave the value phase out
 #pragma unroll 4
         for (int it = 0; it < kTile / kIterKeys; ++it) {
             const int kk = it * kIterKeys + ksub;
@@ -319,6 +324,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 for (int qq = 0; qq < QP; ++qq) acc[qq][u] = fmaf(pq[qq], cv, acc[qq][u]);
             }
         }
+#endif
     }
 
     __syncthreads();   // last value phase over: pbuf and red are free

@@ -49,6 +49,7 @@ struct DecodeArgs {
     const int64_t* length;       // optional device-side number of keys per group (capped by keys_per_group)
     float scale_log2e;           // scale * log2(e): the softmax runs in base 2
     int splits;
+    int vbufs;                   // value tiles in shared memory: 2 = the next tile is copied while this one is used
     float* part;                 // [groups][qpg][splits][d + 2]: accumulator, running max, running sum
 };
 
@@ -83,9 +84,11 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 template <int DR, int QP>
 __host__ __device__ constexpr int pbuf_floats() { return kTile * QP > kWarps * DR ? kTile * QP : kWarps * DR; }
 
+// floats of shared memory in front of the value tiles
 template <int KB, int DR, int QP>
 constexpr size_t decode_smem_floats() {
-    return (size_t)((DR / 2) * (1 << (2 * KB)) + (DR / 8) * 256) * QP + pbuf_floats<DR, QP>() + 3 * QP * DR + kWarps * QP + 8 + 16;
+    return (size_t)((DR / 2) * (1 << (2 * KB)) + (DR / 8) * 256) * QP + pbuf_floats<DR, QP>() + kTile * QP + 3 * QP * DR +
+           kWarps * QP + 8 + 16;
 }
 
 // grid (splits, passes over the queries of a group, groups)
@@ -96,20 +99,26 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     constexpr int kPairs = DR / 2, kEntries = 1 << (2 * KB), kBytes = DR / 8;
     constexpr int kCodeWords = DR * KB / 32, kSignWords = DR / 32;
     constexpr uint32_t kMask = kEntries - 1;
-    constexpr int kCT = DR / 8;                     // threads that share a key in the value phase, 8 coordinates each
-    constexpr int kIterKeys = kThreads / kCT;       // keys the block takes per step of the value phase
+    // scoring: 8 lanes share a key; lane l walks pairs PPL*l .. PPL*l + PPL-1 and sign bytes BPL*l .. of the row
+    constexpr int PPL = kPairs / 8, BPL = kBytes / 8;
+    constexpr int kLaneBits = PPL * 2 * KB;             // bits of the code row one lane looks at (<= 64)
+    constexpr int kSteps = kTile / (kWarps * 4);        // a warp takes 4 keys per step
+    // value phase: 8 coordinates per thread
+    constexpr int kCT = DR / 8;                         // threads that share a key
+    constexpr int kIterKeys = kThreads / kCT;           // keys the block takes per step
     extern __shared__ __align__(16) unsigned char smraw[];
-    float* pair_t = reinterpret_cast<float*>(smraw);   // [kPairs * kEntries][QP]
-    float* byte_t = pair_t + kPairs * kEntries * QP;    // [kBytes * 256][QP]
+    float* pair_t = reinterpret_cast<float*>(smraw);   // [PPL][kEntries][8 lanes][QP]
+    float* byte_t = pair_t + kPairs * kEntries * QP;    // [BPL][256][8 lanes][QP]
     float* pbuf = byte_t + kBytes * 256 * QP;           // [kTile][QP] weight * value norm; at the end [kWarps][DR]
-    float* qin = pbuf + pbuf_floats<DR, QP>();                    // [QP][DR]
+    float* sbuf = pbuf + pbuf_floats<DR, QP>();         // [kTile][QP] scaled scores of the tile
+    float* qin = sbuf + kTile * QP;                     // [QP][DR]
     float* qr = qin + QP * DR;                          // rotated queries
     float* ps = qr + QP * DR;                           // projected queries
     float* red = ps + QP * DR;                          // [kWarps][QP]
     float* sm_m = red + kWarps * QP;                    // [4] running maximum per query
     float* sm_f = sm_m + 4;                             // [4] factor that brings older sums to the new maximum
     float* vcb = sm_f + 4;                              // [16] value codebook
-    uint32_t* vt = reinterpret_cast<uint32_t*>(vcb + 16);   // [kTile][vwords] packed value rows of the tile
+    uint32_t* vt = reinterpret_cast<uint32_t*>(vcb + 16);   // [vbufs][kTile][vwords] packed value rows
 
     const int g = blockIdx.z, q0 = blockIdx.y * QP, split = blockIdx.x;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -150,14 +159,18 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
         ps[i] = sacc;
     }
     __syncthreads();
-    for (int i = t; i < kPairs * kEntries; i += kThreads) {
-        const int pp = i / kEntries, e = i - pp * kEntries;
+    // Tables.  Entry (i, e) of lane l sits at ((i * entries + e) * 8 + l) * QP floats: with QP = 4 the eight
+    // lanes of a key read eight different 16-byte bank groups whatever their codes are.
+    for (int idx = t; idx < kPairs * kEntries; idx += kThreads) {
+        const int l = idx & 7, e = (idx >> 3) & (kEntries - 1), i = idx / (8 * kEntries);
+        const int pp = PPL * l + i;
         const float c0 = __ldg(kp.codebook + (e & ((1 << KB) - 1))), c1 = __ldg(kp.codebook + (e >> KB));
 #pragma unroll
-        for (int qq = 0; qq < QP; ++qq) pair_t[i * QP + qq] = fmaf(c1, qr[qq * DR + 2 * pp + 1], c0 * qr[qq * DR + 2 * pp]);
+        for (int qq = 0; qq < QP; ++qq) pair_t[idx * QP + qq] = fmaf(c1, qr[qq * DR + 2 * pp + 1], c0 * qr[qq * DR + 2 * pp]);
     }
-    for (int i = t; i < kBytes * 256; i += kThreads) {
-        const int pos = i >> 8, v = i & 255, w = pos >> 2, b = pos & 3;
+    for (int idx = t; idx < kBytes * 256; idx += kThreads) {
+        const int l = idx & 7, v = (idx >> 3) & 255, i = idx >> 11;
+        const int pos = BPL * l + i, w = pos >> 2, b = pos & 3;
 #pragma unroll
         for (int qq = 0; qq < QP; ++qq) {
             float acc = 0.f;
@@ -169,7 +182,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 const float x = ps[qq * DR + coord];
                 acc += (v >> bit) & 1 ? x : -x;
             }
-            byte_t[i * QP + qq] = acc;
+            byte_t[idx * QP + qq] = acc;
         }
     }
 
@@ -179,8 +192,16 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     int64_t tile1 = tile0 + tps;
     if (tile1 > tiles_total) tile1 = tiles_total;
 
-    // this thread's share of the value phase: coordinates 8c .. 8c+7 of key `ksub` of every batch of kIterKeys keys;
-    // their codes are the 8 * vbits bits that start at byte vbits * c of the packed row
+    // scoring role: lane l8 of the 8 that share key (warp * 32 + step * 4 + lane / 8) of the tile
+    const int l8 = lane & 7, ksc = warp * 32 + (lane >> 3);
+    constexpr int kLastWord = kCodeWords - 1;
+    const int cw_i = (kLaneBits * l8) >> 5, cw_sh = (kLaneBits * l8) & 31;
+    const int cw_i2 = cw_i + 1 < kLastWord ? cw_i + 1 : kLastWord;
+    const int sw_i = (BPL * l8) >> 2, sw_sh = ((BPL * l8) & 3) * 8;
+    const float* pair_l = pair_t + l8 * QP;
+    const float* byte_l = byte_t + l8 * QP;
+    // value role: coordinates 8c .. 8c+7 of key `ksub` of every batch of kIterKeys keys; their codes are the
+    // 8 * vbits bits that start at byte vbits * c of the packed row
     const int c = t & (kCT - 1), ksub = t / kCT;
     const int vbyte = a.vbits * c, vw = vbyte >> 2, vsh = (vbyte & 3) * 8;
     const int vw2 = vw + 1 < a.vwords ? vw + 1 : vw;
@@ -188,6 +209,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     const uint32_t vmask = (1u << a.vbits) - 1u;
     const int vwords = a.vwords;
     const float alpha = kp.alpha;
+    const int vstride = a.vbufs > 1 ? kTile * vwords : 0;   // words between the two value buffers
 
     float l_part[QP], acc[QP][8];
 #pragma unroll
@@ -196,93 +218,113 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) acc[qq][u] = 0.f;
     }
+    // packed key words and norms of the next tile, fetched one tile ahead
+    uint32_t pw0[kSteps], pw1[kSteps], psg[kSteps];
+    float pnr[kSteps], prn[kSteps], vn = 0.f;
+    auto fetch_keys = [&](int64_t tile) {
+        const int64_t k0 = tile * kTile;
+#pragma unroll
+        for (int st = 0; st < kSteps; ++st) {
+            const int64_t key = k0 + ksc + st * 4;
+            pw0[st] = 0u; pw1[st] = 0u; psg[st] = 0u; pnr[st] = 0.f; prn[st] = 0.f;
+            if (key < n) {
+                const int64_t row = (int64_t)g * a.group_rows + key;
+                const uint32_t* crow = a.kcodes + row * kCodeWords;
+                pw0[st] = __ldg(crow + cw_i);
+                pw1[st] = __ldg(crow + cw_i2);
+                psg[st] = __ldg(a.ksigns + row * kSignWords + sw_i);
+                pnr[st] = __ldg(a.knorms + row);
+                prn[st] = __ldg(a.krnorms + row);
+            }
+        }
+        vn = k0 + t < n ? __ldg(a.vnorms + (int64_t)g * a.group_rows + k0 + t) : 0.f;
+    };
+    // packed value rows of a tile -> shared memory (rows beyond n are not read from memory; what shared memory
+    // holds for them meets a weight of zero)
+    auto fetch_values = [&](int64_t tile, uint32_t* dst) {
+        const int64_t k0 = tile * kTile;
+        int64_t rows = n - k0;
+        if (rows > kTile) rows = kTile;
+        const int nwords = (int)rows * vwords;
+        const uint32_t* src = a.vcodes + ((int64_t)g * a.group_rows + k0) * vwords;
+        if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+            const int n16 = nwords >> 2;
+            for (int i = t; i < n16; i += kThreads) cp_async16(dst + 4 * i, src + 4 * i);
+            for (int i = 4 * n16 + t; i < nwords; i += kThreads) cp_async4(dst + i, src + i);
+        } else {
+            for (int i = t; i < nwords; i += kThreads) cp_async4(dst + i, src + i);
+        }
+        cp_async_commit();
+    };
+    if (tile0 < tile1) {
+        fetch_keys(tile0);
+        if (a.vbufs > 1) fetch_values(tile0, vt);
+    }
     __syncthreads();   // tables complete
 
+    int buf = 0;
     for (int64_t tile = tile0; tile < tile1; ++tile) {
-        const int64_t k0 = tile * kTile, key = k0 + t;
-        const int64_t row = (int64_t)g * a.group_rows + key;
-        float s[QP], vn = 0.f;
-        if (key < n) {
-            uint32_t cw[kCodeWords + 1], sw[kSignWords];
-            const uint32_t* crow = a.kcodes + row * kCodeWords;
-            const uint32_t* srow = a.ksigns + row * kSignWords;
-            if (kCodeWords % 4 == 0) {
+        const int64_t k0 = tile * kTile;
+        const float vn_tile = vn;
+        float mrun[QP];
 #pragma unroll
-                for (int k = 0; k < kCodeWords; k += 4) {
-                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(crow + k));
-                    cw[k] = v.x; cw[k + 1] = v.y; cw[k + 2] = v.z; cw[k + 3] = v.w;
-                }
-            } else {
+        for (int qq = 0; qq < QP; ++qq) mrun[qq] = -CUDART_INF_F;
 #pragma unroll
-                for (int k = 0; k < kCodeWords; k += 2) {
-                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(crow + k));
-                    cw[k] = v.x; cw[k + 1] = v.y;
-                }
-            }
-            cw[kCodeWords] = 0u;
-#pragma unroll
-            for (int k = 0; k < kSignWords; k += 2) {
-                const uint2 v = __ldg(reinterpret_cast<const uint2*>(srow + k));
-                sw[k] = v.x; sw[k + 1] = v.y;
-            }
-            const float nrm = __ldg(a.knorms + row), rn = __ldg(a.krnorms + row);
-            vn = __ldg(a.vnorms + row);
-            float a1[2][QP], a2[QP];
-#pragma unroll
-            for (int qq = 0; qq < QP; ++qq) { a1[0][qq] = 0.f; a1[1][qq] = 0.f; a2[qq] = 0.f; }
+        for (int st = 0; st < kSteps; ++st) {
+            float v[QP];
 #ifndef TQ_DEC_NOSCORE   // measurement switch: leave the table walk out
+            const uint32_t lo = __funnelshift_r(pw0[st], pw1[st], cw_sh);
+            const uint64_t z = kLaneBits > 32 ? ((uint64_t)(pw1[st] >> cw_sh) << 32) | lo : (uint64_t)lo;
+            const uint32_t sg = psg[st] >> sw_sh;
+            float a1[QP], a2[QP];
 #pragma unroll
-            for (int pp = 0; pp < kPairs; ++pp) {
-                const int bit = pp * 2 * KB, wi = bit >> 5, sh = bit & 31;
-                uint32_t e;
-                if (sh + 2 * KB <= 32) e = (cw[wi] >> sh) & kMask;
-                else e = __funnelshift_r(cw[wi], cw[wi + 1], sh) & kMask;
-                float v[QP];
-                ld_vec<QP>(pair_t + (pp * kEntries + e) * QP, v);
+            for (int qq = 0; qq < QP; ++qq) { a1[qq] = 0.f; a2[qq] = 0.f; }
 #pragma unroll
-                for (int qq = 0; qq < QP; ++qq) a1[pp & 1][qq] += v[qq];
+            for (int i = 0; i < PPL; ++i) {
+                const uint32_t e = (uint32_t)(z >> (i * 2 * KB)) & kMask;
+                float x[QP];
+                ld_vec<QP>(pair_l + (i * kEntries + e) * 8 * QP, x);
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) a1[qq] += x[qq];
             }
 #pragma unroll
-            for (int pos = 0; pos < kBytes; ++pos) {
-                float v[QP];
-                ld_vec<QP>(byte_t + (pos * 256 + ((sw[pos >> 2] >> (8 * (pos & 3))) & 255u)) * QP, v);
+            for (int i = 0; i < BPL; ++i) {
+                float x[QP];
+                ld_vec<QP>(byte_l + (i * 256 + ((sg >> (8 * i)) & 255u)) * 8 * QP, x);
 #pragma unroll
-                for (int qq = 0; qq < QP; ++qq) a2[qq] += v[qq];
+                for (int qq = 0; qq < QP; ++qq) a2[qq] += x[qq];
+            }
+            const float ar = alpha * prn[st];
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq) {
+                float s = fmaf(ar, a2[qq], a1[qq]);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                v[qq] = s;
             }
 #else
-            a2[0] = __uint_as_float((cw[0] ^ sw[0]) & 0x3fffffffu) * 1e-30f;
+#pragma unroll
+            for (int qq = 0; qq < QP; ++qq) v[qq] = __uint_as_float((pw0[st] ^ pw1[st] ^ psg[st]) & 0x3fffffffu) * 1e-30f + prn[st];
 #endif
+            const bool valid = k0 + ksc + st * 4 < n;
+            const float sc = pnr[st] * a.scale_log2e;
 #pragma unroll
-            for (int qq = 0; qq < QP; ++qq)
-                s[qq] = nrm * fmaf(alpha * rn, a2[qq], a1[0][qq] + a1[1][qq]) * a.scale_log2e;
-        } else {
-#pragma unroll
-            for (int qq = 0; qq < QP; ++qq) s[qq] = -CUDART_INF_F;
+            for (int qq = 0; qq < QP; ++qq) {
+                v[qq] = valid ? v[qq] * sc : -CUDART_INF_F;
+                mrun[qq] = fmaxf(mrun[qq], v[qq]);
+            }
+            if (l8 == 0) st_vec<QP>(sbuf + (ksc + st * 4) * QP, v);
         }
 #pragma unroll
         for (int qq = 0; qq < QP; ++qq) {
-            float m = s[qq];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float m = mrun[qq];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
             if (lane == 0) red[warp * QP + qq] = m;
         }
-        __syncthreads();   // tile maxima visible; the value phase of the previous tile is over
-        {
-            // packed value rows of this tile -> shared memory (rows beyond n are not read from memory; what
-            // shared memory holds for them meets a weight of zero)
-            int64_t rows = n - k0;
-            if (rows > kTile) rows = kTile;
-            const int nwords = (int)rows * vwords;
-            const uint32_t* src = a.vcodes + ((int64_t)g * a.group_rows + k0) * vwords;   // first row of the tile
-            if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
-                const int n16 = nwords >> 2;
-                for (int i = t; i < n16; i += kThreads) cp_async16(vt + 4 * i, src + 4 * i);
-                for (int i = 4 * n16 + t; i < nwords; i += kThreads) cp_async4(vt + i, src + i);
-            } else {
-                for (int i = t; i < nwords; i += kThreads) cp_async4(vt + i, src + i);
-            }
-            cp_async_commit();
-        }
+        __syncthreads();   // scores and tile maxima visible; the value phase of the previous tile is over
+        if (a.vbufs == 1) fetch_values(tile, vt);
         if (t < QP) {
             float mt = red[t];
 #pragma unroll
@@ -293,7 +335,8 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
         }
         __syncthreads();
         {
-            float pv[QP];
+            float s[QP], pv[QP];
+            ld_vec<QP>(sbuf + t * QP, s);
 #pragma unroll
             for (int qq = 0; qq < QP; ++qq) {
                 const float mn = sm_m[qq], f = sm_f[qq];
@@ -301,18 +344,23 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 l_part[qq] = fmaf(l_part[qq], f, p);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) acc[qq][u] *= f;
-                pv[qq] = p * vn;
+                pv[qq] = p * vn_tile;
             }
             st_vec<QP>(pbuf + t * QP, pv);
         }
         cp_async_wait_all();
         __syncthreads();
+        const uint32_t* vcur = vt + buf * vstride;
+        if (tile + 1 < tile1) {
+            fetch_keys(tile + 1);
+            if (a.vbufs > 1) fetch_values(tile + 1, vt + (buf ^ 1) * vstride);
+        }
 #ifndef TQ_DEC_NOVALUE   // measurement switch: leave the value phase out
 #pragma unroll 4
         for (int it = 0; it < kTile / kIterKeys; ++it) {
             const int kk = it * kIterKeys + ksub;
-            uint32_t cbits = vt[kk * vwords + vw];
-            if (VSTRADDLE) cbits = __funnelshift_r(cbits, vt[kk * vwords + vw2], vsh);
+            uint32_t cbits = vcur[kk * vwords + vw];
+            if (VSTRADDLE) cbits = __funnelshift_r(cbits, vcur[kk * vwords + vw2], vsh);
             else cbits >>= vsh;
             float pq[QP];
             ld_vec<QP>(pbuf + kk * QP, pq);
@@ -325,6 +373,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
             }
         }
 #endif
+        if (a.vbufs > 1) buf ^= 1;
     }
 
     __syncthreads();   // last value phase over: pbuf and red are free
@@ -425,8 +474,10 @@ int sm_count(int device) {
 }
 
 template <int KB, int DR, int QP>
-int launch_partial(const tq_plan* kp, const DecodeArgs& a, int groups, int passes, cudaStream_t st) {
-    const size_t sm = decode_smem_floats<KB, DR, QP>() * 4 + (size_t)kTile * a.vwords * 4;
+int launch_partial(const tq_plan* kp, DecodeArgs a, int groups, int passes, cudaStream_t st) {
+    const size_t fixed = decode_smem_floats<KB, DR, QP>() * 4, vtile = (size_t)kTile * a.vwords * 4;
+    a.vbufs = fixed + 2 * vtile <= 227 * 1024 ? 2 : 1;
+    const size_t sm = fixed + a.vbufs * vtile;
     const dim3 grid((unsigned)a.splits, (unsigned)passes, (unsigned)groups);
     if (a.vbits == 3) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));

@@ -268,6 +268,8 @@ def run_gpu(args):
         enc_m = mse.quantize(keys)
         mse.dequantize(enc_m)
         quant.dequantize(quant.quantize(keys))
+        kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
+        kv.attend(kv_q)
         torch.cuda.synchronize()
         if rank == 0:
             print(json.dumps({"note": "profiling run without host legs", "keys": N_KEYS, "quantize_ms": q_mean,
@@ -278,17 +280,18 @@ def run_gpu(args):
     # ---- the other calls of the path, each timed alone with CUDA events (median of 10), rank 0 only --------
     other = {}
     if rank == 0:
-        def timed(fn, reps=10):
+        def timed(fn, reps=10, inner=1):
             for _ in range(3):
                 fn()
             ms = []
             for _ in range(reps):
                 a_, b_ = ev(), ev()
                 a_.record()
-                fn()
+                for _ in range(inner):
+                    fn()
                 b_.record()
                 torch.cuda.synchronize()
-                ms.append(a_.elapsed_time(b_))
+                ms.append(a_.elapsed_time(b_) / inner)
             return statistics.median(ms)
 
         mse = tg.TurboQuantMSE(D, BITS, seed=SEED)
@@ -312,6 +315,18 @@ def run_gpu(args):
             other[name] = {"ms": ms, "M_per_s": N_KEYS / (ms * 1e-3) / 1e6, "bytes_per_unit": nbytes, "bytes": what,
                            "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_o}
         del enc_m, enc_p
+        # decode attention over a packed key/value cache of the same keys: DECODE_GROUPS sequences x heads,
+        # DECODE_QPG queries each (grouped-query attention), values TurboQuantMSE(d, bits)
+        kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
+        ms = timed(lambda: kv.attend(kv_q), inner=4)
+        nbytes = D * B_MSE // 8 + D // 8 + 8 + D * BITS // 8 + 4
+        gbs = nbytes * N_KEYS / (ms * 1e-3) / 1e9
+        other["decode_attention"] = {
+            "ms": ms, "M_per_s": N_KEYS / (ms * 1e-3) / 1e6, "bytes_per_unit": nbytes,
+            "bytes": "B/key: packed key and packed value in; scores and dequantized values never leave the SM",
+            "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_o,
+            "groups": DECODE_GROUPS, "queries_per_group": DECODE_QPG, "keys_per_group": N_KEYS // DECODE_GROUPS}
+        del kv, kv_q
     # ---- end to end through the public API with host buffers (pinned), rank-local -------------------
     host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
     host_keys.copy_(keys)
@@ -376,6 +391,22 @@ def run_gpu(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+DECODE_GROUPS, DECODE_QPG = 64, 4
+
+
+def decode_cache(tg, torch, quant, mse, keys, dev):
+    """A PackedKVCache of DECODE_GROUPS groups filled with the bench keys (and as many random values), and
+    DECODE_QPG queries per group."""
+    per_group = N_KEYS // DECODE_GROUPS
+    kv = tg.PackedKVCache(quant, mse, DECODE_GROUPS, per_group)
+    gen = torch.Generator(device=dev).manual_seed(20290)
+    values = torch.randn((DECODE_GROUPS, per_group, D), device=dev, generator=gen)
+    kv.append(keys[:DECODE_GROUPS * per_group].view(DECODE_GROUPS, per_group, D), values)
+    del values
+    kv_q = torch.randn((DECODE_GROUPS, DECODE_QPG, D), device=dev, generator=gen)
+    return kv, kv_q
 
 
 def traffic_bytes(read_262144, write_262144):

@@ -325,13 +325,17 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
         }
         __syncthreads();   // scores and tile maxima visible; the value phase of the previous tile is over
         if (a.vbufs == 1) fetch_values(tile, vt);
-        if (t < QP) {
-            float mt = red[t];
+        if (t < ((kWarps * QP + 31) & ~31)) {   // whole warps, so that the shuffles have all their lanes
+            // 16 lanes per query: each takes one warp's maximum, a butterfly leaves the tile maximum in all of them
+            const int qq = t / kWarps, w = t & (kWarps - 1);
+            float mt = qq < QP ? red[w * QP + qq] : -CUDART_INF_F;
 #pragma unroll
-            for (int w = 1; w < kWarps; ++w) mt = fmaxf(mt, red[w * QP + t]);
-            const float mo = sm_m[t], mn = fmaxf(mo, mt);
-            sm_f[t] = mn == -CUDART_INF_F ? 1.f : exp2f(mo - mn);
-            sm_m[t] = mn;
+            for (int o = kWarps / 2; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+            if (w == 0 && qq < QP) {
+                const float mo = sm_m[qq], mn = fmaxf(mo, mt);
+                sm_f[qq] = mn == -CUDART_INF_F ? 1.f : exp2f(mo - mn);
+                sm_m[qq] = mn;
+            }
         }
         __syncthreads();
         {

@@ -143,3 +143,29 @@ def test_no_cpu_fallback_without_a_device(lib_built):
     quant = tg.TurboQuantMSE(8, 2, seed=1, grid_size=513, max_iter=8)
     with pytest.raises(TurboQuantNativeError):
         quant.quantize(np.zeros((3, 8), np.float32))
+
+
+@pytest.mark.parametrize("name", ["d128_b4", "d64_b2", "d128_b1"])
+def test_oracle_decode_attention_on_reference_scores_and_values(name):
+    """decode_attention = softmax(scale * scores) @ values.  The scores and the dequantized values inside are the
+    reference's own recorded outputs (fixtures); the softmax and the weighted sum around them are recomputed
+    here in float64 from the formula of Tensor.softmax / scaled_dot_product_attention."""
+    case = next(c for c in CASES if c["name"] == name)
+    g = golden_case(name)
+    if g["x"].ndim != 2:
+        pytest.skip("flat cases only")
+    d, bits = case["dimension"], case["bits"]
+    mp = orc.mse_params(d, bits, rotation=g["mse_rotation"], codebook=g["mse_codebook"])
+    inner = orc.mse_params(d, max(bits - 1, 1), rotation=g["prod_rotation"], codebook=g["prod_codebook"])
+    pp = orc.ProdParams(d, bits, inner, g["prod_projection"])
+    finite = np.isfinite(g["mse_recon"]).all(axis=1) & np.isfinite(g["scores_broadcast"]).all(axis=0)
+    rows = np.nonzero(finite)[0]
+    kenc = tuple(g[k][rows] for k in ("prod_indices", "prod_qjl", "prod_residual_norms", "prod_norms"))
+    for scale in (None, 0.5):
+        got = orc.decode_attention(pp, mp, g["queries"], kenc, g["mse_indices"][rows], g["mse_norms"][rows], scale)
+        s = g["scores_broadcast"][:, rows].astype(np.float64) * np.float64(np.float32(scale or d ** -0.5))
+        w = np.exp(s - s.max(axis=1, keepdims=True))
+        w /= w.sum(axis=1, keepdims=True)
+        want = w @ g["mse_recon"][rows].astype(np.float64)
+        assert got.dtype == np.float32 and got.shape == (g["queries"].shape[0], d)
+        np.testing.assert_allclose(got, want, rtol=0, atol=2e-6 * np.abs(want).max() + 1e-7)

@@ -419,6 +419,97 @@ def traffic_bytes(read_262144, write_262144):
     return (read_262144 + write_262144) * N_KEYS / 262144.0
 
 
+def run_retrieval(args):
+    """Sharded retrieval at box scale (the largest configuration of the reference's benchmark list): `--total-keys`
+    TurboQuantProd(128, 4) keys split evenly over the ranks, 64 queries, per-shard top-100 merged over NCCL into a
+    global top-100 per query.  Keys are generated on the device per chunk of 2^20 (torch Philox, seed
+    20265 * 2^32 + chunk), quantized and dropped; only the packed encoding stays (72 B/key).  Prints one JSON line
+    with the quantize and search rates and the outcome of size-independent checks: descending scores, unique
+    in-range indices, and agreement with an independent pass over the chunk that holds query 0's best key."""
+    import torch
+    import torch.distributed as dist
+    import project_tensor_b200 as tg
+    from project_tensor_b200.sharded import ShardedKeyIndex, shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    chunk, n_total, n_q, k = 1 << 20, args.total_keys, 64, TOPK
+    if n_total % (chunk * world):
+        raise SystemExit("--total-keys must be a multiple of 2^20 keys per rank")
+    quant = tg.TurboQuantProd(D, BITS, seed=SEED)
+    index = ShardedKeyIndex(quant, n_total)
+    queries = torch.from_numpy(np.random.default_rng(20275).standard_normal((n_q, D)).astype(np.float32)).to(dev)
+
+    def make_chunk(c):
+        gen = torch.Generator(device=dev).manual_seed(20265 * 2 ** 32 + c)
+        return torch.randn((chunk, D), generator=gen, device=dev, dtype=torch.float32)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    start, stop = shard_range(n_total, rank, world)
+    pairs = []
+    for c in range(start // chunk, stop // chunk):
+        x = make_chunk(c)
+        e0, e1 = ev(), ev()
+        e0.record()
+        index.add(x)
+        e1.record()
+        pairs.append((e0, e1))
+        del x
+    torch.cuda.synchronize()
+    add_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    for _ in range(max(args.warmup, 1)):
+        top_s, top_i = index.search(queries, k)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = min(args.steps, 5)
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        top_s, top_i = index.search(queries, k)
+    e1.record()
+    torch.cuda.synchronize()
+    times = torch.tensor([add_ms, e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    add_ms, search_ms = (float(v) for v in times.tolist())
+
+    # ---- checks that do not depend on the size --------------------------------------------------
+    checks = {"descending": bool((top_s[:, :-1] >= top_s[:, 1:]).all()),
+              "indices_in_range": bool(((top_i >= 0) & (top_i < n_total)).all()),
+              "indices_unique": all(len(set(row)) == k for row in top_i.tolist())}
+    c_best = int(top_i[0, 0].item()) // chunk
+    enc = quant.quantize(make_chunk(c_best))
+    part = quant.attention_scores(queries, enc)                       # 64 x 2^20 scores of that chunk, computed alone
+    scale = float(top_s.abs().max())
+    inside = (top_i // chunk) == c_best
+    got = top_s[inside]
+    want = part[torch.nonzero(inside)[:, 0], (top_i[inside] - c_best * chunk)]
+    checks["chunk_scores_agree"] = bool((got - want).abs().max() <= 1e-4 * scale) if got.numel() else True
+    # nothing in the chunk beats the global 100th score without being in the global list
+    kth = top_s[:, -1:].clone()
+    beats = (part > kth + 1e-4 * scale).sum(dim=1)
+    checks["chunk_has_no_missed_key"] = bool((beats <= inside.sum(dim=1)).all())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sharded retrieval: quantize Mvec/s and top-%d search Gkeys/s" % k, "n_gpus": world,
+            "config": {"workload": f"TurboQuantProd d={D} bits={BITS}: {n_total} keys over {world} GPU(s), {n_q} queries, "
+                                   f"per-shard top-{k} + NCCL all-gather + merge", "keys_per_gpu": n_total // world},
+            "quantize_Mvec_per_s": n_total / (add_ms * 1e-3) / 1e6, "quantize_ms_total": add_ms,
+            "search_ms": search_ms, "search_Gkeys_per_s": n_total / (search_ms * 1e-3) / 1e9,
+            "search_Gpairs_per_s": n_total * n_q / (search_ms * 1e-3) / 1e9,
+            "packed_GB_per_gpu": (n_total // world) * 72 / 1e9, "data": "synthetic", "checks": checks}))
+    if world > 1:
+        dist.destroy_process_group()
+    if not all(checks.values()):
+        raise SystemExit("retrieval checks failed: %r" % (checks,))
+
+
 def main():
     global N_KEYS
     ap = argparse.ArgumentParser()
@@ -430,8 +521,13 @@ def main():
                     help="keys per GPU; the default is the benchmark's workload, smaller values are for profiler captures only")
     ap.add_argument("--skip-host-legs", action="store_true",
                     help="leave out the end-to-end and CPU-baseline legs (profiler captures)")
+    ap.add_argument("--workload", default="headline", choices=["headline", "retrieval"],
+                    help="retrieval: the sharded top-100 search over --total-keys keys (not the headline line)")
+    ap.add_argument("--total-keys", type=int, default=134217728, help="keys over all GPUs for --workload retrieval")
     args = ap.parse_args()
     N_KEYS = args.keys
+    if args.workload == "retrieval" and args.impl == "b200":
+        return run_retrieval(args)
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
     if args.impl == "reference":

@@ -107,17 +107,25 @@ class ShardedKeyIndex:
         self.filled = 0
 
     def add(self, keys) -> None:
-        from .turboquant import packed_buffers
-        enc = self.quantizer.quantize(keys)
-        bufs = packed_buffers(enc)
-        m = bufs["norms"].shape[0]
+        """Quantize ``keys`` (m, d) straight into the next m rows of this rank's packed buffers."""
+        from .turboquant import _stage
+        staged = _stage(keys, self.quantizer.dimension, device=self.device)
+        m = int(staged.tensor.shape[0])
         if self.filled + m > self.stop - self.start:
             raise ValueError("more keys than this rank's shard holds")
         s = slice(self.filled, self.filled + m)
-        self.codes[s] = bufs["codes"]
-        self.signs[s] = bufs["signs"]
-        self.norms[s] = bufs["norms"]
-        self.residual_norms[s] = bufs["residual_norms"]
+        out = {"codes": self.codes[s], "signs": self.signs[s], "norms": self.norms[s],
+               "residual_norms": self.residual_norms[s]}
+        if all(t.data_ptr() % 16 == 0 for t in out.values()):
+            self.quantizer.mse._quantize_staged(staged, self.quantizer._plans, True, out=out)
+        else:
+            # a chunk that starts off a 16-byte boundary of the norm arrays (row count so far not a multiple
+            # of 4): the kernels want aligned outputs, so quantize into fresh buffers and copy
+            pk = self.quantizer.mse._quantize_staged(staged, self.quantizer._plans, True)
+            out["codes"].copy_(pk.codes)
+            out["signs"].copy_(pk.signs)
+            out["norms"].copy_(pk.norms)
+            out["residual_norms"].copy_(pk.residual_norms)
         self.filled += m
 
     def encoding(self):

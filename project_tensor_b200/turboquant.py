@@ -478,7 +478,9 @@ class TurboQuantMSE:
         self._plans.set_path({"auto": _native.TQ_PATH_AUTO, "exact": _native.TQ_PATH_EXACT,
                               "tensor": _native.TQ_PATH_TENSOR}[path])
 
-    def _quantize_staged(self, staged: _Staged, plans: _PlanSet, prod: bool) -> _Packed:
+    def _quantize_staged(self, staged: _Staged, plans: _PlanSet, prod: bool, out: Optional[Dict[str, Any]] = None) -> _Packed:
+        """``out``: contiguous device tensors {codes, norms[, signs, residual_norms]} of n rows to write into
+        (e.g. slices of a preallocated index) instead of fresh ones."""
         torch = _torch()
         lib = _native.load()
         x, device = staged.tensor, staged.device
@@ -486,14 +488,14 @@ class TurboQuantMSE:
         code_bytes, sign_bytes = plans.row_bytes()
         handle = plans.handle(device)
         with torch.cuda.device(device):
-            codes = torch.empty((n, code_bytes), dtype=torch.uint8, device=device)
-            norms = torch.empty((n,), dtype=torch.float32, device=device)
+            codes = out["codes"] if out else torch.empty((n, code_bytes), dtype=torch.uint8, device=device)
+            norms = out["norms"] if out else torch.empty((n,), dtype=torch.float32, device=device)
             scratch = torch.empty((max(int(lib.tq_quantize_scratch_bytes(handle, n)), 16),),
                                   dtype=torch.uint8, device=device)
             st = _stream_ptr(device)
             if prod:
-                signs = torch.empty((n, sign_bytes), dtype=torch.uint8, device=device)
-                rnorms = torch.empty((n,), dtype=torch.float32, device=device)
+                signs = out["signs"] if out else torch.empty((n, sign_bytes), dtype=torch.uint8, device=device)
+                rnorms = out["residual_norms"] if out else torch.empty((n,), dtype=torch.float32, device=device)
                 _native.check(lib.tq_prod_quantize(handle, _ptr(x), n, _ptr(codes), _ptr(signs), _ptr(rnorms),
                                                    _ptr(norms), _ptr(scratch), scratch.numel(), st))
             else:

@@ -95,7 +95,7 @@ def make_inputs(name, d, lead, recipe):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a Project-Tensor checkout")
     args = ap.parse_args()
     rq = load_reference_quant(args.reference)
     manifest = {"numpy": np.__version__, "cases": [], "codebooks": []}

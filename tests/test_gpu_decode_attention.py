@@ -143,3 +143,43 @@ def test_empty_cache_gives_zeros_and_argument_checks():
                                  kc.residual_norms.data_ptr(), kc.norms.data_ptr(), cache.value_codes.data_ptr(),
                                  cache.value_norms.data_ptr(), 4, 8, None, 0.0, out.data_ptr(), tiny.data_ptr(), 16, 0)
     assert rc == -4   # TQ_ERR_SCRATCH_TOO_SMALL
+
+
+def test_decode_step_replayed_from_a_cuda_graph():
+    """One captured decode step -- append the new key and value of every group, attend with the length read on
+    the device -- replayed while the cache grows, against the same steps run eagerly on a second cache."""
+    torch = _torch()
+    d, groups, qpg, cap, steps = 128, 8, 4, 640, 6
+    kq, vq = tg.TurboQuantProd(d, 4, seed=2026), tg.TurboQuantMSE(d, 4, seed=77)
+    prefill_k, prefill_v = _randn((groups, 500, d), 61), _randn((groups, 500, d), 62)
+    new_k, new_v = _randn((groups, steps, d), 63), _randn((groups, steps, d), 64)
+    queries = _randn((steps, groups, qpg, d), 65)
+    eager, graphed = PackedKVCache(kq, vq, groups, cap), PackedKVCache(kq, vq, groups, cap)
+    for cache in (eager, graphed):
+        cache.append(prefill_k, prefill_v)
+    k_in, v_in, q_in = torch.zeros(groups, 1, d, device="cuda"), torch.zeros(groups, 1, d, device="cuda"), \
+        torch.zeros(groups, qpg, d, device="cuda")
+    # warm up outside the capture on a scratch cache (function attributes, plans), then capture one step
+    scratch = PackedKVCache(kq, vq, groups, cap)
+    scratch.append(k_in, v_in)
+    scratch.attend(q_in, use_device_length=True)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            graphed.append(k_in, v_in)
+            out = graphed.attend(q_in, use_device_length=True)
+    torch.cuda.current_stream().wait_stream(stream)
+    assert graphed.sync_length() == 500          # capturing executed nothing
+    for t in range(steps):
+        k_in.copy_(new_k[:, t:t + 1])
+        v_in.copy_(new_v[:, t:t + 1])
+        q_in.copy_(queries[t])
+        graph.replay()
+        eager.append(new_k[:, t], new_v[:, t])
+        want = eager.attend(queries[t])
+        torch.cuda.synchronize()
+        assert float((out - want).abs().max()) <= 1e-6 * float(want.abs().max()), t
+    assert graphed.sync_length() == 500 + steps

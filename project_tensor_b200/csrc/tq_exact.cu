@@ -107,14 +107,16 @@ __host__ __device__ inline size_t rows_smem_bytes(int d) {
     return (size_t)(2 * d * kRB + kRB * dp + kRB) * sizeof(float) + (size_t)kRB * dp + 64;
 }
 
-template <bool PROD>
+// MAPPED: results go to the rows the append map names (a cache) instead of the input's own row numbers; a
+// separate instantiation, so that the plain quantizer carries none of it.
+template <bool PROD, bool MAPPED>
 __global__ void __launch_bounds__(1024)
 exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                       uint32_t* __restrict__ signs, float* __restrict__ rnorms, float* __restrict__ norms,
                       TqRecheck lists, unsigned long long* redo_counter, TqRowMap map) {
     extern __shared__ float smem[];
     const int d = p.d, dp = (d + 31) & ~31;
-    const int64_t len0 = map.tokens > 0 ? *map.length : 0;
+    const int64_t len0 = MAPPED ? *map.length : 0;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
     RowsSmem sm;
     sm.vt = smem;
@@ -131,19 +133,23 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
         atomicAdd(redo_counter, (unsigned long long)limit);
 
     for (int64_t g0 = (int64_t)blockIdx.x * kRB; g0 < limit; g0 += (int64_t)gridDim.x * kRB) {
-        int64_t rows[kRB], orow[kRB];   // input row and the row its results go to (-1: none)
+        int64_t rows[kRB];                    // input rows (-1: none)
+        int64_t mapped[MAPPED ? kRB : 1];     // MAPPED: the rows their results go to
 #pragma unroll
         for (int r = 0; r < kRB; ++r) {
             const int64_t idx = g0 + r;
             int64_t row = idx < limit ? (listed ? (int64_t)lists.row_entries[idx] : idx) : -1;
             if (row >= n) row = -1;
             rows[r] = row;
-            orow[r] = row;
-            if (map.tokens > 0 && row >= 0) {
-                const int64_t grp = row / map.tokens, pos = len0 + (row - grp * map.tokens);
-                orow[r] = pos < map.capacity ? grp * map.capacity + pos : -1;   // a full cache takes no more rows
+            if (MAPPED) {
+                mapped[r] = row;
+                if (row >= 0) {
+                    const int64_t grp = row / map.tokens, pos = len0 + (row - grp * map.tokens);
+                    mapped[r] = pos < map.capacity ? grp * map.capacity + pos : -1;   // a full cache takes no more rows
+                }
             }
         }
+        const int64_t* orow = MAPPED ? mapped : rows;
         __syncthreads();  // previous group fully written out
 #pragma unroll
         for (int r = 0; r < kRB; ++r) {
@@ -456,13 +462,20 @@ int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_
     // the listed pass does not know its size on the host: a fixed grid strides over the list
     const int grid = lists_in ? 148 * 4 : grid_for(n, kRB);
     const int threads = (p->dev.d + 31) & ~31;
+#define TQ_LAUNCH_EXACT(P, M)                                                                                              \
+    do {                                                                                                                  \
+        TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<P, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
+        exact_quantize_kernel<P, M><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map); \
+    } while (0)
+    const bool mapped = map.tokens > 0;
     if (prod) {
-        TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map);
+        if (mapped) TQ_LAUNCH_EXACT(true, true);
+        else TQ_LAUNCH_EXACT(true, false);
     } else {
-        TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_quantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map);
+        if (mapped) TQ_LAUNCH_EXACT(false, true);
+        else TQ_LAUNCH_EXACT(false, false);
     }
+#undef TQ_LAUNCH_EXACT
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

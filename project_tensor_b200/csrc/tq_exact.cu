@@ -107,10 +107,46 @@ __host__ __device__ inline size_t rows_smem_bytes(int d) {
     return (size_t)(2 * d * kRB + kRB * dp + kRB) * sizeof(float) + (size_t)kRB * dp + 64;
 }
 
+// acc[r] = sum_k vt[k][r] * M[k * d + tj] for the kRB rows of a block: one FMA per k, k ascending.  The U matrix
+// elements of a batch are fetched before the first of them is used -- written out as two loops because the
+// chains wait on L2 latency, and whether the compiler hoists the loads of a single loop by itself changed the
+// kernel's time by a factor of two from one build to the next.
+template <int U>
+__device__ __forceinline__ void rows_chain(const float* __restrict__ M, int d, int tj, const float* vt, float (&acc)[kRB]) {
+#pragma unroll
+    for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
+    int k0 = 0;
+    for (; k0 + U <= d; k0 += U) {
+        float m[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) m[u] = __ldg(M + (size_t)(k0 + u) * d + tj);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float4 a = *reinterpret_cast<const float4*>(vt + (k0 + u) * kRB);
+            const float4 b = *reinterpret_cast<const float4*>(vt + (k0 + u) * kRB + 4);
+            acc[0] = __fmaf_rn(a.x, m[u], acc[0]); acc[1] = __fmaf_rn(a.y, m[u], acc[1]);
+            acc[2] = __fmaf_rn(a.z, m[u], acc[2]); acc[3] = __fmaf_rn(a.w, m[u], acc[3]);
+            acc[4] = __fmaf_rn(b.x, m[u], acc[4]); acc[5] = __fmaf_rn(b.y, m[u], acc[5]);
+            acc[6] = __fmaf_rn(b.z, m[u], acc[6]); acc[7] = __fmaf_rn(b.w, m[u], acc[7]);
+        }
+    }
+    for (; k0 < d; ++k0) {
+        const float m = __ldg(M + (size_t)k0 * d + tj);
+        const float4 a = *reinterpret_cast<const float4*>(vt + k0 * kRB);
+        const float4 b = *reinterpret_cast<const float4*>(vt + k0 * kRB + 4);
+        acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
+        acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
+        acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
+        acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
+    }
+}
+
 // MAPPED: results go to the rows the append map names (a cache) instead of the input's own row numbers; a
 // separate instantiation, so that the plain quantizer carries none of it.
-template <bool PROD, bool MAPPED>
-__global__ void __launch_bounds__(1024)
+// MAXT: the largest block the instantiation is launched with (d rounded up to 32).  The small one may use up to
+// 255 registers and keeps 32 matrix elements in flight per thread (rows_chain).
+template <bool PROD, bool MAPPED, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                       uint32_t* __restrict__ signs, float* __restrict__ rnorms, float* __restrict__ norms,
                       TqRecheck lists, unsigned long long* redo_counter, TqRowMap map) {
@@ -173,19 +209,9 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
         __syncthreads();
 
         float acc[kRB];
+        constexpr int kU = MAXT <= 256 ? 32 : 16;   // matrix elements in flight per thread
         // rotated[j] = sum_k unit[k] * R[j][k]
-#pragma unroll
-        for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
-#pragma unroll 16
-        for (int k = 0; k < d; ++k) {
-            const float m = __ldg(p.Rt + (size_t)k * d + tj);
-            const float4 a = *reinterpret_cast<const float4*>(sm.vt + k * kRB);
-            const float4 b = *reinterpret_cast<const float4*>(sm.vt + k * kRB + 4);
-            acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
-            acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
-            acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
-            acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
-        }
+        rows_chain<kU>(p.Rt, d, tj, sm.vt, acc);
         if (t < d) {
 #pragma unroll
             for (int r = 0; r < kRB; ++r) {
@@ -203,18 +229,7 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
 
         if (PROD) {
             // recon[j] = sum_k centroid[k] * R[k][j];  residual = unit - recon
-#pragma unroll
-            for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
-#pragma unroll 16
-            for (int k = 0; k < d; ++k) {
-                const float m = __ldg(p.R + (size_t)k * d + tj);
-                const float4 a = *reinterpret_cast<const float4*>(sm.ct + k * kRB);
-                const float4 b = *reinterpret_cast<const float4*>(sm.ct + k * kRB + 4);
-                acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
-                acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
-                acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
-                acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
-            }
+            rows_chain<kU>(p.R, d, tj, sm.ct, acc);
             __syncthreads();  // nobody reads unit[k] of other coordinates any more
 #pragma unroll
             for (int r = 0; r < kRB; ++r) {
@@ -228,18 +243,7 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
                 if (lane == 0 && orow[r] >= 0) rnorms[orow[r]] = rn;
             }
             // projected[j] = sum_k residual[k] * S[j][k]
-#pragma unroll
-            for (int r = 0; r < kRB; ++r) acc[r] = 0.f;
-#pragma unroll 16
-            for (int k = 0; k < d; ++k) {
-                const float m = __ldg(p.St + (size_t)k * d + tj);
-                const float4 a = *reinterpret_cast<const float4*>(sm.vt + k * kRB);
-                const float4 b = *reinterpret_cast<const float4*>(sm.vt + k * kRB + 4);
-                acc[0] = __fmaf_rn(a.x, m, acc[0]); acc[1] = __fmaf_rn(a.y, m, acc[1]);
-                acc[2] = __fmaf_rn(a.z, m, acc[2]); acc[3] = __fmaf_rn(a.w, m, acc[3]);
-                acc[4] = __fmaf_rn(b.x, m, acc[4]); acc[5] = __fmaf_rn(b.y, m, acc[5]);
-                acc[6] = __fmaf_rn(b.z, m, acc[6]); acc[7] = __fmaf_rn(b.w, m, acc[7]);
-            }
+            rows_chain<kU>(p.St, d, tj, sm.vt, acc);
 #pragma unroll
             for (int r = 0; r < kRB; ++r) {
                 const uint32_t word = __ballot_sync(0xffffffffu, t < d && acc[r] >= 0.f);
@@ -462,19 +466,25 @@ int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_
     // the listed pass does not know its size on the host: a fixed grid strides over the list
     const int grid = lists_in ? 148 * 4 : grid_for(n, kRB);
     const int threads = (p->dev.d + 31) & ~31;
-#define TQ_LAUNCH_EXACT(P, M)                                                                                              \
+#define TQ_LAUNCH_EXACT(P, M, T)                                                                                           \
     do {                                                                                                                  \
-        TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<P, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
-        exact_quantize_kernel<P, M><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map); \
+        TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<P, M, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
+        exact_quantize_kernel<P, M, T><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map); \
+    } while (0)
+#define TQ_LAUNCH_EXACT_T(P, M)                  \
+    do {                                         \
+        if (threads <= 256) TQ_LAUNCH_EXACT(P, M, 256); \
+        else TQ_LAUNCH_EXACT(P, M, 1024);        \
     } while (0)
     const bool mapped = map.tokens > 0;
     if (prod) {
-        if (mapped) TQ_LAUNCH_EXACT(true, true);
-        else TQ_LAUNCH_EXACT(true, false);
+        if (mapped) TQ_LAUNCH_EXACT_T(true, true);
+        else TQ_LAUNCH_EXACT_T(true, false);
     } else {
-        if (mapped) TQ_LAUNCH_EXACT(false, true);
-        else TQ_LAUNCH_EXACT(false, false);
+        if (mapped) TQ_LAUNCH_EXACT_T(false, true);
+        else TQ_LAUNCH_EXACT_T(false, false);
     }
+#undef TQ_LAUNCH_EXACT_T
 #undef TQ_LAUNCH_EXACT
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;

@@ -445,7 +445,13 @@ __global__ void decode_combine_kernel(const float* __restrict__ part, int splits
     __syncthreads();
     if (t < d) {
         float o = 0.f;
-        for (int k = 0; k < d; ++k) o = fmaf(avec[k], __ldg(Rv + (size_t)k * d + t), o);
+        for (int k0 = 0; k0 < d; k0 += 32) {   // d is 64 or 128; 32 matrix elements in flight
+            float m[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) m[u] = __ldg(Rv + (size_t)(k0 + u) * d + t);
+#pragma unroll
+            for (int u = 0; u < 32; ++u) o = fmaf(avec[k0 + u], m[u], o);
+        }
         out[(size_t)blockIdx.x * d + t] = o;
     }
 }

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 SRC_DIR = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libtq_sm100.so")
-SOURCES = ["tq_api.cu", "tq_exact.cu", "tq_score.cu", "tq_score_tc.cu", "tq_pack.cu", "tq_tensor.cu", "tq_dequant_tc.cu", "tq_score_few.cu", "tq_decode_attn.cu"]
+SOURCES = ["tq_api.cu", "tq_exact.cu", "tq_score.cu", "tq_score_tc.cu", "tq_pack.cu", "tq_tensor.cu", "tq_dequant_tc.cu", "tq_score_few.cu", "tq_decode_attn.cu", "tq_score_lut.cu"]
 HEADERS = [os.path.join(SRC_DIR, "tq_common.cuh"), os.path.join(SRC_DIR, "tq_ptx.cuh"),
            os.path.join(PKG_DIR, "..", "include", "tq_b200.h")]
 

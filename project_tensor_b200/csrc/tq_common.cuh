@@ -128,6 +128,12 @@ int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, c
                         const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st,
                         int64_t group_rows = 0);
 
+// Lookup-table scoring kernel for three or four queries per group (d = 128 / 64, 1..3 code bits), tq_score_lut.cu.
+bool tq_score_lut_supported(const tq_plan* p, int qpg);
+int tq_launch_score_lut(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
+                        const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st,
+                        int64_t group_rows = 0);
+
 // Scoring kernels.  `group_rows`: rows between the first keys of consecutive groups in the key arrays (0 = the
 // groups follow one another, keys_per_group rows each); top-k indices count rows of the arrays.
 int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes,

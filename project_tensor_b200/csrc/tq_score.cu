@@ -300,6 +300,9 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
     // One or two queries per group and the matrix wanted (the reference's own call): the streaming kernel.
     if (p->path == TQ_PATH_AUTO && topk == 0 && scores && tq_score_few_supported(p, qpg) && keys_per_group > 0 && groups > 0)
         return tq_launch_score_few(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st, group_rows);
+    // Three or four queries per group (grouped-query decode): the lane-interleaved lookup-table kernel.
+    if (p->path == TQ_PATH_AUTO && topk == 0 && scores && tq_score_lut_supported(p, qpg) && keys_per_group > 0 && groups > 0)
+        return tq_launch_score_lut(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st, group_rows);
     // d = 64 has 8-byte sign rows (and 8- or 24-byte code rows): a group must start on a 16-byte boundary
     // for the bulk copies of the tensor-core kernel
     const bool aligned_groups = p->dev.d == 128 || groups == 1 || group_rows % 2 == 0;

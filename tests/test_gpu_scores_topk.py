@@ -171,6 +171,41 @@ def test_one_and_two_queries_on_every_path(tg, d, bits):
     assert parity.max_score_err(got[None, :], ref[None, :], np.linalg.norm(q1), want[3][None, :], d) <= REL_SCORE
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("qpg", [3, 4])
+def test_three_and_four_queries_per_group_on_every_path(tg, bits, qpg):
+    """Grouped-query decode scoring -- 3 or 4 queries per group of keys, d = 128, up to 3 code bits -- runs on the
+    lane-interleaved lookup-table kernel by default: it must agree with the exact and the tensor-core kernels
+    within the score bound (ragged group length, several groups, a single group), and with the oracle."""
+    groups, kpg, d = 5, 4_099, 128
+    n = groups * kpg
+    rng = np.random.default_rng(20269 + bits + qpg)
+    x = rng.standard_normal((n, d)).astype(np.float32) * rng.uniform(0.2, 5.0, (n, 1)).astype(np.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    pp = _oracle_params(prod)
+    want = orc.prod_quantize(pp, x)
+    enc = tg.TurboQuantProdEncoding(indices=want[0], qjl=want[1], residual_norms=want[2], norms=want[3], prefix_shape=(n,))
+    for nq, grp in ((qpg * groups, groups), (qpg, 1)):
+        q = rng.standard_normal((nq, d)).astype(np.float32)
+        res = {}
+        for path in ("exact", "tensor", "auto"):
+            prod.set_kernel_path(path)
+            res[path] = np.asarray(prod.attention_scores(q, enc, groups=grp))
+        prod.set_kernel_path("auto")
+        per = n // grp
+        assert res["auto"].shape == (nq, per)
+        qn = np.linalg.norm(q, axis=1)[:, None]
+        kn = want[3].reshape(grp, per).repeat(nq // grp, axis=0)
+        for path in ("tensor", "auto"):
+            assert parity.max_score_err(res[path], res["exact"], qn, kn, d) <= REL_SCORE, (path, nq, grp)
+        # the oracle, one broadcast call per query as the reference's users do, on the first and the last query
+        for a in (0, nq - 1):
+            g = a // (nq // grp)
+            rows = slice(g * per, (g + 1) * per)
+            ref = orc.prod_attention_score(pp, q[a], *(w[rows] for w in want[:4]), (per,))
+            assert parity.max_score_err(res["auto"][a][None, :], ref[None, :], qn[a], want[3][rows][None, :], d) <= REL_SCORE
+
+
 @pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("bits", [2, 4])
 @pytest.mark.parametrize("n", [1, 129, 20_003])

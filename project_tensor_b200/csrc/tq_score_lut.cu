@@ -9,8 +9,8 @@
 // PPL*l .. PPL*l+PPL-1 and sign bytes BPL*l .., and entry (i, e) of lane l sits at ((i * entries + e) * 8 + l) * 4
 // floats.  The eight lanes of a key therefore read eight different 16-byte bank groups whatever their codes are
 // (one thread per key, as in the one-query kernel, loses 2.7x to bank conflicts with 16-byte entries).  The
-// partial sums of the eight lanes meet in a three-step butterfly.  Measured against the tensor-core kernel (whose
-// cost does not shrink below 16 queries): 179 vs 191 us for 64 groups x 4 queries x 32,768 keys at d = 128.
+// partial sums of the eight lanes meet in a reduce-scatter of four shuffles.  Measured against the tensor-core kernel (whose
+// cost does not shrink below 16 queries): 156 vs 191 us for 64 groups x 4 queries x 32,768 keys at d = 128.
 #include "tq_common.cuh"
 
 #include <stdint.h>
@@ -39,6 +39,7 @@ score_lut_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
     constexpr int PPL = kPairs / 8, BPL = kBytes / 8;
     constexpr int kLaneBits = PPL * 2 * KB;             // bits of the code row one lane looks at (<= 48)
     constexpr int kSteps = kTile / (kWarps * 4);        // a warp takes 4 keys per step
+    constexpr bool kNeedW1 = 32 % kLaneBits != 0;       // a lane's bits can lie across two words
     extern __shared__ __align__(16) float smf[];
     float* pair_t = smf;                                // [PPL][kEntries][8 lanes][QP]
     float* byte_t = pair_t + kPairs * kEntries * QP;    // [BPL][256][8 lanes][QP]
@@ -107,6 +108,8 @@ score_lut_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
     const int cw_i = (kLaneBits * l8) >> 5, cw_sh = (kLaneBits * l8) & 31;
     const int cw_i2 = cw_i + 1 < kLastWord ? cw_i + 1 : kLastWord;
     const int sw_i = (BPL * l8) >> 2, sw_sh = ((BPL * l8) & 3) * 8;
+    const bool b0 = l8 & 1, b1 = l8 & 2;
+    const int qsel = 2 * (l8 & 1) + ((l8 >> 1) & 1);   // the query whose sum this lane holds after the exchange
     const float* pair_l = pair_t + l8 * QP;
     const float* byte_l = byte_t + l8 * QP;
     const float alpha = p.alpha;
@@ -122,7 +125,7 @@ score_lut_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
             const int64_t row = gbase + key;
             const uint32_t* crow = codes + row * kCodeWords;
             pw0[st] = __ldg(crow + cw_i);
-            pw1[st] = __ldg(crow + cw_i2);
+            if (kNeedW1) pw1[st] = __ldg(crow + cw_i2);
             psg[st] = __ldg(signs + row * kSignWords + sw_i);
             pnr[st] = __ldg(norms + row);
             prn[st] = __ldg(rnorms + row);
@@ -159,14 +162,18 @@ score_lut_kernel(TqDev p, const float* __restrict__ q, const uint32_t* __restric
                 const float4 x = *reinterpret_cast<const float4*>(byte_l + (i * 256 + ((sg >> (8 * i)) & 255u)) * 8 * QP);
                 a2[0] += x.x; a2[1] += x.y; a2[2] += x.z; a2[3] += x.w;
             }
+            // The eight partial sums of each of the four queries meet in a reduce-scatter: lanes trade the half of
+            // their values the partner keeps (2 shuffles, then 1), and one more exchange joins the two groups of
+            // four lanes: 4 shuffles instead of the 12 of four butterflies.  Lane l8 ends with query qsel.
+            float v[QP];
 #pragma unroll
-            for (int qq = 0; qq < QP; ++qq) {
-                float s = fmaf(ar, a2[qq], a1[qq]);
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if (l8 == qq) sb[qq * kTile + ksc + st * 4] = nr * s;   // lane qq of the eight stores query qq
-            }
+            for (int qq = 0; qq < QP; ++qq) v[qq] = fmaf(ar, a2[qq], a1[qq]);
+            const float rx = __shfl_xor_sync(0xffffffffu, b0 ? v[0] : v[2], 1);
+            const float ry = __shfl_xor_sync(0xffffffffu, b0 ? v[1] : v[3], 1);
+            const float ax = (b0 ? v[2] : v[0]) + rx, ay = (b0 ? v[3] : v[1]) + ry;
+            float s = (b1 ? ay : ax) + __shfl_xor_sync(0xffffffffu, b1 ? ax : ay, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (l8 < 4) sb[qsel * kTile + ksc + st * 4] = nr * s;
         }
         __syncthreads();   // the tile's scores are in shared memory; the other buffer's readers are done
         if (k0 + t < n) {
@@ -202,7 +209,7 @@ int launch_lut(const tq_plan* p, const float* q, const uint32_t* codes, const ui
 
 bool tq_score_lut_supported(const tq_plan* p, int qpg) {
     // d = 64 is compiled and correct, but the tensor-core kernel is a little faster there (130 vs 135 us for
-    // 64 groups x 4 queries x 32,768 keys; at d = 128: 191 vs 179 us)
+    // 64 groups x 4 queries x 32,768 keys; at d = 128: 191 vs 156 us)
     return p->has_projection && p->dev.d == 128 && p->dev.bits >= 1 && p->dev.bits <= 3 && qpg >= 3 && qpg <= 4;
 }
 

@@ -198,6 +198,9 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     const int cw_i = (kLaneBits * l8) >> 5, cw_sh = (kLaneBits * l8) & 31;
     const int cw_i2 = cw_i + 1 < kLastWord ? cw_i + 1 : kLastWord;
     const int sw_i = (BPL * l8) >> 2, sw_sh = ((BPL * l8) & 3) * 8;
+    const bool b0 = l8 & 1, b1 = l8 & 2;
+    // the query whose sum the lane holds after the exchange among the eight lanes of a key
+    const int qsel = QP == 4 ? 2 * (l8 & 1) + ((l8 >> 1) & 1) : QP == 2 ? (l8 & 1) : 0;
     const float* pair_l = pair_t + l8 * QP;
     const float* byte_l = byte_t + l8 * QP;
     // value role: coordinates 8c .. 8c+7 of key `ksub` of every batch of kIterKeys keys; their codes are the
@@ -266,9 +269,7 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     for (int64_t tile = tile0; tile < tile1; ++tile) {
         const int64_t k0 = tile * kTile;
         const float vn_tile = vn;
-        float mrun[QP];
-#pragma unroll
-        for (int qq = 0; qq < QP; ++qq) mrun[qq] = -CUDART_INF_F;
+        float mrun = -CUDART_INF_F;    // running maximum of this lane's query (qsel) over its keys of the tile
 #pragma unroll
         for (int st = 0; st < kSteps; ++st) {
             float v[QP];
@@ -296,32 +297,38 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
             }
             const float ar = alpha * prn[st];
 #pragma unroll
-            for (int qq = 0; qq < QP; ++qq) {
-                float s = fmaf(ar, a2[qq], a1[qq]);
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
+            for (int qq = 0; qq < QP; ++qq) v[qq] = fmaf(ar, a2[qq], a1[qq]);
+            // The eight partial sums of every query meet in a reduce-scatter: lanes trade the values their partner
+            // keeps, so QP = 4 takes 2 + 1 + 1 shuffles instead of the 12 of four butterflies (shuffles share the
+            // pipe of the lookups).  The lane ends with the sum of query qsel.
+            float s;
+            if constexpr (QP == 4) {
+                const float rx = __shfl_xor_sync(0xffffffffu, b0 ? v[0] : v[2], 1);
+                const float ry = __shfl_xor_sync(0xffffffffu, b0 ? v[1] : v[3], 1);
+                const float ax = (b0 ? v[2] : v[0]) + rx, ay = (b0 ? v[3] : v[1]) + ry;
+                s = (b1 ? ay : ax) + __shfl_xor_sync(0xffffffffu, b1 ? ax : ay, 2);
+            } else if constexpr (QP == 2) {
+                s = (b0 ? v[1] : v[0]) + __shfl_xor_sync(0xffffffffu, b0 ? v[0] : v[1], 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
-                s += __shfl_xor_sync(0xffffffffu, s, 4);
-                v[qq] = s;
+            } else {
+                s = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
             }
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
 #else
-#pragma unroll
-            for (int qq = 0; qq < QP; ++qq) v[qq] = __uint_as_float((pw0[st] ^ pw1[st] ^ psg[st]) & 0x3fffffffu) * 1e-30f + prn[st];
+            float s = __uint_as_float((pw0[st] ^ pw1[st] ^ psg[st]) & 0x3fffffffu) * 1e-30f + prn[st];
 #endif
             const bool valid = k0 + ksc + st * 4 < n;
-            const float sc = pnr[st] * a.scale_log2e;
-#pragma unroll
-            for (int qq = 0; qq < QP; ++qq) {
-                v[qq] = valid ? v[qq] * sc : -CUDART_INF_F;
-                mrun[qq] = fmaxf(mrun[qq], v[qq]);
-            }
-            if (l8 == 0) st_vec<QP>(sbuf + (ksc + st * 4) * QP, v);
+            s = valid ? s * (pnr[st] * a.scale_log2e) : -CUDART_INF_F;
+            mrun = fmaxf(mrun, s);
+            if (l8 < QP) sbuf[(ksc + st * 4) * QP + qsel] = s;
         }
-#pragma unroll
-        for (int qq = 0; qq < QP; ++qq) {
-            float m = mrun[qq];
+        {
+            // lanes 0..QP-1 of the warp end with the maximum of their query over the warp's 32 keys
+            float m = mrun;
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
-            if (lane == 0) red[warp * QP + qq] = m;
+            if (lane < QP) red[warp * QP + qsel] = m;
         }
         __syncthreads();   // scores and tile maxima visible; the value phase of the previous tile is over
         if (a.vbufs == 1) fetch_values(tile, vt);

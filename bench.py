@@ -270,6 +270,7 @@ def run_gpu(args):
         quant.dequantize(quant.quantize(keys))
         kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
         kv.attend(kv_q)
+        kv.keys.scores(kv_q)
         torch.cuda.synchronize()
         if rank == 0:
             print(json.dumps({"note": "profiling run without host legs", "keys": N_KEYS, "quantize_ms": q_mean,
@@ -326,7 +327,16 @@ def run_gpu(args):
             "bytes": "B/key: packed key and packed value in; scores and dequantized values never leave the SM",
             "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_o,
             "groups": DECODE_GROUPS, "queries_per_group": DECODE_QPG, "keys_per_group": N_KEYS // DECODE_GROUPS}
-        del kv, kv_q
+        # the decode step's scores alone: every group of keys scored by its DECODE_QPG query heads, matrix out
+        enc_g = kv.keys.encoding(0)     # plans and buffers of the cache; scored through the cache's own call
+        ms = timed(lambda: kv.keys.scores(kv_q), inner=4)
+        nbytes = D * B_MSE // 8 + D // 8 + 8 + 4 * DECODE_QPG
+        gbs = nbytes * N_KEYS / (ms * 1e-3) / 1e9
+        other["attention_score_%d_queries_per_group" % DECODE_QPG] = {
+            "ms": ms, "M_per_s": N_KEYS / (ms * 1e-3) / 1e6, "bytes_per_unit": nbytes,
+            "bytes": "B/key: packed key in, %d scores out (grouped-query decode: %d groups)" % (DECODE_QPG, DECODE_GROUPS),
+            "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_o}
+        del kv, kv_q, enc_g
     # ---- end to end through the public API with host buffers (pinned), rank-local -------------------
     host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
     host_keys.copy_(keys)

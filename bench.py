@@ -281,7 +281,8 @@ def run_gpu(args):
     # ---- the other calls of the path, each timed alone with CUDA events (median of 10), rank 0 only --------
     other = {}
     if rank == 0:
-        def timed(fn, reps=10, inner=1):
+        def timed(fn, reps=10, inner=4):     # `inner` calls back to back between the events: the rate of the call, not the
+                                             # latency of one launch into an idle GPU
             for _ in range(3):
                 fn()
             ms = []
@@ -319,7 +320,7 @@ def run_gpu(args):
         # decode attention over a packed key/value cache of the same keys: DECODE_GROUPS sequences x heads,
         # DECODE_QPG queries each (grouped-query attention), values TurboQuantMSE(d, bits)
         kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
-        ms = timed(lambda: kv.attend(kv_q), inner=4)
+        ms = timed(lambda: kv.attend(kv_q))
         nbytes = D * B_MSE // 8 + D // 8 + 8 + D * BITS // 8 + 4
         gbs = nbytes * N_KEYS / (ms * 1e-3) / 1e9
         other["decode_attention"] = {
@@ -329,7 +330,7 @@ def run_gpu(args):
             "groups": DECODE_GROUPS, "queries_per_group": DECODE_QPG, "keys_per_group": N_KEYS // DECODE_GROUPS}
         # the decode step's scores alone: every group of keys scored by its DECODE_QPG query heads, matrix out
         enc_g = kv.keys.encoding(0)     # plans and buffers of the cache; scored through the cache's own call
-        ms = timed(lambda: kv.keys.scores(kv_q), inner=4)
+        ms = timed(lambda: kv.keys.scores(kv_q))
         nbytes = D * B_MSE // 8 + D // 8 + 8 + 4 * DECODE_QPG
         gbs = nbytes * N_KEYS / (ms * 1e-3) / 1e9
         other["attention_score_%d_queries_per_group" % DECODE_QPG] = {

@@ -143,6 +143,17 @@ def test_no_cpu_fallback_without_a_device(lib_built):
     quant = tg.TurboQuantMSE(8, 2, seed=1, grid_size=513, max_iter=8)
     with pytest.raises(TurboQuantNativeError):
         quant.quantize(np.zeros((3, 8), np.float32))
+    # the caches hold device memory from the start: they refuse to exist without a device, and argument
+    # errors still come first
+    prod = tg.TurboQuantProd(8, 2, seed=1, grid_size=513, max_iter=8)
+    with pytest.raises(TurboQuantNativeError):
+        tg.PackedKeyCache(prod, 2, 16)
+    with pytest.raises(TurboQuantNativeError):
+        tg.PackedKVCache(prod, quant, 2, 16)
+    with pytest.raises(TypeError):
+        tg.PackedKeyCache(quant, 2, 16)
+    with pytest.raises(ValueError):
+        tg.PackedKeyCache(prod, 0, 16)
 
 
 @pytest.mark.parametrize("name", ["d128_b4", "d64_b2", "d128_b1"])

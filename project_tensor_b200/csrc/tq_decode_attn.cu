@@ -265,10 +265,9 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     }
     __syncthreads();   // tables complete
 
-    int buf = 0;
-    for (int64_t tile = tile0; tile < tile1; ++tile) {
+    // scoring phase of a tile: its scaled scores go to sbuf, the warp's maximum per query to red
+    auto score_tile = [&](int64_t tile) {
         const int64_t k0 = tile * kTile;
-        const float vn_tile = vn;
         float mrun = -CUDART_INF_F;    // running maximum of this lane's query (qsel) over its keys of the tile
 #pragma unroll
         for (int st = 0; st < kSteps; ++st) {
@@ -330,6 +329,33 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
             if (lane < QP) red[warp * QP + qsel] = m;
         }
+    };
+    // value phase of a tile: weights (pbuf) times centroid values, added to the accumulators
+    auto value_tile = [&](const uint32_t* vcur) {
+#ifndef TQ_DEC_NOVALUE   // measurement switch: leave the value phase out
+#pragma unroll 4
+        for (int it = 0; it < kTile / kIterKeys; ++it) {
+            const int kk = it * kIterKeys + ksub;
+            uint32_t cbits = vcur[kk * vwords + vw];
+            if (VSTRADDLE) cbits = __funnelshift_r(cbits, vcur[kk * vwords + vw2], vsh);
+            else cbits >>= vsh;
+            float pq[QP];
+            ld_vec<QP>(pbuf + kk * QP, pq);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float cv = vcb[cbits & vmask];
+                cbits >>= vbits;
+#pragma unroll
+                for (int qq = 0; qq < QP; ++qq) acc[qq][u] = fmaf(pq[qq], cv, acc[qq][u]);
+            }
+        }
+#endif
+    };
+    if (tile0 < tile1) score_tile(tile0);
+
+    int buf = 0;
+    for (int64_t tile = tile0; tile < tile1; ++tile) {
+        const float vn_tile = vn;
         __syncthreads();   // scores and tile maxima visible; the value phase of the previous tile is over
         if (a.vbufs == 1) fetch_values(tile, vt);
         if (t < ((kWarps * QP + 31) & ~31)) {   // whole warps, so that the shuffles have all their lanes
@@ -366,24 +392,14 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
             fetch_keys(tile + 1);
             if (a.vbufs > 1) fetch_values(tile + 1, vt + (buf ^ 1) * vstride);
         }
-#ifndef TQ_DEC_NOVALUE   // measurement switch: leave the value phase out
-#pragma unroll 4
-        for (int it = 0; it < kTile / kIterKeys; ++it) {
-            const int kk = it * kIterKeys + ksub;
-            uint32_t cbits = vcur[kk * vwords + vw];
-            if (VSTRADDLE) cbits = __funnelshift_r(cbits, vcur[kk * vwords + vw2], vsh);
-            else cbits >>= vsh;
-            float pq[QP];
-            ld_vec<QP>(pbuf + kk * QP, pq);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float cv = vcb[cbits & vmask];
-                cbits >>= vbits;
-#pragma unroll
-                for (int qq = 0; qq < QP; ++qq) acc[qq][u] = fmaf(pq[qq], cv, acc[qq][u]);
-            }
+        // Between here and the next barrier every warp owes the value phase of this tile and the scoring phase of
+        // the next one.  Even warps take them in that order, odd warps in the other, so that at any time half of
+        // the SM's warps walk the tables (16-byte shared-memory loads) while the other half multiply and add.
+        const bool more = tile + 1 < tile1;
+        for (int ph = 0; ph < 2; ++ph) {
+            if (((ph ^ warp) & 1) == 0) value_tile(vcur);
+            else if (more) score_tile(tile + 1);
         }
-#endif
         if (a.vbufs > 1) buf ^= 1;
     }
 

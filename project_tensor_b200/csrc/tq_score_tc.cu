@@ -571,7 +571,8 @@ int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
 }  // namespace
 
 // ---- host-side planning ---------------------------------------------------------------------------
-constexpr int64_t kChunkKeys = 1 << 20;     // keys per group scored into scratch at a time when only top-k is wanted
+constexpr int64_t kChunkKeys = 1 << 22;     // keys per group scored into scratch at a time when only top-k is wanted
+                                            // (2^20: 221 us per 1M keys and 32 queries, 2^21: 198, 2^23: 185; scratch 16 B x queries per key)
 constexpr int64_t kSegLen = 65536;          // scores per selection block (smaller segments cost more in per-block selection than they gain)
 
 struct ScoreTcPlan {

@@ -90,10 +90,11 @@ def test_topk_equals_sorted_matrix(tg, path, n, nq, k):
 
 
 def test_topk_over_several_scratch_chunks(tg):
-    """2,500,000 keys: without a matrix from the caller the scores pass through scratch in chunks of 2^20
-    keys; the per-chunk candidates must merge into the same top-100 as a sort of the full matrix."""
+    """9,000,000 keys: without a matrix from the caller the scores pass through scratch in chunks of 2^22
+    keys (two full ones and a ragged third); the per-chunk candidates must merge into the same top-100 as a
+    sort of the full matrix."""
     import torch
-    d, n, nq, k = 128, 2_500_000, 8, 100
+    d, n, nq, k = 128, 9_000_000, 8, 100
     gen = torch.Generator(device="cuda").manual_seed(20265)
     x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
     q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)

@@ -555,7 +555,8 @@ int tq_plan_last_recheck_rows(const tq_plan* p, void* stream, int64_t* rows) {
     return TQ_OK;
 }
 
-// Debug helpers (not part of the public header): raw access to the plan's counter block.
+#ifdef TQ_PROF
+// Measurement builds only: raw access to the plan's counter block (per-role cycle counters).
 int tq_debug_read_counters(const tq_plan* p, long long* out, int n) {
     if (!p || n > 32) return -1;
     return cudaMemcpy(out, p->counters, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
@@ -564,5 +565,7 @@ int tq_debug_zero_counters(const tq_plan* p) {
     if (!p) return -1;
     return cudaMemset(p->counters, 0, 256) == cudaSuccess ? 0 : -3;
 }
+
+#endif
 
 }  // extern "C"

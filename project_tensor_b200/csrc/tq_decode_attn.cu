@@ -272,7 +272,6 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
 #pragma unroll
         for (int st = 0; st < kSteps; ++st) {
             float v[QP];
-#ifndef TQ_DEC_NOSCORE   // measurement switch: leave the table walk out
             const uint32_t lo = __funnelshift_r(pw0[st], pw1[st], cw_sh);
             const uint64_t z = kLaneBits > 32 ? ((uint64_t)(pw1[st] >> cw_sh) << 32) | lo : (uint64_t)lo;
             const uint32_t sg = psg[st] >> sw_sh;
@@ -314,9 +313,6 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
             }
             s += __shfl_xor_sync(0xffffffffu, s, 4);
-#else
-            float s = __uint_as_float((pw0[st] ^ pw1[st] ^ psg[st]) & 0x3fffffffu) * 1e-30f + prn[st];
-#endif
             const bool valid = k0 + ksc + st * 4 < n;
             s = valid ? s * (pnr[st] * a.scale_log2e) : -CUDART_INF_F;
             mrun = fmaxf(mrun, s);
@@ -332,7 +328,6 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
     };
     // value phase of a tile: weights (pbuf) times centroid values, added to the accumulators
     auto value_tile = [&](const uint32_t* vcur) {
-#ifndef TQ_DEC_NOVALUE   // measurement switch: leave the value phase out
 #pragma unroll 4
         for (int it = 0; it < kTile / kIterKeys; ++it) {
             const int kk = it * kIterKeys + ksub;
@@ -349,7 +344,6 @@ decode_partial_kernel(TqDev kp, DecodeArgs a) {
                 for (int qq = 0; qq < QP; ++qq) acc[qq][u] = fmaf(pq[qq], cv, acc[qq][u]);
             }
         }
-#endif
     };
     if (tile0 < tile1) score_tile(tile0);
 

@@ -7,6 +7,13 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Cycle counters per role exist only in measurement builds (-DTQ_PROF).
+#ifdef TQ_PROF
+#define TQ_PROF_CODE(...) __VA_ARGS__
+#else
+#define TQ_PROF_CODE(...)
+#endif
+
 namespace tqptx {
 
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
@@ -66,6 +73,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return mbar_wait_slow(bar, parity, abort_flag);
 }
 
+// The same wait executed by every lane of a converged warp; the answer is the same for all of them.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, ok);
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // Bytes of a row block that a bulk copy may not take (it moves multiples of 16 bytes): the last `bytes % 16`
 // bytes, copied here with plain 4-byte loads by the calling thread.  Call before the arrive on the mbarrier
 // that publishes the block, so that its release covers these stores.  `bytes` is a multiple of 4.
@@ -123,6 +142,21 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same instruction with the accumulate flag fixed at compile time: `first` overwrites the accumulator.
+__device__ __forceinline__ void mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
         : "memory");
 }
 // mbarrier arrive once every tcgen05.mma issued so far by this thread has completed.

@@ -62,7 +62,9 @@ struct ScoreTcArgs {
     float* scores;                // points at (group 0, first query of this pass, key_off)
     float alpha;
     unsigned long long* status;
-    long long* prof;              // optional per-role cycle counters (debug), may be null
+#ifdef TQ_PROF
+    long long* prof;              // per-role cycle counters (measurement builds only)
+#endif
 };
 
 enum {
@@ -213,7 +215,10 @@ score_tc_kernel(const ScoreTcArgs a) {
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp walks the tiles and waits; one elected lane issues, with every operand computed from
+        // warp-uniform values (a single lane of a diverged warp pays about 64 cycles per instruction).
+        {
+            const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
             const uint32_t lbo = 128, sbo = (D / 8) * 128;
             int64_t prev_g = -1, gcount = 0;
             int bb = 0;
@@ -226,39 +231,44 @@ score_tc_kernel(const ScoreTcArgs a) {
                 const uint32_t par2 = (uint32_t)((i >> 1) & 1);
                 if (g != prev_g) {
                     bb = (int)(gcount & 1);
-                    if (!mbar_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
+                    if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
                     prev_g = g;
                     ++gcount;
                     const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
                     dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
                     dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
                 }
-                long long c0 = clock64();
-                if (!mbar_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
-                long long c1 = clock64();
+                TQ_PROF_CODE(long long c0 = clock64();)
+                if (!warp_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
+                TQ_PROF_CODE(long long c1 = clock64();)
                 const int db = kDBufs == 2 ? b : 0;
                 const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
-                if (!mbar_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
+                if (!warp_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
                 tc_fence_after();
-                long long c2 = clock64();
-                if (a.prof && blockIdx.x == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
-                const uint32_t base = tmem + b * kBufCols;
-                const uint32_t d1 = tmem + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
-#pragma unroll
-                for (int kb = 0; kb < DR / 16; ++kb) {
-                    // the start-address field counts 16-byte units: one k-block (two core matrices) further
-                    const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
-                    const uint64_t qh = dq_hi + step, ph = dp_hi + step;
-                    // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
-                    mma_ts(d1, base + kColHi + kb * 8, qh, kIdesc2, kb > 0);
-                    mma_ts(d1, base + kColLo + kb * 8, qh, kIdesc1, 1);
-                    mma_ts(d2, base + kColSg + kb * 8, ph, kIdesc2, kb > 0);
-                }
-                mma_commit(BAR(SB_D_FULL + db));
-                mma_commit(BAR(SB_A_EMPTY + b));
-                if (a.prof && blockIdx.x == 0) a.prof[10] += clock64() - c2;
+                TQ_PROF_CODE(long long c2 = clock64(); if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
+                const uint32_t base = tm + b * kBufCols;
+                const uint32_t d1 = tm + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
                 const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
-                if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+                if (elect_one()) {
+                    // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
+                    mma_ts_first(d1, base + kColHi, dq_hi, kIdesc2);
+                    mma_ts_acc(d1, base + kColLo, dq_hi, kIdesc1);
+                    mma_ts_first(d2, base + kColSg, dp_hi, kIdesc2);
+#pragma unroll 1
+                    for (int kb = 1; kb < DR / 16; ++kb) {
+                        // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                        const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                        const uint64_t qh = dq_hi + step, ph = dp_hi + step;
+                        mma_ts_acc(d1, base + kColHi + kb * 8, qh, kIdesc2);
+                        mma_ts_acc(d1, base + kColLo + kb * 8, qh, kIdesc1);
+                        mma_ts_acc(d2, base + kColSg + kb * 8, ph, kIdesc2);
+                    }
+                    mma_commit(BAR(SB_D_FULL + db));
+                    mma_commit(BAR(SB_A_EMPTY + b));
+                    if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+                }
+                __syncwarp();
+                TQ_PROF_CODE(if (a.prof && blockIdx.x == 0 && lane == 0) a.prof[10] += clock64() - c2;)
             }
         }
     } else if (warp < kFirstEpiWarp) {
@@ -270,15 +280,15 @@ score_tc_kernel(const ScoreTcArgs a) {
         const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
         constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
-        long long pc[5] = {0, 0, 0, 0, 0};
+        TQ_PROF_CODE(long long pc[5] = {0, 0, 0, 0, 0};)
         for (int64_t t = t0; t < (half < kHalves ? t1 : t0); ++t) {
             const int64_t i = t - t0;
             const int s = (int)(i % kStages);
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            long long c0 = clock64();
+            TQ_PROF_CODE(long long c0 = clock64();)
             bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
-            long long c1 = clock64(); pc[0] += c1 - c0;
+            TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
             uint32_t w[kHalfWords + 1], sw[2];
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
@@ -292,11 +302,11 @@ score_tc_kernel(const ScoreTcArgs a) {
             }
             __syncwarp();
             if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
-            c0 = clock64(); pc[1] += c0 - c1;
+            TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
             if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
-            c1 = clock64(); pc[2] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); pc[2] += c1 - c0;)
             tc_fence_after();
-            c0 = clock64(); pc[3] += c0 - c1;
+            TQ_PROF_CODE(c0 = clock64(); pc[3] += c0 - c1;)
             const uint32_t abase = tmem + lane_addr + b * kBufCols + half * 32;
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb) {
@@ -318,16 +328,18 @@ score_tc_kernel(const ScoreTcArgs a) {
                 tmem_st16(abase + kColLo + sb * 16, lo);
                 tmem_st16(abase + kColSg + sb * 16, sg);
             }
-            c1 = clock64(); pc[4] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); pc[4] += c1 - c0;)
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+#ifdef TQ_PROF
             if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
                 for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
                 a.prof[5] = clock64() - c1;  // last st wait
                 a.prof[6] = t1 - t0;
             }
+#endif
         }
     } else {
         // ---- epilogue -----------------------------------------------------------------------------
@@ -362,12 +374,12 @@ score_tc_kernel(const ScoreTcArgs a) {
                 const bool wrap = kt + 1 == a.tiles_per_group;
                 fetch_norms(wrap ? g + 1 : g, wrap ? 0 : kt + 1, nrm_next, rn_next);
             }
-            long long c0 = clock64();
+            TQ_PROF_CODE(long long c0 = clock64();)
             const int db = kDBufs == 2 ? b : 0;
             const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
             mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
             tc_fence_after();
-            long long c1 = clock64();
+            TQ_PROF_CODE(long long c1 = clock64();)
             const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
             const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
             uint32_t ua[16], ub[16], va[16], vb[16];
@@ -376,7 +388,7 @@ score_tc_kernel(const ScoreTcArgs a) {
             tmem_ld16(dbase + 2 * QPAD, va);       // Sg p_hi
             tmem_ld16(dbase + 3 * QPAD, vb);       // Sg p_lo
             tmem_wait_ld();
-            long long c2 = clock64();
+            TQ_PROF_CODE(long long c2 = clock64();)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
@@ -394,9 +406,11 @@ score_tc_kernel(const ScoreTcArgs a) {
                     }
                 }
             }
+#ifdef TQ_PROF
             if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32) {
                 a.prof[12] += c1 - c0; a.prof[13] += c2 - c1; a.prof[14] += clock64() - c2;
             }
+#endif
             const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
             if (last_of_group) {
                 __syncwarp();
@@ -648,7 +662,9 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             a.scores = mat + (int64_t)q0 * row_stride;
             a.alpha = p->dev.alpha;
             a.status = p->counters + 1;
-            a.prof = getenv("TQ_PROF") ? reinterpret_cast<long long*>(p->counters + 8) : nullptr;
+#ifdef TQ_PROF
+            a.prof = reinterpret_cast<long long*>(p->counters + 8);
+#endif
             const int grid = (int)(a.total_tiles < sms ? a.total_tiles : sms);
             int r = TQ_ERR_UNSUPPORTED;
 #define TQ_SC(B)                                                                                             \

@@ -75,7 +75,9 @@ struct TensorArgs {
     float* rnorms;
     TqRecheck lists;
     unsigned long long* status;  // [0]: set to a non-zero code when a wait timed out
-    long long* prof;             // optional cycle counters per role (debug), may be null
+#ifdef TQ_PROF
+    long long* prof;             // cycle counters per role (measurement builds only)
+#endif
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -92,7 +94,8 @@ struct Smem {
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
     static constexpr int kPendBytes = 8 * kPendCap * (8 + 4);   // per epilogue warp: 64-bit and 32-bit entries
-    static constexpr int kMiscBytes = 8 * kTileRows * 4 + 4 * kTileRows + 512 + 4 * kTileRows * 4 + kCells * 16 + kPendBytes;
+    static constexpr int kRsBytes = 4 * 2 * kTileRows * 4;       // |rho|^2 partial sums: [4 tiles][2 halves][128]
+    static constexpr int kMiscBytes = 8 * kTileRows * 4 + 4 * kTileRows + 512 + kRsBytes + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
     static_assert(total <= 227 * 1024, "shared memory plan");
 };
@@ -254,7 +257,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     unsigned char* force = smem + L::off_misc + 8 * kTileRows * 4;                      // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 8 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
-    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - 4 * kTileRows * 4 - kCells * 16);  // [2 tiles][2 halves][128]
+    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - L::kRsBytes - kCells * 16);  // [4 tiles][2 halves][128]
     float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
     unsigned char* pend_base = smem + L::off_misc + L::kMiscBytes - L::kPendBytes;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -262,7 +265,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long prof_t0 = clock64();
+    TQ_PROF_CODE(const long long prof_t0 = clock64();)
 
     // ---- one-time set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
@@ -294,7 +297,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const long long prof_t1 = clock64();
+    TQ_PROF_CODE(const long long prof_t1 = clock64();)
 
     const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
     constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
@@ -325,7 +328,12 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         }
     } else if (warp == 1) {
         // ---- MMA issuer ------------------------------------------------------------------------
-        if (lane == 0) {
+        // The whole warp walks the loop and waits; one elected lane issues.  Everything an instruction takes
+        // (tensor-memory addresses, descriptors) is computed from warp-uniform values, so it sits in uniform
+        // registers and an issue costs a few cycles; issued from a single lane of a diverged warp the same
+        // instructions cost about 64 cycles each, more when the other warps of the scheduler are busy.
+        {
+            const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
             const uint32_t sbo = (kW / 8) * 128, lbo = 128;
             const uint32_t b_rhi = smem_base + L::off_b, b_rlo = b_rhi + L::kBBytes;
             const uint32_t b_mhi = b_rlo + L::kBBytes, b_mlo = b_mhi + L::kBBytes;
@@ -338,60 +346,71 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             // residual epilogue of a tile overlaps tensor work of its neighbour.
             const int64_t iters = PROD ? my_tiles + 1 : my_tiles;
             for (int64_t i = 0; i < iters; ++i) {
-                const bool pr = a.prof && blockIdx.x == 0;
+                TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && lane == 0;)
                 if (i < my_tiles) {
                     const int b = (int)(i & 1);
                     const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-                    long long c0 = clock64();
-                    if (!mbar_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
-                    long long c1 = clock64();
-                    if (!mbar_wait(BAR(BAR_ACC_EMPTY + b), par2 ^ 1u, abort_flag)) break;
+                    TQ_PROF_CODE(long long c0 = clock64();)
+                    if (!warp_wait(BAR(BAR_A_FULL + b), par2, abort_flag)) break;
+                    TQ_PROF_CODE(long long c1 = clock64();)
+                    if (!warp_wait(BAR(BAR_ACC_EMPTY + b), par2 ^ 1u, abort_flag)) break;
                     tc_fence_after();
-                    long long c2 = clock64();
-                    if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; }
-                    const uint32_t acc = tmem + ACC_COL(b);
-                    const uint32_t a_hi = tmem + A_COL(b), a_lo = a_hi + kABlock;
+                    TQ_PROF_CODE(long long c2 = clock64(); if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
+                    const uint32_t acc = tm + ACC_COL(b);
+                    const uint32_t a_hi = tm + A_COL(b), a_lo = a_hi + kABlock;
+                    if (elect_one()) {
+                        mma_ts_first(acc, a_hi, d_rhi, kIdesc);
+                        mma_ts_acc(acc, a_hi, d_rlo, kIdesc);
+                        mma_ts_acc(acc, a_lo, d_rhi, kIdesc);
 #pragma unroll 1
-                    for (int kb = 0; kb < D / 16; ++kb) {
-                        const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
-                        const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
-                        mma_ts(acc, a_hi + kb * 8, dh, kIdesc, kb > 0);
-                        mma_ts(acc, a_hi + kb * 8, dl, kIdesc, 1);
-                        mma_ts(acc, a_lo + kb * 8, dh, kIdesc, 1);
+                        for (int kb = 1; kb < D / 16; ++kb) {
+                            const uint64_t dh = d_rhi + (uint64_t)(kb * 2 * lbo >> 4);
+                            const uint64_t dl = d_rlo + (uint64_t)(kb * 2 * lbo >> 4);
+                            mma_ts_acc(acc, a_hi + kb * 8, dh, kIdesc);
+                            mma_ts_acc(acc, a_hi + kb * 8, dl, kIdesc);
+                            mma_ts_acc(acc, a_lo + kb * 8, dh, kIdesc);
+                        }
+                        mma_commit(BAR(BAR_ACC_FULL + b));
+                        if (!PROD) mma_commit(BAR(BAR_A_EMPTY + b));
                     }
-                    mma_commit(BAR(BAR_ACC_FULL + b));
-                    if (!PROD) mma_commit(BAR(BAR_A_EMPTY + b));
-                    if (pr) a.prof[10] += clock64() - c2;
+                    __syncwarp();
+                    TQ_PROF_CODE(if (pr) a.prof[10] += clock64() - c2;)
                 }
                 if (PROD && i >= 1) {
                     const int64_t j = i - 1;
                     const int b = (int)(j & 1);
                     const uint32_t par2 = (uint32_t)((j >> 1) & 1);
-                    long long c0 = clock64();
-                    if (!mbar_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
+                    TQ_PROF_CODE(long long c0 = clock64();)
+                    if (!warp_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
                     tc_fence_after();
-                    long long c1 = clock64(); if (pr) a.prof[11] += c1 - c0;
+                    TQ_PROF_CODE(long long c1 = clock64(); if (pr) a.prof[11] += c1 - c0;)
                     // The second accumulator goes to the A block of the OTHER buffer: MMA 1 of tile j + 1, issued
                     // above, was its last reader, and using it (rather than this tile's own A block) lets the
                     // converters refill a block one tile earlier.  The last tile has no successor whose
                     // converter waited for the previous sign epilogue to leave that block, so wait here.
                     if (i == my_tiles && j >= 1 &&
-                        !mbar_wait(BAR(BAR_A_EMPTY + (b ^ 1)), (uint32_t)((((j + 1) >> 1) & 1) ^ 1), abort_flag))
+                        !warp_wait(BAR(BAR_A_EMPTY + (b ^ 1)), (uint32_t)((((j + 1) >> 1) & 1) ^ 1), abort_flag))
                         break;
-                    const uint32_t acc2 = tmem + A_COL(b ^ 1);
-                    const uint32_t rho = tmem + ACC_COL(b);     // rho hi / lo pairs, 16 + 16 columns per 32 coordinates
+                    const uint32_t acc2 = tm + A_COL(b ^ 1);
+                    const uint32_t rho = tm + ACC_COL(b);     // rho hi / lo pairs, 16 + 16 columns per 32 coordinates
+                    if (elect_one()) {
+                        mma_ts_first(acc2, rho, d_mhi, kIdesc);
+                        mma_ts_acc(acc2, rho, d_mlo, kIdesc);
+                        mma_ts_acc(acc2, rho + 16, d_mhi, kIdesc);
 #pragma unroll 1
-                    for (int kb = 0; kb < D / 16; ++kb) {
-                        const uint64_t dh = d_mhi + (uint64_t)(kb * 2 * lbo >> 4);
-                        const uint64_t dl = d_mlo + (uint64_t)(kb * 2 * lbo >> 4);
-                        const uint32_t r_hi = rho + (kb >> 1) * 32 + (kb & 1) * 8, r_lo = r_hi + 16;
-                        mma_ts(acc2, r_hi, dh, kIdesc, kb > 0);
-                        mma_ts(acc2, r_hi, dl, kIdesc, 1);
-                        mma_ts(acc2, r_lo, dh, kIdesc, 1);
+                        for (int kb = 1; kb < D / 16; ++kb) {
+                            const uint64_t dh = d_mhi + (uint64_t)(kb * 2 * lbo >> 4);
+                            const uint64_t dl = d_mlo + (uint64_t)(kb * 2 * lbo >> 4);
+                            const uint32_t r_hi = rho + (kb >> 1) * 32 + (kb & 1) * 8, r_lo = r_hi + 16;
+                            mma_ts_acc(acc2, r_hi, dh, kIdesc);
+                            mma_ts_acc(acc2, r_hi, dl, kIdesc);
+                            mma_ts_acc(acc2, r_lo, dh, kIdesc);
+                        }
+                        mma_commit(BAR(BAR_ACC2_FULL + b));
+                        mma_commit(BAR(BAR_ACC_EMPTY + b));         // rho has been read: the accumulator block is free
                     }
-                    mma_commit(BAR(BAR_ACC2_FULL + b));
-                    mma_commit(BAR(BAR_ACC_EMPTY + b));         // rho has been read: the accumulator block is free
-                    if (pr) a.prof[12] += clock64() - c1;
+                    __syncwarp();
+                    TQ_PROF_CODE(if (pr) a.prof[12] += clock64() - c1;)
                 }
             }
         }
@@ -409,16 +428,15 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             float x[kXs];
             bool fail = false;
-            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32;
-            long long c0 = clock64(), c1;
+            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32; long long c0 = clock64(), c1;)
 #pragma unroll
             for (int bb = 0; bb < kXs / 32; ++bb) {
                 const int64_t g = g_base + half * (kXs / 32) + bb;
                 const int slot = (int)(g % L::kRingBoxes);
                 const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
-                long long cw0 = clock64();
+                TQ_PROF_CODE(long long cw0 = clock64();)
                 if (!fail && !mbar_wait(BAR(BAR_FULL + slot), par, abort_flag)) fail = true;
-                if (pr) a.prof[6] += clock64() - cw0;
+                TQ_PROF_CODE(if (pr) a.prof[6] += clock64() - cw0;)
                 const unsigned char* box = smem + L::off_ring + slot * kBoxBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -440,10 +458,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             // before the barrier of that tile, while a slow partner may still be reading this tile's
             float* ssq = ssq_all + b * 4 * kTileRows;
             ssq[half * kTileRows + row] = ss;
-            c1 = clock64(); if (pr) a.prof[0] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[0] += c1 - c0;)
             if (kActiveParts > 1) bar_sync(1 + quarter, 32 * kActiveParts);  // the warps that share these 32 rows
             else __syncwarp();
-            c0 = clock64(); if (pr) a.prof[1] += c0 - c1;
+            TQ_PROF_CODE(c0 = clock64(); if (pr) a.prof[1] += c0 - c1;)
             float tot = ssq[row];
 #pragma unroll
             for (int pt = 1; pt < kActiveParts; ++pt) tot += ssq[pt * kTileRows + row];
@@ -460,7 +478,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             }
             if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
             tc_fence_after();
-            c1 = clock64(); if (pr) a.prof[2] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[2] += c1 - c0;)
             const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * (kXs / 2);
 #pragma unroll
             for (int s = 0; s < kXs / 32; ++s) {
@@ -477,12 +495,12 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
             }
-            c0 = clock64(); if (pr) a.prof[3] += c0 - c1;
+            TQ_PROF_CODE(c0 = clock64(); if (pr) a.prof[3] += c0 - c1;)
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + b));
-            if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; }
+            TQ_PROF_CODE(if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; })
         }
     } else {
         // ---- epilogue: one thread per row -----------------------------------------------------------
@@ -511,11 +529,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
             const bool live = grow < a.n;
-            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32;
-            long long c0 = clock64(), c1;
+            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
             mbar_wait(BAR(BAR_ACC_FULL + b), par2, abort_flag);
             tc_fence_after();
-            c1 = clock64(); if (pr) a.prof[16] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[16] += c1 - c0;)
             const bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
             float rs = 0.f;
             const uint32_t acc = tmem + lane_addr + ACC_COL(b);
@@ -577,8 +594,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             if (PROD) {
                 tmem_wait_st();
                 // this thread's share of |rho|^2; summed in the sign epilogue of the same tile, which every
-                // epilogue warp reaches only after all of them have arrived on RHO_FULL below
-                rs_part[(b * 2 + (chunk0 ? 1 : 0)) * kTileRows + row] = rs;
+                // epilogue warp reaches only after all of them have arrived on RHO_FULL below.  Four slots: the
+                // warp of the other half may run ahead of this one (it needs MMA 1 of a later tile, not this
+                // warp's progress), but its first epilogue of tile i + 4 cannot start before every warp has
+                // finished the first epilogue of tile i + 2, which follows the sign epilogue of tile i.
+                rs_part[((int)(i & 3) * 2 + (chunk0 ? 1 : 0)) * kTileRows + row] = rs;
             }
             tc_fence_before();
             __syncwarp();
@@ -595,7 +615,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 for (int ch = 0; ch < kChunks; ++ch) pend_codes(a.lists, pend, nm[ch], grow, (chunk0 + ch) * 32, lane);
             }
             if (!PROD) pend_rows(a.lists, pend, redo_row && live, grow, lane);
-            if (pr) a.prof[17] += clock64() - c1;
+            TQ_PROF_CODE(if (pr) a.prof[17] += clock64() - c1;)
         };
         // second-accumulator epilogue of tile j (Prod): sign bits, guard test, release of the tile's A block
         auto epilogue2 = [&](int64_t j) {
@@ -604,16 +624,16 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const uint32_t par2 = (uint32_t)((j >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
             const bool live = grow < a.n;
-            const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32;
+            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
             bool redo_row = force[(j & 3) * kTileRows + row] != 0;
-            long long c0 = clock64(), c1;
             mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag);
             tc_fence_after();
-            c1 = clock64(); if (pr) a.prof[18] += c1 - c0;
+            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[18] += c1 - c0;)
             const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
             if (chunk0 == 0 && live) {   // rs is in 2^10 units
-                const float rs_all = kHalves == 2 ? rs_part[(b * 2) * kTileRows + row] + rs_part[(b * 2 + 1) * kTileRows + row]
-                                                  : rs_part[(b * 2) * kTileRows + row];
+                const int sl = (int)(j & 3) * 2;
+                const float rs_all = kHalves == 2 ? rs_part[sl * kTileRows + row] + rs_part[(sl + 1) * kTileRows + row]
+                                                  : rs_part[sl * kTileRows + row];
                 a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
             }
             uint32_t sw[kChunks];
@@ -645,7 +665,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + (b ^ 1)));  // the converters may refill that A block
             if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw[0], sw[1]);
             pend_rows(a.lists, pend, redo_row && live, grow, lane);
-            if (pr) a.prof[19] += clock64() - c1;
+            TQ_PROF_CODE(if (pr) a.prof[19] += clock64() - c1;)
         };
         if (PROD) {
             static_assert(kChunks == 2, "the sign store writes two words per thread");
@@ -666,12 +686,14 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
+#ifdef TQ_PROF
     if (a.prof && threadIdx.x == 0) {
         const long long t2 = clock64();
         atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 21), (unsigned long long)(t2 - prof_t0));
         atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 22), (unsigned long long)(prof_t1 - prof_t0));
         if (blockIdx.x == 0) a.prof[23] = t2 - prof_t0;
     }
+#endif
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
@@ -885,7 +907,9 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     args.rnorms = rnorms;
     args.lists = *lists;
     args.status = p->counters + 1;
-    args.prof = getenv("TQ_PROF") ? reinterpret_cast<long long*>(p->counters + 8) : nullptr;
+#ifdef TQ_PROF
+    args.prof = reinterpret_cast<long long*>(p->counters + 8);   // cycle counters per role, measurement builds only
+#endif
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)d, (cuuint64_t)n};

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <cuda.h>
+
 #include "../../include/tq_b200.h"
 
 #define TQ_MAX_DIM 1024
@@ -163,6 +165,12 @@ int tq_launch_unpack_codes(const tq_plan* p, const uint32_t* codes, int64_t n, u
 int tq_launch_pack_codes(const tq_plan* p, const uint8_t* in, int64_t n, uint32_t* codes, cudaStream_t st);
 int tq_launch_unpack_signs(const tq_plan* p, const uint32_t* signs, int64_t n, int8_t* out, cudaStream_t st);
 int tq_launch_pack_signs(const tq_plan* p, const int8_t* in, int64_t n, uint32_t* signs, cudaStream_t st);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (the library does not link libcuda).
+typedef CUresult (*TqEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TqEncodeTiledFn tq_encode_tiled_fn();   // tq_tensor.cu; null if the driver does not offer the entry point
 
 // ---- small device helpers ---------------------------------------------------------------------
 // Bit position of coordinate j's QJL sign inside its 32-bit word: the even coordinates of a group of

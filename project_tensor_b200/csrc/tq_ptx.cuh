@@ -40,25 +40,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Same test, but the thread may be suspended by the hardware for up to `hint_ns` while the phase
-// is incomplete (it is woken when the phase completes), so a waiting warp does not burn issue slots.
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok != 0;
-}
 // Bounded wait.  Returns false when the limit ran out or another thread has already given up.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (*abort_flag) return false;  // somebody already gave up: do not block again
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
+        if (mbar_try_wait(bar, parity)) return true;   // blocks inside the hardware for a while before it answers
         if ((it & 7u) == 7u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitLimitCycles) {

@@ -25,8 +25,10 @@
 #include "tq_ptx.cuh"
 #include "tq_topk.cuh"
 
+#include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 namespace {
 
@@ -34,14 +36,20 @@ using namespace tqptx;
 
 constexpr int D = 128;
 constexpr int kTileKeys = 128;
-// Warps: bulk copy, MMA, 8 expanders, then 4 epilogue warps per 16 queries of the pass.
-template <int QPAD> struct ScoreThreads { static constexpr int kEpiPerRow = QPAD / 16; static constexpr int kThreads = (10 + 4 * kEpiPerRow) * 32; };
+// Warps: bulk copy, MMA, 16 expanders (one thread per quarter key), then 4 epilogue warps per 16 queries of the pass.
+constexpr int kExpWarps = 16;
+template <int QPAD> struct ScoreThreads {
+    static constexpr int kEpiPerRow = QPAD / 16;
+    static constexpr int kEpiThreads = 4 * kEpiPerRow * 32;
+    static constexpr int kThreads = (2 + kExpWarps) * 32 + kEpiThreads;
+};
 constexpr int kFirstExpWarp = 2;
-constexpr int kFirstEpiWarp = 10;
-constexpr int kStages = 8;
+constexpr int kFirstEpiWarp = kFirstExpWarp + kExpWarps;
+constexpr int kMaxStages = 8;
 constexpr float kCentScale = 1024.f;
 constexpr int kRowBytesB = D * 2;  // one query row of one fp16 operand matrix
 constexpr int kPrepSmemBytes = 2 * D * D * 4;  // rotation and projection matrices staged by the preparation kernel
+constexpr int kEpiBarrier = 1;     // named barrier of the epilogue warps
 
 __host__ __device__ constexpr int prep_group_bytes(int qpad) { return 4 * qpad * kRowBytesB + 2 * qpad * 4; }
 
@@ -60,6 +68,8 @@ struct ScoreTcArgs {
     int64_t out_group_stride;     // floats between groups in `scores`
     int64_t out_row_stride;       // floats between query rows
     float* scores;                // points at (group 0, first query of this pass, key_off)
+    int tile_store;               // 1: score tiles leave through shared memory and a bulk tensor store (tmap_out)
+    int norms_bulk;               // 1: norms and residual norms travel with the packed rows through the key ring
     float alpha;
     unsigned long long* status;
 #ifdef TQ_PROF
@@ -84,6 +94,17 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// Shared memory -> global, one box of a 3-D tensor map (keys, queries of the pass, groups); parts of the box
+// outside the tensor are not written.
+__device__ __forceinline__ void tensor_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until all but the newest `N` bulk groups of this thread have finished reading shared memory.
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
@@ -103,23 +124,32 @@ struct ScoreSmem {
     static constexpr int kLutBytes = kLutEntries * 32 * 8;
     static constexpr int kCodeRowBytes = DR * BITS / 8;
     static constexpr int kSignRowBytes = DR / 8;
-    static constexpr int kStageBytes = kTileKeys * (kCodeRowBytes + kSignRowBytes);
+    static constexpr int kNormOff = kTileKeys * (kCodeRowBytes + kSignRowBytes);   // norms, then residual norms, of the tile's keys
+    static constexpr int kStageBytes = kNormOff + 2 * kTileKeys * 4;
     static constexpr int kBBytes = (prep_group_bytes(QPAD) + 127) & ~127;
+    static constexpr int kOutBytes = QPAD * kTileKeys * 4;          // one staged tile of scores [query][key]
+    static constexpr int kFixed = kLutBytes + 2 * kBBytes + 2 * kOutBytes + 512 + 128 + 128;
+    static constexpr int kFit = (227 * 1024 - kFixed) / kStageBytes;
+    static constexpr int kStages = kFit < kMaxStages ? kFit : kMaxStages;
+    static_assert(kStages >= 3, "key ring too short");
     static constexpr int off_lut = 0;
     static constexpr int off_b = off_lut + kLutBytes;
-    static constexpr int off_ring = off_b + 2 * kBBytes;
+    static constexpr int off_out = off_b + 2 * kBBytes;
+    static constexpr int off_ring = off_out + 2 * kOutBytes;
     static constexpr int off_misc = off_ring + kStages * kStageBytes;
     static constexpr int total = off_misc + 512 + 128;
 };
 
 template <int BITS, int QPAD, int DR>
 __global__ void __launch_bounds__(ScoreThreads<QPAD>::kThreads, 1)
-score_tc_kernel(const ScoreTcArgs a) {
+score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs a) {
     static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
-    constexpr int kHalves = DR / 64;
+    constexpr int kParts = DR / 32;              // expander warps per lane quarter that have data
     using L = ScoreSmem<BITS, QPAD, DR>;
+    constexpr int kStages = L::kStages;
     constexpr int kThreads = ScoreThreads<QPAD>::kThreads;
     constexpr int kEpiPerRow = ScoreThreads<QPAD>::kEpiPerRow;
+    constexpr int kEpiThreads = ScoreThreads<QPAD>::kEpiThreads;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const uint32_t smem_base = smem_u32(smem);
@@ -129,11 +159,15 @@ score_tc_kernel(const ScoreTcArgs a) {
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TQ_PROF_CODE(const long long prof_t0 = clock64();)
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) { mbar_init(BAR(SB_K_FULL + i), 1); mbar_init(BAR(SB_K_EMPTY + i), 4 * kHalves); }
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(BAR(SB_K_FULL + i), 1);
+            mbar_init(BAR(SB_K_EMPTY + i), 4 * kParts + (a.norms_bulk ? 4 * kEpiPerRow : 0));   // expanders (+ epilogue warps)
+        }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(SB_A_FULL + i), 4 * kHalves);
+            mbar_init(BAR(SB_A_FULL + i), 4 * kParts);
             mbar_init(BAR(SB_A_EMPTY + i), 1);
             mbar_init(BAR(SB_D_FULL + i), 1);
             mbar_init(BAR(SB_D_EMPTY + i), 4 * kEpiPerRow);
@@ -165,6 +199,7 @@ score_tc_kernel(const ScoreTcArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    TQ_PROF_CODE(const long long prof_t1 = clock64();)
 
     // contiguous tile range of this CTA, so that it rarely changes group
     const int64_t t0 = a.total_tiles * (int64_t)blockIdx.x / gridDim.x;
@@ -208,10 +243,19 @@ score_tc_kernel(const ScoreTcArgs a) {
                 // the multiple, plain loads the few bytes behind it
                 copy_tail_words(stage, csrc, cb);
                 copy_tail_words(stage + kTileKeys * L::kCodeRowBytes, ssrc, sb);
-                mbar_arrive_expect_tx(BAR(SB_K_FULL + s), (cb & ~15u) + (sb & ~15u));
+                const uint32_t nb = a.norms_bulk ? (uint32_t)valid * 4u : 0u;
+                if (nb) {
+                    copy_tail_words(stage + L::kNormOff, reinterpret_cast<const unsigned char*>(a.norms + row0), nb);
+                    copy_tail_words(stage + L::kNormOff + kTileKeys * 4, reinterpret_cast<const unsigned char*>(a.rnorms + row0), nb);
+                }
+                mbar_arrive_expect_tx(BAR(SB_K_FULL + s), (cb & ~15u) + (sb & ~15u) + 2 * (nb & ~15u));
                 const uint32_t dst = smem_base + L::off_ring + s * L::kStageBytes;
                 if (cb & ~15u) bulk_load(dst, csrc, cb & ~15u, BAR(SB_K_FULL + s));
                 if (sb & ~15u) bulk_load(dst + kTileKeys * L::kCodeRowBytes, ssrc, sb & ~15u, BAR(SB_K_FULL + s));
+                if (nb & ~15u) {
+                    bulk_load(dst + L::kNormOff, a.norms + row0, nb & ~15u, BAR(SB_K_FULL + s));
+                    bulk_load(dst + L::kNormOff + kTileKeys * 4, a.rnorms + row0, nb & ~15u, BAR(SB_K_FULL + s));
+                }
             }
         }
     } else if (warp == 1) {
@@ -272,16 +316,15 @@ score_tc_kernel(const ScoreTcArgs a) {
             }
         }
     } else if (warp < kFirstEpiWarp) {
-        // ---- expanders ----------------------------------------------------------------------------
-        const int half = (warp - kFirstExpWarp) >> 2;
+        // ---- expanders: one thread per quarter key (32 coordinates) ---------------------------------
+        const int part = (warp - kFirstExpWarp) >> 2;
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
-        constexpr int kHalfWords = 2 * BITS;  // code words of 64 coordinates
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
         TQ_PROF_CODE(long long pc[5] = {0, 0, 0, 0, 0};)
-        for (int64_t t = t0; t < (half < kHalves ? t1 : t0); ++t) {
+        for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
             const int64_t i = t - t0;
             const int s = (int)(i % kStages);
             const int b = (int)(i & 1);
@@ -289,54 +332,49 @@ score_tc_kernel(const ScoreTcArgs a) {
             TQ_PROF_CODE(long long c0 = clock64();)
             bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
             TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
-            uint32_t w[kHalfWords + 1], sw[2];
+            uint32_t w[BITS + 1], sw;
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
-                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + half * 2;
+                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
+                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
 #pragma unroll
-                for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
-                w[kHalfWords] = 0;
-                sw[0] = fail ? 0u : ~sg[0];
-                sw[1] = fail ? 0u : ~sg[1];
+                for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
+                w[BITS] = 0;
+                sw = fail ? 0u : ~sg[0];
             }
             __syncwarp();
             if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
             TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
-            if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
-            TQ_PROF_CODE(c1 = clock64(); pc[2] += c1 - c0;)
-            tc_fence_after();
-            TQ_PROF_CODE(c0 = clock64(); pc[3] += c0 - c1;)
-            const uint32_t abase = tmem + lane_addr + b * kBufCols + half * 32;
+            // expand while the A buffer may still be in use; only the stores wait for it
+            uint32_t hi[16], lo[16], sg[16];
 #pragma unroll
-            for (int sb = 0; sb < 2; ++sb) {
-                uint32_t hi[16], lo[16], sg[16];
-#pragma unroll
-                for (int p = 0; p < 16; ++p) {
-                    const int pair = sb * 16 + p;
-                    const int bit = pair * 2 * BITS, wi = bit >> 5, sh = bit & 31;
-                    uint32_t e;
-                    if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
-                    else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
-                    const uint2 v = lut_lane[e * 32];
-                    hi[p] = v.x;
-                    lo[p] = v.y;
-                    // sign word sb covers coordinates 32*sb .. 32*sb+31 of this half; pair p: bits p, 16+p
-                    sg[p] = ((sw[sb] << (15 - p)) & 0x80008000u) | 0x3c003c00u;
-                }
-                tmem_st16(abase + kColHi + sb * 16, hi);
-                tmem_st16(abase + kColLo + sb * 16, lo);
-                tmem_st16(abase + kColSg + sb * 16, sg);
+            for (int p = 0; p < 16; ++p) {
+                const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                uint32_t e;
+                if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                const uint2 v = lut_lane[e * 32];
+                hi[p] = v.x;
+                lo[p] = v.y;
+                // the sign word covers the 32 coordinates of this part; pair p: bits p, 16+p
+                sg[p] = ((sw << (15 - p)) & 0x80008000u) | 0x3c003c00u;
             }
             TQ_PROF_CODE(c1 = clock64(); pc[4] += c1 - c0;)
+            if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+            TQ_PROF_CODE(c0 = clock64(); pc[2] += c0 - c1;)
+            tc_fence_after();
+            const uint32_t abase = tmem + lane_addr + b * kBufCols + part * 16;
+            tmem_st16(abase + kColHi, hi);
+            tmem_st16(abase + kColLo, lo);
+            tmem_st16(abase + kColSg, sg);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+            TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
 #ifdef TQ_PROF
             if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
                 for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
-                a.prof[5] = clock64() - c1;  // last st wait
                 a.prof[6] = t1 - t0;
             }
 #endif
@@ -346,6 +384,8 @@ score_tc_kernel(const ScoreTcArgs a) {
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
+        const bool store_leader = threadIdx.x == kFirstEpiWarp * 32;
         int64_t prev_g = -1, gcount = 0;
         int bb = 0;
         int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
@@ -359,7 +399,7 @@ score_tc_kernel(const ScoreTcArgs a) {
             r_out = live_n ? __ldg(a.rnorms + grow_n) : 0.f;
         };
         float nrm_next = 0.f, rn_next = 0.f;
-        if (t0 < t1) fetch_norms(g, kt, nrm_next, rn_next);
+        if (t0 < t1 && !a.norms_bulk) fetch_norms(g, kt, nrm_next, rn_next);
         for (int64_t t = t0; t < t1; ++t, ++kt) {
             if (kt == a.tiles_per_group) { kt = 0; ++g; }
             const int64_t i = t - t0;
@@ -368,11 +408,24 @@ score_tc_kernel(const ScoreTcArgs a) {
             if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
             const int64_t key = kt * kTileKeys + row;          // within this launch's key range
             const bool live = key < a.key_cnt;
-            const float nrm = nrm_next;
-            const float arn = a.alpha * rn_next;
-            if (t + 1 < t1) {
-                const bool wrap = kt + 1 == a.tiles_per_group;
-                fetch_norms(wrap ? g + 1 : g, wrap ? 0 : kt + 1, nrm_next, rn_next);
+            float nrm, arn;
+            if (a.norms_bulk) {
+                // norms ride in the key ring (a load from global memory here costs a full trip to HBM per tile,
+                // which one tile of lookahead does not hide once a tile takes less than a microsecond)
+                const int s = (int)(i % kStages);
+                mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+                const float* nr = reinterpret_cast<const float*>(smem + L::off_ring + s * L::kStageBytes + L::kNormOff);
+                nrm = live ? nr[row] : 0.f;
+                arn = live ? a.alpha * nr[kTileKeys + row] : 0.f;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(SB_K_EMPTY + s));
+            } else {
+                nrm = nrm_next;
+                arn = a.alpha * rn_next;
+                if (t + 1 < t1) {
+                    const bool wrap = kt + 1 == a.tiles_per_group;
+                    fetch_norms(wrap ? g + 1 : g, wrap ? 0 : kt + 1, nrm_next, rn_next);
+                }
             }
             TQ_PROF_CODE(long long c0 = clock64();)
             const int db = kDBufs == 2 ? b : 0;
@@ -380,28 +433,51 @@ score_tc_kernel(const ScoreTcArgs a) {
             mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
             tc_fence_after();
             TQ_PROF_CODE(long long c1 = clock64();)
-            const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
             const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
-            uint32_t ua[16], ub[16], va[16], vb[16];
-            tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
-            tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
-            tmem_ld16(dbase + 2 * QPAD, va);       // Sg p_hi
-            tmem_ld16(dbase + 3 * QPAD, vb);       // Sg p_lo
-            tmem_wait_ld();
-            TQ_PROF_CODE(long long c2 = clock64();)
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
             const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB) + q16;
-            float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
-            if (live) {
+            float sc[16];
+            {
+                uint32_t ua[16], ub[16];
+                tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
+                tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
+                tmem_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 16; ++k) sc[k] = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].x;
+                tmem_ld16(dbase + 2 * QPAD, ua);       // Sg p_hi
+                tmem_ld16(dbase + 3 * QPAD, ub);       // Sg p_lo
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const float s2 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].y;
+                    sc[k] = nrm * fmaf(arn, s2, sc[k]);
+                }
+            }
+            TQ_PROF_CODE(long long c2 = clock64();)
+            if (a.tile_store) {
+                // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
+                // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
+                // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
+                // i - 2 must have read its buffer before tile i overwrites it.
+                float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
+                if (store_leader) bulk_wait_read<1>();
+                bar_sync(kEpiBarrier, kEpiThreads);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
+                fence_async_smem();
+                bar_sync(kEpiBarrier, kEpiThreads);
+                if (store_leader) {
+                    tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
+                    bulk_commit();
+                }
+            } else if (live) {
+                float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
                     if (q16 + k < a.nq) {
-                        const float2 sc = ds[k];  // (descale of D1, descale of D2)
-                        const float s1 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * sc.x;
-                        const float s2 = (__uint_as_float(va[k]) + __uint_as_float(vb[k])) * sc.y;
-                        __stcs(out, nrm * fmaf(arn, s2, s1));
+                        __stcs(out, sc[k]);
                         out += a.out_row_stride;
                     }
                 }
@@ -417,11 +493,13 @@ score_tc_kernel(const ScoreTcArgs a) {
                 if (lane == 0) mbar_arrive(BAR(SB_B_EMPTY + bb));
             }
         }
+        if (store_leader) bulk_wait_all();   // the staged tiles must have left before the block's shared memory goes away
     }
 
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 2ull);
+    TQ_PROF_CODE(if (a.prof && blockIdx.x == 0 && threadIdx.x == 0) { a.prof[16] = clock64() - prof_t0; a.prof[17] = prof_t1 - prof_t0; })
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
@@ -574,10 +652,10 @@ int pow2_at_least(int v) {
 }
 
 template <int BITS, int QPAD, int DR>
-int launch_score(const ScoreTcArgs& args, int grid, cudaStream_t st) {
+int launch_score(const CUtensorMap& map, const ScoreTcArgs& args, int grid, cudaStream_t st) {
     const int sm = ScoreSmem<BITS, QPAD, DR>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(args);
+    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args);
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -661,16 +739,32 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             a.out_group_stride = group_stride; a.out_row_stride = row_stride;
             a.scores = mat + (int64_t)q0 * row_stride;
             a.alpha = p->dev.alpha;
+            a.norms_bulk = (groups == 1 || group_rows % 4 == 0) && key_off % 4 == 0 ? 1 : 0;   // 16-byte aligned tile starts
             a.status = p->counters + 1;
 #ifdef TQ_PROF
             a.prof = reinterpret_cast<long long*>(p->counters + 8);
 #endif
             const int grid = (int)(a.total_tiles < sms ? a.total_tiles : sms);
+            // Score tiles leave through a bulk tensor store when the matrix allows one: 16-byte aligned base and
+            // row pitch.  Box = 128 keys x the queries of the pass x one group; extents clip ragged edges.
+            CUtensorMap map;
+            memset(&map, 0, sizeof(map));
+            a.tile_store = 0;
+            if ((reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0 && row_stride % 4 == 0 && key_cnt > 0 && tq_encode_tiled_fn()) {
+                const cuuint64_t gdim[3] = {(cuuint64_t)key_cnt, (cuuint64_t)nq, (cuuint64_t)groups};
+                const cuuint64_t gstride[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)group_stride * 4};
+                const cuuint32_t box[3] = {(cuuint32_t)kTileKeys, (cuuint32_t)qpad, 1};
+                const cuuint32_t estr[3] = {1, 1, 1};
+                const CUresult cr = tq_encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, a.scores, gdim, gstride, box, estr,
+                                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (cr == CUDA_SUCCESS) a.tile_store = 1;
+            }
             int r = TQ_ERR_UNSUPPORTED;
 #define TQ_SC(B)                                                                                             \
     case B:                                                                                                  \
-        if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(a, grid, st) : launch_score<B, 32, 64>(a, grid, st);   \
-        else r = qpad == 16 ? launch_score<B, 16, 128>(a, grid, st) : launch_score<B, 32, 128>(a, grid, st);                \
+        if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(map, a, grid, st) : launch_score<B, 32, 64>(map, a, grid, st);   \
+        else r = qpad == 16 ? launch_score<B, 16, 128>(map, a, grid, st) : launch_score<B, 32, 128>(map, a, grid, st);                \
         break;
             switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }
 #undef TQ_SC

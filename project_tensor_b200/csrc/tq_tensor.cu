@@ -703,22 +703,6 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // fp16 bits of a float, round to nearest even (host)
 uint16_t host_half_bits(float f) {
     const __half h = __float2half_rn(f);
@@ -794,6 +778,18 @@ bool build_cell_lut(const float* bnd_scaled, int nb, float margin, float* scale,
 
 }  // namespace
 
+TqEncodeTiledFn tq_encode_tiled_fn() {
+    static TqEncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TqEncodeTiledFn>(p);
+    }
+    return fn;
+}
+
 struct TensorConsts {
     void* dev = nullptr;   // one allocation: operand matrices + lookup tables
     TensorArgs args{};     // pointers into `dev` and the scalar parameters
@@ -858,7 +854,7 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     bool ok = cudaMemcpy(base, mats.data(), mat_bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
               cudaMemcpy(base + mat_bytes, lut4, sizeof(lut4), cudaMemcpyHostToDevice) == cudaSuccess &&
               cudaMemcpy(base + mat_bytes + sizeof(lut4), lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
-    if (!ok || !encode_tiled_fn()) {
+    if (!ok || !tq_encode_tiled_fn()) {
         cudaFree(t->dev);
         delete t;
         return tq_fail(TQ_ERR_CUDA, "upload of tensor-path constants failed");
@@ -916,7 +912,7 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     const cuuint64_t gstride[1] = {(cuuint64_t)d * 4};
     const cuuint32_t box[2] = {32, (cuuint32_t)kTileRows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), gdim, gstride,
+    const CUresult r = tq_encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), gdim, gstride,
                                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return tq_fail(TQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);

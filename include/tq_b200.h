@@ -58,6 +58,10 @@ const char* tq_last_error(void);
 /* Number of CUDA devices this process can see, or a negative TQ_ERR_*. */
 int tq_device_count(void);
 
+/* Kernels launched by this library in this process so far, all devices and streams (a running total; take
+ * the difference around a region).  No reference counterpart: the reference launches whatever CuPy launches. */
+int64_t tq_kernel_launches(void);
+
 /*
  * Upload the constants of one quantizer to `device`.
  * Replaces the per-call `xp.asarray(self.rotation / codebook / boundaries / projection)` of
@@ -229,6 +233,17 @@ int tq_decode_attention(const tq_plan* kplan, const tq_plan* vplan, const float*
  */
 int tq_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
                   float* out_scores, int64_t* out_idx, void* stream);
+
+/*
+ * The same merge over the result of ONE all-gather: every rank sends one block of `list_bytes` bytes that
+ * holds its float32 [queries][topk] scores at offset 0 and its int64 [queries][topk] indices at offset
+ * `idx_offset_bytes`; `gathered` is the `lists` blocks back to back, as the collective leaves them.  Nothing is
+ * repacked between the scoring call (which writes scores and indices straight into the send block), the
+ * collective and this merge.  list_bytes: a multiple of 8; idx_offset_bytes: a multiple of 16, at least
+ * 4*queries*topk.  No reference counterpart (the reference is single-device).
+ */
+int tq_topk_merge_gathered(const void* gathered, int64_t list_bytes, int64_t idx_offset_bytes, int lists, int queries,
+                           int topk, float* out_scores, int64_t* out_idx, void* stream);
 
 /*
  * Conversions between the packed layouts and the reference's array fields

@@ -20,6 +20,7 @@ SIGNATURES = {
     "tq_version": (c_int, []),
     "tq_last_error": (c_char_p, []),
     "tq_device_count": (c_int, []),
+    "tq_kernel_launches": (c_int64, []),
     "tq_plan_create": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p)]),
     "tq_plan_destroy": (None, [c_void_p]),
     "tq_plan_set_path": (c_int, [c_void_p, c_int]),
@@ -53,6 +54,7 @@ SIGNATURES = {
                                     c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_float, c_void_p, c_void_p, c_size_t,
                                     c_void_p]),
     "tq_topk_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "tq_topk_merge_gathered": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "tq_unpack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_pack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_unpack_signs": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),

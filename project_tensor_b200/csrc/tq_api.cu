@@ -6,6 +6,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -71,6 +72,9 @@ bool use_tensor(const tq_plan* p, int* err) {
 }
 }  // namespace
 
+static std::atomic<long long> g_launches{0};
+void tq_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 int tq_fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -83,6 +87,8 @@ extern "C" {
 
 int tq_version(void) { return TQ_VERSION; }
 const char* tq_last_error(void) { return g_err; }
+
+int64_t tq_kernel_launches(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 int tq_device_count(void) {
     int n = 0;
@@ -504,6 +510,25 @@ int tq_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int 
     TQ_TRY(check_ptr(out_idx, "out_idx"));
     return tq_launch_topk_merge(in_scores, in_idx, lists, queries, topk, out_scores, out_idx,
                                 static_cast<cudaStream_t>(stream));
+}
+
+int tq_topk_merge_gathered(const void* gathered, int64_t list_bytes, int64_t idx_offset_bytes, int lists, int queries,
+                           int topk, float* out_scores, int64_t* out_idx, void* stream) {
+    if (lists < 1 || queries < 0 || topk < 1 || topk > TQ_MAX_TOPK)
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "bad merge sizes lists=%d queries=%d topk=%d", lists, queries, topk);
+    if ((double)lists * topk >= 4294967295.0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "lists * topk too large");
+    if (queries == 0) return TQ_OK;
+    const int64_t cnt = (int64_t)queries * topk;
+    if (list_bytes % 8 != 0 || idx_offset_bytes % 16 != 0 || idx_offset_bytes < 4 * cnt || list_bytes < idx_offset_bytes + 8 * cnt)
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "block of %lld bytes with indices at %lld does not hold %lld scores and indices",
+                       (long long)list_bytes, (long long)idx_offset_bytes, (long long)cnt);
+    TQ_TRY(check_ptr(gathered, "gathered"));
+    TQ_TRY(check_ptr(out_scores, "out_scores"));
+    TQ_TRY(check_ptr(out_idx, "out_idx"));
+    const unsigned char* base = static_cast<const unsigned char*>(gathered);
+    return tq_launch_topk_merge(reinterpret_cast<const float*>(base), reinterpret_cast<const int64_t*>(base + idx_offset_bytes),
+                                lists, queries, topk, out_scores, out_idx, static_cast<cudaStream_t>(stream), list_bytes / 4,
+                                list_bytes / 8);
 }
 
 int tq_unpack_codes(const tq_plan* p, const void* codes, int64_t n, uint8_t* indices, void* stream) {

@@ -89,6 +89,9 @@ int tq_fail(int code, const char* fmt, ...);
             return tq_fail(TQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
     } while (0)
 
+// Every kernel launch of the library is counted (tq_kernel_launches reports the total).
+void tq_count_launch();
+
 // ---- launchers implemented in the kernel files -----------------------------------------------
 // Exact (reference-order float32) kernels.  With `lists` null every row is computed; otherwise
 // first the listed coordinates are re-decided (tq_launch_exact_code_check), then the listed rows
@@ -157,8 +160,10 @@ int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float
                                const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes,
                                cudaStream_t st);
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk);
+// list strides in elements (floats / int64s); 0 = the lists follow one another, queries * topk entries each
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
-                         float* out_scores, int64_t* out_idx, cudaStream_t st);
+                         float* out_scores, int64_t* out_idx, cudaStream_t st, int64_t score_list_stride = 0,
+                         int64_t idx_list_stride = 0);
 
 // Packing helpers.
 int tq_launch_unpack_codes(const tq_plan* p, const uint32_t* codes, int64_t n, uint8_t* out, cudaStream_t st);

@@ -508,10 +508,10 @@ int launch_partial(const tq_plan* kp, DecodeArgs a, int groups, int passes, cuda
     const dim3 grid((unsigned)a.splits, (unsigned)passes, (unsigned)groups);
     if (a.vbits == 3) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        decode_partial_kernel<KB, DR, QP, true><<<grid, kThreads, sm, st>>>(kp->dev, a);
+        decode_partial_kernel<KB, DR, QP, true><<<grid, kThreads, sm, st>>>(kp->dev, a); tq_count_launch();
     } else {
         TQ_CUDA_TRY(cudaFuncSetAttribute(decode_partial_kernel<KB, DR, QP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        decode_partial_kernel<KB, DR, QP, false><<<grid, kThreads, sm, st>>>(kp->dev, a);
+        decode_partial_kernel<KB, DR, QP, false><<<grid, kThreads, sm, st>>>(kp->dev, a); tq_count_launch();
     }
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
@@ -567,7 +567,7 @@ int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float
     switch (kb) { TQ_DEC(1) TQ_DEC(2) TQ_DEC(3) TQ_DEC(4) }
 #undef TQ_DEC
     if (r != TQ_OK) return r;
-    decode_combine_kernel<<<(unsigned)(groups * qpg), (d + 31) & ~31, d * sizeof(float), st>>>(a.part, a.splits, d, vp->dev.R, out);
+    decode_combine_kernel<<<(unsigned)(groups * qpg), (d + 31) & ~31, d * sizeof(float), st>>>(a.part, a.splits, d, vp->dev.R, out); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

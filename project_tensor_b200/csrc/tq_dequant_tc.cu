@@ -460,7 +460,7 @@ template <int BITS, bool PROD, int DR, bool PAIR = false>
 int launch_one(const DequantArgs& args, int grid, cudaStream_t st) {
     const int sm = DqSmem<BITS, PROD, DR>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(dequant_tc_kernel<BITS, PROD, DR, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    dequant_tc_kernel<BITS, PROD, DR, PAIR><<<grid, kThreads, sm, st>>>(args);
+    dequant_tc_kernel<BITS, PROD, DR, PAIR><<<grid, kThreads, sm, st>>>(args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -450,7 +450,7 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
                                const TqRecheck* lists, cudaStream_t st) {
     if (n == 0) return TQ_OK;
     const int dp = (p->dev.d + 31) & ~31;
-    exact_code_check_kernel<<<148 * 8, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists);
+    exact_code_check_kernel<<<148 * 8, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -469,7 +469,7 @@ int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_
 #define TQ_LAUNCH_EXACT(P, M, T)                                                                                           \
     do {                                                                                                                  \
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_quantize_kernel<P, M, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
-        exact_quantize_kernel<P, M, T><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map); \
+        exact_quantize_kernel<P, M, T><<<grid, threads, sm, st>>>(p->dev, x, n, codes, signs, rnorms, norms, lists, redo_counter, map); tq_count_launch(); \
     } while (0)
 #define TQ_LAUNCH_EXACT_T(P, M)                  \
     do {                                         \
@@ -496,7 +496,7 @@ __global__ void append_advance_kernel(int64_t* length, int64_t tokens, int64_t c
 }
 
 int tq_launch_append_advance(int64_t* length, int64_t tokens, int64_t capacity, cudaStream_t st) {
-    append_advance_kernel<<<1, 1, 0, st>>>(length, tokens, capacity);
+    append_advance_kernel<<<1, 1, 0, st>>>(length, tokens, capacity); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -511,10 +511,10 @@ int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* code
     const int threads = (d + 31) & ~31;
     if (prod) {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_dequantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_dequantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
+        exact_dequantize_kernel<true><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out); tq_count_launch();
     } else {
         TQ_CUDA_TRY(cudaFuncSetAttribute(exact_dequantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        exact_dequantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out);
+        exact_dequantize_kernel<false><<<grid, threads, sm, st>>>(p->dev, codes, signs, rnorms, norms, n, out); tq_count_launch();
     }
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
@@ -527,7 +527,7 @@ int tq_launch_exact_pairwise(const tq_plan* p, const float* q, const uint32_t* c
     const int dp = (p->dev.d + 31) & ~31;
     const size_t sm = (size_t)kWarps * 3 * dp * sizeof(float);
     TQ_CUDA_TRY(cudaFuncSetAttribute(exact_pairwise_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-    exact_pairwise_score_kernel<<<grid_for(n, kWarps), kWarps * 32, sm, st>>>(p->dev, q, codes, signs, rnorms, norms, n, scores);
+    exact_pairwise_score_kernel<<<grid_for(n, kWarps), kWarps * 32, sm, st>>>(p->dev, q, codes, signs, rnorms, norms, n, scores); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -68,25 +68,25 @@ int blocks_for(int64_t total) {
 
 int tq_launch_unpack_codes(const tq_plan* p, const uint32_t* codes, int64_t n, uint8_t* out, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    unpack_codes_kernel<<<blocks_for(n * p->dev.d), 256, 0, st>>>(codes, n, p->dev.d, p->dev.bits, p->dev.code_words, out);
+    unpack_codes_kernel<<<blocks_for(n * p->dev.d), 256, 0, st>>>(codes, n, p->dev.d, p->dev.bits, p->dev.code_words, out); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
 int tq_launch_pack_codes(const tq_plan* p, const uint8_t* in, int64_t n, uint32_t* codes, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    pack_codes_kernel<<<blocks_for(n * p->dev.code_words), 256, 0, st>>>(in, n, p->dev.d, p->dev.bits, p->dev.code_words, codes);
+    pack_codes_kernel<<<blocks_for(n * p->dev.code_words), 256, 0, st>>>(in, n, p->dev.d, p->dev.bits, p->dev.code_words, codes); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
 int tq_launch_unpack_signs(const tq_plan* p, const uint32_t* signs, int64_t n, int8_t* out, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    unpack_signs_kernel<<<blocks_for(n * p->dev.d), 256, 0, st>>>(signs, n, p->dev.d, p->dev.sign_words, out);
+    unpack_signs_kernel<<<blocks_for(n * p->dev.d), 256, 0, st>>>(signs, n, p->dev.d, p->dev.sign_words, out); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
 int tq_launch_pack_signs(const tq_plan* p, const int8_t* in, int64_t n, uint32_t* signs, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    pack_signs_kernel<<<blocks_for(n * p->dev.sign_words), 256, 0, st>>>(in, n, p->dev.d, p->dev.sign_words, signs);
+    pack_signs_kernel<<<blocks_for(n * p->dev.sign_words), 256, 0, st>>>(in, n, p->dev.d, p->dev.sign_words, signs); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -197,20 +197,21 @@ merge_keys_kernel(const unsigned long long* __restrict__ part, int lists, int qp
 // Merge (score, index) lists gathered from several shards: [lists][queries][topk] -> [queries][topk].
 __global__ void __launch_bounds__(256)
 merge_pairs_kernel(const float* __restrict__ in_scores, const int64_t* __restrict__ in_idx, int lists,
-                   int queries, int topk, int k2, float* __restrict__ out_scores,
-                   int64_t* __restrict__ out_idx) {
+                   size_t score_list_stride, size_t idx_list_stride, int queries, int topk, int k2,
+                   float* __restrict__ out_scores, int64_t* __restrict__ out_idx) {
     extern __shared__ __align__(16) unsigned char smraw[];
     unsigned long long* a = reinterpret_cast<unsigned long long*>(smraw);  // [2*k2]
     const int qi = blockIdx.x;
     for (int i = threadIdx.x; i < 2 * k2; i += blockDim.x) a[i] = 0ull;
     __syncthreads();
     for (int l = 0; l < lists; ++l) {
-        const size_t base = ((size_t)l * queries + qi) * topk;
+        const size_t row = (size_t)qi * topk;   // lists may lie apart (one block per rank after an all-gather)
         for (int i = threadIdx.x; i < k2; i += blockDim.x) {
             unsigned long long ck = 0ull;
             // position in the concatenation of all lists stands in for the index: earlier list and
             // earlier slot win ties, which is ascending row order for contiguous shards
-            if (i < topk && in_idx[base + i] >= 0) ck = make_key(in_scores[base + i], (uint32_t)(l * topk + i));
+            if (i < topk && in_idx[l * idx_list_stride + row + i] >= 0)
+                ck = make_key(in_scores[l * score_list_stride + row + i], (uint32_t)(l * topk + i));
             a[k2 + i] = ck;
         }
         block_sort_desc(a, 2 * k2);
@@ -223,9 +224,9 @@ merge_pairs_kernel(const float* __restrict__ in_scores, const int64_t* __restric
             out_idx[o] = -1;
         } else {
             const uint32_t pos = 0xffffffffu - (uint32_t)ck;
-            const size_t src = ((size_t)(pos / topk) * queries + qi) * topk + (pos % topk);
-            out_scores[o] = in_scores[src];
-            out_idx[o] = in_idx[src];
+            const size_t l = pos / topk, src = (size_t)qi * topk + (pos % topk);
+            out_scores[o] = in_scores[l * score_list_stride + src];
+            out_idx[o] = in_idx[l * idx_list_stride + src];
         }
     }
 }
@@ -286,7 +287,7 @@ int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int
                          float* top_scores, int64_t* top_idx, cudaStream_t st) {
     const int k2 = pow2_at_least(topk);
     merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(part, lists, qpg, topk, k2,
-                                                                                           idx_base, top_scores, top_idx);
+                                                                                           idx_base, top_scores, top_idx); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -331,7 +332,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
             const size_t cnt = (size_t)groups * qpg * topk;
             TQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, cnt * sizeof(unsigned long long), st));
             merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(
-                static_cast<unsigned long long*>(scratch), 1, qpg, topk, pow2_at_least(topk), idx_base, top_scores, top_idx);
+                static_cast<unsigned long long*>(scratch), 1, qpg, topk, pow2_at_least(topk), idx_base, top_scores, top_idx); tq_count_launch();
             TQ_CUDA_TRY(cudaGetLastError());
         }
         return TQ_OK;
@@ -342,23 +343,26 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     score_kernel<<<dim3(s.nblk, groups), kThreads, sm, st>>>(p->dev, q, qpg, codes, signs, rnorms, norms,
                                                              keys_per_group, group_rows, s.keys_per_block, scores, topk, s.cap2,
-                                                             static_cast<unsigned long long*>(scratch));
+                                                             static_cast<unsigned long long*>(scratch)); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     if (topk > 0) {
         const int k2 = pow2_at_least(topk);
         merge_keys_kernel<<<dim3(qpg, groups), 256, 0, st>>>(
-            static_cast<unsigned long long*>(scratch), s.nblk, qpg, topk, k2, idx_base, top_scores, top_idx);
+            static_cast<unsigned long long*>(scratch), s.nblk, qpg, topk, k2, idx_base, top_scores, top_idx); tq_count_launch();
         TQ_CUDA_TRY(cudaGetLastError());
     }
     return TQ_OK;
 }
 
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
-                         float* out_scores, int64_t* out_idx, cudaStream_t st) {
+                         float* out_scores, int64_t* out_idx, cudaStream_t st, int64_t score_list_stride,
+                         int64_t idx_list_stride) {
     if (queries == 0) return TQ_OK;
     const int k2 = pow2_at_least(topk);
-    merge_pairs_kernel<<<queries, 256, 2 * k2 * sizeof(unsigned long long), st>>>(in_scores, in_idx, lists, queries,
-                                                                                  topk, k2, out_scores, out_idx);
+    if (score_list_stride <= 0) score_list_stride = (int64_t)queries * topk;
+    if (idx_list_stride <= 0) idx_list_stride = (int64_t)queries * topk;
+    merge_pairs_kernel<<<queries, 256, 2 * k2 * sizeof(unsigned long long), st>>>(in_scores, in_idx, lists, (size_t)score_list_stride,
+                                                                                  (size_t)idx_list_stride, queries, topk, k2, out_scores, out_idx); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -137,7 +137,7 @@ int launch_few(const tq_plan* p, const float* q, const uint32_t* codes, const ui
     const int64_t cap = (int64_t)sms * 4;   // the tables cost a few microseconds per block: a few blocks per SM, grid-stride
     if (blocks > cap) blocks = cap;
     score_few_kernel<BITS, DR><<<dim3((unsigned)blocks, (unsigned)qpg, (unsigned)groups), kFewThreads, sm, st>>>(
-        p->dev, q, codes, signs, rnorms, norms, keys_per_group, group_rows, qpg, scores);
+        p->dev, q, codes, signs, rnorms, norms, keys_per_group, group_rows, qpg, scores); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

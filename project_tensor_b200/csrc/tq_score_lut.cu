@@ -200,7 +200,7 @@ int launch_lut(const tq_plan* p, const float* q, const uint32_t* codes, const ui
     if (blocks > tiles) blocks = tiles;
     if (blocks < 1) blocks = 1;
     score_lut_kernel<KB, DR><<<dim3((unsigned)blocks, 1, (unsigned)groups), kThreads, sm, st>>>(
-        p->dev, q, codes, signs, rnorms, norms, n, group_rows, qpg, scores);
+        p->dev, q, codes, signs, rnorms, norms, n, group_rows, qpg, scores); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -655,7 +655,7 @@ template <int BITS, int QPAD, int DR>
 int launch_score(const CUtensorMap& map, const ScoreTcArgs& args, int grid, cudaStream_t st) {
     const int sm = ScoreSmem<BITS, QPAD, DR>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args);
+    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -727,7 +727,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
             const int qpad = nq <= 16 ? 16 : 32;
             TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
-            score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep);
+            score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
             TQ_CUDA_TRY(cudaGetLastError());
             ScoreTcArgs a{};
             a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
@@ -775,7 +775,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
             topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, 0, st>>>(
                 mat, row_stride, group_stride, qpg, key_cnt, kSegLen, group_rows, key_off, topk, pow2_at_least(topk),
-                (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part);
+                (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part); tq_count_launch();
             TQ_CUDA_TRY(cudaGetLastError());
         }
     }

@@ -884,7 +884,7 @@ template <int D, int BITS, bool PROD>
 static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
     const int sm = Smem<D, PROD>::total;
     TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize_kernel<D, BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    tensor_quantize_kernel<D, BITS, PROD><<<grid, Threads<PROD>::kThreads, sm, st>>>(map, args);
+    tensor_quantize_kernel<D, BITS, PROD><<<grid, Threads<PROD>::kThreads, sm, st>>>(map, args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -26,6 +26,11 @@ def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
+class ShardExchangeTimeout(RuntimeError):
+    """The all-gather of a TopkExchange did not complete in time: a rank is missing, hung or gone.  The
+    process group is unusable afterwards (its abort has been asked for where the backend has one)."""
+
+
 def _merge_on_gpu(gathered_scores, gathered_idx):
     """[W, Q, k] candidate lists -> ([Q, k], [Q, k]) through tq_topk_merge."""
     import torch
@@ -39,32 +44,100 @@ def _merge_on_gpu(gathered_scores, gathered_idx):
     return out_s, out_i
 
 
-def merge_topk_across_ranks(top_scores, top_idx, group=None, merge: Optional[Callable] = None):
+class TopkExchange:
+    """The one collective of the path: every rank's per-query top-k -> the global top-k on every rank.
+
+    A rank owns one send block of bytes, float32 [Q][k] scores at offset 0 and int64 [Q][k] global indices at
+    a 16-byte aligned offset behind them.  ``top_scores`` / ``top_idx`` are views of that block: hand them to
+    ``TurboQuantProd.attention_scores(..., out=(ex.top_scores, ex.top_idx))`` and the scoring call writes the
+    candidates where the collective reads them.  ``start()`` enqueues ONE all-gather of the blocks without
+    blocking the host or the compute stream; ``finish()`` makes the current stream wait for it and runs the merge
+    kernel straight on the gathered blocks (``tq_topk_merge_gathered``).  Between the two the caller may enqueue the
+    next step's work, which then overlaps the collective.
+
+    ``timeout_s``: with a value, ``finish()`` waits on the host, at most that long, for the collective; when the
+    time runs out it asks the backend to abort the group and raises ``ShardExchangeTimeout`` instead of hanging on
+    a rank that never joined.  ``merge`` replaces the GPU merge kernel by a function of the gathered
+    ``(scores [W, Q, k], idx [W, Q, k])``; the CPU tests run the plumbing over gloo that way.
+    """
+
+    def __init__(self, queries: int, k: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        self.queries, self.k, self.group = int(queries), int(k), group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        cnt = self.queries * self.k
+        self.idx_offset = (4 * cnt + 15) // 16 * 16
+        self.block_bytes = self.idx_offset + 8 * cnt
+        self.send = torch.empty((self.block_bytes,), dtype=torch.uint8, device=device)
+        self.top_scores = self.send[:4 * cnt].view(torch.float32).view(self.queries, self.k)
+        self.top_idx = self.send[self.idx_offset:].view(torch.int64).view(self.queries, self.k)
+        self.gathered = (self.send[None] if self.world == 1 else
+                         torch.empty((self.world, self.block_bytes), dtype=torch.uint8, device=device))
+        self._work = None
+
+    def start(self):
+        import torch.distributed as dist
+        if self.world > 1:
+            if self.send.is_cuda:
+                self._work = dist.all_gather_into_tensor(self.gathered, self.send, group=self.group, async_op=True)
+            else:  # gloo
+                self._work = dist.all_gather(list(self.gathered.unbind(0)), self.send, group=self.group, async_op=True)
+        return self
+
+    def _abort_group(self):
+        import torch.distributed as dist
+        try:
+            pg = self.group if self.group is not None else dist.group.WORLD
+            backend = pg._get_backend(self.send.device)
+            if hasattr(backend, "abort"):
+                backend.abort()
+        except Exception:
+            pass    # best effort: the caller gets the time-out either way
+
+    def finish(self, merge: Optional[Callable] = None, timeout_s: Optional[float] = None):
+        import time
+        import torch
+        work, self._work = self._work, None
+        if work is not None:
+            if timeout_s is not None:
+                deadline = time.monotonic() + float(timeout_s)
+                while not work.is_completed():
+                    if time.monotonic() > deadline:
+                        self._abort_group()
+                        raise ShardExchangeTimeout(
+                            f"all-gather of the top-{self.k} candidates did not complete within {timeout_s} s "
+                            f"({self.world} ranks expected)")
+                    time.sleep(0.0005)
+            work.wait()     # NCCL: the current stream waits for the collective; gloo: the host does
+        cnt = self.queries * self.k
+        if merge is not None:
+            gs = self.gathered[:, :4 * cnt].contiguous().view(torch.float32).view(self.world, self.queries, self.k)
+            gi = self.gathered[:, self.idx_offset:].contiguous().view(torch.int64).view(self.world, self.queries, self.k)
+            return merge(gs, gi)
+        dev = self.send.device
+        out_s = torch.empty((self.queries, self.k), dtype=torch.float32, device=dev)
+        out_i = torch.empty((self.queries, self.k), dtype=torch.int64, device=dev)
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            _native.check(_native.load().tq_topk_merge_gathered(
+                self.gathered.data_ptr(), self.block_bytes, self.idx_offset, self.world, self.queries, self.k,
+                out_s.data_ptr(), out_i.data_ptr(), stream))
+        return out_s, out_i
+
+
+def merge_topk_across_ranks(top_scores, top_idx, group=None, merge: Optional[Callable] = None,
+                            timeout_s: Optional[float] = None):
     """All-gather every rank's per-query top-k (``top_scores`` float32 [Q, k] descending, ``top_idx``
     int64 [Q, k] global key indices) and merge them into the global top-k, identical on all ranks.
     Ties go to the lower rank, i.e. to the lower global index for contiguous shards.
 
-    ``merge`` replaces the GPU merge kernel; the CPU tests use it to exercise the gather plumbing
-    over gloo without a device."""
-    import torch
-    import torch.distributed as dist
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    top_scores = top_scores.contiguous()
-    top_idx = top_idx.contiguous()
-    if world == 1:
-        gathered_s, gathered_i = top_scores[None], top_idx[None]
-    else:
-        # one collective for both arrays: the score bits ride in an int64 beside the indices
-        k = top_scores.shape[-1]
-        packed = torch.cat((top_scores.view(torch.int32).to(torch.int64), top_idx), dim=-1)
-        gathered = torch.empty((world,) + tuple(packed.shape), dtype=torch.int64, device=packed.device)
-        if packed.is_cuda:
-            dist.all_gather_into_tensor(gathered, packed, group=group)
-        else:  # gloo
-            dist.all_gather(list(gathered.unbind(0)), packed, group=group)
-        gathered_s = gathered[..., :k].to(torch.int32).view(torch.float32).contiguous()
-        gathered_i = gathered[..., k:].contiguous()
-    return (merge or _merge_on_gpu)(gathered_s, gathered_i)
+    Convenience form of ``TopkExchange`` for results that already exist as two tensors (they are copied into
+    a send block first); see there for ``merge`` and ``timeout_s``."""
+    ex = TopkExchange(top_scores.shape[0], top_scores.shape[1], top_scores.device, group=group)
+    ex.top_scores.copy_(top_scores)
+    ex.top_idx.copy_(top_idx)
+    return ex.start().finish(merge=merge, timeout_s=timeout_s)
 
 
 def gather_score_slabs(scores, group=None):
@@ -135,9 +208,14 @@ class ShardedKeyIndex:
                      self.device, self.quantizer._plans)
         return _encoding_from_packed(TurboQuantProdEncoding, pk, (n,))
 
-    def search(self, queries, k: int, group=None):
-        top_s, top_i = self.quantizer.attention_scores(queries, self.encoding(), topk=k, index_base=self.start)
-        import torch
-        if not isinstance(top_s, torch.Tensor):
-            top_s, top_i = torch.as_tensor(top_s, device=self.device), torch.as_tensor(top_i, device=self.device)
-        return merge_topk_across_ranks(top_s, top_i, group=group)
+    def search_start(self, queries, k: int, group=None) -> TopkExchange:
+        """Score this rank's keys and enqueue the all-gather of the candidates; ``.finish()`` of the returned
+        exchange gives the global (scores, indices).  Work enqueued in between overlaps the collective."""
+        from .turboquant import _stage
+        q = _stage(queries, self.quantizer.dimension, device=self.device).tensor
+        ex = TopkExchange(q.shape[0], k, self.device, group=group)
+        self.quantizer.attention_scores(q, self.encoding(), topk=k, index_base=self.start, out=(ex.top_scores, ex.top_idx))
+        return ex.start()
+
+    def search(self, queries, k: int, group=None, timeout_s: Optional[float] = None):
+        return self.search_start(queries, k, group=group).finish(timeout_s=timeout_s)

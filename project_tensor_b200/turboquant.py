@@ -605,7 +605,8 @@ class TurboQuantProd:
         return _deliver(scores, staged.kind).reshape(shape)
 
     def attention_scores(self, queries: Any, encoding: TurboQuantProdEncoding, *, topk: Optional[int] = None,
-                         groups: int = 1, return_matrix: Optional[bool] = None, index_base: int = 0):
+                         groups: int = 1, return_matrix: Optional[bool] = None, index_base: int = 0,
+                         out: Optional[Tuple[Any, Any]] = None):
         """Score many queries against shared keys in one pass over the packed keys.
 
         ``queries`` has shape (..., d) and flattens to Q rows; the N keys are split into ``groups``
@@ -617,7 +618,9 @@ class TurboQuantProd:
         Returns the score matrix of shape (Q, N // groups) when ``topk`` is None; with ``topk=k``
         returns ``(top_scores, top_indices)`` of shape (Q, k), descending, indices counted over
         all N keys plus ``index_base`` (set ``return_matrix=True`` to get the matrix as a third
-        element as well).
+        element as well).  ``out=(top_scores, top_indices)``: contiguous device tensors of shape (Q, k), float32 and
+        int64, that receive the top-k instead of fresh ones (e.g. the send block of ``sharded.TopkExchange``, so
+        that the candidates need no repacking before the collective).
         """
         pk = _as_packed(encoding, self._plans, need_signs=True)
         staged = _stage(queries, self.dimension, device=pk.device)
@@ -637,8 +640,15 @@ class TurboQuantProd:
         handle = self._plans.handle(pk.device)
         with torch.cuda.device(pk.device):
             scores = torch.empty((nq, kpg), dtype=torch.float32, device=pk.device) if want_matrix else None
-            top_s = torch.empty((nq, k), dtype=torch.float32, device=pk.device) if k else None
-            top_i = torch.empty((nq, k), dtype=torch.int64, device=pk.device) if k else None
+            if out is not None and k:
+                top_s, top_i = out
+                if (tuple(top_s.shape) != (nq, k) or tuple(top_i.shape) != (nq, k) or top_s.dtype != torch.float32
+                        or top_i.dtype != torch.int64 or not top_s.is_contiguous() or not top_i.is_contiguous()
+                        or top_s.device != pk.device or top_i.device != pk.device):
+                    raise ValueError(f"out must be contiguous float32 / int64 tensors of shape ({nq}, {k}) on {pk.device}")
+            else:
+                top_s = torch.empty((nq, k), dtype=torch.float32, device=pk.device) if k else None
+                top_i = torch.empty((nq, k), dtype=torch.int64, device=pk.device) if k else None
             need = int(lib.tq_topk_scratch_bytes(handle, groups, qpg, kpg, k))
             scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=pk.device)
             _native.check(lib.tq_score_batched(handle, _ptr(q), groups, qpg, _ptr(pk.codes), _ptr(pk.signs),

@@ -73,3 +73,52 @@ def test_two_rank_gather_and_merge_over_gloo():
         ret = mgr.dict()
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert ret.get(0) and ret.get(1)
+
+
+def _absent_rank_worker(rank, world, port, ret):
+    """Rank 1 initialises the group and then never enters the collective (it sleeps and leaves); rank 0 must get
+    ShardExchangeTimeout after its limit instead of waiting forever.  Host-side failure only: no device involved."""
+    import time
+    from project_tensor_b200.sharded import ShardExchangeTimeout, TopkExchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if rank == 1:
+        time.sleep(4.0)
+        ret[1] = "left without joining"
+        os._exit(0)
+    ex = TopkExchange(3, 5, torch.device("cpu"))
+    ex.top_scores.copy_(torch.arange(15, dtype=torch.float32).view(3, 5))
+    ex.top_idx.copy_(torch.arange(15, dtype=torch.int64).view(3, 5))
+    t0 = time.monotonic()
+    try:
+        ex.start().finish(merge=numpy_merge, timeout_s=1.0)
+        ret[0] = "returned"
+    except ShardExchangeTimeout as exc:
+        ret[0] = ("timeout", time.monotonic() - t0, str(exc))
+    os._exit(0)      # the group is unusable after the time-out; do not wait for the absent rank on the way out
+
+
+def test_exchange_times_out_when_a_rank_never_joins():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_absent_rank_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert ret.get(1) == "left without joining"
+        kind, waited, msg = ret.get(0)
+        assert kind == "timeout" and 0.9 <= waited < 3.0, (kind, waited)
+        assert "did not complete within" in msg and "2 ranks" in msg
+
+
+def test_exchange_block_layout():
+    """The send block holds scores and indices at the offsets tq_topk_merge_gathered is told about."""
+    from project_tensor_b200.sharded import TopkExchange
+    ex = TopkExchange(3, 5, torch.device("cpu"))
+    assert ex.idx_offset % 16 == 0 and ex.idx_offset >= 4 * 15 and ex.block_bytes == ex.idx_offset + 8 * 15
+    ex.top_scores.fill_(1.5)
+    ex.top_idx.fill_(7)
+    assert ex.send[:60].view(torch.float32).eq(1.5).all()
+    assert ex.send[ex.idx_offset:].view(torch.int64).eq(7).all()
+    got_s, got_i = ex.start().finish(merge=numpy_merge)      # world of one: nothing to gather
+    assert got_s.shape == (3, 5) and bool((got_i == 7).all())

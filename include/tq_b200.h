@@ -262,6 +262,19 @@ int tq_pack_signs(const tq_plan* plan, const int8_t* qjl, int64_t n, void* signs
  */
 int tq_plan_last_recheck_rows(const tq_plan* plan, void* stream, int64_t* rows);
 
+/*
+ * Bounded waits.  Inside the tensor-core kernels every wait on a barrier has a limit; when one runs out the
+ * kernel stops storing results, lets the copies and tensor instructions it has in flight finish, sets the plan's
+ * status word and returns -- the context stays usable, the outputs of that call are incomplete.
+ * tq_plan_status reads the word back (synchronises `stream`): 0 = no kernel of this plan has given up since the
+ * last query; 1 / 2 / 3 = a quantize / scoring / dequantize kernel has (the word is cleared by the query).  The
+ * Python classes query it wherever they synchronise anyway and raise instead of handing out such results.
+ * tq_plan_set_wait_limit changes the limit (cycles; default about 2 s) for later launches of this plan.
+ * No reference counterpart (NumPy has nothing to wait for).
+ */
+int tq_plan_status(const tq_plan* plan, void* stream, int64_t* status);
+int tq_plan_set_wait_limit(tq_plan* plan, int64_t cycles);
+
 #ifdef __cplusplus
 }
 #endif

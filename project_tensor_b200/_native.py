@@ -60,6 +60,8 @@ SIGNATURES = {
     "tq_unpack_signs": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_pack_signs": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_plan_last_recheck_rows": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
+    "tq_plan_set_wait_limit": (c_int, [c_void_p, c_int64]),
+    "tq_plan_status": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
 }
 
 _lib = None

@@ -55,6 +55,7 @@ class PackedKeyCache:
     def sync_length(self) -> int:
         """Read the length back from the device (needed after replaying a CUDA graph that appends)."""
         self._length = int(self.length_device.item())
+        self._plans.check_status(self.device)
         return self._length
 
     def reset(self) -> None:
@@ -137,9 +138,9 @@ class PackedKeyCache:
                     top_s.fill_(float("-inf"))
                     top_i.fill_(-1)
                 if k == 0:
-                    return _tq._deliver(mat, staged.kind)
-                result = (_tq._deliver(top_s, staged.kind), _tq._deliver(top_i, staged.kind))
-                return result + (_tq._deliver(mat, staged.kind),) if want_matrix else result
+                    return _tq._deliver(mat, staged.kind, self._plans)
+                result = (_tq._deliver(top_s, staged.kind, self._plans), _tq._deliver(top_i, staged.kind))
+                return result + (_tq._deliver(mat, staged.kind, self._plans),) if want_matrix else result
             need = int(lib.tq_topk_scratch_bytes(handle, self.groups, qpg, n, k))
             scratch = torch.empty((max(need, 16),), dtype=torch.uint8, device=dev)
             _native.check(lib.tq_score_cache(handle, q.data_ptr(), self.groups, qpg, self.codes.data_ptr(),
@@ -152,9 +153,9 @@ class PackedKeyCache:
                 base = (torch.arange(self.groups, device=dev, dtype=torch.int64) * self.capacity).view(-1, 1, 1)
                 top_i = torch.where(top_i >= 0, top_i - base, top_i)
         if k == 0:
-            return _tq._deliver(mat, staged.kind)
-        result = (_tq._deliver(top_s, staged.kind), _tq._deliver(top_i, staged.kind))
-        return result + (_tq._deliver(mat, staged.kind),) if want_matrix else result
+            return _tq._deliver(mat, staged.kind, self._plans)
+        result = (_tq._deliver(top_s, staged.kind, self._plans), _tq._deliver(top_i, staged.kind))
+        return result + (_tq._deliver(mat, staged.kind, self._plans),) if want_matrix else result
 
     # ---- views ----------------------------------------------------------------------------------
     def encoding(self, group: int):

@@ -119,6 +119,7 @@ int tq_plan_create(int d, int bits_mse, const float* rotation, const float* code
     memset(p, 0, sizeof(*p));
     p->device = device;
     p->path = TQ_PATH_AUTO;
+    p->wait_kcycles = 4000000;   // ~2 s at 2 GHz
     p->has_projection = projection != nullptr;
     const int levels = 1 << bits_mse;
     const size_t dd = (size_t)d * d;
@@ -445,6 +446,11 @@ int tq_score_cache(const tq_plan* p, const float* q, int groups, int q_per_group
     if ((double)groups * (double)group_rows >= 4294967296.0)
         return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups * keys_per_group must stay below 2^32");
     if (topk < 0 || topk > TQ_MAX_TOPK) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "topk outside [0, %d]", TQ_MAX_TOPK);
+    // the selection kernels run one grid row per (group, query)
+    if (topk > 0 && (int64_t)groups * q_per_group > 65535)
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "top-k over %d groups x %d queries: groups * q_per_group must stay below 65536",
+                       groups, q_per_group);
+    if (q_per_group > 65535) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "q_per_group > 65535");
     if (!scores && topk == 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "nothing to compute: scores is null and topk is 0");
     if (groups == 0 || q_per_group == 0) return TQ_OK;
     TQ_TRY(check_ptr(q, "q"));
@@ -479,6 +485,7 @@ int tq_decode_attention(const tq_plan* kp, const tq_plan* vp, const float* q, in
     if (groups < 0 || q_per_group < 0 || keys_per_group < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "negative size");
     if (group_rows < keys_per_group) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "group_rows is smaller than keys_per_group");
     if (groups > 65535) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups > 65535");
+    if (q_per_group > 65535) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "q_per_group > 65535 (one grid row per pass of queries)");
     if ((double)groups * (double)group_rows >= 4294967296.0)
         return tq_fail(TQ_ERR_INVALID_ARGUMENT, "groups * group_rows must stay below 2^32");
     if (!(scale == scale) || scale < 0.f) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "scale must be a number >= 0 (0 selects d^-1/2)");
@@ -566,6 +573,26 @@ int tq_pack_signs(const tq_plan* p, const int8_t* qjl, int64_t n, void* signs, v
     if (!qjl) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "qjl is null");
     DeviceScope scope(p->device);
     return tq_launch_pack_signs(p, qjl, n, static_cast<uint32_t*>(signs), static_cast<cudaStream_t>(stream));
+}
+
+int tq_plan_set_wait_limit(tq_plan* p, int64_t cycles) {
+    TQ_TRY(check_plan(p, false));
+    if (cycles < 1024 || cycles > (int64_t)1 << 40) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "wait limit outside [2^10, 2^40] cycles");
+    p->wait_kcycles = (int)(cycles >> 10);
+    return TQ_OK;
+}
+
+int tq_plan_status(const tq_plan* p, void* stream, int64_t* status) {
+    TQ_TRY(check_plan(p, false));
+    if (!status) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "status is null");
+    DeviceScope scope(p->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned long long v = 0;
+    TQ_CUDA_TRY(cudaMemcpyAsync(&v, p->counters + 1, sizeof(v), cudaMemcpyDeviceToHost, st));
+    TQ_CUDA_TRY(cudaStreamSynchronize(st));
+    *status = (int64_t)v;
+    if (v != 0) TQ_CUDA_TRY(cudaMemsetAsync(p->counters + 1, 0, sizeof(v), st));   // reported once
+    return TQ_OK;
 }
 
 int tq_plan_last_recheck_rows(const tq_plan* p, void* stream, int64_t* rows) {

@@ -77,7 +77,9 @@ struct tq_plan {
     void* slab;              // one device allocation holding every constant
     TensorConsts* tensor;    // host-side bookkeeping for the tensor-core kernels (may be null)
     DequantConsts* dequant;  // operand matrices of the tensor-core dequantize kernels (may be null)
-    unsigned long long* counters;  // device: [0] rows re-done by the exact kernel in the last quantize
+    unsigned long long* counters;  // device: [0] rows re-done by the exact kernel in the last quantize, [1] status word
+                                   // (non-zero once a tensor-core kernel gave up on a bounded wait; sticky until read)
+    int wait_kcycles;              // limit of a bounded wait inside the tensor-core kernels, in units of 1024 cycles
 };
 
 // ---- error plumbing (tq_api.cu) -------------------------------------------------------------

@@ -58,6 +58,7 @@ struct DequantArgs {
     float* out;                  // reconstructions [n][d]; or, in pair mode, scores [n]
     const float* pair_q;         // pair mode: one query row per key, [n][d]
     unsigned long long* status;
+    int wait_kcycles;            // limit of one bounded wait, in units of 1024 cycles
 };
 
 enum {
@@ -126,7 +127,8 @@ dequant_tc_kernel(const DequantArgs a) {
         for (int i = 0; i < 8; ++i) { mbar_init(BAR(DB_K_FULL + i), 1); mbar_init(BAR(DB_K_EMPTY + i), 4 * kHalves); }
         for (int i = 0; i < kSlots; ++i) { mbar_init(BAR(DB_A_FULL + i), 4 * kHalves); mbar_init(BAR(DB_A_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(BAR(DB_D_FULL + i), 1); mbar_init(BAR(DB_D_EMPTY + i), 4 * kHalves); }
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = a.wait_kcycles;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     {   // pair lookup table: entry e = (code0 | code1 << BITS) -> (half2 hi(c0), hi(c1)), (half2 lo(c0), lo(c1)),
@@ -167,6 +169,7 @@ dequant_tc_kernel(const DequantArgs a) {
     if (warp == 0) {
         // ---- bulk-copy producer -----------------------------------------------------------------
         if (lane == 0) {
+            int64_t issued = 0;
             for (int64_t i = 0; i < my_tiles; ++i) {
                 const int64_t tile = blockIdx.x + i * gridDim.x;
                 const int s = (int)(i % kStages);
@@ -192,11 +195,19 @@ dequant_tc_kernel(const DequantArgs a) {
                     mbar_arrive_expect_tx(BAR(DB_K_FULL + s), cb & ~15u);
                     if (cb & ~15u) bulk_load(dst, csrc, cb & ~15u, BAR(DB_K_FULL + s));
                 }
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // copies armed above may still be on their way into this block's shared memory
+                for (int64_t ii = issued > kStages ? issued - kStages : 0; ii < issued; ++ii)
+                    mbar_drain(BAR(DB_K_FULL + (int)(ii % kStages)), (uint32_t)((ii / kStages) & 1));
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer --------------------------------------------------------------------------
-        if (lane == 0) {
+        // The whole warp walks the loop and waits; one elected lane issues from warp-uniform operands.
+        {
+            const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
             const uint32_t lbo = 128, sbo = (D / 8) * 128;
             const uint32_t b0 = smem_base + L::off_b;
             const uint64_t d_rhi = make_smem_desc(b0, lbo, sbo), d_rlo = make_smem_desc(b0 + kMatBytes, lbo, sbo);
@@ -205,28 +216,34 @@ dequant_tc_kernel(const DequantArgs a) {
             for (int64_t i = 0; i < my_tiles; ++i) {
                 const int b = (int)(i & 1);
                 const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-                if (!mbar_wait(BAR(DB_D_EMPTY + b), par2 ^ 1u, abort_flag)) break;
-                const uint32_t acc = tmem + kColD + b * D;
+                if (!warp_wait(BAR(DB_D_EMPTY + b), par2 ^ 1u, abort_flag)) break;
+                const uint32_t acc = tm + kColD + b * D;
                 bool ok = true;
 #pragma unroll
                 for (int op = 0; op < kOps; ++op) {              // 0: C_hi, 1: C_lo, 2: B_hi, 3: B_lo
                     const int64_t n = (int64_t)kOps * i + op;
                     const int slot = (int)(n & (kSlots - 1));
-                    if (!mbar_wait(BAR(DB_A_FULL + slot), (uint32_t)((n / kSlots) & 1), abort_flag)) { ok = false; break; }
+                    if (!warp_wait(BAR(DB_A_FULL + slot), (uint32_t)((n / kSlots) & 1), abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t aop = tmem + slot * kSlotCols;
+                    const uint32_t aop = tm + slot * kSlotCols;
                     const uint64_t bh = op < 2 ? d_rhi : d_shi, bl = op < 2 ? d_rlo : d_slo;
+                    if (elect_one()) {
+                        if (op == 0) mma_ts_first(acc, aop, bh, kIdesc); else mma_ts_acc(acc, aop, bh, kIdesc);
+                        if ((op & 1) == 0) mma_ts_acc(acc, aop, bl, kIdesc);   // hi operand also meets the lo matrix
 #pragma unroll 1
-                    for (int kb = 0; kb < DR / 16; ++kb) {
-                        // the start-address field counts 16-byte units: one k-block (two core matrices) further
-                        const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
-                        mma_ts(acc, aop + kb * 8, bh + step, kIdesc, (op > 0 || kb > 0) ? 1u : 0u);
-                        if ((op & 1) == 0) mma_ts(acc, aop + kb * 8, bl + step, kIdesc, 1u);   // hi operand also meets the lo matrix
+                        for (int kb = 1; kb < DR / 16; ++kb) {
+                            // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                            const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                            mma_ts_acc(acc, aop + kb * 8, bh + step, kIdesc);
+                            if ((op & 1) == 0) mma_ts_acc(acc, aop + kb * 8, bl + step, kIdesc);
+                        }
+                        mma_commit(BAR(DB_A_EMPTY + slot));
                     }
-                    mma_commit(BAR(DB_A_EMPTY + slot));
+                    __syncwarp();
                 }
                 if (!ok) break;
-                mma_commit(BAR(DB_D_FULL + b));
+                if (elect_one()) mma_commit(BAR(DB_D_FULL + b));
+                __syncwarp();
             }
         }
     } else if (warp < kFirstEpiWarp) {
@@ -351,7 +368,8 @@ dequant_tc_kernel(const DequantArgs a) {
                 }
             };
             if (PAIR) fetch_q(0);
-            mbar_wait(BAR(DB_D_FULL + b), par2, abort_flag);
+            // after a give-up nothing is written: the accumulator cannot be trusted
+            const int64_t n_live = mbar_wait(BAR(DB_D_FULL + b), par2, abort_flag) ? a.n : 0;
             tc_fence_after();
             const uint32_t acc = tmem + lane_addr + kColD + b * D + colhalf * 64;
             uint32_t va[32], vb[32];
@@ -392,7 +410,7 @@ dequant_tc_kernel(const DequantArgs a) {
                     if (colhalf == 0) dot += part[row];
                 }
                 const int64_t grow = tile * kTileKeys + row;
-                if (colhalf == 0 && grow < a.n) a.out[grow] = dot * sc;
+                if (colhalf == 0 && grow < n_live) a.out[grow] = dot * sc;
                 continue;
             }
             // Through a per-warp staging block in shared memory, so that the global stores of a warp cover
@@ -411,7 +429,7 @@ dequant_tc_kernel(const DequantArgs a) {
                 for (int it = 0; it < 8; ++it) {
                     const int r = it * 4 + (lane >> 3), c4 = lane & 7;
                     const float4 val = *reinterpret_cast<const float4*>(stg + r * L::kOutRowBytes + c4 * 16);
-                    if (row0 + r < a.n)
+                    if (row0 + r < n_live)
                         __stcs(reinterpret_cast<float4*>(a.out + (row0 + r) * DR + colhalf * 64 + ch * 32) + c4, val);
                 }
                 __syncwarp();
@@ -420,6 +438,7 @@ dequant_tc_kernel(const DequantArgs a) {
     }
 
     // ---- teardown ---------------------------------------------------------------------------------
+    if (*abort_flag) __nanosleep(20000);   // tensor instructions issued before the give-up may still be running
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 3ull);
@@ -517,6 +536,7 @@ int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, con
     a.ntiles = (n + kTileKeys - 1) / kTileKeys;
     a.out = out;
     a.status = p->counters + 1;
+    a.wait_kcycles = p->wait_kcycles;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     const int grid = (int)(a.ntiles < sms ? a.ntiles : sms);
@@ -551,6 +571,7 @@ int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* code
     a.out = scores;
     a.pair_q = q;
     a.status = p->counters + 1;
+    a.wait_kcycles = p->wait_kcycles;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     const int grid = (int)(a.ntiles < sms ? a.ntiles : sms);

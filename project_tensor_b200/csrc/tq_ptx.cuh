@@ -16,7 +16,9 @@
 
 namespace tqptx {
 
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+// Limit of one bounded wait in units of 1024 cycles: ~2 s at 2 GHz by default.  Every kernel keeps two words in shared
+// memory: [0] the give-up flag that all roles watch, [1] the limit for this launch (from the plan).
+constexpr int kDefaultWaitKcycles = 4000000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -48,7 +50,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;   // blocks inside the hardware for a while before it answers
         if ((it & 7u) == 7u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > ((long long)abort_flag[1] << 10)) {
                 *abort_flag = 1;
                 return false;
             }
@@ -58,6 +60,16 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, abort_flag);
+}
+
+// After a give-up: wait, bounded and without looking at the flag, for a phase that this thread armed itself (bulk
+// copies in flight towards this block's shared memory, tensor instructions still writing tensor memory), so that
+// nothing lands in memory the block has already left.  ~0.5 ms at most.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 14); ++it) {
+        if (mbar_try_wait(bar, parity)) return;
+        __nanosleep(32);
+    }
 }
 
 // The same wait executed by every lane of a converged warp; the answer is the same for all of them.

@@ -72,6 +72,7 @@ struct ScoreTcArgs {
     int norms_bulk;               // 1: norms and residual norms travel with the packed rows through the key ring
     float alpha;
     unsigned long long* status;
+    int wait_kcycles;             // limit of one bounded wait, in units of 1024 cycles
 #ifdef TQ_PROF
     long long* prof;              // per-role cycle counters (measurement builds only)
 #endif
@@ -174,7 +175,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             mbar_init(BAR(SB_B_FULL + i), 1);
             mbar_init(BAR(SB_B_EMPTY + i), 1 + 4 * kEpiPerRow);  // last MMA of the group + every epilogue warp
         }
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = a.wait_kcycles;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     {   // pair lookup table: entry e = (code0 | code1 << BITS) -> (half2 hi(c0), hi(c1)), (half2 lo(c0), lo(c1))
@@ -216,7 +218,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
 
     if (warp == 0) {
         if (lane == 0) {
-            int64_t prev_g = -1, gcount = 0;
+            int64_t prev_g = -1, gcount = 0, issued = 0;
             int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
             for (int64_t t = t0; t < t1; ++t, ++kt) {
                 if (kt == a.tiles_per_group) { kt = 0; ++g; }
@@ -256,6 +258,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     bulk_load(dst + L::kNormOff, a.norms + row0, nb & ~15u, BAR(SB_K_FULL + s));
                     bulk_load(dst + L::kNormOff + kTileKeys * 4, a.rnorms + row0, nb & ~15u, BAR(SB_K_FULL + s));
                 }
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // copies armed above may still be on their way into this block's shared memory
+                for (int64_t ii = issued > kStages ? issued - kStages : 0; ii < issued; ++ii)
+                    mbar_drain(BAR(SB_K_FULL + (int)(ii % kStages)), (uint32_t)((ii / kStages) & 1));
+                for (int64_t gg = gcount > 2 ? gcount - 2 : 0; gg < gcount; ++gg)
+                    mbar_drain(BAR(SB_B_FULL + (int)(gg & 1)), (uint32_t)((gg >> 1) & 1));
             }
         }
     } else if (warp == 1) {
@@ -430,7 +440,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             TQ_PROF_CODE(long long c0 = clock64();)
             const int db = kDBufs == 2 ? b : 0;
             const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
-            mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);
+            const bool got = mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);   // false: some role gave up
             tc_fence_after();
             TQ_PROF_CODE(long long c1 = clock64();)
             const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
@@ -456,7 +466,9 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 }
             }
             TQ_PROF_CODE(long long c2 = clock64();)
-            if (a.tile_store) {
+            if (!got) {
+                // nothing is written for a tile whose accumulators cannot be trusted
+            } else if (a.tile_store) {
                 // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
                 // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
                 // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
@@ -496,6 +508,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         if (store_leader) bulk_wait_all();   // the staged tiles must have left before the block's shared memory goes away
     }
 
+    if (*abort_flag) __nanosleep(20000);   // tensor instructions issued before the give-up may still be running
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 2ull);
@@ -741,6 +754,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             a.alpha = p->dev.alpha;
             a.norms_bulk = (groups == 1 || group_rows % 4 == 0) && key_off % 4 == 0 ? 1 : 0;   // 16-byte aligned tile starts
             a.status = p->counters + 1;
+            a.wait_kcycles = p->wait_kcycles;
 #ifdef TQ_PROF
             a.prof = reinterpret_cast<long long*>(p->counters + 8);
 #endif

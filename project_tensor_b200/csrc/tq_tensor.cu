@@ -75,6 +75,7 @@ struct TensorArgs {
     float* rnorms;
     TqRecheck lists;
     unsigned long long* status;  // [0]: set to a non-zero code when a wait timed out
+    int wait_kcycles;            // limit of one bounded wait, in units of 1024 cycles
 #ifdef TQ_PROF
     long long* prof;             // cycle counters per role (measurement builds only)
 #endif
@@ -279,7 +280,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
         mbar_init(BAR(BAR_ACC2_FULL + 1), 1);
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = a.wait_kcycles;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x < kCells) cell_lut[threadIdx.x] = a.cell_lut[threadIdx.x];
@@ -324,6 +326,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                                  BAR(BAR_FULL + slot));
                 }
                 if (!ok) break;
+            }
+            if (*abort_flag) {
+                // copies armed above may still be on their way into this block's shared memory
+                for (int64_t gg = g > L::kRingBoxes ? g - L::kRingBoxes : 0; gg < g; ++gg)
+                    mbar_drain(BAR(BAR_FULL + (int)(gg % L::kRingBoxes)), (uint32_t)((gg / L::kRingBoxes) & 1));
             }
         }
     } else if (warp == 1) {
@@ -473,7 +480,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const float sc = ok ? kScaleA / nrm : 0.f;
             if (half == 0) {
                 const int64_t grow = tile * kTileRows + row;
-                if (grow < a.n) a.norms[grow] = nrm;
+                if (grow < a.n && !fail) a.norms[grow] = nrm;
                 force[(i & 3) * kTileRows + row] = odd ? 1 : 0;
             }
             if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
@@ -528,9 +535,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
-            const bool live = grow < a.n;
+            const bool live_row = grow < a.n;
             TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
-            mbar_wait(BAR(BAR_ACC_FULL + b), par2, abort_flag);
+            const bool got = mbar_wait(BAR(BAR_ACC_FULL + b), par2, abort_flag);   // false: some role gave up, the
+            const bool live = live_row && got;                                      // accumulator is not to be trusted
             tc_fence_after();
             TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[16] += c1 - c0;)
             const bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
@@ -623,10 +631,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             const int b = (int)(j & 1);
             const uint32_t par2 = (uint32_t)((j >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
-            const bool live = grow < a.n;
             TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
             bool redo_row = force[(j & 3) * kTileRows + row] != 0;
-            mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag);
+            const bool live = mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag) && grow < a.n;   // no stores after a give-up
             tc_fence_after();
             TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[18] += c1 - c0;)
             const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
@@ -683,6 +690,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     }
 
     // ---- teardown -----------------------------------------------------------------------------------
+    if (*abort_flag) __nanosleep(20000);   // tensor instructions issued before the give-up may still be running
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
@@ -903,6 +911,7 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     args.rnorms = rnorms;
     args.lists = *lists;
     args.status = p->counters + 1;
+    args.wait_kcycles = p->wait_kcycles;
 #ifdef TQ_PROF
     args.prof = reinterpret_cast<long long*>(p->counters + 8);   // cycle counters per role, measurement builds only
 #endif

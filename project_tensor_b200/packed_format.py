@@ -8,16 +8,20 @@ persistent KV cache, a vector index, a shard handed to another rank -- needs a f
 File layout (all integers little-endian):
 
     offset 0    8 bytes   magic  b"TQPACKED"
-    offset 8    u32       format version (1)
+    offset 8    u32       format version (2)
     offset 12   u32       length H of the header text
     offset 16   H bytes   header, UTF-8 JSON (see ``_header``)
+    offset 16+H u32       CRC-32 of the H header bytes
     ...         padding with zero bytes to a multiple of 64
     sections              the arrays named in header["sections"], each starting on a multiple of 64 bytes
                           counted from the start of the file, raw little-endian, C order
 
 The header names the quantizer by content, not by seed: SHA-256 of the float32 codebook, rotation and
-projection, so that a reader refuses to interpret codes with other constants than the writer's.  Every section
-carries a CRC-32 of its bytes.
+projection, so that a reader refuses to interpret codes with other constants than the writer's.  The header and
+every section carry a CRC-32 of their bytes, and a reader checks the header against itself before it trusts it:
+the sections must be exactly those of the quantizer's kind, with the row count, row widths and dtypes the header's
+own dimension and bit width imply (the kernels index the arrays by these numbers, so a header that overstates
+them would send them past the end of the buffers).
 
 Bit layout of the rows (the same as the device buffers, csrc/tq_common.cuh):
   * codes: coordinate j occupies bits [j*b, (j+1)*b) of the row read as a little-endian bit stream, rows padded
@@ -39,7 +43,7 @@ from typing import Any, Dict, Tuple
 import numpy as np
 
 MAGIC = b"TQPACKED"
-VERSION = 1
+VERSION = 2
 _ALIGN = 64
 _SECTION_DTYPES = {"codes": "<u1", "signs": "<u1", "norms": "<f4", "residual_norms": "<f4"}
 
@@ -178,7 +182,7 @@ def write_packed(target, fingerprint: Dict[str, Any], prefix_shape: Tuple[int, .
     # two passes: the header's length decides where the sections start, and the header names those offsets;
     # offsets are written with a fixed width so that the length does not depend on their values
     def layout(header_len: int):
-        pos = 16 + header_len
+        pos = 16 + header_len + 4
         pos += _pad(pos)
         secs = []
         for name in names:
@@ -199,8 +203,8 @@ def write_packed(target, fingerprint: Dict[str, Any], prefix_shape: Tuple[int, .
     own = isinstance(target, (str, bytes)) or hasattr(target, "__fspath__")
     f = open(target, "wb") if own else target
     try:
-        f.write(MAGIC + struct.pack("<II", VERSION, len(header2)) + header2)
-        pos = 16 + len(header2)
+        f.write(MAGIC + struct.pack("<II", VERSION, len(header2)) + header2 + struct.pack("<I", zlib.crc32(header2) & 0xFFFFFFFF))
+        pos = 16 + len(header2) + 4
         f.write(b"\0" * _pad(pos))
         pos += _pad(pos)
         for name in names:
@@ -258,6 +262,7 @@ def read_packed(source, *, mmap: bool = False, verify: bool = True) -> PackedFil
             head = f.read(16)
             hlen = struct.unpack("<II", head[8:16])[1] if len(head) == 16 else 0
             header_bytes = f.read(hlen)
+            header_crc = f.read(4)
             if not mmap:
                 f.seek(0)
                 data = f.read()
@@ -265,17 +270,21 @@ def read_packed(source, *, mmap: bool = False, verify: bool = True) -> PackedFil
         head = data[:16]
         hlen = struct.unpack("<II", head[8:16])[1] if len(head) == 16 else 0
         header_bytes = data[16:16 + hlen]
+        header_crc = data[16 + hlen:16 + hlen + 4]
     if len(head) != 16 or head[:8] != MAGIC:
         raise PackedFormatError("not a packed TurboQuant encoding (bad magic)")
     version = struct.unpack("<II", head[8:16])[0]
     if version != VERSION:
         raise PackedFormatError(f"format version {version} is not supported (this reader knows {VERSION})")
-    if len(header_bytes) != hlen:
+    if len(header_bytes) != hlen or len(header_crc) != 4:
         raise PackedFormatError("file ends inside the header")
+    if struct.unpack("<I", header_crc)[0] != (zlib.crc32(header_bytes) & 0xFFFFFFFF):
+        raise PackedFormatError("header CRC-32 mismatch (file damaged or edited)")
     try:
         header = json.loads(header_bytes.decode("utf-8"))
     except (UnicodeDecodeError, json.JSONDecodeError) as e:
         raise PackedFormatError(f"unreadable header: {e}") from None
+    _check_header(header)
     buffers: Dict[str, np.ndarray] = {}
     for sec in header["sections"]:
         off, nbytes = int(sec["offset"]), int(sec["nbytes"])
@@ -294,6 +303,39 @@ def read_packed(source, *, mmap: bool = False, verify: bool = True) -> PackedFil
                 raise PackedFormatError(f"section {sec['name']!r}: CRC-32 mismatch (file damaged)")
         buffers[sec["name"]] = arr
     return PackedFile(header, buffers)
+
+
+def _check_header(header: Dict[str, Any]) -> None:
+    """The header against itself: kind -> section names, (dimension, bits) -> row widths, rows -> every section's
+    first extent and the prefix shape.  A reader indexes the arrays by these numbers."""
+    try:
+        q = header["quantizer"]
+        kind, d, b = q["kind"], int(q["dimension"]), int(q["bits_mse"])
+        rows = int(header["rows"])
+        prefix = [int(v) for v in header["prefix_shape"]]
+        secs = {sec["name"]: sec for sec in header["sections"]}
+        if len(secs) != len(header["sections"]):
+            raise PackedFormatError("a section is listed twice")
+        if kind not in ("mse", "prod") or d < 2 or b < 1 or rows < 0 or any(v < 0 for v in prefix):
+            raise PackedFormatError("header values out of range")
+        names = ["codes", "norms"] + (["signs", "residual_norms"] if kind == "prod" else [])
+        if sorted(secs) != sorted(names):
+            raise PackedFormatError(f"a {kind} file must hold the sections {names}, found {sorted(secs)}")
+        want = {"codes": [rows, code_row_bytes(d, b)], "norms": [rows], "signs": [rows, sign_row_bytes(d)],
+                "residual_norms": [rows]}
+        for name in names:
+            sec = secs[name]
+            if [int(v) for v in sec["shape"]] != want[name]:
+                raise PackedFormatError(f"section {name!r} has shape {sec['shape']}, the header's own numbers "
+                                        f"({rows} rows, d = {d}, {b} code bits) require {want[name]}")
+            if sec["dtype"] != _SECTION_DTYPES[name]:
+                raise PackedFormatError(f"section {name!r} has dtype {sec['dtype']!r}, expected {_SECTION_DTYPES[name]!r}")
+        if int(np.prod(prefix, dtype=np.int64)) != rows:
+            raise PackedFormatError(f"prefix_shape {prefix} does not describe {rows} rows")
+    except (KeyError, TypeError, ValueError) as e:
+        if isinstance(e, PackedFormatError):
+            raise
+        raise PackedFormatError(f"malformed header: {e!r}") from None
 
 
 def check_same_quantizer(file_fingerprint: Dict[str, Any], quantizer) -> None:

@@ -133,8 +133,12 @@ def _stage(data: Any, dim: int, device=None) -> _Staged:
     return _Staged(t.reshape(-1, dim).to(torch.float32).contiguous(), prefix, kind, t.device)
 
 
-def _deliver(tensor, kind: str):
-    """Hand a device tensor back in the caller's kind of array."""
+def _deliver(tensor, kind: str, plans: "Optional[_PlanSet]" = None):
+    """Hand a device tensor back in the caller's kind of array.  A result that goes to host memory synchronises
+    anyway; with ``plans`` the status word of the kernels is read at that point, so that the output of a kernel
+    that gave up on a bounded wait is never handed out as if it were complete."""
+    if plans is not None and kind in ("numpy", "torch_cpu"):
+        plans.check_status(tensor.device)
     if kind == "numpy":
         return tensor.cpu().numpy()
     if kind == "torch_cpu":
@@ -185,6 +189,27 @@ class _PlanSet:
                 _native.check(lib.tq_plan_set_path(h, self._path))
             self._plans[idx] = h
         return h
+
+    def check_status(self, device) -> None:
+        """Raise if a tensor-core kernel of this quantizer gave up on a bounded wait on ``device`` since the last
+        check (synchronises the current stream of that device)."""
+        idx = device.index if device.index is not None else _torch().cuda.current_device()
+        h = self._plans.get(idx)
+        if h is None:
+            return
+        status = ctypes.c_int64(0)
+        with _torch().cuda.device(idx):
+            _native.check(_native.load().tq_plan_status(h, _stream_ptr(device), ctypes.byref(status)))
+        if status.value:
+            what = {1: "quantize", 2: "scoring", 3: "dequantize"}.get(status.value, "tensor-core")
+            raise _native.TurboQuantNativeError(
+                f"a {what} kernel gave up on a bounded wait (status {status.value}); the results of the calls "
+                f"since the last check are incomplete")
+
+    def set_wait_limit(self, cycles: int) -> None:
+        """Limit of one bounded wait inside the tensor-core kernels, in GPU cycles, for plans that exist already."""
+        for h in self._plans.values():
+            _native.check(_native.load().tq_plan_set_wait_limit(h, int(cycles)))
 
     def set_path(self, path: int) -> None:
         self._path = path
@@ -241,7 +266,7 @@ def _unpack_codes(pk: _Packed):
         with torch.cuda.device(pk.device):
             _native.check(_native.load().tq_unpack_codes(pk.plans.handle(pk.device), _ptr(pk.codes), pk.n,
                                                          _ptr(out), _stream_ptr(pk.device)))
-    return _deliver(out, pk.kind)
+    return _deliver(out, pk.kind, pk.plans)
 
 
 def _unpack_signs(pk: _Packed):
@@ -251,7 +276,7 @@ def _unpack_signs(pk: _Packed):
         with torch.cuda.device(pk.device):
             _native.check(_native.load().tq_unpack_signs(pk.plans.handle(pk.device), _ptr(pk.signs), pk.n,
                                                          _ptr(out), _stream_ptr(pk.device)))
-    return _deliver(out, pk.kind)
+    return _deliver(out, pk.kind, pk.plans)
 
 
 @dataclass
@@ -275,10 +300,10 @@ class TurboQuantProdEncoding:
 # materialise the reference-shaped arrays when somebody reads them.
 for _cls in (TurboQuantMSEEncoding, TurboQuantProdEncoding):
     _cls.indices = _lazy_field("indices", _unpack_codes)
-    _cls.norms = _lazy_field("norms", lambda pk: _deliver(pk.norms, pk.kind))
+    _cls.norms = _lazy_field("norms", lambda pk: _deliver(pk.norms, pk.kind, pk.plans))
 TurboQuantProdEncoding.qjl = _lazy_field("qjl", _unpack_signs)
 TurboQuantProdEncoding.residual_norms = _lazy_field(
-    "residual_norms", lambda pk: _deliver(pk.residual_norms, pk.kind))
+    "residual_norms", lambda pk: _deliver(pk.residual_norms, pk.kind, pk.plans))
 
 
 def _encoding_from_packed(cls, pk: _Packed, prefix):
@@ -317,7 +342,8 @@ def packed_to_host(encoding, out: Optional[Dict[str, Any]] = None, wait: bool = 
             host[name] = dst
         dst.copy_(dev_t, non_blocking=True)
     if wait:
-        torch.cuda.current_stream().synchronize()
+        pk = encoding.__dict__["_packed"]
+        pk.plans.check_status(pk.device)     # synchronises the stream, and refuses results of a kernel that gave up
     return host
 
 
@@ -386,6 +412,7 @@ def quantize_to_host(quantizer, keys, chunk_rows: int = 131072, out: Optional[Di
             alive.append(pk)
         s_out.synchronize()
         torch.cuda.current_stream().wait_stream(s_run)
+        plans.check_status(device)     # a chunk whose kernel gave up on a bounded wait must not pass as quantized
     return host
 
 
@@ -517,7 +544,7 @@ class TurboQuantMSE:
             _native.check(_native.load().tq_mse_dequantize(self._plans.handle(pk.device), _ptr(pk.codes),
                                                            _ptr(pk.norms), pk.n, _ptr(out),
                                                            _stream_ptr(pk.device)))
-        return _deliver(out, pk.kind).reshape(tuple(encoding.prefix_shape) + (self.dimension,))
+        return _deliver(out, pk.kind, pk.plans).reshape(tuple(encoding.prefix_shape) + (self.dimension,))
 
 
 class TurboQuantProd:
@@ -561,7 +588,7 @@ class TurboQuantProd:
             _native.check(_native.load().tq_prod_dequantize(
                 self._plans.handle(pk.device), _ptr(pk.codes), _ptr(pk.signs), _ptr(pk.residual_norms),
                 _ptr(pk.norms), pk.n, _ptr(out), _stream_ptr(pk.device)))
-        return _deliver(out, pk.kind).reshape(tuple(encoding.prefix_shape) + (self.dimension,))
+        return _deliver(out, pk.kind, pk.plans).reshape(tuple(encoding.prefix_shape) + (self.dimension,))
 
     def attention_score(self, query: Any, encoding: TurboQuantProdEncoding):
         """One query row broadcast over all keys, or one query row per key (_quant.py:334-358)."""
@@ -602,7 +629,7 @@ class TurboQuantProd:
                                                     _ptr(pk.residual_norms), _ptr(pk.norms), num_codes,
                                                     _ptr(scores), _stream_ptr(pk.device)))
         shape = q_prefix if (broadcast or q.shape[0] != 1) else tuple(encoding.prefix_shape)
-        return _deliver(scores, staged.kind).reshape(shape)
+        return _deliver(scores, staged.kind, self._plans).reshape(shape)
 
     def attention_scores(self, queries: Any, encoding: TurboQuantProdEncoding, *, topk: Optional[int] = None,
                          groups: int = 1, return_matrix: Optional[bool] = None, index_base: int = 0,
@@ -656,8 +683,8 @@ class TurboQuantProd:
                                                _ptr(top_s), _ptr(top_i), int(index_base), _ptr(scratch),
                                                scratch.numel(), _stream_ptr(pk.device)))
         if k == 0:
-            return _deliver(scores, staged.kind)
-        result = (_deliver(top_s, staged.kind), _deliver(top_i, staged.kind))
+            return _deliver(scores, staged.kind, self._plans)
+        result = (_deliver(top_s, staged.kind, self._plans), _deliver(top_i, staged.kind))
         return result + (_deliver(scores, staged.kind),) if want_matrix else result
 
 

@@ -374,3 +374,30 @@ def test_d64_tensor_paths_match_exact_paths(tg, bits, n):
             ref_s = quant.attention_scores(q, ref).cpu().numpy()
             scale = np.linalg.norm(q.cpu().numpy(), axis=1)[:, None]
             assert parity.max_score_err(got_s, ref_s, scale, ref_bufs["norms"].cpu().numpy()[None, :], d) <= REL_SCORE
+
+
+def test_a_wait_that_runs_out_is_reported_not_hidden(tg):
+    """Every wait inside the tensor-core kernels is bounded.  With the limit set to a few thousand cycles -- less than
+    the first tile's trip from memory -- some wait runs out: the kernel must come back (all roles leave their loops,
+    copies and tensor instructions in flight are waited for), the plan's status word must say so, the Python layer must
+    raise at its next synchronisation point instead of handing the encoding out, and the next call with the normal limit
+    must be correct again on the same context."""
+    import torch
+    from project_tensor_b200 import _native
+    x = torch.randn((65536, 128), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    quant = tg.TurboQuantProd(128, 4, seed=2026)
+    good = quant.quantize(x)
+    torch.cuda.synchronize()
+    quant._plans.check_status(x.device)                 # nothing to report so far
+    quant._plans.set_wait_limit(2048)
+    enc = quant.quantize(x)
+    with pytest.raises(_native.TurboQuantNativeError, match="gave up on a bounded wait"):
+        quant._plans.check_status(x.device)
+    quant._plans.check_status(x.device)                 # reported once, then clear
+    quant._plans.set_wait_limit(4_000_000_000)
+    again = quant.quantize(x)
+    from project_tensor_b200 import packed_buffers
+    a, b = packed_buffers(again), packed_buffers(good)
+    assert torch.equal(a["codes"], b["codes"]) and torch.equal(a["signs"], b["signs"])
+    quant._plans.check_status(x.device)
+    del enc

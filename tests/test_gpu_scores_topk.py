@@ -251,3 +251,50 @@ def test_c_abi_broadcast_entry_point(tg, d, bits):
                                          torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert torch.equal(out, want)
+
+
+def test_c_abi_rejects_grids_beyond_the_launch_limits(tg):
+    """A top-k over more than 65,535 (group, query) pairs would need a grid the selection kernels cannot have: the
+    entry point must say so before anything is enqueued (not fail halfway with a launch error)."""
+    import torch
+    from project_tensor_b200 import _native
+    lib = _native.load()
+    prod = tg.TurboQuantProd(128, 4, seed=2026)
+    handle = prod._plans.handle(torch.device("cuda", torch.cuda.current_device()))
+    dummy = torch.zeros((64,), dtype=torch.float32, device="cuda")
+    p = dummy.data_ptr()
+    before = int(lib.tq_kernel_launches())
+    rc = lib.tq_score_cache(handle, p, 8192, 16, p, p, p, p, 4, 4, None, 5, p, p, 0, p, 256,
+                            torch.cuda.current_stream().cuda_stream)
+    assert rc == -1 and b"groups * q_per_group" in lib.tq_last_error()
+    assert int(lib.tq_kernel_launches()) == before
+    # the merge over gathered blocks checks its block geometry the same way
+    rc = lib.tq_topk_merge_gathered(p, 100, 48, 2, 3, 4, p, p, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1 and b"does not hold" in lib.tq_last_error()
+
+
+def test_merge_on_gathered_blocks_equals_merge_on_lists(tg):
+    """tq_topk_merge_gathered reads scores and indices out of the per-rank blocks of one all-gather; it must give what
+    tq_topk_merge gives on the same lists laid out as two arrays."""
+    import torch
+    from project_tensor_b200 import _native
+    from project_tensor_b200.sharded import TopkExchange
+    lib = _native.load()
+    lists, q, k = 3, 7, 100
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    s = torch.randn((lists, q, k), device="cuda", generator=gen).sort(dim=2, descending=True).values.contiguous()
+    i = torch.randint(0, 1 << 40, (lists, q, k), device="cuda", generator=gen)
+    ex = TopkExchange(q, k, torch.device("cuda", torch.cuda.current_device()))
+    gathered = torch.empty((lists, ex.block_bytes), dtype=torch.uint8, device="cuda")
+    for l in range(lists):
+        gathered[l, :4 * q * k] = s[l].reshape(-1).view(torch.uint8)
+        gathered[l, ex.idx_offset:] = i[l].reshape(-1).view(torch.uint8)
+    out = [torch.empty((q, k), dtype=torch.float32, device="cuda"), torch.empty((q, k), dtype=torch.int64, device="cuda"),
+           torch.empty((q, k), dtype=torch.float32, device="cuda"), torch.empty((q, k), dtype=torch.int64, device="cuda")]
+    st = torch.cuda.current_stream().cuda_stream
+    _native.check(lib.tq_topk_merge(s.data_ptr(), i.data_ptr(), lists, q, k, out[0].data_ptr(), out[1].data_ptr(), st))
+    _native.check(lib.tq_topk_merge_gathered(gathered.data_ptr(), ex.block_bytes, ex.idx_offset, lists, q, k,
+                                             out[2].data_ptr(), out[3].data_ptr(), st))
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], out[2]) and torch.equal(out[1], out[3])
+    assert torch.equal(out[0], s.permute(1, 0, 2).reshape(q, -1).sort(dim=1, descending=True).values[:, :k])

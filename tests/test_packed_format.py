@@ -123,6 +123,55 @@ def test_damage_and_mismatch_are_refused():
                          "signs": np.zeros((40, 8), np.uint8), "residual_norms": np.zeros(40, np.float32)})
 
 
+def _rewrite_header(data: bytes, edit) -> bytes:
+    """The same file with its JSON header changed by `edit` (a hand edit or a damaged header that happens to
+    parse); `fix_crc` decides whether the header's own checksum is recomputed, as a careful editor would."""
+    import json
+    import struct
+    import zlib
+    hlen = struct.unpack("<II", data[8:16])[1]
+    doc = json.loads(data[16:16 + hlen].decode())
+    edit(doc)
+    first = min(int(sec["offset"]) for sec in json.loads(data[16:16 + hlen].decode())["sections"])
+    new = json.dumps(doc, sort_keys=True).encode()
+    head = data[:8] + struct.pack("<II", struct.unpack("<II", data[8:16])[0], len(new)) + new + struct.pack("<I", zlib.crc32(new) & 0xFFFFFFFF)
+    assert len(head) <= first, "the edits below keep the sections where they are"
+    return head + b"\0" * (first - len(head)) + data[first:]
+
+
+def test_a_header_that_contradicts_itself_is_refused():
+    """rows, shapes, section set and prefix shape are what the kernels index by: a header whose numbers do not
+    agree with each other must not reach the device, whether or not its checksum was fixed up."""
+    quant = tg.TurboQuantProd(64, 3, seed=5)
+    _, _, enc = _oracle_prod_encoding(64, 3, 40, seed=5)
+    buf = io.BytesIO()
+    pf.save_encoding(buf, quant, enc)
+    data = buf.getvalue()
+    assert pf.read_packed(data).rows == 40
+    # a header edited without fixing its checksum
+    import struct
+    hlen = struct.unpack("<II", data[8:16])[1]
+    raw = bytearray(data)
+    at = data.index(b'"rows": 40')
+    raw[at + 8:at + 10] = b"99"
+    with pytest.raises(pf.PackedFormatError, match="header CRC"):
+        pf.read_packed(bytes(raw))
+
+    def rows_up(doc): doc["rows"] = 99                                   # more rows than the sections hold
+    def codes_wide(doc): [sec for sec in doc["sections"] if sec["name"] == "codes"][0]["shape"][1] = 99
+    def signs_gone(doc):
+        for sec in doc["sections"]:
+            if sec["name"] == "signs":
+                sec["name"] = "sigma"
+    def prefix_off(doc): doc["prefix_shape"] = [41]
+    def kind_mse(doc): doc["quantizer"]["kind"] = "mse"                  # four sections in an MSE file
+    def dtype_off(doc): [sec for sec in doc["sections"] if sec["name"] == "norms"][0]["dtype"] = "<i4"
+    for edit, what in ((rows_up, "require"), (codes_wide, "require|inconsistent"), (signs_gone, "must hold"),
+                       (prefix_off, "prefix_shape"), (kind_mse, "must hold"), (dtype_off, "dtype")):
+        with pytest.raises(pf.PackedFormatError, match=what):
+            pf.read_packed(_rewrite_header(data, edit))
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("d,bits", [(128, 4), (64, 3), (256, 2)])
 def test_gpu_buffers_follow_the_numpy_layout(d, bits):

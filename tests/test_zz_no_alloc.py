@@ -68,3 +68,32 @@ def test_noalloc_quantize_rejects_batches_beyond_its_limit(lib_built):
     rc = lib.tq_mse_quantize_noalloc(handle, x.data_ptr(), n, out.data_ptr(), norms.data_ptr(), None)
     assert rc == -2
     assert b"at most 262144 rows" in lib.tq_last_error()
+
+
+def test_noalloc_quantize_at_its_largest_batch_leaves_device_memory_as_it_was(lib_built):
+    """262,144 rows is the largest batch the entry point takes, and the one for which its static work lists are
+    tightest.  The call must agree with the regular entry point there too, and the device's free memory must read the
+    same before and after it: nothing was allocated or freed on its behalf (inputs and outputs exist beforehand)."""
+    import torch
+    import project_tensor_b200 as tg
+    from project_tensor_b200 import _native
+    lib = _native.load()
+    dev = torch.device("cuda", 0)
+    quant = tg.TurboQuantMSE(128, 4, seed=2026)
+    handle = quant._plans.handle(dev)
+    code_bytes = int(lib.tq_code_row_bytes(handle))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    n = 262144
+    x = torch.randn((n, 128), generator=torch.Generator(device=dev).manual_seed(78), device=dev, dtype=torch.float32)
+    codes_a, norms_a, codes_b, norms_b = _call_pair(lib, handle, x, n, code_bytes, stream, torch)   # includes the first-call set-up
+    assert torch.equal(codes_a, codes_b) and torch.equal(norms_a, norms_b)
+    codes_b.fill_(0xAB)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(2):
+        rc = lib.tq_mse_quantize_noalloc(handle, x.data_ptr(), n, codes_b.data_ptr(), norms_b.data_ptr(), stream)
+        assert rc == 0, lib.tq_last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert free_after == free_before
+    assert torch.equal(codes_a, codes_b) and torch.equal(norms_a, norms_b)

@@ -418,7 +418,7 @@ def run_gpu(args):
 
     peak, peak_kind = measured_peaks()
     # ---- the other calls of the path, each timed alone (median of 10 groups of 4 calls), rank 0 only --------
-    other, configs, parity = {}, None, None
+    other, configs, parity, quality = {}, None, None, None
     if rank == 0:
         mse = tg.TurboQuantMSE(D, BITS, seed=SEED)
         enc_m = mse.quantize(keys)
@@ -449,6 +449,9 @@ def run_gpu(args):
         del kv, kv_q
         if world == 1:
             parity = parity_report(quant, keys, queries, 131072)
+            quality = tg.quality_report(mse, quant, keys, queries, ks=(1, 10, 100))
+            quality["what"] = ("the reference harness's metrics (validate_turboquant.py) on this run's 1,048,576 N(0,1) keys and 32 queries, "
+                               "computed on the device chunk by chunk; recall against the exact float32 products")
     # ---- end to end through the public API with host buffers, every rank ---------------------------------
     host_keys = torch.empty((N_KEYS, D), dtype=torch.float32).pin_memory()
     host_keys.copy_(keys)
@@ -547,6 +550,8 @@ def run_gpu(args):
         }
         if parity is not None:
             line["parity"] = parity
+        if quality is not None:
+            line["quality"] = quality
         if configs is not None:
             line["configs"] = configs
         if world == 1:

@@ -14,10 +14,11 @@ from .turboquant import (Tensor, TurboQuantMSE, TurboQuantMSEEncoding, TurboQuan
 from .codebook import _build_lloyd_max_codebook  # used by the reference's own tests
 from .packed_format import PackedFormatError, load_encoding, read_packed, save_encoding, write_packed
 from .cache import PackedKeyCache, PackedKVCache
+from .quality import quality_report
 
 __all__ = ["Tensor", "TurboQuantMSE", "TurboQuantMSEEncoding", "TurboQuantProd",
            "TurboQuantProdEncoding", "packed_buffers", "packed_to_host", "quantize_to_host", "turboquant_mse",
-           "turboquant_prod", "PackedFormatError", "PackedKeyCache", "PackedKVCache", "load_encoding", "read_packed", "save_encoding", "write_packed"]
+           "turboquant_prod", "quality_report", "PackedFormatError", "PackedKeyCache", "PackedKVCache", "load_encoding", "read_packed", "save_encoding", "write_packed"]
 
 
 def set_device(device: str) -> None:

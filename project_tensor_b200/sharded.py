@@ -140,6 +140,40 @@ def merge_topk_across_ranks(top_scores, top_idx, group=None, merge: Optional[Cal
     return ex.start().finish(merge=merge, timeout_s=timeout_s)
 
 
+def scatter_merge_topk(top_scores, top_idx, group=None, merge: Optional[Callable] = None):
+    """Global top-k for many queries without every rank merging every query: rank r of W receives all ranks'
+    candidates for queries [r*Q/W, (r+1)*Q/W) only (one all-to-all of the candidate lists, the exchange pattern of a
+    reduce-scatter) and merges those; returns ``(scores [Q/W, k], idx [Q/W, k], first_query)``.  Compared with the
+    all-gather form, every rank receives and merges 1/W of the candidates, which matters once Q * k * W entries no
+    longer fit a small message.  Q must be a multiple of W.  ``merge`` as in TopkExchange."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    nq, k = top_scores.shape
+    if nq % world:
+        raise ValueError(f"{nq} queries do not split evenly over {world} ranks")
+    per = nq // world
+    send_s = top_scores.contiguous().view(world, per, k)
+    send_i = top_idx.contiguous().view(world, per, k)
+    if world == 1:
+        recv_s, recv_i = send_s, send_i
+    else:
+        recv_s, recv_i = torch.empty_like(send_s), torch.empty_like(send_i)
+        if send_s.is_cuda:
+            dist.all_to_all_single(recv_s, send_s, group=group)      # block j of the result comes from rank j
+            dist.all_to_all_single(recv_i, send_i, group=group)
+        else:  # gloo has no all-to-all for every build: W broadcast-free point exchanges through all_gather
+            all_s = [torch.empty_like(send_s) for _ in range(world)]
+            all_i = [torch.empty_like(send_i) for _ in range(world)]
+            dist.all_gather(all_s, send_s, group=group)
+            dist.all_gather(all_i, send_i, group=group)
+            recv_s = torch.stack([a[rank] for a in all_s])
+            recv_i = torch.stack([a[rank] for a in all_i])
+    out_s, out_i = (merge or _merge_on_gpu)(recv_s.contiguous(), recv_i.contiguous())
+    return out_s, out_i, rank * per
+
+
 def gather_score_slabs(scores, group=None):
     """All-gather per-shard score slabs [Q, n_local] into [Q, n_total] (equal shard sizes)."""
     import torch

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from project_tensor_b200.sharded import gather_score_slabs, merge_topk_across_ranks, shard_range
+from project_tensor_b200.sharded import gather_score_slabs, merge_topk_across_ranks, scatter_merge_topk, shard_range
 
 
 def test_shard_range_covers_everything_once():
@@ -60,6 +60,16 @@ def _worker(rank, world, port, ret):
         assert np.array_equal(got_s.numpy(), np.take_along_axis(scores, want, axis=1))
         slab = gather_score_slabs(torch.from_numpy(local.copy()))
         assert np.array_equal(slab.numpy(), scores)
+        # the scatter form: every rank merges only its own slice of the queries
+        q4 = 4
+        scores4 = rng.standard_normal((q4, n)).astype(np.float32)
+        local4 = scores4[:, lo:hi]
+        order4 = np.argsort(-local4, axis=1, kind="stable")[:, :k]
+        s_s, s_i, first = scatter_merge_topk(torch.from_numpy(np.take_along_axis(local4, order4, axis=1)),
+                                             torch.from_numpy(order4.astype(np.int64) + lo), merge=numpy_merge)
+        want4 = np.argsort(-scores4, axis=1, kind="stable")[:, :k]
+        assert first == rank * (q4 // world) and s_i.shape == (q4 // world, k)
+        assert np.array_equal(s_i.numpy(), want4[first:first + q4 // world])
         ret[rank] = True
     finally:
         dist.destroy_process_group()

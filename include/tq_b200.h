@@ -273,6 +273,17 @@ int tq_plan_last_recheck_rows(const tq_plan* plan, void* stream, int64_t* rows);
  * No reference counterpart (NumPy has nothing to wait for).
  */
 int tq_plan_status(const tq_plan* plan, void* stream, int64_t* status);
+
+/*
+ * Device time of the main kernel of each call, for benchmarks: with timing on, every tq_*_quantize call on the
+ * tensor-core path records a CUDA event before and after its tensor-core kernel (kind 0; the exact second stage
+ * lies outside the pair) and every tq_score_batched / tq_score_cache call around each launch of the tensor-core
+ * scoring kernel (kind 1).  tq_plan_kernel_ms returns how many of the most recent launches of `kind` it wrote to
+ * ms[] (at most max_count, at most 1,024), oldest first, in milliseconds; synchronise the stream before.  Turning
+ * timing on or off resets the record.  No reference counterpart.
+ */
+int tq_plan_time_kernels(tq_plan* plan, int on);
+int tq_plan_kernel_ms(const tq_plan* plan, int kind, float* ms, int max_count);
 int tq_plan_set_wait_limit(tq_plan* plan, int64_t cycles);
 
 #ifdef __cplusplus

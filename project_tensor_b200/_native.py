@@ -61,6 +61,8 @@ SIGNATURES = {
     "tq_pack_signs": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "tq_plan_last_recheck_rows": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
     "tq_plan_set_wait_limit": (c_int, [c_void_p, c_int64]),
+    "tq_plan_time_kernels": (c_int, [c_void_p, c_int]),
+    "tq_plan_kernel_ms": (c_int, [c_void_p, c_int, c_void_p, c_int]),
     "tq_plan_status": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
 }
 

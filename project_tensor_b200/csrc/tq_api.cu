@@ -203,6 +203,11 @@ int tq_plan_create(int d, int bits_mse, const float* rotation, const float* code
 void tq_plan_destroy(tq_plan* p) {
     if (!p) return;
     DeviceScope scope(p->device);
+    if (p->timer) {
+        for (int k = 0; k < 2; ++k)
+            for (int i = 0; i < kTimerSlots; ++i) { cudaEventDestroy(p->timer->ev[k][i][0]); cudaEventDestroy(p->timer->ev[k][i][1]); }
+        delete p->timer;
+    }
     tq_tensor_plan_free(p);
     tq_dequant_tc_plan_free(p);
     if (p->slab) cudaFree(p->slab);
@@ -263,7 +268,6 @@ static int quantize_common(const tq_plan* p, bool prod, const float* x, int64_t 
         lists.code_entries = reinterpret_cast<unsigned long long*>(sc + sizeof(TqRecheckHeader));
         lists.row_entries = reinterpret_cast<unsigned int*>(sc + sizeof(TqRecheckHeader) + 8 * (size_t)lists.code_cap);
         TQ_CUDA_TRY(cudaMemsetAsync(lists.hdr, 0, sizeof(TqRecheckHeader), st));
-        TQ_CUDA_TRY(cudaMemsetAsync(p->counters, 0, sizeof(unsigned long long), st));
         TQ_TRY(tq_launch_tensor_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
                                          rnorms, norms, &lists, st));
         TQ_TRY(tq_launch_exact_code_check(p, prod, x, n, static_cast<uint32_t*>(codes), &lists, st));
@@ -573,6 +577,43 @@ int tq_pack_signs(const tq_plan* p, const int8_t* qjl, int64_t n, void* signs, v
     if (!qjl) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "qjl is null");
     DeviceScope scope(p->device);
     return tq_launch_pack_signs(p, qjl, n, static_cast<uint32_t*>(signs), static_cast<cudaStream_t>(stream));
+}
+
+int tq_plan_time_kernels(tq_plan* p, int on) {
+    TQ_TRY(check_plan(p, false));
+    DeviceScope scope(p->device);
+    if (on && !p->timer) {
+        TqKernelTimer* t = new (std::nothrow) TqKernelTimer();
+        if (!t) return tq_fail(TQ_ERR_CUDA, "out of host memory");
+        t->count[0] = t->count[1] = 0;
+        for (int k = 0; k < 2; ++k)
+            for (int i = 0; i < kTimerSlots; ++i)
+                for (int e = 0; e < 2; ++e) TQ_CUDA_TRY(cudaEventCreate(&t->ev[k][i][e]));
+        p->timer = t;
+    }
+    if (p->timer) p->timer->count[0] = p->timer->count[1] = 0;
+    if (!on && p->timer) {
+        for (int k = 0; k < 2; ++k)
+            for (int i = 0; i < kTimerSlots; ++i) { cudaEventDestroy(p->timer->ev[k][i][0]); cudaEventDestroy(p->timer->ev[k][i][1]); }
+        delete p->timer;
+        p->timer = nullptr;
+    }
+    return TQ_OK;
+}
+
+int tq_plan_kernel_ms(const tq_plan* p, int kind, float* ms, int max_count) {
+    if (!p || kind < 0 || kind > 1 || !ms || max_count < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "bad arguments");
+    if (!p->timer) return 0;
+    DeviceScope scope(p->device);
+    long long n = p->timer->count[kind];
+    if (n > kTimerSlots) n = kTimerSlots;      // the ring keeps the most recent launches
+    if (n > max_count) n = max_count;
+    for (long long i = 0; i < n; ++i) {
+        const long long slot = (p->timer->count[kind] - n + i) % kTimerSlots;
+        if (cudaEventElapsedTime(&ms[i], p->timer->ev[kind][slot][0], p->timer->ev[kind][slot][1]) != cudaSuccess)
+            return tq_fail(TQ_ERR_CUDA, "an event of launch %lld has not completed; synchronise the stream first", i);
+    }
+    return (int)n;
 }
 
 int tq_plan_set_wait_limit(tq_plan* p, int64_t cycles) {

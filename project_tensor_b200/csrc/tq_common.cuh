@@ -65,6 +65,15 @@ struct TqDev {
     const float* boundaries;  // [levels-1]
 };
 
+// Optional timing of the main kernel of a quantize (kind 0) or batched scoring (kind 1) call: a ring of event pairs,
+// one pair per launch, read back by tq_plan_kernel_ms after the stream has been synchronised.
+constexpr int kTimerSlots = 1024;
+struct TqKernelTimer {
+    cudaEvent_t ev[2][kTimerSlots][2];
+    long long count[2];
+};
+inline void tq_timer_mark(const struct tq_plan* p, int kind, int edge, cudaStream_t st);   // defined below the plan
+
 struct TensorConsts;  // defined in tq_tensor.cu
 struct DequantConsts; // defined in tq_dequant_tc.cu
 
@@ -80,7 +89,15 @@ struct tq_plan {
     unsigned long long* counters;  // device: [0] rows re-done by the exact kernel in the last quantize, [1] status word
                                    // (non-zero once a tensor-core kernel gave up on a bounded wait; sticky until read)
     int wait_kcycles;              // limit of a bounded wait inside the tensor-core kernels, in units of 1024 cycles
+    struct TqKernelTimer* timer;   // event pairs around the main kernels while tq_plan_time_kernels is on (else null)
 };
+
+inline void tq_timer_mark(const tq_plan* p, int kind, int edge, cudaStream_t st) {
+    TqKernelTimer* t = p->timer;
+    if (!t) return;
+    cudaEventRecord(t->ev[kind][t->count[kind] % kTimerSlots][edge], st);
+    if (edge == 1) ++t->count[kind];
+}
 
 // ---- error plumbing (tq_api.cu) -------------------------------------------------------------
 int tq_fail(int code, const char* fmt, ...);

@@ -166,7 +166,7 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
     const bool listed = lists.hdr != nullptr && lists.hdr->overflow == 0;
     const int64_t limit = listed ? (int64_t)min(lists.hdr->n_rows, lists.row_cap) : n;
     if (lists.hdr != nullptr && redo_counter && blockIdx.x == 0 && t == 0)
-        atomicAdd(redo_counter, (unsigned long long)limit);
+        *redo_counter = (unsigned long long)limit;     // rows redone by this call (a plain store: no clearing launch needed)
 
     for (int64_t g0 = (int64_t)blockIdx.x * kRB; g0 < limit; g0 += (int64_t)gridDim.x * kRB) {
         int64_t rows[kRB];                    // input rows (-1: none)

@@ -775,6 +775,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
                 if (cr == CUDA_SUCCESS) a.tile_store = 1;
             }
             int r = TQ_ERR_UNSUPPORTED;
+            tq_timer_mark(p, 1, 0, st);
 #define TQ_SC(B)                                                                                             \
     case B:                                                                                                  \
         if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(map, a, grid, st) : launch_score<B, 32, 64>(map, a, grid, st);   \
@@ -782,6 +783,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
         break;
             switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }
 #undef TQ_SC
+            tq_timer_mark(p, 1, 1, st);
             if (r != TQ_OK) return r == TQ_ERR_UNSUPPORTED ? tq_fail(r, "no tensor-core scoring kernel for bits=%d", bits) : r;
         }
         if (topk > 0) {

@@ -94,7 +94,8 @@ struct Smem {
     static constexpr int off_b = 0;
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
-    static constexpr int kPendBytes = 8 * kPendCap * (8 + 4);   // per epilogue warp: 64-bit and 32-bit entries
+    static constexpr int kPendBytes = 8 * kPendCap * (8 + 4) + (PROD ? 8 * kPendCap * 4 : 0);   // per epilogue warp: 64-bit and 32-bit
+                                                                // entries; Prod: row entries of the 8 converter warps behind them
     static constexpr int kRsBytes = 4 * 2 * kTileRows * 4;       // |rho|^2 partial sums: [4 tiles][2 halves][128]
     static constexpr int kMiscBytes = 8 * kTileRows * 4 + 4 * kTileRows + 512 + kRsBytes + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
@@ -159,7 +160,7 @@ __device__ __forceinline__ void pend_rows(const TqRecheck& l, WarpPending& w, bo
 
 // One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
 // and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
-// the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 by cell, lut_ncent by code.
+// the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 (boundaries below the cell) by cell, lut_ncent by code.
 template <int BITS, bool PROD>
 __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
                                               float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
@@ -189,8 +190,10 @@ __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float
 #pragma unroll
         for (int t = 0; t < kGroup; ++t) {
             const int e = g + t;
-            const float dlt = __uint_as_float(v[e]) - bnd[t];
-            code[t] = (uint32_t)base1[t] - (dlt > 0.f ? 0u : 1u);
+            // boundary - value is negative exactly when the value lies above the boundary: its sign bit is the step from
+            // "boundaries below the cell" to the code (a value equal to the boundary is inside the guard band)
+            const float dlt = bnd[t] - __uint_as_float(v[e]);
+            code[t] = (uint32_t)base1[t] + (__float_as_uint(dlt) >> 31);
             if (fabsf(dlt) < guard) nearmask |= 1u << e;
             const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
             w[wi] += code[t] << sh;
@@ -203,6 +206,7 @@ __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float
                 const float ncent = __shfl_sync(0xffffffffu, lut_ncent, (int)code[t]);
                 r[t] = fmaf(__uint_as_float(v[g + t]), kScaleRho, ncent);  // 2^10 * (value - centroid)
             }
+            // (packed fp32x2 arithmetic here made the kernel slower: the pairs have to be moved into adjacent registers)
 #pragma unroll
             for (int t = 0; t < kGroup; t += 2) {
                 rs = fmaf(r[t], r[t], rs);
@@ -429,7 +433,76 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         int64_t g_base = 0;
-        for (int64_t i = 0; i < (half < kActiveParts ? my_tiles : 0); ++i, g_base += L::kBoxesPerTile) {
+        const int64_t conv_tiles = half < kActiveParts ? my_tiles : 0;
+        // TurboQuantProd: these warps also run the sign epilogue (second accumulator -> sign bits, residual norm, rows
+        // for the exact stage).  They wait about half of every tile for a free A block, while the epilogue warps are the
+        // longest chain of the kernel; the second accumulator of tile j sits in the A block that the conversion of tile
+        // j + 3 refills, so "sign epilogue of tile i - 3, then conversion of tile i" is the order the data allows anyway.
+        WarpPending pend;
+        pend.codes = nullptr;
+        pend.rows = reinterpret_cast<unsigned int*>(pend_base + 8 * kPendCap * 12) + cw * kPendCap;
+        pend.n_codes = 0;
+        pend.n_rows = 0;
+        auto sign_epilogue = [&](int64_t j) {
+            constexpr int kChunks = 2;
+            const int chunk0 = half * kChunks;
+            const int64_t tile = blockIdx.x + j * gridDim.x;
+            const int b = (int)(j & 1);
+            const uint32_t par2 = (uint32_t)((j >> 1) & 1);
+            const int64_t grow = tile * kTileRows + row;
+            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32; long long c0 = clock64(), c1;)
+            bool redo_row = force[(j & 3) * kTileRows + row] != 0;
+            const bool live = mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag) && grow < a.n;   // no stores after a give-up
+            tc_fence_after();
+            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[18] += c1 - c0;)
+            const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
+            if (chunk0 == 0 && live) {   // rs is in 2^10 units
+                const int sl = (int)(j & 3) * 2;
+                const float rs_all = kHalves == 2 ? rs_part[sl * kTileRows + row] + rs_part[(sl + 1) * kTileRows + row]
+                                                  : rs_part[sl * kTileRows + row];
+                a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
+            }
+            uint32_t va[32];
+            uint32_t sw0 = 0, sw1 = 0;
+#pragma unroll 1
+            for (int ch = 0; ch < kChunks; ++ch) {
+                tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
+                tmem_wait_ld();
+                uint32_t wd[4] = {0u, 0u, 0u, 0u};                    // four partial chains instead of one long one
+                float am[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const uint32_t bits = va[e];
+                    // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
+                    // inside the guard band and recomputed anyway)
+                    wd[e & 3] |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
+                    am[e & 3] = fminf(am[e & 3], fabsf(__uint_as_float(bits)));
+                }
+                const uint32_t word = (wd[0] | wd[1]) | (wd[2] | wd[3]);
+                const float amin = fminf(fminf(am[0], am[1]), fminf(am[2], am[3]));
+                if (ch == 0) sw0 = word; else sw1 = word;
+                redo_row = redo_row || (amin < a.sign_guard);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + (b ^ 1)));  // that A block may be refilled
+            if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw0, sw1);
+            pend_rows(a.lists, pend, redo_row && live, grow, lane);
+            TQ_PROF_CODE(if (pr) a.prof[19] += clock64() - c1;)
+        };
+        const int64_t conv_iters = PROD ? (conv_tiles > 0 ? conv_tiles + 3 : 0) : conv_tiles;
+        for (int64_t i = 0; i < conv_iters; ++i) {
+            if (PROD) {
+                if (i >= 3) {
+                    sign_epilogue(i - 3);
+                } else if (i == 2) {
+                    // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 must have read it
+                    mbar_wait(BAR(BAR_ACC_FULL + 0), 0u, abort_flag);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
+                }
+                if (i >= conv_tiles) continue;
+            }
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
@@ -457,10 +530,23 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(BAR_EMPTY + slot));
             }
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            // TurboQuantMSE (32 values per thread): two values per instruction (fma / mul / add .f32x2), 3 % faster;
+            // TurboQuantProd (64 values per thread): scalar, the packed form is 7 % slower there (register pairs)
+            float ss;
+            if (!PROD) {
+                float2 s2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int k = 0; k < kXs; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
-            const float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+                for (int k = 0; k < kXs; k += 2) {
+                    const float2 xx = make_float2(x[k], x[k + 1]);
+                    s2[(k >> 1) & 1] = __ffma2_rn(xx, xx, s2[(k >> 1) & 1]);
+                }
+                ss = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
+            } else {
+                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < kXs; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
+                ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            }
             // partial sums of a tile go to the buffer of its parity: a fast warp writes the next tile's sums
             // before the barrier of that tile, while a slow partner may still be reading this tile's
             float* ssq = ssq_all + b * 4 * kTileRows;
@@ -477,7 +563,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             // rows the tensor-core pass cannot represent go to the exact kernel: overflowed or
             // denormal-range norms
             const bool odd = !(tot < 3.0e38f) || (ok && tot < 1.0e-30f);
-            const float sc = ok ? kScaleA / nrm : 0.f;
+            // scale 0 for rows that go to the exact kernel anyway (zero, overflowed or denormal-range norms): their
+            // products are 0, or NaN for rows that hold Inf / NaN, which stay in their own accumulator rows
+            const float sc = (ok && !odd) ? kScaleA / nrm : 0.f;
             if (half == 0) {
                 const int64_t grow = tile * kTileRows + row;
                 if (grow < a.n && !fail) a.norms[grow] = nrm;
@@ -492,12 +580,24 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int p = 0; p < 16; ++p) {
-                    const float u0 = (ok && !odd) ? x[s * 32 + 2 * p] * sc : 0.f;
-                    const float u1 = (ok && !odd) ? x[s * 32 + 2 * p + 1] * sc : 0.f;
-                    const __half2 h = __floats2half2_rn(u0, u1);
-                    const float2 hf = __half22float2(h);
+                    float u0, u1, l0, l1;
+                    __half2 h;
+                    if (!PROD) {
+                        const float2 u = __fmul2_rn(make_float2(x[s * 32 + 2 * p], x[s * 32 + 2 * p + 1]), make_float2(sc, sc));
+                        h = __floats2half2_rn(u.x, u.y);
+                        const float2 hf = __half22float2(h);
+                        const float2 l = __fadd2_rn(u, make_float2(-hf.x, -hf.y));
+                        l0 = l.x; l1 = l.y; u0 = u.x; u1 = u.y;
+                    } else {
+                        u0 = x[s * 32 + 2 * p] * sc;
+                        u1 = x[s * 32 + 2 * p + 1] * sc;
+                        h = __floats2half2_rn(u0, u1);
+                        const float2 hf = __half22float2(h);
+                        l0 = u0 - hf.x; l1 = u1 - hf.y;
+                    }
+                    (void)u0; (void)u1;
                     hi[p] = *reinterpret_cast<const uint32_t*>(&h);
-                    lo[p] = pack_half2(u0 - hf.x, u1 - hf.y);
+                    lo[p] = pack_half2(l0, l1);
                 }
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
@@ -508,7 +608,9 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + b));
             TQ_PROF_CODE(if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; })
+            g_base += L::kBoxesPerTile;
         }
+        if (PROD && pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
     } else {
         // ---- epilogue: one thread per row -----------------------------------------------------------
         const int quarter = warp & 3;
@@ -522,7 +624,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
         // lookup tables held in the lanes of the warp: per cell (boundary, 1 + boundaries below), per code
         // (- centroid * 2^10)
         const float lut_bnd = cell_lut[lane].x;
-        const int lut_base1 = __float_as_int(cell_lut[lane].y);
+        const int lut_base1 = __float_as_int(cell_lut[lane].y) - 1;   // boundaries below the cell = code of a value below its boundary
         const float lut_ncent = a.code_ncent[lane];
         WarpPending pend;
         pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + (warp - kFirstEpiWarp) * kPendCap;
@@ -625,66 +727,8 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             if (!PROD) pend_rows(a.lists, pend, redo_row && live, grow, lane);
             TQ_PROF_CODE(if (pr) a.prof[17] += clock64() - c1;)
         };
-        // second-accumulator epilogue of tile j (Prod): sign bits, guard test, release of the tile's A block
-        auto epilogue2 = [&](int64_t j) {
-            const int64_t tile = blockIdx.x + j * gridDim.x;
-            const int b = (int)(j & 1);
-            const uint32_t par2 = (uint32_t)((j >> 1) & 1);
-            const int64_t grow = tile * kTileRows + row;
-            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
-            bool redo_row = force[(j & 3) * kTileRows + row] != 0;
-            const bool live = mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag) && grow < a.n;   // no stores after a give-up
-            tc_fence_after();
-            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[18] += c1 - c0;)
-            const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
-            if (chunk0 == 0 && live) {   // rs is in 2^10 units
-                const int sl = (int)(j & 3) * 2;
-                const float rs_all = kHalves == 2 ? rs_part[sl * kTileRows + row] + rs_part[(sl + 1) * kTileRows + row]
-                                                  : rs_part[sl * kTileRows + row];
-                a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
-            }
-            uint32_t sw[kChunks];
-            uint32_t va[32];
-            uint32_t sw0 = 0, sw1 = 0;
-#pragma unroll 1
-            for (int ch = 0; ch < kChunks; ++ch) {
-                tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
-                tmem_wait_ld();
-                uint32_t wd[4] = {0u, 0u, 0u, 0u};                    // four partial chains instead of one long one
-                float am[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const uint32_t bits = va[e];
-                    // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
-                    // inside the guard band and recomputed anyway)
-                    wd[e & 3] |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
-                    am[e & 3] = fminf(am[e & 3], fabsf(__uint_as_float(bits)));
-                }
-                const uint32_t word = (wd[0] | wd[1]) | (wd[2] | wd[3]);
-                const float amin = fminf(fminf(am[0], am[1]), fminf(am[2], am[3]));
-                if (ch == 0) sw0 = word; else sw1 = word;
-                redo_row = redo_row || (amin < a.sign_guard);
-            }
-            sw[0] = sw0;
-            sw[kChunks - 1] = sw1;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + (b ^ 1)));  // the converters may refill that A block
-            if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw[0], sw[1]);
-            pend_rows(a.lists, pend, redo_row && live, grow, lane);
-            TQ_PROF_CODE(if (pr) a.prof[19] += clock64() - c1;)
-        };
-        if (PROD) {
-            static_assert(kChunks == 2, "the sign store writes two words per thread");
-            for (int64_t i = 0; i <= epi_tiles && epi_tiles > 0; ++i) {
-                if (i < epi_tiles) epilogue1(i);
-                if (i >= 1) epilogue2(i - 1);
-                // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 has read it
-                else if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
-            }
-        } else {
-            for (int64_t i = 0; i < epi_tiles; ++i) epilogue1(i);
-        }
+        static_assert(kChunks == 2, "a thread owns two 32-column chunks");
+        for (int64_t i = 0; i < epi_tiles; ++i) epilogue1(i);
         if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
         if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
     }
@@ -930,10 +974,13 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     const int grid = (int)(args.ntiles < sms ? args.ntiles : sms);
     const int bits = p->dev.bits;
+    tq_timer_mark(p, 0, 0, st);
+    int rc = TQ_ERR_UNSUPPORTED;
 #define TQ_DISPATCH(B)                                                                                     \
     case B:                                                                                                \
-        if (d == 64) return prod ? launch_one<64, B, true>(map, args, grid, st) : launch_one<64, B, false>(map, args, grid, st); \
-        return prod ? launch_one<128, B, true>(map, args, grid, st) : launch_one<128, B, false>(map, args, grid, st);
+        if (d == 64) rc = prod ? launch_one<64, B, true>(map, args, grid, st) : launch_one<64, B, false>(map, args, grid, st); \
+        else rc = prod ? launch_one<128, B, true>(map, args, grid, st) : launch_one<128, B, false>(map, args, grid, st);      \
+        break;
     switch (bits) {
         TQ_DISPATCH(1)
         TQ_DISPATCH(2)
@@ -941,5 +988,7 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
         TQ_DISPATCH(4)
     }
 #undef TQ_DISPATCH
+    tq_timer_mark(p, 0, 1, st);
+    if (rc != TQ_ERR_UNSUPPORTED) return rc;
     return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for bits=%d", bits);
 }

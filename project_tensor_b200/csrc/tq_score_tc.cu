@@ -27,12 +27,14 @@
 
 #include <cuda.h>
 #include <math.h>
+#include <math_constants.h>
 #include <stdlib.h>
 #include <string.h>
 
 namespace {
 
 using namespace tqptx;
+using namespace tqtopk;
 
 constexpr int D = 128;
 constexpr int kTileKeys = 128;
@@ -70,6 +72,15 @@ struct ScoreTcArgs {
     float* scores;                // points at (group 0, first query of this pass, key_off)
     int tile_store;               // 1: score tiles leave through shared memory and a bulk tensor store (tmap_out)
     int norms_bulk;               // 1: norms and residual norms travel with the packed rows through the key ring
+    int tile_stride;              // tile kt of a group covers keys [kt * tile_stride * 128, +128): > 1 scores a sample of the tiles
+    // Top-k without a score matrix (candidate mode): a score that reaches its query's threshold is appended to that
+    // query's candidate list (sortable key: score bits | row) instead of being written anywhere else.
+    int fused;                    // 0: score matrix; 1: candidates through a staging list; 2: the sampled pass (every score, fixed slots)
+    int qpg_total, q0;            // queries per group over all passes, first query of this pass
+    const float* thr;             // [groups][qpg_total] lower bound of the k-th best score so far (-inf: none)
+    unsigned int* cnt;            // [groups][qpg_total] entries appended to each list
+    unsigned long long* cand;     // [groups][qpg_total][cand_cap]
+    int64_t cand_cap;
     float alpha;
     unsigned long long* status;
     int wait_kcycles;             // limit of one bounded wait, in units of 1024 cycles
@@ -141,7 +152,9 @@ struct ScoreSmem {
     static constexpr int total = off_misc + 512 + 128;
 };
 
-template <int BITS, int QPAD, int DR>
+// CAND: candidate mode (top-k without a score matrix) is a kernel of its own, so that the matrix kernel carries none
+// of its registers and code.
+template <int BITS, int QPAD, int DR, bool CAND>
 __global__ void __launch_bounds__(ScoreThreads<QPAD>::kThreads, 1)
 score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs a) {
     static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
@@ -234,9 +247,10 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 const int64_t i = t - t0;
                 const int s = (int)(i % kStages);
                 if (!mbar_wait(BAR(SB_K_EMPTY + s), (uint32_t)((i / kStages) & 1) ^ 1u, abort_flag)) break;
-                int64_t valid = a.key_cnt - kt * kTileKeys;
+                const int64_t k0 = kt * a.tile_stride * kTileKeys;      // first key of the tile within this launch's range
+                int64_t valid = a.key_cnt - k0;
                 if (valid > kTileKeys) valid = kTileKeys;
-                const int64_t row0 = g * a.keys_per_group + a.key_off + kt * kTileKeys;
+                const int64_t row0 = g * a.keys_per_group + a.key_off + k0;
                 const uint32_t cb = (uint32_t)valid * L::kCodeRowBytes, sb = (uint32_t)valid * L::kSignRowBytes;
                 const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + row0 * L::kCodeRowBytes;
                 const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(a.signs) + row0 * L::kSignRowBytes;
@@ -402,12 +416,39 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         // norm and residual norm of this thread's key, fetched one tile ahead of their use (a load issued
         // in the tile that needs it would stall the stores for a full trip to memory)
         auto fetch_norms = [&](int64_t gg, int64_t kk, float& n_out, float& r_out) {
-            const int64_t key_n = kk * kTileKeys + row;
+            const int64_t key_n = kk * a.tile_stride * kTileKeys + row;
             const bool live_n = key_n < a.key_cnt;
             const int64_t grow_n = gg * a.keys_per_group + a.key_off + key_n;
             n_out = live_n ? __ldg(a.norms + grow_n) : 0.f;
             r_out = live_n ? __ldg(a.rnorms + grow_n) : 0.f;
         };
+        // candidate mode: thresholds of the current group, and in place of the score tile buffers a staging list of
+        // survivors (keys, then the numbers of their lists) and 16 x 32 parked scores per warp
+        int64_t thr_g = -1;
+        float* thr_s = reinterpret_cast<float*>(bars + SB_COUNT + 2);   // [QPAD]
+        int* st_count = reinterpret_cast<int*>(thr_s + QPAD);
+        constexpr int kStageCap = (2 * L::kOutBytes - 4 * kEpiPerRow * 16 * 32 * 4) / 12 / 128 * 128;    // 1,280 entries (32 queries), 640 (16)
+        static_assert(kStageCap >= 512, "candidate staging must fit the score tile buffers");
+        unsigned long long* st_keys = reinterpret_cast<unsigned long long*>(smem + L::off_out);
+        uint32_t* st_list = reinterpret_cast<uint32_t*>(smem + L::off_out + kStageCap * 8);
+        float* warp_scores = reinterpret_cast<float*>(smem + L::off_out + kStageCap * 12) + (warp - kFirstEpiWarp) * 16 * 32;
+        const int epi_t = threadIdx.x - kFirstEpiWarp * 32;
+        auto flush_staging = [&]() {      // all epilogue threads, after a barrier that made every append visible
+            int n = *st_count;
+            if (n > kStageCap) n = kStageCap;
+            for (int i = epi_t; i < n; i += kEpiThreads) {
+                const int64_t l = st_list[i];
+                const int64_t gp = (int64_t)atomicAdd(a.cnt + l, 1u);
+                if (gp < a.cand_cap) a.cand[l * a.cand_cap + gp] = st_keys[i];
+            }
+            bar_sync(kEpiBarrier, kEpiThreads);
+            if (epi_t == 0) *st_count = 0;
+            bar_sync(kEpiBarrier, kEpiThreads);
+        };
+        if (CAND) {
+            if (epi_t == 0) *st_count = 0;
+            bar_sync(kEpiBarrier, kEpiThreads);
+        }
         float nrm_next = 0.f, rn_next = 0.f;
         if (t0 < t1 && !a.norms_bulk) fetch_norms(g, kt, nrm_next, rn_next);
         for (int64_t t = t0; t < t1; ++t, ++kt) {
@@ -416,7 +457,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
-            const int64_t key = kt * kTileKeys + row;          // within this launch's key range
+            const int64_t key = kt * a.tile_stride * kTileKeys + row;          // within this launch's key range
             const bool live = key < a.key_cnt;
             float nrm, arn;
             if (a.norms_bulk) {
@@ -466,8 +507,67 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 }
             }
             TQ_PROF_CODE(long long c2 = clock64();)
-            if (!got) {
-                // nothing is written for a tile whose accumulators cannot be trusted
+            // After a give-up (`got` false) nothing is written for the tile, but every epilogue warp still walks through the
+            // named barriers below: the warps learn of the give-up at different tiles, and a barrier that some of them
+            // skipped would never complete.
+            if (CAND) {
+                if (g != thr_g) {      // thresholds of this group's queries (constant during the launch) into shared memory
+                    thr_g = g;
+                    bar_sync(kEpiBarrier, kEpiThreads);      // everybody is done with the previous group's
+                    if (epi_t < QPAD) thr_s[epi_t] = epi_t < a.nq ? __ldg(a.thr + g * a.qpg_total + a.q0 + epi_t) : CUDART_INF_F;
+                    bar_sync(kEpiBarrier, kEpiThreads);
+                }
+                const uint32_t rowid = (uint32_t)(g * a.keys_per_group + a.key_off + key);   // row of the key arrays
+                const int64_t q_first = g * a.qpg_total + a.q0 + q16;
+                if (a.fused == 2) {
+                    // The sampled pass (thresholds at -inf, every score is a candidate): the slot of a score is known
+                    // without a counter (tile of the sample x 128 + row); the host presets the lists' lengths.
+                    // A key beyond the end of the group leaves an empty slot.
+#pragma unroll
+                    for (int k = 0; k < 16; ++k)
+                        if (q16 + k < a.nq)
+                            a.cand[(q_first + k) * a.cand_cap + kt * kTileKeys + row] = live && got ? make_key(sc[k], rowid) : 0ull;
+                } else {
+                    // This thread's 16 scores against their thresholds: a mask, and the scores parked in shared memory
+                    // so that the loop below can pick them by a run-time index.  The loop runs once per query that has a
+                    // survivor among the warp's 32 keys and is kept rolled: the candidate path must stay small, this
+                    // kernel lives on its instruction cache (the same logic unrolled over the 16 queries doubled the
+                    // kernel's time without a single survivor).
+                    float* mine = warp_scores + lane;
+                    uint32_t pm = 0;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        pm |= (live && got && sc[k] >= thr_s[q16 + k]) ? (1u << k) : 0u;
+                        mine[k * 32] = sc[k];
+                    }
+                    // Survivors go to a staging list in shared memory (a global counter update per survivor would put a
+                    // trip to L2 on this warp's path every tile); the list is emptied into the global lists, all its
+                    // entries at once, when it is half full (looked at every eighth tile: the barrier couples the warps).
+                    if ((i & 7) == 0 && bar_or(kEpiBarrier, kEpiThreads, *st_count > kStageCap / 2)) flush_staging();
+                    uint32_t wm = __reduce_or_sync(0xffffffffu, pm);
+#pragma unroll 1
+                    while (wm != 0u) {
+                        const int k = __ffs(wm) - 1;
+                        wm &= wm - 1u;
+                        const bool pass = (pm >> k) & 1u;
+                        const uint32_t votes = __ballot_sync(0xffffffffu, pass);
+                        const int leader = __ffs(votes) - 1;
+                        uint32_t base = 0;
+                        if (lane == leader) base = (uint32_t)atomicAdd(st_count, (int)__popc(votes));
+                        base = __shfl_sync(0xffffffffu, base, leader);
+                        if (pass) {
+                            const uint32_t pos = base + __popc(votes & ((1u << lane) - 1u));
+                            const unsigned long long ck = make_key(mine[k * 32], rowid);
+                            if (pos < (uint32_t)kStageCap) {
+                                st_keys[pos] = ck;
+                                st_list[pos] = (uint32_t)(q_first + k);
+                            } else {      // the staging list is full (nearly every score passes): straight to the global list
+                                const int64_t gp = (int64_t)atomicAdd(a.cnt + q_first + k, 1u);
+                                if (gp < a.cand_cap) a.cand[(q_first + k) * a.cand_cap + gp] = ck;
+                            }
+                        }
+                    }
+                }
             } else if (a.tile_store) {
                 // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
                 // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
@@ -480,11 +580,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
                 fence_async_smem();
                 bar_sync(kEpiBarrier, kEpiThreads);
-                if (store_leader) {
+                if (store_leader && got) {
                     tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
                     bulk_commit();
                 }
-            } else if (live) {
+            } else if (live && got) {
                 float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
@@ -504,6 +604,10 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(SB_B_EMPTY + bb));
             }
+        }
+        if (CAND) {
+            bar_sync(kEpiBarrier, kEpiThreads);
+            flush_staging();
         }
         if (store_leader) bulk_wait_all();   // the staged tiles must have left before the block's shared memory goes away
     }
@@ -588,8 +692,6 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     if (j == 0) ds[slot] = make_float2(1.f / (e1 * kCentScale), 1.f / e2);
 }
 
-using namespace tqtopk;
-
 // grid (segments, rows): block scans scores[row][seg*seg_len ...) and writes its k best as sortable keys
 // to part[((group*lists_per_group + list_base + seg) * qpg + qi) * topk ...].  Candidates above the
 // running threshold are collected in shared memory; when the buffer could overflow in the next batch
@@ -658,6 +760,72 @@ topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t g
     for (int i = threadIdx.x; i < topk; i += kSelThreads) dst[i] = buf[i];
 }
 
+// Candidate mode, after a scoring pass: one block per (query, group) takes the query's candidate list (and, mode 0,
+// its best list so far), keeps the k best as sorted keys in best[group][query][topk], raises the query's threshold
+// to the k-th best score (once there are k) and empties the list.  Mode 1 (the sampled pass that only finds a
+// first threshold) leaves the best list alone: its keys will be scored again by the full pass.
+__global__ void __launch_bounds__(256)
+select_candidates_kernel(const unsigned long long* __restrict__ cand, unsigned int* __restrict__ cnt, int64_t cap,
+                         unsigned long long* __restrict__ best, float* __restrict__ thr, int qpg, int topk, int k2, int mode) {
+    __shared__ __align__(16) unsigned long long a[kSelCap];
+    __shared__ int hist[256];
+    __shared__ int scratch[4];
+    __shared__ int count;
+    __shared__ unsigned long long cut;   // keys at or below it cannot be among the k best any more
+    const int64_t q = (int64_t)blockIdx.y * qpg + blockIdx.x;
+    const unsigned long long* list = cand + q * cap;
+    unsigned long long* mine = best + q * topk;
+    const int64_t n = min((int64_t)cnt[q], cap);
+    if (threadIdx.x == 0) { count = 0; cut = 0ull; }
+    __syncthreads();
+    if (mode == 0) {
+        for (int i = threadIdx.x; i < topk; i += blockDim.x) {
+            const unsigned long long v = mine[i];
+            if (v != 0ull) a[atomicAdd(&count, 1)] = v;
+        }
+        __syncthreads();
+    }
+    constexpr int kBatch = 2048;
+    for (int64_t base = 0; base < n; base += kBatch) {
+        if (count + kBatch > kSelCap) {  // uniform: count only changes between barriers
+            const int c = count;
+            __syncthreads();
+            if (c > topk) {
+                const unsigned long long kth = block_select_topk(a, c, topk, hist, scratch);
+                if (threadIdx.x == 0) { count = topk; cut = kth; }
+            }
+            __syncthreads();
+        }
+        const unsigned long long t = cut;
+        const int64_t end = base + kBatch < n ? base + kBatch : n;
+        for (int64_t i = base + threadIdx.x; i < end; i += blockDim.x) {
+            const unsigned long long v = __ldcs(list + i);
+            if (v > t) a[atomicAdd(&count, 1)] = v;      // also drops the empty slots
+        }
+        __syncthreads();
+    }
+    const int c = count;
+    const int keep = c < topk ? c : topk;
+    if (keep < c) block_select_topk(a, c, keep, hist, scratch);
+    __syncthreads();
+    for (int i = keep + threadIdx.x; i < k2; i += blockDim.x) a[i] = 0ull;
+    block_sort_desc(a, k2);
+    if (mode == 0)
+        for (int i = threadIdx.x; i < topk; i += blockDim.x) mine[i] = a[i];
+    if (threadIdx.x == 0) {
+        if (keep == topk) thr[q] = unordered_bits((uint32_t)(a[topk - 1] >> 32));
+        cnt[q] = 0u;
+    }
+}
+
+// thresholds to -inf, best lists to empty, list lengths to `first_count` (what the sampled pass will leave in them; 0 without one)
+__global__ void init_candidates_kernel(float* thr, unsigned int* cnt, unsigned long long* best, int64_t lists, int topk,
+                                       unsigned int first_count) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < lists) { thr[i] = -CUDART_INF_F; cnt[i] = first_count; }
+    if (i < lists * topk) best[i] = 0ull;
+}
+
 int pow2_at_least(int v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -667,8 +835,14 @@ int pow2_at_least(int v) {
 template <int BITS, int QPAD, int DR>
 int launch_score(const CUtensorMap& map, const ScoreTcArgs& args, int grid, cudaStream_t st) {
     const int sm = ScoreSmem<BITS, QPAD, DR>::total;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    score_tc_kernel<BITS, QPAD, DR><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args); tq_count_launch();
+    if (args.fused) {
+        TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+        score_tc_kernel<BITS, QPAD, DR, true><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args); tq_count_launch();
+        TQ_CUDA_TRY(cudaGetLastError());
+        return TQ_OK;
+    }
+    TQ_CUDA_TRY(cudaFuncSetAttribute(score_tc_kernel<BITS, QPAD, DR, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    score_tc_kernel<BITS, QPAD, DR, false><<<grid, ScoreThreads<QPAD>::kThreads, sm, st>>>(map, args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -704,8 +878,42 @@ static ScoreTcPlan plan_score(int groups, int qpg, int64_t keys_per_group, int t
     return s;
 }
 
+// Candidate mode (top-k without any score matrix) for key sets of several chunks: per query a threshold, a counter,
+// a best-k list and a candidate list that can hold every key of one chunk (so no list can overflow, whatever the data).
+constexpr int64_t kCandChunk = 1 << 21;     // keys per group per scoring launch
+constexpr int64_t kSampleEvery = 64;        // the first threshold comes from every 64th tile of the first chunk
+
+struct CandPlan {
+    int64_t chunk, nchunks, cand_cap, lists;
+    size_t off_thr, off_cnt, off_best, off_cand, total;
+};
+
+static CandPlan plan_candidates(int groups, int qpg, int64_t keys_per_group, int topk) {
+    CandPlan s{};
+    auto pad = [](size_t b) { return (b + 255) & ~size_t(255); };
+    s.chunk = kCandChunk;
+    s.nchunks = (keys_per_group + s.chunk - 1) / s.chunk;
+    s.cand_cap = s.chunk;
+    s.lists = (int64_t)groups * qpg;
+    s.off_thr = pad((size_t)groups * prep_group_bytes(32));
+    s.off_cnt = s.off_thr + pad((size_t)s.lists * 4);
+    s.off_best = s.off_cnt + pad((size_t)s.lists * 4);
+    s.off_cand = s.off_best + pad((size_t)s.lists * (topk > 0 ? topk : 1) * 8);
+    s.total = s.off_cand + pad((size_t)s.lists * s.cand_cap * 8);
+    return s;
+}
+
+// Candidate mode pays a sampled pass and two selections up front; it wins once a key set spans several chunks
+// (measured: 8,388,608 keys x 32 queries 158 us per 1,048,576 keys against 188 us through a scratch matrix; a single
+// chunk of 1,048,576 keys 307 us against 224 us).
+static bool use_candidates(const float* scores, int topk, int64_t keys_per_group) {
+    return scores == nullptr && topk > 0 && keys_per_group > 2 * kCandChunk;
+}
+
 int64_t tq_score_tc_scratch(int groups, int qpg, int64_t keys_per_group, int topk) {
-    return (int64_t)plan_score(groups, qpg, keys_per_group, topk, true).total;
+    const size_t a = plan_score(groups, qpg, keys_per_group, topk, true).total;
+    const size_t b = use_candidates(nullptr, topk, keys_per_group) ? plan_candidates(groups, qpg, keys_per_group, topk).total : 0;
+    return (int64_t)(a > b ? a : b);
 }
 
 int tq_merge_keys_launch(const unsigned long long* part, int lists, int qpg, int groups, int topk, int64_t idx_base,
@@ -716,25 +924,25 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
                        float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
                        size_t scratch_bytes, cudaStream_t st, int64_t group_rows) {
     if (group_rows <= 0) group_rows = keys_per_group;
+    const bool candidates = use_candidates(scores, topk, keys_per_group);
     const ScoreTcPlan sp = plan_score(groups, qpg, keys_per_group, topk, scores == nullptr);
-    if (!scratch || scratch_bytes < sp.total)
-        return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "score scratch: need %zu bytes, got %zu", sp.total, scratch_bytes);
+    const CandPlan cp = plan_candidates(groups, qpg, keys_per_group, topk);
+    const size_t need = candidates ? cp.total : sp.total;
+    if (!scratch || scratch_bytes < need)
+        return tq_fail(TQ_ERR_SCRATCH_TOO_SMALL, "score scratch: need %zu bytes, got %zu", need, scratch_bytes);
     unsigned char* sc = static_cast<unsigned char*>(scratch);
-    unsigned char* prep = sc + sp.off_prep;
-    unsigned long long* part = reinterpret_cast<unsigned long long*>(sc + sp.off_part);
-    float* tmp = reinterpret_cast<float*>(sc + sp.off_matrix);
+    unsigned char* prep = sc;     // both layouts start with the prepared queries
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     const int bits = p->dev.bits;
+    float* thr = reinterpret_cast<float*>(sc + cp.off_thr);
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(sc + cp.off_cnt);
+    unsigned long long* best = reinterpret_cast<unsigned long long*>(sc + cp.off_best);
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(sc + cp.off_cand);
 
-    if (topk > 0) TQ_CUDA_TRY(cudaMemsetAsync(part, 0, sp.part_bytes, st));  // zero = empty slot
-    const int64_t nchunks = scores ? 1 : sp.nchunks;  // with a caller matrix everything is scored in one go
-    for (int64_t c = 0; c < nchunks; ++c) {
-        const int64_t key_off = scores ? 0 : c * sp.chunk;
-        int64_t key_cnt = scores ? keys_per_group : keys_per_group - key_off;
-        if (!scores && key_cnt > sp.chunk) key_cnt = sp.chunk;
-        float* mat = scores ? scores : tmp;
-        const int64_t row_stride = scores ? keys_per_group : sp.chunk;
+    // One scoring launch per pass of at most 32 queries over keys [key_off, key_off + key_cnt) of every group (every
+    // tile_stride-th tile of them), into a matrix (mat != null) or into the candidate lists.
+    auto score_passes = [&](int64_t key_off, int64_t key_cnt, int tile_stride, float* mat, int64_t row_stride) -> int {
         const int64_t group_stride = (int64_t)qpg * row_stride;
         for (int q0 = 0; q0 < qpg; q0 += 32) {
             const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
@@ -746,25 +954,31 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
             a.prep = prep; a.codebook = p->dev.codebook;
             a.keys_per_group = group_rows; a.key_off = key_off; a.key_cnt = key_cnt;
-            a.tiles_per_group = (key_cnt + kTileKeys - 1) / kTileKeys;
+            a.tile_stride = tile_stride;
+            const int64_t tiles = (key_cnt + kTileKeys - 1) / kTileKeys;
+            a.tiles_per_group = (tiles + tile_stride - 1) / tile_stride;
             a.total_tiles = a.tiles_per_group * groups;
             a.nq = nq;
             a.out_group_stride = group_stride; a.out_row_stride = row_stride;
-            a.scores = mat + (int64_t)q0 * row_stride;
+            a.scores = mat ? mat + (int64_t)q0 * row_stride : nullptr;
             a.alpha = p->dev.alpha;
             a.norms_bulk = (groups == 1 || group_rows % 4 == 0) && key_off % 4 == 0 ? 1 : 0;   // 16-byte aligned tile starts
+            a.fused = mat ? 0 : (tile_stride > 1 ? 2 : 1);    // 2: the sampled pass
+            a.qpg_total = qpg; a.q0 = q0;
+            a.thr = thr; a.cnt = cnt; a.cand = cand; a.cand_cap = cp.cand_cap;
             a.status = p->counters + 1;
             a.wait_kcycles = p->wait_kcycles;
 #ifdef TQ_PROF
             a.prof = reinterpret_cast<long long*>(p->counters + 8);
 #endif
+            if (a.total_tiles == 0) continue;
             const int grid = (int)(a.total_tiles < sms ? a.total_tiles : sms);
             // Score tiles leave through a bulk tensor store when the matrix allows one: 16-byte aligned base and
             // row pitch.  Box = 128 keys x the queries of the pass x one group; extents clip ragged edges.
             CUtensorMap map;
             memset(&map, 0, sizeof(map));
             a.tile_store = 0;
-            if ((reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0 && row_stride % 4 == 0 && key_cnt > 0 && tq_encode_tiled_fn()) {
+            if (mat && (reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0 && row_stride % 4 == 0 && key_cnt > 0 && tq_encode_tiled_fn()) {
                 const cuuint64_t gdim[3] = {(cuuint64_t)key_cnt, (cuuint64_t)nq, (cuuint64_t)groups};
                 const cuuint64_t gstride[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)group_stride * 4};
                 const cuuint32_t box[3] = {(cuuint32_t)kTileKeys, (cuuint32_t)qpad, 1};
@@ -786,16 +1000,71 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             tq_timer_mark(p, 1, 1, st);
             if (r != TQ_OK) return r == TQ_ERR_UNSUPPORTED ? tq_fail(r, "no tensor-core scoring kernel for bits=%d", bits) : r;
         }
-        if (topk > 0) {
-            const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
-            // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
-            topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, 0, st>>>(
-                mat, row_stride, group_stride, qpg, key_cnt, kSegLen, group_rows, key_off, topk, pow2_at_least(topk),
-                (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part); tq_count_launch();
-            TQ_CUDA_TRY(cudaGetLastError());
+        return TQ_OK;
+    };
+
+    if (!candidates) {
+        // A score matrix exists: the caller's (everything scored in one go) or, when only the top-k is wanted, a scratch
+        // matrix per chunk of keys; the top-k is selected from it segment by segment and the lists are merged at the end.
+        unsigned long long* part = reinterpret_cast<unsigned long long*>(sc + sp.off_part);
+        float* tmp = reinterpret_cast<float*>(sc + sp.off_matrix);
+        if (topk > 0) TQ_CUDA_TRY(cudaMemsetAsync(part, 0, sp.part_bytes, st));  // zero = empty slot
+        const int64_t nchunks = scores ? 1 : sp.nchunks;
+        for (int64_t c = 0; c < nchunks; ++c) {
+            const int64_t key_off = scores ? 0 : c * sp.chunk;
+            int64_t key_cnt = scores ? keys_per_group : keys_per_group - key_off;
+            if (!scores && key_cnt > sp.chunk) key_cnt = sp.chunk;
+            float* mat = scores ? scores : tmp;
+            const int64_t row_stride = scores ? keys_per_group : sp.chunk;
+            const int rc = score_passes(key_off, key_cnt, 1, mat, row_stride);
+            if (rc != TQ_OK) return rc;
+            if (topk > 0) {
+                const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
+                // lists of chunk c occupy slots [c*segs_per_chunk, ...); unused slots stay zero (= empty)
+                topk_rows_kernel<<<dim3((unsigned)segs, (unsigned)(groups * qpg)), kSelThreads, 0, st>>>(
+                    mat, row_stride, (int64_t)qpg * row_stride, qpg, key_cnt, kSegLen, group_rows, key_off, topk, pow2_at_least(topk),
+                    (int)sp.lists_per_group, (int)(c * sp.segs_per_chunk), part); tq_count_launch();
+                TQ_CUDA_TRY(cudaGetLastError());
+            }
         }
+        if (topk > 0)
+            return tq_merge_keys_launch(part, (int)sp.lists_per_group, qpg, groups, topk, idx_base, top_scores, top_idx, st);
+        return TQ_OK;
     }
-    if (topk > 0)
-        return tq_merge_keys_launch(part, (int)sp.lists_per_group, qpg, groups, topk, idx_base, top_scores, top_idx, st);
-    return TQ_OK;
+
+    // Top-k only over several chunks.  Every query keeps a threshold (a lower bound of its k-th best score so far); the
+    // scoring kernel appends the scores that reach it to the query's candidate list and nothing else leaves the kernel;
+    // after every launch the lists are folded into the running best-k lists, which raises the thresholds for the next
+    // chunk.  The first threshold comes from scoring every 64th tile of the first chunk with the threshold at -inf: the
+    // k-th best of a subset is a lower bound of the k-th best of the whole, so the full pass that follows loses nothing
+    // and appends only about 64 k scores per query.
+    const int k2 = pow2_at_least(topk);
+    const int64_t cells = cp.lists * topk;
+    const int64_t tiles0 = (cp.chunk + kTileKeys - 1) / kTileKeys;
+    const int64_t sample_tiles = (tiles0 + kSampleEvery - 1) / kSampleEvery;
+    init_candidates_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(thr, cnt, best, cp.lists, topk,
+                                                                            (unsigned int)(sample_tiles * kTileKeys)); tq_count_launch();
+    TQ_CUDA_TRY(cudaGetLastError());
+    auto select = [&](int mode) -> int {
+        select_candidates_kernel<<<dim3((unsigned)qpg, (unsigned)groups), 256, 0, st>>>(cand, cnt, cp.cand_cap, best, thr, qpg, topk, k2, mode);
+        tq_count_launch();
+        TQ_CUDA_TRY(cudaGetLastError());
+        return TQ_OK;
+    };
+    for (int64_t c = 0; c < cp.nchunks; ++c) {
+        const int64_t key_off = c * cp.chunk;
+        int64_t key_cnt = keys_per_group - key_off;
+        if (key_cnt > cp.chunk) key_cnt = cp.chunk;
+        if (c == 0) {
+            int rc = score_passes(key_off, key_cnt, (int)kSampleEvery, nullptr, 0);
+            if (rc != TQ_OK) return rc;
+            rc = select(1);
+            if (rc != TQ_OK) return rc;
+        }
+        int rc = score_passes(key_off, key_cnt, 1, nullptr, 0);
+        if (rc != TQ_OK) return rc;
+        rc = select(0);
+        if (rc != TQ_OK) return rc;
+    }
+    return tq_merge_keys_launch(best, 1, qpg, groups, topk, idx_base, top_scores, top_idx, st);
 }

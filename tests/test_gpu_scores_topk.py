@@ -90,9 +90,9 @@ def test_topk_equals_sorted_matrix(tg, path, n, nq, k):
 
 
 def test_topk_over_several_scratch_chunks(tg):
-    """9,000,000 keys: without a matrix from the caller the scores pass through scratch in chunks of 2^22
-    keys (two full ones and a ragged third); the per-chunk candidates must merge into the same top-100 as a
-    sort of the full matrix."""
+    """9,000,000 keys: without a matrix from the caller the keys are scored in chunks of 2^21 (four full ones and a
+    ragged fifth) with only the scores above each query's running threshold kept; the result must be the same
+    top-100 as a sort of the full matrix."""
     import torch
     d, n, nq, k = 128, 9_000_000, 8, 100
     gen = torch.Generator(device="cuda").manual_seed(20265)
@@ -106,6 +106,60 @@ def test_topk_over_several_scratch_chunks(tg):
     srt = torch.sort(mat, dim=1, descending=True, stable=True)
     assert torch.equal(top_s, srt.values[:, :k])
     assert torch.equal(top_i, srt.indices[:, :k] + 7)
+
+
+def _sorted_topk(mat, k):
+    import torch
+    srt = torch.sort(mat, dim=1, descending=True, stable=True)
+    return srt.values[:, :k], srt.indices[:, :k]
+
+
+def test_topk_without_matrix_when_every_key_beats_the_threshold(tg):
+    """Above 4,194,304 keys per group the top-k comes from candidate lists filled by the scoring kernel (scores that
+    reach the query's running threshold) instead of a scratch matrix.  Worst cases for that scheme, 4,500,003 keys:
+    query 0 meets keys whose scores rise with the index (every key passes the threshold of its moment, so the lists
+    fill to their capacity), query 1 the same keys falling (nothing passes after the sampled pass), long runs of
+    identical keys tie exactly (ties go to the lower index), and 38 random queries make a second pass of queries.
+    The result must equal a stable sort of the full matrix, for k = 100 and k = 300."""
+    import torch
+    d, n, nq = 128, 4_500_003, 40
+    gen = torch.Generator(device="cuda").manual_seed(20266)
+    u = torch.randn((d,), generator=gen, device="cuda", dtype=torch.float32)
+    scale = 0.5 + (torch.arange(n, device="cuda", dtype=torch.float32) // 1000) * (1000.0 / n)   # runs of 1000 equal keys
+    x = scale[:, None] * u[None, :]
+    x[n // 2:n // 2 + 200_000] = torch.randn((200_000, d), generator=gen, device="cuda")
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    q[0] = u
+    q[1] = -u
+    prod = tg.TurboQuantProd(d, 4, seed=2026)
+    enc = prod.quantize(x)
+    del x, scale
+    mat = prod.attention_scores(q, enc)
+    for k in (100, 300):
+        top_s, top_i = prod.attention_scores(q, enc, topk=k)
+        want_s, want_i = _sorted_topk(mat, k)
+        assert torch.equal(top_s, want_s), k
+        assert torch.equal(top_i, want_i), k
+
+
+def test_topk_without_matrix_for_query_groups(tg):
+    """Two key groups of 4,300,000 keys (ragged last tile and last chunk), three queries per group, k = 64: the
+    candidate lists are per query of every group and the indices count from the start of the group's keys."""
+    import torch
+    d, groups, kpg, qpg, k = 64, 2, 4_300_000, 3, 64
+    gen = torch.Generator(device="cuda").manual_seed(20267)
+    x = torch.randn((groups * kpg, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((groups * qpg, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, 3, seed=2026)
+    enc = prod.quantize(x)
+    del x
+    mat = prod.attention_scores(q, enc, groups=groups)
+    assert mat.shape == (groups * qpg, kpg)
+    top_s, top_i = prod.attention_scores(q, enc, groups=groups, topk=k, index_base=5)
+    want_s, want_i = _sorted_topk(mat, k)
+    assert torch.equal(top_s, want_s)
+    for r in range(groups * qpg):
+        assert torch.equal(top_i[r], want_i[r] + (r // qpg) * kpg + 5)
 
 
 def test_sharded_index_matches_single_index(tg):

@@ -270,9 +270,14 @@ static int quantize_common(const tq_plan* p, bool prod, const float* x, int64_t 
         TQ_CUDA_TRY(cudaMemsetAsync(lists.hdr, 0, sizeof(TqRecheckHeader), st));
         TQ_TRY(tq_launch_tensor_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
                                          rnorms, norms, &lists, st));
+        tq_timer_mark(p, 2, 0, st);
         TQ_TRY(tq_launch_exact_code_check(p, prod, x, n, static_cast<uint32_t*>(codes), &lists, st));
-        return tq_launch_exact_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
-                                        rnorms, norms, &lists, p->counters, st);
+        tq_timer_mark(p, 2, 1, st);
+        tq_timer_mark(p, 3, 0, st);
+        const int rc = tq_launch_exact_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs),
+                                                rnorms, norms, &lists, p->counters, st);
+        tq_timer_mark(p, 3, 1, st);
+        return rc;
     }
     if (err != TQ_OK) return err;
     return tq_launch_exact_quantize(p, prod, x, n, static_cast<uint32_t*>(codes), static_cast<uint32_t*>(signs), rnorms,
@@ -585,15 +590,16 @@ int tq_plan_time_kernels(tq_plan* p, int on) {
     if (on && !p->timer) {
         TqKernelTimer* t = new (std::nothrow) TqKernelTimer();
         if (!t) return tq_fail(TQ_ERR_CUDA, "out of host memory");
-        t->count[0] = t->count[1] = 0;
-        for (int k = 0; k < 2; ++k)
+        for (int k = 0; k < kTimerKinds; ++k) t->count[k] = 0;
+        for (int k = 0; k < kTimerKinds; ++k)
             for (int i = 0; i < kTimerSlots; ++i)
                 for (int e = 0; e < 2; ++e) TQ_CUDA_TRY(cudaEventCreate(&t->ev[k][i][e]));
         p->timer = t;
     }
-    if (p->timer) p->timer->count[0] = p->timer->count[1] = 0;
+    if (p->timer)
+        for (int k = 0; k < kTimerKinds; ++k) p->timer->count[k] = 0;
     if (!on && p->timer) {
-        for (int k = 0; k < 2; ++k)
+        for (int k = 0; k < kTimerKinds; ++k)
             for (int i = 0; i < kTimerSlots; ++i) { cudaEventDestroy(p->timer->ev[k][i][0]); cudaEventDestroy(p->timer->ev[k][i][1]); }
         delete p->timer;
         p->timer = nullptr;
@@ -602,7 +608,7 @@ int tq_plan_time_kernels(tq_plan* p, int on) {
 }
 
 int tq_plan_kernel_ms(const tq_plan* p, int kind, float* ms, int max_count) {
-    if (!p || kind < 0 || kind > 1 || !ms || max_count < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "bad arguments");
+    if (!p || kind < 0 || kind >= kTimerKinds || !ms || max_count < 0) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "bad arguments");
     if (!p->timer) return 0;
     DeviceScope scope(p->device);
     long long n = p->timer->count[kind];

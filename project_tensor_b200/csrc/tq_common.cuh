@@ -68,9 +68,10 @@ struct TqDev {
 // Optional timing of the main kernel of a quantize (kind 0) or batched scoring (kind 1) call: a ring of event pairs,
 // one pair per launch, read back by tq_plan_kernel_ms after the stream has been synchronised.
 constexpr int kTimerSlots = 1024;
+constexpr int kTimerKinds = 4;   // 0 quantize kernel, 1 scoring kernel, 2 coordinate re-check, 3 row re-computation
 struct TqKernelTimer {
-    cudaEvent_t ev[2][kTimerSlots][2];
-    long long count[2];
+    cudaEvent_t ev[kTimerKinds][kTimerSlots][2];
+    long long count[kTimerKinds];
 };
 inline void tq_timer_mark(const struct tq_plan* p, int kind, int edge, cudaStream_t st);   // defined below the plan
 

@@ -255,48 +255,67 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
 }
 
 
-// Second stage of the tensor-core quantizers, part 1: one warp per listed (row, coordinate).
+// Second stage of the tensor-core quantizers, part 1: one thread per listed (row, coordinate).
 // The coordinate's rotated value is recomputed exactly as the reference does (norm by pairwise sum,
 // IEEE division, one FMA per k, k ascending) and its code re-decided.  If the stored code differs it is
 // patched in place (MSE); for TurboQuantProd the residual of the whole row depends on it, so the
-// row goes to the row list instead.
-__global__ void __launch_bounds__(256)
+// row goes to the row list instead.  A list holds some ten thousand entries per million rows and a dependent access
+// to global memory costs about a microsecond, so the kernel is as long as its chain of such accesses: header, entry,
+// then the whole row into registers (D / 4 loads of 16 bytes in flight at once) together with the first half of the
+// matrix row.  D is 64 or 128 (the tensor-core geometries), so the row sum is a single block of NumPy's pairwise
+// scheme: eight interleaved sums.
+template <int D>
+__global__ void __launch_bounds__(128)
 exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                         TqRecheck lists) {
-    extern __shared__ float smem[];
+    constexpr int Q = D / 4;
+    const unsigned int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+    // asked for before the header is known to allow it (the list's capacity bounds the index)
+    unsigned long long ent = e0 < lists.code_cap ? lists.code_entries[e0] : 0ull;
     if (lists.hdr->overflow) return;  // the row pass will redo everything
     const unsigned int count = min(lists.hdr->n_codes, lists.code_cap);
-    const int d = p.d, dp = (d + 31) & ~31;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    float* xs = smem + (size_t)warp * 3 * dp;   // row, then unit row
-    float* sq = xs + dp;                        // squares
-    float* rs = sq + dp;                        // row j of the rotation
-    for (unsigned int e = blockIdx.x * nwarps + warp; e < count; e += gridDim.x * nwarps) {
-        const unsigned long long ent = lists.code_entries[e];
+    for (unsigned int e = e0; e < count; e += gridDim.x * blockDim.x) {
+        if (e != e0) ent = lists.code_entries[e];
         const int64_t row = (int64_t)(ent >> 8);
         const int j = (int)(ent & 255u);
-        if (row >= n || j >= d) continue;
-        const float* xr = x + row * d;
-        const float* rj = p.R + (size_t)j * d;
-        __syncwarp();
-        for (int k = lane; k < d; k += 32) {
-            const float v = xr[k];
-            xs[k] = v;
-            sq[k] = __fmul_rn(v, v);
-            rs[k] = __ldg(rj + k);
-        }
-        __syncwarp();
-        const float nrm = __fsqrt_rn(np_pairwise_sum(sq, d, lane));
-        const bool ok = nrm > 0.f;
-        for (int k = lane; k < d; k += 32) xs[k] = ok ? __fdiv_rn(xs[k], nrm) : 0.f;
-        __syncwarp();
-        float acc = 0.f;  // every lane runs the same chain on broadcast reads
-#pragma unroll 8
-        for (int k = 0; k < d; ++k) acc = __fmaf_rn(xs[k], rs[k], acc);
-        if (lane != 0) continue;
-        const uint32_t code = (uint32_t)count_below(p.boundaries, p.levels - 1, acc);
+        if (row >= n || j >= D) continue;
+        const float4* xr = reinterpret_cast<const float4*>(x + row * D);
+        const float4* rj = reinterpret_cast<const float4*>(p.R + (size_t)j * D);
         uint32_t* crow = codes + row * p.code_words;
+        float4 xv[Q], rv[Q / 2];
+#pragma unroll
+        for (int i = 0; i < Q; ++i) xv[i] = xr[i];
+#pragma unroll
+        for (int i = 0; i < Q / 2; ++i) rv[i] = __ldg(rj + i);
         const uint32_t old = tq_get_code(crow, j, p.bits);
+        float r8[8] = {__fmul_rn(xv[0].x, xv[0].x), __fmul_rn(xv[0].y, xv[0].y), __fmul_rn(xv[0].z, xv[0].z), __fmul_rn(xv[0].w, xv[0].w),
+                       __fmul_rn(xv[1].x, xv[1].x), __fmul_rn(xv[1].y, xv[1].y), __fmul_rn(xv[1].z, xv[1].z), __fmul_rn(xv[1].w, xv[1].w)};
+#pragma unroll
+        for (int i = 2; i < Q; i += 2) {
+            const float4 a = xv[i], b = xv[i + 1];
+            r8[0] = __fadd_rn(r8[0], __fmul_rn(a.x, a.x)); r8[1] = __fadd_rn(r8[1], __fmul_rn(a.y, a.y));
+            r8[2] = __fadd_rn(r8[2], __fmul_rn(a.z, a.z)); r8[3] = __fadd_rn(r8[3], __fmul_rn(a.w, a.w));
+            r8[4] = __fadd_rn(r8[4], __fmul_rn(b.x, b.x)); r8[5] = __fadd_rn(r8[5], __fmul_rn(b.y, b.y));
+            r8[6] = __fadd_rn(r8[6], __fmul_rn(b.z, b.z)); r8[7] = __fadd_rn(r8[7], __fmul_rn(b.w, b.w));
+        }
+        const float sumsq = __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
+                                      __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
+        const float nrm = __fsqrt_rn(sumsq);
+        const bool ok = nrm > 0.f;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < Q; ++i) {
+            if (i == Q / 2) {   // second half of the matrix row into the registers of the first
+#pragma unroll
+                for (int u = 0; u < Q / 2; ++u) rv[u] = __ldg(rj + Q / 2 + u);
+            }
+            const float4 v = xv[i], m = rv[i % (Q / 2)];
+            acc = __fmaf_rn(ok ? __fdiv_rn(v.x, nrm) : 0.f, m.x, acc);
+            acc = __fmaf_rn(ok ? __fdiv_rn(v.y, nrm) : 0.f, m.y, acc);
+            acc = __fmaf_rn(ok ? __fdiv_rn(v.z, nrm) : 0.f, m.z, acc);
+            acc = __fmaf_rn(ok ? __fdiv_rn(v.w, nrm) : 0.f, m.w, acc);
+        }
+        const uint32_t code = (uint32_t)count_below(p.boundaries, p.levels - 1, acc);
         if (old == code) continue;
         if (prod) {
             const unsigned int pos = atomicAdd(&lists.hdr->n_rows, 1u);
@@ -449,8 +468,13 @@ int grid_for(int64_t work_items, int per_block) {
 int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                                const TqRecheck* lists, cudaStream_t st) {
     if (n == 0) return TQ_OK;
-    const int dp = (p->dev.d + 31) & ~31;
-    exact_code_check_kernel<<<148 * 8, 256, (size_t)8 * 3 * dp * sizeof(float), st>>>(p->dev, prod, x, n, codes, *lists); tq_count_launch();
+    // as many threads as a list of typical length has entries (about 1 in 50 rows); longer lists take more passes
+    int64_t blocks = (n / 48 + 127) / 128;
+    blocks = blocks < 8 ? 8 : (blocks > 148 * 4 ? 148 * 4 : blocks);
+    if (p->dev.d == 128) exact_code_check_kernel<128><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
+    else if (p->dev.d == 64) exact_code_check_kernel<64><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
+    else return tq_fail(TQ_ERR_UNSUPPORTED, "the coordinate re-check is written for d = 64 and d = 128");
+    tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

@@ -46,14 +46,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (*abort_flag) return false;  // somebody already gave up: do not block again
     const long long t0 = clock64();
-    for (uint32_t it = 0;; ++it) {
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;   // blocks inside the hardware for a while before it answers
-        if ((it & 7u) == 7u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > ((long long)abort_flag[1] << 10)) {
-                *abort_flag = 1;
-                return false;
-            }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > ((long long)abort_flag[1] << 10)) {
+            *abort_flag = 1;
+            return false;
         }
     }
 }
@@ -108,6 +106,12 @@ __device__ __forceinline__ bool bar_or(int id, int count, bool pred) {
 }
 
 // Plain named barrier over `count` threads (a multiple of 32).
+// min(m, |a|, |b|) as one three-input minimum (sm_100)
+__device__ __forceinline__ float min3_abs(float m, float a, float b) {
+    float r;
+    asm("{\n\t.reg .f32 ta, tb;\n\tabs.f32 ta, %2;\n\tabs.f32 tb, %3;\n\tmin.f32 %0, %1, ta, tb;\n\t}" : "=f"(r) : "f"(m), "f"(a), "f"(b));
+    return r;
+}
 __device__ __forceinline__ void bar_sync(int id, int count) {
     asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }

@@ -39,13 +39,14 @@ namespace {
 using namespace tqptx;
 
 constexpr int kTileRows = 128;
-// Warps: TMA, MMA, 8 converters, then 8 epilogue warps: two threads per row, each owning half of the columns.
-// Warp roles: TMA, MMA, the converter warps, then 8 epilogue warps.  TurboQuantMSE has 16 converter warps (a
-// thread converts 32 values of a row), TurboQuantProd 8 (64 values): the converters' per-tile chain bounds the
-// MSE kernel, while the Prod epilogue needs the registers that more warps would take away.
-template <bool PROD> struct Threads {
-    static constexpr int kEpiPerRow = 2;
-    static constexpr int kConvWarps = PROD ? 8 : 16;
+// Warps: TMA, MMA, then the workers.  UNI (the kernels that run): 16 workers, four per row, each owning 32 columns of
+// its row through every phase of a tile -- conversion, first-accumulator epilogue and (TurboQuantProd) sign epilogue.
+// All workers walk the same code, so whichever phase the tensor pipe has finished finds warps to run it; with the
+// phases given to different warps (!UNI: converter warps and 8 epilogue warps, two per row; kept for comparison)
+// the issue slots were idle 44 % of the time although every warp had a backlog, because each role waited for the other.
+template <bool PROD, bool UNI> struct Threads {
+    static constexpr int kEpiPerRow = UNI ? 0 : 2;
+    static constexpr int kConvWarps = UNI ? 16 : (PROD ? 8 : 16);
     static constexpr int kFirstEpiWarp = 2 + kConvWarps;
     static constexpr int kThreads = (2 + kConvWarps + 4 * kEpiPerRow) * 32;
 };
@@ -57,13 +58,12 @@ constexpr float kAccScale = kScaleA * kScaleB;  // accumulator = 2^20 * rotated 
 constexpr float kScaleRho = 1.f / 1024.f;       // accumulator units -> 2^10 * rho for the second A operand
 constexpr float kScaleM = 16.f;                 // R S^T -> second B operand
 constexpr int kCells = 32;
-constexpr int kPendCap = 64;               // second-stage entries staged per epilogue warp and list
+constexpr int kPendCap = 32;               // second-stage entries staged per warp and list (a ballot adds up to 32)
 constexpr float kCellMul = 31.99998f;
 
 struct TensorArgs {
     const __half* bmat;      // [R_hi | R_lo | M_hi | M_lo], each d*d halves in the interleaved layout
-    const float4* cell_lut;  // [32] per cell: boundary (x 2^20, +inf if none), 1 + boundaries below the cell
-                             // (as int bits), -centroid below * 2^10, -centroid above * 2^10
+    const float2* cell_lut;  // [32] per cell: boundary (x 2^20, +inf if none), boundaries below the cell (as int bits)
     const float* code_ncent; // [32] entry l: -centroid(l mod levels) * 2^10
     float cell_scale, cell_offset;
     float code_guard, sign_guard;  // in accumulator units
@@ -85,7 +85,7 @@ struct TensorArgs {
 // Shared-memory plan
 // ---------------------------------------------------------------------------------------------
 constexpr int kW = 128;   // width of the operand layouts in tensor and shared memory; d = 64 is zero-padded to it
-template <int D, bool PROD>
+template <int D, bool PROD, bool UNI>
 struct Smem {
     static constexpr int kBoxesPerTile = D / 32;
     static constexpr int kBBytes = kW * kW * 2;                     // one fp16 operand matrix (padded)
@@ -94,9 +94,12 @@ struct Smem {
     static constexpr int off_b = 0;
     static constexpr int off_ring = off_b + kNumB * kBBytes;
     static constexpr int off_misc = off_ring + kRingBoxes * kBoxBytes;  // sumsq exchange, force flags, barriers
-    static constexpr int kPendBytes = 8 * kPendCap * (8 + 4) + (PROD ? 8 * kPendCap * 4 : 0);   // per epilogue warp: 64-bit and 32-bit
-                                                                // entries; Prod: row entries of the 8 converter warps behind them
-    static constexpr int kRsBytes = 4 * 2 * kTileRows * 4;       // |rho|^2 partial sums: [4 tiles][2 halves][128]
+    static constexpr int kPendWarps = Threads<PROD, UNI>::kConvWarps + 4 * Threads<PROD, UNI>::kEpiPerRow;   // every worker warp
+                                                                // stages entries: a 64-bit and a 32-bit list each
+    static constexpr int kPendBytes = kPendWarps * kPendCap * (8 + 4);
+    static constexpr int kRsSlots = UNI ? 3 : 4;                 // tiles whose |rho|^2 partial sums are alive at once
+    static constexpr int kRsParts = UNI ? 4 : 2;                 // threads per row in the first epilogue
+    static constexpr int kRsBytes = kRsSlots * kRsParts * kTileRows * 4;
     static constexpr int kMiscBytes = 8 * kTileRows * 4 + 4 * kTileRows + 512 + kRsBytes + kCells * 16 + kPendBytes;
     static constexpr int total = off_misc + kMiscBytes + 1024;      // + slack to align the base to 1024
     static_assert(total <= 227 * 1024, "shared memory plan");
@@ -161,6 +164,8 @@ __device__ __forceinline__ void pend_rows(const TqRecheck& l, WarpPending& w, bo
 // One 32-column chunk of the first accumulator for one row: codes (packed into w), guard-band test,
 // and for TurboQuantProd the scaled residual split into fp16 hi/lo pairs;
 // the lookup tables live in the lanes of the warp: lut_bnd / lut_base1 (boundaries below the cell) by cell, lut_ncent by code.
+// (One shuffle instead of two -- the count packed into the low mantissa bits of the boundary, taken apart with an AND --
+// was slower: 217 -> 226 us for TurboQuantProd, 162 -> 183 us for TurboQuantMSE; the integer pipe is the scarcer one.)
 template <int BITS, bool PROD>
 __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float lut_bnd, int lut_base1, float lut_ncent,
                                               float cell_scale, float cell_offset, float guard, uint32_t (&w)[BITS + 1],
@@ -187,17 +192,25 @@ __device__ __forceinline__ uint32_t process_chunk(const uint32_t (&v)[32], float
             bnd[t] = __shfl_sync(0xffffffffu, lut_bnd, cell[t]);
             base1[t] = __shfl_sync(0xffffffffu, lut_base1, cell[t]);
         }
+        float dlt[kGroup];
+        float nearest = 3.0e38f;   // smallest |boundary - value| of the group
 #pragma unroll
         for (int t = 0; t < kGroup; ++t) {
             const int e = g + t;
             // boundary - value is negative exactly when the value lies above the boundary: its sign bit is the step from
             // "boundaries below the cell" to the code (a value equal to the boundary is inside the guard band)
-            const float dlt = bnd[t] - __uint_as_float(v[e]);
-            code[t] = (uint32_t)base1[t] + (__float_as_uint(dlt) >> 31);
-            if (fabsf(dlt) < guard) nearmask |= 1u << e;
+            dlt[t] = bnd[t] - __uint_as_float(v[e]);
+            code[t] = (uint32_t)base1[t] + (__float_as_uint(dlt[t]) >> 31);
             const int bit = e * BITS, wi = bit >> 5, sh = bit & 31;
             w[wi] += code[t] << sh;
             if (sh + BITS > 32) w[wi + 1] += code[t] >> (32 - sh);
+        }
+#pragma unroll
+        for (int t = 0; t < kGroup; t += 2) nearest = min3_abs(nearest, dlt[t], dlt[t + 1]);
+        if (nearest < guard) {   // about one group in five thousand
+#pragma unroll
+            for (int t = 0; t < kGroup; ++t)
+                if (fabsf(dlt[t]) < guard) nearmask |= 1u << (g + t);
         }
         if (PROD) {
             float r[kGroup];
@@ -239,21 +252,22 @@ __device__ __noinline__ void pend_codes(const TqRecheck& l, WarpPending& w, uint
     }
 }
 
-template <int D, int BITS, bool PROD>
-__global__ void __launch_bounds__(Threads<PROD>::kThreads, 1)
+template <int D, int BITS, bool PROD, bool UNI>
+__global__ void __launch_bounds__(Threads<PROD, UNI>::kThreads, 1)
 tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
     static_assert(D == 128 || D == 64, "this kernel is written for d = 128 and d = 64");
     // d = 64 runs in the layouts of d = 128 with the upper half of every row absent: the converter warps
     // and the epilogue warps of that half stay idle, the contractions stop after d / 16 k-blocks and cover
     // N = d output coordinates.
-    constexpr int kHalves = D / 64;
-    constexpr int kThreads = Threads<PROD>::kThreads;
-    constexpr int kEpiPerRow = Threads<PROD>::kEpiPerRow;
-    constexpr int kFirstEpiWarp = Threads<PROD>::kFirstEpiWarp;
-    constexpr int kConvParts = Threads<PROD>::kConvWarps / 4;   // converter threads per row
+    constexpr int kThreads = Threads<PROD, UNI>::kThreads;
+    constexpr int kFirstEpiWarp = Threads<PROD, UNI>::kFirstEpiWarp;
+    constexpr int kConvParts = Threads<PROD, UNI>::kConvWarps / 4;   // converter threads per row
     constexpr int kXs = kW / kConvParts;                        // values a converter thread handles (64 or 32)
     constexpr int kActiveParts = D / kXs;                       // parts that have data (d = 64: half of them)
-    using L = Smem<D, PROD>;
+    using L = Smem<D, PROD, UNI>;
+    constexpr int kEpiChunks = UNI ? 1 : 2;                     // 32-column chunks a thread owns in the first epilogue
+    constexpr int kEpiParts = D / (32 * kEpiChunks);            // first-epilogue threads per row that have data
+    constexpr int kSignChunks = kXs / 32;                       // chunks a thread owns in the sign epilogue
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t smem_base = smem_u32(smem);
@@ -262,25 +276,25 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     unsigned char* force = smem + L::off_misc + 8 * kTileRows * 4;                      // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::off_misc + 8 * kTileRows * 4 + 4 * kTileRows);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
-    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - L::kRsBytes - kCells * 16);  // [4 tiles][2 halves][128]
-    float4* cell_lut = reinterpret_cast<float4*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
+    float* rs_part = reinterpret_cast<float*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - L::kRsBytes - kCells * 16);  // [kRsSlots][kRsParts][128]
+    float2* cell_lut = reinterpret_cast<float2*>(smem + L::off_misc + L::kMiscBytes - L::kPendBytes - kCells * 16);  // [32]
     unsigned char* pend_base = smem + L::off_misc + L::kMiscBytes - L::kPendBytes;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    TQ_PROF_CODE(const long long prof_t0 = clock64();)
+    TQ_PROF_CODE(const long long prof_t0 = clock64(); long long prof_acc[21] = {0};)   // per-thread sums, written out once at the end
 
     // ---- one-time set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8; ++i) { mbar_init(BAR(BAR_FULL + i), 1); mbar_init(BAR(BAR_EMPTY + i), 4); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(BAR_A_FULL + i), 4 * kActiveParts);              // the converter warps that have data
-            mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kHalves : 1);       // Prod: freed by the sign epilogue
+            mbar_init(BAR(BAR_A_EMPTY + i), PROD ? 4 * kActiveParts : 1);  // Prod: freed by the sign epilogue
             mbar_init(BAR(BAR_ACC_FULL + i), 1);
-            mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kHalves);     // Prod: freed when MMA 2 has read rho
-            mbar_init(BAR(BAR_RHO_FULL + i), 4 * kHalves);
+            mbar_init(BAR(BAR_ACC_EMPTY + i), PROD ? 1 : 4 * kEpiParts);   // Prod: freed when MMA 2 has read rho
+            mbar_init(BAR(BAR_RHO_FULL + i), 4 * kEpiParts);
         }
         mbar_init(BAR(BAR_ACC2_FULL), 1);
         mbar_init(BAR(BAR_ACC2_FULL + 1), 1);
@@ -366,7 +380,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     TQ_PROF_CODE(long long c1 = clock64();)
                     if (!warp_wait(BAR(BAR_ACC_EMPTY + b), par2 ^ 1u, abort_flag)) break;
                     tc_fence_after();
-                    TQ_PROF_CODE(long long c2 = clock64(); if (pr) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
+                    TQ_PROF_CODE(long long c2 = clock64(); if (pr) { prof_acc[8] += c1 - c0; prof_acc[9] += c2 - c1; })
                     const uint32_t acc = tm + ACC_COL(b);
                     const uint32_t a_hi = tm + A_COL(b), a_lo = a_hi + kABlock;
                     if (elect_one()) {
@@ -385,7 +399,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                         if (!PROD) mma_commit(BAR(BAR_A_EMPTY + b));
                     }
                     __syncwarp();
-                    TQ_PROF_CODE(if (pr) a.prof[10] += clock64() - c2;)
+                    TQ_PROF_CODE(if (pr) prof_acc[10] += clock64() - c2;)
                 }
                 if (PROD && i >= 1) {
                     const int64_t j = i - 1;
@@ -394,7 +408,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     TQ_PROF_CODE(long long c0 = clock64();)
                     if (!warp_wait(BAR(BAR_RHO_FULL + b), par2, abort_flag)) break;
                     tc_fence_after();
-                    TQ_PROF_CODE(long long c1 = clock64(); if (pr) a.prof[11] += c1 - c0;)
+                    TQ_PROF_CODE(long long c1 = clock64(); if (pr) prof_acc[11] += c1 - c0;)
                     // The second accumulator goes to the A block of the OTHER buffer: MMA 1 of tile j + 1, issued
                     // above, was its last reader, and using it (rather than this tile's own A block) lets the
                     // converters refill a block one tile earlier.  The last tile has no successor whose
@@ -421,64 +435,89 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                         mma_commit(BAR(BAR_ACC_EMPTY + b));         // rho has been read: the accumulator block is free
                     }
                     __syncwarp();
-                    TQ_PROF_CODE(if (pr) a.prof[12] += clock64() - c1;)
+                    TQ_PROF_CODE(if (pr) prof_acc[12] += clock64() - c1;)
                 }
             }
         }
-    } else if (warp < kFirstEpiWarp) {
-        // ---- converters: fp32 rows -> unit length, fp16 hi/lo, into tensor memory ----------------
-        const int cw = warp - kFirstConvWarp;      // 0 .. kConvWarps-1
-        const int half = cw >> 2;                  // which kXs floats of the row
+    } else {
+        // ---- workers ------------------------------------------------------------------------------
+        // Roles of this warp: UNI: every role, on the 32 columns [32 * half, 32 * half + 32) of its rows; otherwise a
+        // converter warp (which also runs the sign epilogue of TurboQuantProd) or a first-epilogue warp.
+        const bool conv_role = UNI || warp < kFirstEpiWarp;
+        const bool epi_role = UNI || warp >= kFirstEpiWarp;
+        const int cw = warp - kFirstConvWarp;      // 0 .. workers-1
+        const int half = cw >> 2;                  // converter: which kXs floats of the row
         const int quarter = warp & 3;              // TMEM lane quarter this warp may touch
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        int64_t g_base = 0;
-        const int64_t conv_tiles = half < kActiveParts ? my_tiles : 0;
-        // TurboQuantProd: these warps also run the sign epilogue (second accumulator -> sign bits, residual norm, rows
-        // for the exact stage).  They wait about half of every tile for a free A block, while the epilogue warps are the
-        // longest chain of the kernel; the second accumulator of tile j sits in the A block that the conversion of tile
-        // j + 3 refills, so "sign epilogue of tile i - 3, then conversion of tile i" is the order the data allows anyway.
+        constexpr int kCodeWords = D * BITS / 32;  // words per packed row
+        const int colgroup = UNI ? half : (warp - kFirstEpiWarp) >> 2;   // first epilogue: which kEpiChunks chunks of the row
+        const int chunk0 = colgroup * kEpiChunks;
+        const bool conv_active = conv_role && half < kActiveParts;      // d = 64: the warps of the absent columns idle
+        const bool epi_active = epi_role && colgroup < kEpiParts;
+        // lookup tables held in the lanes of the warp: per cell (boundary, boundaries below), per code (- centroid * 2^10)
+        const float lut_bnd = cell_lut[lane].x;
+        const int lut_base1 = __float_as_int(cell_lut[lane].y);   // boundaries below the cell = code of a value below its boundary
+        const float lut_ncent = a.code_ncent[lane];
         WarpPending pend;
-        pend.codes = nullptr;
-        pend.rows = reinterpret_cast<unsigned int*>(pend_base + 8 * kPendCap * 12) + cw * kPendCap;
+        pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + cw * kPendCap;
+        pend.rows = reinterpret_cast<unsigned int*>(pend_base + L::kPendWarps * kPendCap * 8) + cw * kPendCap;
         pend.n_codes = 0;
         pend.n_rows = 0;
+        int64_t g_base = 0;
+
+        // -- sign epilogue of tile j (TurboQuantProd): second accumulator -> sign bits, residual norm, rows for the exact
+        // stage.  The second accumulator of tile j sits in the A block that the conversion of tile j + 3 refills, so
+        // "sign epilogue of tile i - 3, then conversion of tile i" is the order the data allows anyway.
         auto sign_epilogue = [&](int64_t j) {
-            constexpr int kChunks = 2;
-            const int chunk0 = half * kChunks;
+            const int sc0 = half * kSignChunks;
             const int64_t tile = blockIdx.x + j * gridDim.x;
             const int b = (int)(j & 1);
             const uint32_t par2 = (uint32_t)((j >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
             TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstConvWarp * 32; long long c0 = clock64(), c1;)
-            bool redo_row = force[(j & 3) * kTileRows + row] != 0;
+            bool redo_row = sc0 == 0 && force[(j & 3) * kTileRows + row] != 0;
             const bool live = mbar_wait(BAR(BAR_ACC2_FULL + b), par2, abort_flag) && grow < a.n;   // no stores after a give-up
             tc_fence_after();
-            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[18] += c1 - c0;)
+            TQ_PROF_CODE(c1 = clock64(); if (pr) prof_acc[18] += c1 - c0;)
             const uint32_t acc2 = tmem + lane_addr + A_COL(b ^ 1);
-            if (chunk0 == 0 && live) {   // rs is in 2^10 units
-                const int sl = (int)(j & 3) * 2;
-                const float rs_all = kHalves == 2 ? rs_part[sl * kTileRows + row] + rs_part[(sl + 1) * kTileRows + row]
-                                                  : rs_part[sl * kTileRows + row];
+            if (sc0 == 0 && live) {   // rs is in 2^10 units
+                const float* rp = rs_part + (int)(j % L::kRsSlots) * L::kRsParts * kTileRows + row;
+                float rs_all = rp[0];
+#pragma unroll
+                for (int pt = 1; pt < kEpiParts; ++pt) rs_all += rp[pt * kTileRows];
                 a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
             }
             uint32_t va[32];
             uint32_t sw0 = 0, sw1 = 0;
 #pragma unroll 1
-            for (int ch = 0; ch < kChunks; ++ch) {
-                tmem_ld32(acc2 + (chunk0 + ch) * 32, va);
+            for (int ch = 0; ch < kSignChunks; ++ch) {
+                TQ_PROF_CODE(const long long l0 = clock64();)
+                tmem_ld32(acc2 + (sc0 + ch) * 32, va);
                 tmem_wait_ld();
-                uint32_t wd[4] = {0u, 0u, 0u, 0u};                    // four partial chains instead of one long one
+                TQ_PROF_CODE(if (pr) prof_acc[15] += clock64() - l0;)
+                // Word layout: coordinate e of the chunk sits at bit (e >> 1) + 16 * (e & 1), bit = 1 for a non-negative
+                // projection (-0.0 counts as negative here; such a row is inside the guard band and recomputed anyway).
+                // One funnel shift per coordinate pushes its sign bit into a chain: four chains of eight (even / odd
+                // coordinates, lower / upper half), filled from the highest coordinate down, inverted at the end.
+                uint32_t wd[4] = {0u, 0u, 0u, 0u};
                 float am[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const uint32_t bits = va[e];
-                    // bit = 1 for a non-negative projection (-0.0 counts as negative here; such a row is
-                    // inside the guard band and recomputed anyway)
-                    wd[e & 3] |= ((~bits) >> 31) << ((e >> 1) + ((e & 1) << 4));
-                    am[e & 3] = fminf(am[e & 3], fabsf(__uint_as_float(bits)));
+                for (int i = 7; i >= 0; --i) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int e = (c >> 1) * 16 + 2 * i + (c & 1);     // chain c: parity c & 1, half c >> 1
+                        wd[c] = __funnelshift_l(va[e], wd[c], 1);          // (chain << 1) | sign bit
+                    }
                 }
-                const uint32_t word = (wd[0] | wd[1]) | (wd[2] | wd[3]);
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        am[c] = min3_abs(am[c], __uint_as_float(va[e + 2 * c]), __uint_as_float(va[e + 2 * c + 1]));
+                }
+                // chains 0 / 1: even / odd coordinates 0..15 -> bits 0..7 / 16..23; chains 2 / 3: coordinates 16..31 -> 8..15 / 24..31
+                const uint32_t word = ~((wd[0] | (wd[2] << 8)) | ((wd[1] | (wd[3] << 8)) << 16));
                 const float amin = fminf(fminf(am[0], am[1]), fminf(am[2], am[3]));
                 if (ch == 0) sw0 = word; else sw1 = word;
                 redo_row = redo_row || (amin < a.sign_guard);
@@ -486,23 +525,16 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + (b ^ 1)));  // that A block may be refilled
-            if (live) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + chunk0) = make_uint2(sw0, sw1);
-            pend_rows(a.lists, pend, redo_row && live, grow, lane);
-            TQ_PROF_CODE(if (pr) a.prof[19] += clock64() - c1;)
-        };
-        const int64_t conv_iters = PROD ? (conv_tiles > 0 ? conv_tiles + 3 : 0) : conv_tiles;
-        for (int64_t i = 0; i < conv_iters; ++i) {
-            if (PROD) {
-                if (i >= 3) {
-                    sign_epilogue(i - 3);
-                } else if (i == 2) {
-                    // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 must have read it
-                    mbar_wait(BAR(BAR_ACC_FULL + 0), 0u, abort_flag);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
-                }
-                if (i >= conv_tiles) continue;
+            if (live) {
+                if (kSignChunks == 2) *reinterpret_cast<uint2*>(a.signs + grow * (D / 32) + sc0) = make_uint2(sw0, sw1);
+                else a.signs[grow * (D / 32) + sc0] = sw0;
             }
+            pend_rows(a.lists, pend, redo_row && live, grow, lane);
+            TQ_PROF_CODE(if (pr) prof_acc[19] += clock64() - c1;)
+        };
+
+        // -- conversion of tile i: fp32 rows -> unit length, fp16 hi/lo, into tensor memory
+        auto convert = [&](int64_t i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
@@ -516,7 +548,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 const uint32_t par = (uint32_t)((g / L::kRingBoxes) & 1);
                 TQ_PROF_CODE(long long cw0 = clock64();)
                 if (!fail && !mbar_wait(BAR(BAR_FULL + slot), par, abort_flag)) fail = true;
-                TQ_PROF_CODE(if (pr) a.prof[6] += clock64() - cw0;)
+                TQ_PROF_CODE(if (pr) prof_acc[6] += clock64() - cw0;)
                 const unsigned char* box = smem + L::off_ring + slot * kBoxBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -530,10 +562,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(BAR_EMPTY + slot));
             }
-            // TurboQuantMSE (32 values per thread): two values per instruction (fma / mul / add .f32x2), 3 % faster;
-            // TurboQuantProd (64 values per thread): scalar, the packed form is 7 % slower there (register pairs)
+            // 32 values per thread: two values per instruction (fma / mul / add .f32x2), 3 % faster; 64 values per
+            // thread: scalar, the packed form is 7 % slower there (register pairs)
+            constexpr bool kPacked = kXs == 32;
             float ss;
-            if (!PROD) {
+            if (kPacked) {
                 float2 s2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
                 for (int k = 0; k < kXs; k += 2) {
@@ -551,10 +584,10 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             // before the barrier of that tile, while a slow partner may still be reading this tile's
             float* ssq = ssq_all + b * 4 * kTileRows;
             ssq[half * kTileRows + row] = ss;
-            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[0] += c1 - c0;)
+            TQ_PROF_CODE(c1 = clock64(); if (pr) prof_acc[0] += c1 - c0;)
             if (kActiveParts > 1) bar_sync(1 + quarter, 32 * kActiveParts);  // the warps that share these 32 rows
             else __syncwarp();
-            TQ_PROF_CODE(c0 = clock64(); if (pr) a.prof[1] += c0 - c1;)
+            TQ_PROF_CODE(c0 = clock64(); if (pr) prof_acc[1] += c0 - c1;)
             float tot = ssq[row];
 #pragma unroll
             for (int pt = 1; pt < kActiveParts; ++pt) tot += ssq[pt * kTileRows + row];
@@ -573,142 +606,122 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             }
             if (!mbar_wait(BAR(BAR_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
             tc_fence_after();
-            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[2] += c1 - c0;)
+            TQ_PROF_CODE(c1 = clock64(); if (pr) prof_acc[2] += c1 - c0;)
             const uint32_t a_hi = tmem + lane_addr + A_COL(b) + half * (kXs / 2);
 #pragma unroll
             for (int s = 0; s < kXs / 32; ++s) {
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int p = 0; p < 16; ++p) {
-                    float u0, u1, l0, l1;
+                    float l0, l1;
                     __half2 h;
-                    if (!PROD) {
+                    if (kPacked) {
                         const float2 u = __fmul2_rn(make_float2(x[s * 32 + 2 * p], x[s * 32 + 2 * p + 1]), make_float2(sc, sc));
                         h = __floats2half2_rn(u.x, u.y);
                         const float2 hf = __half22float2(h);
                         const float2 l = __fadd2_rn(u, make_float2(-hf.x, -hf.y));
-                        l0 = l.x; l1 = l.y; u0 = u.x; u1 = u.y;
+                        l0 = l.x; l1 = l.y;
                     } else {
-                        u0 = x[s * 32 + 2 * p] * sc;
-                        u1 = x[s * 32 + 2 * p + 1] * sc;
+                        const float u0 = x[s * 32 + 2 * p] * sc;
+                        const float u1 = x[s * 32 + 2 * p + 1] * sc;
                         h = __floats2half2_rn(u0, u1);
                         const float2 hf = __half22float2(h);
                         l0 = u0 - hf.x; l1 = u1 - hf.y;
                     }
-                    (void)u0; (void)u1;
                     hi[p] = *reinterpret_cast<const uint32_t*>(&h);
                     lo[p] = pack_half2(l0, l1);
                 }
                 tmem_st16(a_hi + s * 16, hi);
                 tmem_st16(a_hi + kABlock + s * 16, lo);
             }
-            TQ_PROF_CODE(c0 = clock64(); if (pr) a.prof[3] += c0 - c1;)
+            TQ_PROF_CODE(c0 = clock64(); if (pr) prof_acc[3] += c0 - c1;)
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + b));
-            TQ_PROF_CODE(if (pr) { a.prof[4] += clock64() - c0; a.prof[5] += 1; })
+            TQ_PROF_CODE(if (pr) { prof_acc[4] += clock64() - c0; prof_acc[5] += 1; })
             g_base += L::kBoxesPerTile;
-        }
-        if (PROD && pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
-    } else {
-        // ---- epilogue: one thread per row -----------------------------------------------------------
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        constexpr int kCodeWords = D * BITS / 32;  // words per packed row
-        constexpr int kChunks = 2;                                    // 32-column chunks per thread
-        const int colgroup = (warp - kFirstEpiWarp) >> 2;             // which 64 columns of the row
-        const int chunk0 = colgroup * kChunks;                        // first chunk of this thread
-        const int64_t epi_tiles = colgroup < kHalves ? my_tiles : 0;  // with d = 64 the warps of the upper half idle
-        // lookup tables held in the lanes of the warp: per cell (boundary, 1 + boundaries below), per code
-        // (- centroid * 2^10)
-        const float lut_bnd = cell_lut[lane].x;
-        const int lut_base1 = __float_as_int(cell_lut[lane].y) - 1;   // boundaries below the cell = code of a value below its boundary
-        const float lut_ncent = a.code_ncent[lane];
-        WarpPending pend;
-        pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + (warp - kFirstEpiWarp) * kPendCap;
-        pend.rows = reinterpret_cast<unsigned int*>(pend_base + 8 * kPendCap * 8) + (warp - kFirstEpiWarp) * kPendCap;
-        pend.n_codes = 0;
-        pend.n_rows = 0;
-        // first-accumulator epilogue of tile i: codes (+ rho for Prod)
+        };
+
+        // -- first-accumulator epilogue of tile i: codes (+ rho for TurboQuantProd)
         auto epilogue1 = [&](int64_t i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const int b = (int)(i & 1);
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
             const int64_t grow = tile * kTileRows + row;
             const bool live_row = grow < a.n;
-            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32; long long c0 = clock64(), c1;)
+            TQ_PROF_CODE(const bool pr = a.prof && blockIdx.x == 0 && threadIdx.x == (UNI ? kFirstConvWarp : kFirstEpiWarp) * 32; long long c0 = clock64(), c1;)
             const bool got = mbar_wait(BAR(BAR_ACC_FULL + b), par2, abort_flag);   // false: some role gave up, the
             const bool live = live_row && got;                                      // accumulator is not to be trusted
             tc_fence_after();
-            TQ_PROF_CODE(c1 = clock64(); if (pr) a.prof[16] += c1 - c0;)
+            TQ_PROF_CODE(c1 = clock64(); if (pr) prof_acc[16] += c1 - c0;)
             const bool redo_row = force[(i & 3) * kTileRows + row] != 0;  // whole row to the exact stage
             float rs = 0.f;
             const uint32_t acc = tmem + lane_addr + ACC_COL(b);
-            uint32_t nm[kChunks];
+            uint32_t nm[kEpiChunks];
+            auto store_codes = [&](int ch, const uint32_t (&w)[BITS + 1]) {
+                if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
+                    uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
+                    if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                    else {
+#pragma unroll
+                        for (int k = 0; k < BITS; ++k) dst[k] = w[k];
+                    }
+                }
+            };
             if (PROD) {
                 // a real loop over the chunks: half the code of the unrolled form, which matters for the
                 // instruction cache more than the loop overhead does
                 uint32_t nm0 = 0, nm1 = 0;
 #pragma unroll 1
-                for (int ch = 0; ch < kChunks; ++ch) {
+                for (int ch = 0; ch < kEpiChunks; ++ch) {
                     uint32_t va[32];
+                    TQ_PROF_CODE(const long long l0 = clock64();)
                     tmem_ld32(acc + (chunk0 + ch) * 32, va);
                     tmem_wait_ld();
+                    TQ_PROF_CODE(if (pr) prof_acc[13] += clock64() - l0;)
                     uint32_t w[BITS + 1], rhi[16], rlo[16];
                     const uint32_t m = process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset,
                                                                  a.code_guard, w, rhi, rlo, rs);
                     if (ch == 0) nm0 = m; else nm1 = m;
-                    if (live) {  // this chunk's packed codes: BITS words at a BITS*4-byte aligned offset of the row
-                        uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
-                        if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                        else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-                        else {
-#pragma unroll
-                            for (int k = 0; k < BITS; ++k) dst[k] = w[k];
-                        }
-                    }
+                    store_codes(ch, w);
                     // rho replaces the chunk it was computed from: 16 columns of hi pairs, 16 of lo pairs
                     tmem_st16(acc + (chunk0 + ch) * 32, rhi);
                     tmem_st16(acc + (chunk0 + ch) * 32 + 16, rlo);
                 }
                 nm[0] = nm0;
-                nm[kChunks - 1] = nm1;
+                nm[kEpiChunks - 1] = kEpiChunks == 1 ? nm0 : nm1;
             } else {
                 uint32_t va[32], vb[32];
                 tmem_ld32(acc + chunk0 * 32, va);
                 tmem_wait_ld();
 #pragma unroll
-                for (int ch = 0; ch < kChunks; ++ch) {
+                for (int ch = 0; ch < kEpiChunks; ++ch) {
                     // fetch the next chunk while this one is processed
-                    if (ch + 1 < kChunks) {
+                    if (ch + 1 < kEpiChunks) {
                         if (ch & 1) tmem_ld32(acc + (chunk0 + ch + 1) * 32, va); else tmem_ld32(acc + (chunk0 + ch + 1) * 32, vb);
                     }
                     uint32_t w[BITS + 1], rhi[16], rlo[16];
                     nm[ch] = (ch & 1)
                         ? process_chunk<BITS, PROD>(vb, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs)
                         : process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
-                    if (live) {
-                        uint32_t* dst = a.codes + grow * kCodeWords + (chunk0 + ch) * BITS;
-                        if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                        else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-                        else {
-#pragma unroll
-                            for (int k = 0; k < BITS; ++k) dst[k] = w[k];
-                        }
-                    }
-                    if (ch + 1 < kChunks) tmem_wait_ld();
+                    store_codes(ch, w);
+                    if (ch + 1 < kEpiChunks) tmem_wait_ld();
                 }
             }
             if (PROD) {
+                TQ_PROF_CODE(const long long l0 = clock64();)
                 tmem_wait_st();
-                // this thread's share of |rho|^2; summed in the sign epilogue of the same tile, which every
-                // epilogue warp reaches only after all of them have arrived on RHO_FULL below.  Four slots: the
-                // warp of the other half may run ahead of this one (it needs MMA 1 of a later tile, not this
-                // warp's progress), but its first epilogue of tile i + 4 cannot start before every warp has
-                // finished the first epilogue of tile i + 2, which follows the sign epilogue of tile i.
-                rs_part[((int)(i & 3) * 2 + (chunk0 ? 1 : 0)) * kTileRows + row] = rs;
+                TQ_PROF_CODE(if (pr) prof_acc[14] += clock64() - l0;)
+                // this thread's share of |rho|^2; summed in the sign epilogue of the same tile, which every worker reaches
+                // only after all of them have arrived on RHO_FULL below.  A slot is written again kRsSlots tiles later.
+                // !UNI, four slots: the warp of the other half may run ahead of this one (it needs MMA 1 of a later tile,
+                // not this warp's progress), but its first epilogue of tile i + 4 cannot start before every warp has
+                // finished the first epilogue of tile i + 2, which follows the sign epilogue of tile i.  UNI, three slots:
+                // the first epilogue of tile i + 3 follows the conversion of tile i + 4, which waits for the sign epilogue
+                // of tile i + 1 of every worker, and each worker runs that one after its sign epilogue of tile i.
+                rs_part[((int)(i % L::kRsSlots) * L::kRsParts + colgroup) * kTileRows + row] = rs;
             }
             tc_fence_before();
             __syncwarp();
@@ -716,19 +729,61 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
             // second-stage work is recorded after the accumulator went back to the tensor pipe
             uint32_t any_nm = 0;
 #pragma unroll
-            for (int ch = 0; ch < kChunks; ++ch) {
+            for (int ch = 0; ch < kEpiChunks; ++ch) {
                 if (!live || redo_row) nm[ch] = 0;
                 any_nm |= nm[ch];
             }
             if (__any_sync(0xffffffffu, any_nm != 0u)) {
 #pragma unroll
-                for (int ch = 0; ch < kChunks; ++ch) pend_codes(a.lists, pend, nm[ch], grow, (chunk0 + ch) * 32, lane);
+                for (int ch = 0; ch < kEpiChunks; ++ch) pend_codes(a.lists, pend, nm[ch], grow, (chunk0 + ch) * 32, lane);
             }
-            if (!PROD) pend_rows(a.lists, pend, redo_row && live, grow, lane);
-            TQ_PROF_CODE(if (pr) a.prof[17] += clock64() - c1;)
+            if (!PROD) pend_rows(a.lists, pend, redo_row && live && chunk0 == 0, grow, lane);
+            TQ_PROF_CODE(if (pr) prof_acc[17] += clock64() - c1;)
         };
-        static_assert(kChunks == 2, "a thread owns two 32-column chunks");
-        for (int64_t i = 0; i < epi_tiles; ++i) epilogue1(i);
+
+        if (UNI) {
+            // Per iteration: sign epilogue of tile it - 3, conversion of tile it, first epilogue of tile it - 1.  The tensor
+            // pipe runs the first contraction of tile it during the first epilogue of tile it - 1 and the second
+            // contraction of tile it - 1 during the next iteration's sign epilogue and conversion, so in steady state
+            // no phase finds its barrier unfinished.
+            const int64_t tiles = conv_active ? my_tiles : 0;
+            const int64_t iters = tiles > 0 ? tiles + (PROD ? 3 : 1) : 0;
+            for (int64_t it = 0; it < iters; ++it) {
+                if (PROD) {
+                    if (it >= 3) {
+                        sign_epilogue(it - 3);
+                    } else if (it == 2) {
+                        // A block 0 carries no second accumulator before tile 2 refills it; MMA 1 of tile 0 must have read it
+                        mbar_wait(BAR(BAR_ACC_FULL + 0), 0u, abort_flag);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
+                    }
+                }
+                if (it < tiles) convert(it);
+                if (it >= 1 && it - 1 < tiles) epilogue1(it - 1);
+            }
+        } else if (conv_role) {
+            // TurboQuantProd: the converter warps also run the sign epilogue: they wait about half of every tile for a
+            // free A block, while the epilogue warps are the longest chain of this variant.
+            const int64_t conv_tiles = conv_active ? my_tiles : 0;
+            const int64_t conv_iters = PROD ? (conv_tiles > 0 ? conv_tiles + 3 : 0) : conv_tiles;
+            for (int64_t i = 0; i < conv_iters; ++i) {
+                if (PROD) {
+                    if (i >= 3) {
+                        sign_epilogue(i - 3);
+                    } else if (i == 2) {
+                        mbar_wait(BAR(BAR_ACC_FULL + 0), 0u, abort_flag);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(BAR(BAR_A_EMPTY + 0));
+                    }
+                    if (i >= conv_tiles) continue;
+                }
+                convert(i);
+            }
+        } else {
+            const int64_t epi_tiles = epi_active ? my_tiles : 0;
+            for (int64_t i = 0; i < epi_tiles; ++i) epilogue1(i);
+        }
         if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
         if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
     }
@@ -739,6 +794,11 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
 #ifdef TQ_PROF
+    if (a.prof && blockIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < 21; ++k)
+            if (prof_acc[k]) atomicAdd(reinterpret_cast<unsigned long long*>(a.prof + k), (unsigned long long)prof_acc[k]);
+    }
     if (a.prof && threadIdx.x == 0) {
         const long long t2 = clock64();
         atomicMax(reinterpret_cast<unsigned long long*>(a.prof + 21), (unsigned long long)(t2 - prof_t0));
@@ -866,15 +926,10 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     int lut_base[kCells];
     const float guard = TQ_CODE_GUARD * kAccScale;
     if (!build_cell_lut(bnd_s.data(), nb, 4.f * guard, &cs, &co, lut_bnd, lut_base)) return TQ_OK;
-    float lut4[kCells * 4];
+    float lut2[kCells * 2];
     for (int c = 0; c < kCells; ++c) {
-        const int base = lut_base[c];                     // boundaries in lower cells = code of a value below this cell's boundary
-        const int above = base + 1 < levels ? base + 1 : base;
-        const int base1 = base + 1;
-        lut4[4 * c + 0] = lut_bnd[c];
-        memcpy(&lut4[4 * c + 1], &base1, 4);
-        lut4[4 * c + 2] = -codebook[base] * kScaleA;      // - centroid * 2^10 (the A-operand scale)
-        lut4[4 * c + 3] = -codebook[above] * kScaleA;
+        lut2[2 * c] = lut_bnd[c];
+        memcpy(&lut2[2 * c + 1], &lut_base[c], 4);       // boundaries in lower cells = code of a value below this cell's boundary
     }
     for (int l = 0; l < kCells; ++l) lut_cent[l] = -codebook[l % levels] * kScaleA;
 
@@ -904,15 +959,15 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
     }
     unsigned char* base = static_cast<unsigned char*>(t->dev);
     bool ok = cudaMemcpy(base, mats.data(), mat_bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
-              cudaMemcpy(base + mat_bytes, lut4, sizeof(lut4), cudaMemcpyHostToDevice) == cudaSuccess &&
-              cudaMemcpy(base + mat_bytes + sizeof(lut4), lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+              cudaMemcpy(base + mat_bytes, lut2, sizeof(lut2), cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(base + mat_bytes + kCells * 16, lut_cent, kCells * 4, cudaMemcpyHostToDevice) == cudaSuccess;
     if (!ok || !tq_encode_tiled_fn()) {
         cudaFree(t->dev);
         delete t;
         return tq_fail(TQ_ERR_CUDA, "upload of tensor-path constants failed");
     }
     t->args.bmat = reinterpret_cast<const __half*>(base);
-    t->args.cell_lut = reinterpret_cast<const float4*>(base + mat_bytes);
+    t->args.cell_lut = reinterpret_cast<const float2*>(base + mat_bytes);
     t->args.code_ncent = reinterpret_cast<const float*>(base + mat_bytes + kCells * 16);
     t->args.cell_scale = cs;
     t->args.cell_offset = co;
@@ -932,11 +987,18 @@ void tq_tensor_plan_free(tq_plan* p) {
     }
 }
 
+#ifndef TQ_UNI_PROD
+#define TQ_UNI_PROD false
+#endif
+#ifndef TQ_UNI_MSE
+#define TQ_UNI_MSE false
+#endif
 template <int D, int BITS, bool PROD>
 static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
-    const int sm = Smem<D, PROD>::total;
-    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize_kernel<D, BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
-    tensor_quantize_kernel<D, BITS, PROD><<<grid, Threads<PROD>::kThreads, sm, st>>>(map, args); tq_count_launch();
+    constexpr bool UNI = PROD ? TQ_UNI_PROD : TQ_UNI_MSE;
+    const int sm = Smem<D, PROD, UNI>::total;
+    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize_kernel<D, BITS, PROD, UNI>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm));
+    tensor_quantize_kernel<D, BITS, PROD, UNI><<<grid, Threads<PROD, UNI>::kThreads, sm, st>>>(map, args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }

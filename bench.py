@@ -587,7 +587,9 @@ def run_gpu(args):
 
 # DRAM bytes (read, written) of one launch of the dominant kernels over 262,144 keys, from the ncu captures
 # summarised in profiles/ (dram__bytes_read.sum, dram__bytes_write.sum); both grow in proportion to the keys.
-TRAFFIC_QUANT_262144 = (135.7e6, 19.3e6)
+# (the score matrix of the small case stays in L2 during the capture: its 33.5 MB are counted as written here, as they
+# are at the bench's size, where the matrix is larger than L2)
+TRAFFIC_QUANT_262144 = (136.1e6, 21.1e6)
 TRAFFIC_SCORE_262144 = (18.95e6, 33.5e6)
 
 DECODE_GROUPS, DECODE_QPG = 64, 4

@@ -269,7 +269,8 @@ int tq_plan_last_recheck_rows(const tq_plan* plan, void* stream, int64_t* rows);
  * tq_plan_status reads the word back (synchronises `stream`): 0 = no kernel of this plan has given up since the
  * last query; 1 / 2 / 3 = a quantize / scoring / dequantize kernel has (the word is cleared by the query).  The
  * Python classes query it wherever they synchronise anyway and raise instead of handing out such results.
- * tq_plan_set_wait_limit changes the limit (cycles; default about 2 s) for later launches of this plan.
+ * tq_plan_set_wait_limit changes the limit (cycles; default about 2 s) for later launches of this plan; 0 makes a
+ * kernel give up at the first barrier it finds unfinished, which is how the tests walk this path without a fault.
  * No reference counterpart (NumPy has nothing to wait for).
  */
 int tq_plan_status(const tq_plan* plan, void* stream, int64_t* status);

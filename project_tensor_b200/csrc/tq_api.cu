@@ -624,7 +624,8 @@ int tq_plan_kernel_ms(const tq_plan* p, int kind, float* ms, int max_count) {
 
 int tq_plan_set_wait_limit(tq_plan* p, int64_t cycles) {
     TQ_TRY(check_plan(p, false));
-    if (cycles < 1024 || cycles > (int64_t)1 << 40) return tq_fail(TQ_ERR_INVALID_ARGUMENT, "wait limit outside [2^10, 2^40] cycles");
+    if (cycles != 0 && (cycles < 1024 || cycles > (int64_t)1 << 40))
+        return tq_fail(TQ_ERR_INVALID_ARGUMENT, "wait limit outside [2^10, 2^40] cycles (0: give up at the first wait)");
     p->wait_kcycles = (int)(cycles >> 10);
     return TQ_OK;
 }

@@ -42,29 +42,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// The same with a hint of how long the hardware may keep the thread suspended before it answers "not yet".
-__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
-#ifndef TQ_SUSPEND_NS
-#define TQ_SUSPEND_NS 8000
-#endif
 // Bounded wait.  Returns false when the limit ran out or another thread has already given up.  Every answer "not yet"
 // costs the waiting warp a dozen instructions on the scheduler it shares with working warps (a profile of the quantize
-// kernel showed a quarter of all executed instructions in these loops), hence the suspend hint and the short loop body.
+// kernel showed a quarter of all executed instructions in these loops), hence the short loop body.  (A suspend-time hint
+// on the try_wait -- 8 us, 1 ms -- changed no kernel's time, and it lets a wait outlive a limit shorter than the hint.)
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (*abort_flag) return false;  // somebody already gave up: do not block again
+    if (abort_flag[1] == 0) {       // limit 0: give up at the first wait that would have to wait (how the path is tested)
+        *abort_flag = 1;
+        return false;
+    }
     const long long deadline = clock64() + ((long long)abort_flag[1] << 10);
     for (;;) {
-        if (mbar_try_wait_for(bar, parity, TQ_SUSPEND_NS)) return true;
+        if (mbar_try_wait(bar, parity)) return true;   // blocks inside the hardware for a while before it answers
         if (clock64() > deadline) {
             *abort_flag = 1;
             return false;
@@ -72,8 +62,20 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
         if (*abort_flag) return false;
     }
 }
+// Has the phase completed?  Answers at once (try_wait may keep the thread suspended for a while first).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, abort_flag);
 }
 

@@ -377,11 +377,11 @@ def test_d64_tensor_paths_match_exact_paths(tg, bits, n):
 
 
 def test_a_wait_that_runs_out_is_reported_not_hidden(tg):
-    """Every wait inside the tensor-core kernels is bounded.  With the limit set to a few thousand cycles -- less than
-    the first tile's trip from memory -- some wait runs out: the kernel must come back (all roles leave their loops,
-    copies and tensor instructions in flight are waited for), the plan's status word must say so, the Python layer must
-    raise at its next synchronisation point instead of handing the encoding out, and the next call with the normal limit
-    must be correct again on the same context."""
+    """Every wait inside the tensor-core kernels is bounded.  With the limit set to 0 the first wait that finds its
+    barrier unfinished counts as run out (at the start of a kernel every consumer is in that position): the kernel must
+    come back (all roles leave their loops, copies and tensor instructions in flight are waited for), the plan's status
+    word must say so, the Python layer must raise at its next synchronisation point instead of handing the encoding
+    out, and the next call with the normal limit must be correct again on the same context."""
     import torch
     from project_tensor_b200 import _native
     x = torch.randn((65536, 128), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
@@ -389,7 +389,7 @@ def test_a_wait_that_runs_out_is_reported_not_hidden(tg):
     good = quant.quantize(x)
     torch.cuda.synchronize()
     quant._plans.check_status(x.device)                 # nothing to report so far
-    quant._plans.set_wait_limit(2048)
+    quant._plans.set_wait_limit(0)
     enc = quant.quantize(x)
     with pytest.raises(_native.TurboQuantNativeError, match="gave up on a bounded wait"):
         quant._plans.check_status(x.device)

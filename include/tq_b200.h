@@ -276,11 +276,11 @@ int tq_plan_last_recheck_rows(const tq_plan* plan, void* stream, int64_t* rows);
 int tq_plan_status(const tq_plan* plan, void* stream, int64_t* status);
 
 /*
- * Device time of the main kernel of each call, for benchmarks: with timing on, every tq_*_quantize call on the
+ * Device time of the main kernel of each call, for benchmarks: with timing on (bit 0 of `on`), every tq_*_quantize call on the
  * tensor-core path records a CUDA event before and after its tensor-core kernel (kind 0; the exact second stage
  * lies outside the pair) and every tq_score_batched / tq_score_cache call around each launch of the tensor-core
  * scoring kernel (kind 1); the two kernels of the quantizers' exact second stage have pairs of their own (kind 2: the
- * re-check of listed coordinates, kind 3: the re-computation of listed rows).  tq_plan_kernel_ms returns how many of the most recent launches of `kind` it wrote to
+ * re-check of listed coordinates, kind 3: the re-computation of listed rows; recorded when bit 1 of `on` is set).  tq_plan_kernel_ms returns how many of the most recent launches of `kind` it wrote to
  * ms[] (at most max_count, at most 1,024), oldest first, in milliseconds; synchronise the stream before.  Turning
  * timing on or off resets the record.  No reference counterpart.
  */

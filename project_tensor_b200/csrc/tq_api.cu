@@ -596,8 +596,10 @@ int tq_plan_time_kernels(tq_plan* p, int on) {
                 for (int e = 0; e < 2; ++e) TQ_CUDA_TRY(cudaEventCreate(&t->ev[k][i][e]));
         p->timer = t;
     }
-    if (p->timer)
+    if (p->timer) {
         for (int k = 0; k < kTimerKinds; ++k) p->timer->count[k] = 0;
+        p->timer->kinds = (on & 1 ? 0x3 : 0) | (on & 2 ? 0xc : 0);   // bit 0: the main kernels, bit 1: the second-stage kernels
+    }
     if (!on && p->timer) {
         for (int k = 0; k < kTimerKinds; ++k)
             for (int i = 0; i < kTimerSlots; ++i) { cudaEventDestroy(p->timer->ev[k][i][0]); cudaEventDestroy(p->timer->ev[k][i][1]); }

@@ -72,6 +72,7 @@ constexpr int kTimerKinds = 4;   // 0 quantize kernel, 1 scoring kernel, 2 coord
 struct TqKernelTimer {
     cudaEvent_t ev[kTimerKinds][kTimerSlots][2];
     long long count[kTimerKinds];
+    int kinds;   // bit k: launches of kind k are timed
 };
 inline void tq_timer_mark(const struct tq_plan* p, int kind, int edge, cudaStream_t st);   // defined below the plan
 
@@ -95,7 +96,7 @@ struct tq_plan {
 
 inline void tq_timer_mark(const tq_plan* p, int kind, int edge, cudaStream_t st) {
     TqKernelTimer* t = p->timer;
-    if (!t) return;
+    if (!t || !((t->kinds >> kind) & 1)) return;
     cudaEventRecord(t->ev[kind][t->count[kind] % kTimerSlots][edge], st);
     if (edge == 1) ++t->count[kind];
 }

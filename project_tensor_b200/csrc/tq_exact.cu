@@ -209,7 +209,10 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
         __syncthreads();
 
         float acc[kRB];
-        constexpr int kU = MAXT <= 256 ? 32 : 16;   // matrix elements in flight per thread
+#ifndef TQ_EXACT_U
+#define TQ_EXACT_U 32
+#endif
+        constexpr int kU = MAXT <= 256 ? TQ_EXACT_U : 16;   // matrix elements in flight per thread
         // rotated[j] = sum_k unit[k] * R[j][k]
         rows_chain<kU>(p.Rt, d, tj, sm.vt, acc);
         if (t < d) {

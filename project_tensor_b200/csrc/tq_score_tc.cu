@@ -713,6 +713,26 @@ topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t g
     if (k1 > n) k1 = n;
     if (threadIdx.x == 0) { cnt = 0; thr = 0ull; }
     __syncthreads();
+    // First threshold without filling the buffer: every thread takes the best of 32 scores from the head of the segment
+    // (8,192 in all); the k-th best of those 256 maxima is a score that at least k scores of the segment reach, and on
+    // data without order about 3 % of all scores do, so the candidates of the whole segment fit the buffer and the one
+    // selection at the end is all there is (without it the first 4,096 scores all pass, each through the shared counter,
+    // and a selection is needed as soon as they have).  Data that defeats the estimate only brings the cut-backs back.
+    constexpr int kPre = 4 * kSelPerThread;
+    if (topk <= kSelThreads && k1 - k0 >= (int64_t)kPre * kSelThreads) {
+        uint32_t best = 0u;
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) {
+            const uint32_t o = ordered_bits(__ldg(src + k0 + j * kSelThreads + threadIdx.x));
+            best = o > best ? o : best;
+        }
+        buf[threadIdx.x] = (unsigned long long)best;
+        block_sort_desc(buf, kSelThreads);
+        const unsigned long long t0 = buf[topk - 1] << 32;   // below every key that carries this score
+        __syncthreads();
+        if (threadIdx.x == 0) thr = t0;
+        __syncthreads();
+    }
     // The scores of the next batch are already on their way while this one is filtered, and the common
     // case (nothing to prune) costs one barrier per batch.
     float nxt[kSelPerThread];
@@ -732,12 +752,18 @@ topk_rows_kernel(const float* __restrict__ scores, int64_t row_stride, int64_t g
                 nxt[j] = key < k1 ? __ldcs(src + key) : 0.f;
             }
         }
+        // The test that nearly every score fails is one 32-bit compare of the score's sortable bits with the upper half
+        // of the threshold; the 64-bit key, the bound check and the append are behind it.
         const unsigned long long t = thr;
+        const uint32_t t_hi = (uint32_t)(t >> 32);
 #pragma unroll
         for (int j = 0; j < kSelPerThread; ++j) {
-            const int64_t key = kb + j * kSelThreads + threadIdx.x;
-            const unsigned long long ck = make_key(v[j], row0 + (uint32_t)key);
-            if (key < k1 && ck > t) buf[atomicAdd(&cnt, 1)] = ck;
+            const uint32_t o = ordered_bits(v[j]);
+            if (o >= t_hi) {
+                const int64_t key = kb + j * kSelThreads + threadIdx.x;
+                const unsigned long long ck = ((unsigned long long)o << 32) | (unsigned long long)(0xffffffffu - (row0 + (uint32_t)key));
+                if (key < k1 && ck > t) buf[atomicAdd(&cnt, 1)] = ck;
+            }
         }
         // Each thread tests the count it sees after its own appends; the thread that appended last sees the
         // final count, so the OR over the block is the test on the final count and is the same for everyone.

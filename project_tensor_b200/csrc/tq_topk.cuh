@@ -35,7 +35,7 @@ constexpr int kSelBatch = kSelPerThread * kSelThreads;   // scores examined betw
 constexpr int kSelCap = 4096;                            // candidate buffer (64-bit keys) per block
 
 // Keep the `k` largest of the `c` distinct keys in buf[0..c) (c <= kSelCap), unsorted, in buf[0..k); returns
-// the k-th largest key.  Radix select, 8 bits per pass from the top, with a 256-bin histogram in shared
+// the k-th largest key or a lower bound of it that no other key of the buffer reaches.  Radix select, 8 bits per pass from the top, with a 256-bin histogram in shared
 // memory; far cheaper than sorting the buffer.  Whole block; c and k are uniform, k <= c.
 static __device__ unsigned long long block_select_topk(unsigned long long* buf, int c, int k, int* hist /*[256]*/,
                                                 int* scratch /*[4]*/) {
@@ -66,7 +66,12 @@ static __device__ unsigned long long block_select_topk(unsigned long long* buf, 
                 int acc = before;
                 for (int b = 0; b < 8; ++b) {
                     const int bin = 255 - 8 * lane - b;
-                    if (acc + hist[bin] >= remaining) { scratch[0] = bin; scratch[1] = remaining - acc; break; }
+                    if (acc + hist[bin] >= remaining) {
+                        scratch[0] = bin;
+                        scratch[1] = remaining - acc;
+                        scratch[3] = acc + hist[bin] == remaining;   // the whole bin belongs to the k largest
+                        break;
+                    }
                     acc += hist[bin];
                 }
             }
@@ -75,9 +80,12 @@ static __device__ unsigned long long block_select_topk(unsigned long long* buf, 
         prefix |= (unsigned long long)scratch[0] << shift;
         mask |= 255ull << shift;
         remaining = scratch[1];
+        const bool whole_bin = scratch[3] != 0;
         __syncthreads();
+        if (whole_bin) break;   // every key with this prefix is in: the lower bits need no passes (usual after four)
     }
-    // prefix is now the k-th largest key; gather the keys >= prefix (exactly k, keys are distinct)
+    // prefix is now the k-th largest key, or its leading bytes with zeros behind them when the selection stopped at a
+    // bin that is taken whole; gather the keys >= prefix (exactly k, keys are distinct)
     unsigned long long keep[kSelCap / kSelThreads];
     int nkeep = 0;
     for (int i = threadIdx.x, j = 0; j < kSelCap / kSelThreads; i += blockDim.x, ++j) {

@@ -508,7 +508,7 @@ def run_gpu(args):
             "attention_score_matrix": {
                 "value": N_KEYS / (mat_ms * 1e-3) / 1e9, "unit": "Gkeys/s", "ms": mat_ms,
                 "h2d_bytes_per_step": N_QUERIES * D * 4, "d2h_bytes_per_step": N_QUERIES * N_KEYS * 4,
-                "what": "attention_scores(NumPy queries, device-resident packed keys) -> NumPy 32 x N matrix (pageable host memory)"}}
+                "what": "attention_scores(NumPy queries, device-resident packed keys) -> NumPy 32 x N matrix (page-locked block of the caching host allocator behind the array)"}}
         del enc_p
     e2e = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:

@@ -140,9 +140,9 @@ def _deliver(tensor, kind: str, plans: "Optional[_PlanSet]" = None):
     if plans is not None and kind in ("numpy", "torch_cpu"):
         plans.check_status(tensor.device)
     if kind == "numpy":
-        return tensor.cpu().numpy()
+        return _to_host(tensor).numpy()
     if kind == "torch_cpu":
-        return tensor.cpu()
+        return _to_host(tensor)
     if kind == "cupy":
         try:
             import cupy
@@ -150,6 +150,23 @@ def _deliver(tensor, kind: str, plans: "Optional[_PlanSet]" = None):
         except ImportError:  # CuPy-like producer without CuPy importable: give the torch view
             return tensor
     return tensor
+
+
+_PINNED_FROM_BYTES = 1 << 20
+
+
+def _to_host(tensor):
+    """Device tensor -> CPU tensor.  Results of a megabyte and more land in page-locked memory from torch's caching host
+    allocator (the block goes back to that cache when the array that wraps it dies): a copy into pageable memory runs at
+    a few GB/s, so that the 128 MiB score matrix of 32 queries x 1,048,576 keys took 62 ms to hand back, against 3 ms
+    at the rate of the link."""
+    torch = _torch()
+    if tensor.device.type != "cuda" or tensor.numel() * tensor.element_size() < _PINNED_FROM_BYTES:
+        return tensor.cpu()
+    host = torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
+    host.copy_(tensor, non_blocking=True)
+    torch.cuda.current_stream(tensor.device).synchronize()
+    return host
 
 
 def _ptr(t) -> int:

@@ -110,6 +110,16 @@ int tq_fail(int code, const char* fmt, ...);
             return tq_fail(TQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
     } while (0)
 
+// A named NVTX range around the launches of one step of a call (a profiler shows the library's kernels grouped by it;
+// without a profiler attached the calls do nothing).
+#include <nvtx3/nvToolsExt.h>
+struct TqRange {
+    explicit TqRange(const char* name) { nvtxRangePushA(name); }
+    ~TqRange() { nvtxRangePop(); }
+    TqRange(const TqRange&) = delete;
+    TqRange& operator=(const TqRange&) = delete;
+};
+
 // Every kernel launch of the library is counted (tq_kernel_launches reports the total).
 void tq_count_launch();
 

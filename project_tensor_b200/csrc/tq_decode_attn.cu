@@ -544,6 +544,7 @@ int tq_launch_decode_attention(const tq_plan* kp, const tq_plan* vp, const float
                                const uint32_t* vcodes, const float* vnorms, int64_t keys_per_group, int64_t group_rows,
                                const int64_t* length, float scale, float* out, void* scratch, size_t scratch_bytes,
                                cudaStream_t st) {
+    TqRange range("tq.decode_attention");
     const int d = kp->dev.d, kb = kp->dev.bits;
     const int qp = queries_per_pass(kb, qpg);
     const int passes = (qpg + qp - 1) / qp;

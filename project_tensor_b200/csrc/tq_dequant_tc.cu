@@ -525,6 +525,7 @@ void tq_dequant_tc_plan_free(tq_plan* p) {
 
 int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
                          const float* norms, int64_t n, float* out, cudaStream_t st) {
+    TqRange range("tq.dequantize.tensor_core");
     if (n == 0) return TQ_OK;
     if (!p->dequant) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core dequantize constants in this plan");
     DequantArgs a{};
@@ -559,6 +560,7 @@ int tq_launch_dequant_tc(const tq_plan* p, bool prod, const uint32_t* codes, con
 // attention_score with one query row per key on the dequantize kernel: scores[i] = q[i] . dequantize(key i).
 int tq_launch_pairwise_tc(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs, const float* rnorms,
                           const float* norms, int64_t n, float* scores, cudaStream_t st) {
+    TqRange range("tq.score.pairwise.tensor_core");
     if (n == 0) return TQ_OK;
     if (!p->dequant || !p->has_projection) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core dequantize constants in this plan");
     DequantArgs a{};

@@ -468,6 +468,7 @@ int grid_for(int64_t work_items, int per_block) {
 
 int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                                const TqRecheck* lists, cudaStream_t st) {
+    TqRange range("tq.quantize.recheck_coordinates");
     if (n == 0) return TQ_OK;
     // as many threads as a list of typical length has entries (about 1 in 50 rows); longer lists take more passes
     int64_t blocks = (n / 48 + 127) / 128;
@@ -483,6 +484,7 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
 int tq_launch_exact_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                              uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists_in,
                              unsigned long long* redo_counter, cudaStream_t st, const TqRowMap* map_in) {
+    TqRange range("tq.quantize.exact_rows");
     if (n == 0) return TQ_OK;
     const size_t sm = rows_smem_bytes(p->dev.d);
     const TqRowMap map = map_in ? *map_in : TqRowMap{0, 0, nullptr};
@@ -529,6 +531,7 @@ int tq_launch_append_advance(int64_t* length, int64_t tokens, int64_t capacity, 
 int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* codes, const uint32_t* signs,
                                const float* rnorms, const float* norms, int64_t n, float* out,
                                cudaStream_t st) {
+    TqRange range("tq.dequantize.exact");
     if (n == 0) return TQ_OK;
     const int d = p->dev.d;
     const size_t sm = (size_t)2 * d * kRB * sizeof(float);
@@ -548,6 +551,7 @@ int tq_launch_exact_dequantize(const tq_plan* p, bool prod, const uint32_t* code
 int tq_launch_exact_pairwise(const tq_plan* p, const float* q, const uint32_t* codes, const uint32_t* signs,
                              const float* rnorms, const float* norms, int64_t n, float* scores,
                              cudaStream_t st) {
+    TqRange range("tq.score.pairwise.exact");
     if (n == 0) return TQ_OK;
     const int dp = (p->dev.d + 31) & ~31;
     const size_t sm = (size_t)kWarps * 3 * dp * sizeof(float);

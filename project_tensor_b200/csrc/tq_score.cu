@@ -319,6 +319,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
                             int64_t keys_per_group, float* scores, int topk, float* top_scores,
                             int64_t* top_idx, int64_t idx_base, void* scratch, size_t scratch_bytes,
                             cudaStream_t st, int64_t group_rows) {
+    TqRange range("tq.score.general");
     if (group_rows <= 0) group_rows = keys_per_group;
     const ScoreGeometry s = geometry(groups, keys_per_group, topk);
     if (topk > 0) {
@@ -357,6 +358,7 @@ int tq_launch_score_general(const tq_plan* p, const float* q, int groups, int qp
 int tq_launch_topk_merge(const float* in_scores, const int64_t* in_idx, int lists, int queries, int topk,
                          float* out_scores, int64_t* out_idx, cudaStream_t st, int64_t score_list_stride,
                          int64_t idx_list_stride) {
+    TqRange range("tq.topk.merge");
     if (queries == 0) return TQ_OK;
     const int k2 = pow2_at_least(topk);
     if (score_list_stride <= 0) score_list_stride = (int64_t)queries * topk;

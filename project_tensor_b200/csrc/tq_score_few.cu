@@ -152,6 +152,7 @@ bool tq_score_few_supported(const tq_plan* p, int qpg) {
 int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, const uint32_t* codes, const uint32_t* signs,
                         const float* rnorms, const float* norms, int64_t keys_per_group, float* scores, cudaStream_t st,
                         int64_t group_rows) {
+    TqRange range("tq.score.one_or_two_queries");
     if (group_rows <= 0) group_rows = keys_per_group;
     const int d = p->dev.d, bits = p->dev.bits;
     int r = TQ_ERR_UNSUPPORTED;

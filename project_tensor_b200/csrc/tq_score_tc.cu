@@ -950,6 +950,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
                        const uint32_t* signs, const float* rnorms, const float* norms, int64_t keys_per_group,
                        float* scores, int topk, float* top_scores, int64_t* top_idx, int64_t idx_base, void* scratch,
                        size_t scratch_bytes, cudaStream_t st, int64_t group_rows) {
+    TqRange range("tq.score.tensor_core");
     if (group_rows <= 0) group_rows = keys_per_group;
     const bool candidates = use_candidates(scores, topk, keys_per_group);
     const ScoreTcPlan sp = plan_score(groups, qpg, keys_per_group, topk, scores == nullptr);

@@ -1005,6 +1005,7 @@ static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, 
 
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                               uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists, cudaStream_t st) {
+    TqRange range("tq.quantize.tensor_core");
     if (!p->tensor) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for this plan");
     const int d = p->dev.d;
     if (n > (int64_t)0x7fffff00) return tq_fail(TQ_ERR_UNSUPPORTED, "n above 2^31 rows per call");

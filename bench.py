@@ -468,7 +468,8 @@ def run_gpu(args):
     host_keys.copy_(keys)
     host_np = host_keys.numpy()
 
-    def wall_ms(fn, reps=3, warm=2):
+    def wall_ms(fn, reps=5, warm=2):
+        """Wall-clock time of one call, median of `reps` (the host is shared: a mean would carry every hiccup of it)."""
         out = []
         for it in range(warm + reps):
             torch.cuda.synchronize()
@@ -477,7 +478,7 @@ def run_gpu(args):
             torch.cuda.synchronize()
             if it >= warm:
                 out.append(1e3 * (time.perf_counter() - t0))
-        return statistics.mean(out)
+        return statistics.median(out)
 
     state = {"out": None}
 
@@ -496,7 +497,7 @@ def run_gpu(args):
         q_np = queries.cpu().numpy()
         enc_p = quant.quantize(keys)
         topk_ms = wall_ms(lambda: quant.attention_scores(q_np, enc_p, topk=TOPK), reps=5)
-        mat_ms = wall_ms(lambda: quant.attention_scores(q_np, enc_p), reps=3)
+        mat_ms = wall_ms(lambda: quant.attention_scores(q_np, enc_p), reps=5)
         e2e_extra = {
             "quantize_drop_in_call": {
                 "value": N_KEYS / (drop_ms * 1e-3) / 1e6, "unit": "Mvec/s", "ms": drop_ms,

@@ -7,8 +7,9 @@
 namespace tqtopk {
 
 static __device__ __forceinline__ uint32_t ordered_bits(float s) {
+    // negative: all bits flipped, otherwise the sign bit set -- as one shift and one three-input logic operation
     const uint32_t u = __float_as_uint(s);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
 }
 static __device__ __forceinline__ unsigned long long make_key(float s, uint32_t row) {
     return ((unsigned long long)ordered_bits(s) << 32) | (unsigned long long)(0xffffffffu - row);

@@ -142,11 +142,14 @@ def test_topk_without_matrix_when_every_key_beats_the_threshold(tg):
         assert torch.equal(top_i, want_i), k
 
 
-def test_topk_without_matrix_for_query_groups(tg):
+@pytest.mark.parametrize("kpg", [4_300_000, 4_200_003])
+def test_topk_without_matrix_for_query_groups(tg, kpg):
     """Two key groups of 4,300,000 keys (ragged last tile and last chunk), three queries per group, k = 64: the
-    candidate lists are per query of every group and the indices count from the start of the group's keys."""
+    candidate lists are per query of every group and the indices count from the start of the group's keys.  With
+    4,200,003 keys per group the second group's tiles start off a 16-byte boundary in the norm arrays, so the norms
+    come by plain loads instead of riding with the packed rows."""
     import torch
-    d, groups, kpg, qpg, k = 64, 2, 4_300_000, 3, 64
+    d, groups, qpg, k = 64, 2, 3, 64
     gen = torch.Generator(device="cuda").manual_seed(20267)
     x = torch.randn((groups * kpg, d), generator=gen, device="cuda", dtype=torch.float32)
     q = torch.randn((groups * qpg, d), generator=gen, device="cuda", dtype=torch.float32)

@@ -178,7 +178,7 @@ int tq_plan_create(int d, int bits_mse, const float* rotation, const float* code
     p->counters = reinterpret_cast<unsigned long long*>(base + o_cnt);
 
     p->tensor_ok = false;
-    if (tq_tensor_supported(d, bits_mse)) {
+    if (tq_tensor_quantize_supported(d, bits_mse, projection != nullptr)) {
         const int r = tq_tensor_plan_init(p, rotation, codebook, projection);
         if (r != TQ_OK) {
             cudaFree(p->slab);
@@ -204,7 +204,7 @@ void tq_plan_destroy(tq_plan* p) {
     if (!p) return;
     DeviceScope scope(p->device);
     if (p->timer) {
-        for (int k = 0; k < 2; ++k)
+        for (int k = 0; k < kTimerKinds; ++k)
             for (int i = 0; i < kTimerSlots; ++i) { cudaEventDestroy(p->timer->ev[k][i][0]); cudaEventDestroy(p->timer->ev[k][i][1]); }
         delete p->timer;
     }

@@ -142,6 +142,7 @@ int tq_launch_exact_pairwise(const tq_plan* p, const float* q, const uint32_t* c
 
 // Tensor-core (tcgen05) kernels.
 bool tq_tensor_supported(int d, int bits);
+bool tq_tensor_quantize_supported(int d, int bits, bool has_projection);
 int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection);
 void tq_tensor_plan_free(tq_plan* p);
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,

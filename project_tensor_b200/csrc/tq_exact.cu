@@ -263,13 +263,56 @@ exact_quantize_kernel(TqDev p, const float* __restrict__ x, int64_t n, uint32_t*
 // row goes to the row list instead.  A list holds some ten thousand entries per million rows and a dependent access
 // to global memory costs about a microsecond, so the kernel is as long as its chain of such accesses: header, entry,
 // then the whole row into registers (D / 4 loads of 16 bytes in flight at once) together with the first half of the
-// matrix row.  D is 64 or 128 (the tensor-core geometries), so the row sum is a single block of NumPy's pairwise
-// scheme: eight interleaved sums.
+// matrix row.  D is 64, 128 or 256 (the tensor-core geometries): the row sum is one block of NumPy's pairwise scheme
+// (eight interleaved sums) per 128 values.
+// Sum of squares of Q * 4 consecutive values as NumPy sums a block of its pairwise scheme (eight interleaved sums);
+// the values stay in xv.
+template <int Q>
+__device__ __forceinline__ float block_sumsq(const float4* __restrict__ xr, float4 (&xv)[Q]) {
+#pragma unroll
+    for (int i = 0; i < Q; ++i) xv[i] = xr[i];
+    float r8[8] = {__fmul_rn(xv[0].x, xv[0].x), __fmul_rn(xv[0].y, xv[0].y), __fmul_rn(xv[0].z, xv[0].z), __fmul_rn(xv[0].w, xv[0].w),
+                   __fmul_rn(xv[1].x, xv[1].x), __fmul_rn(xv[1].y, xv[1].y), __fmul_rn(xv[1].z, xv[1].z), __fmul_rn(xv[1].w, xv[1].w)};
+#pragma unroll
+    for (int i = 2; i < Q; i += 2) {
+        const float4 a = xv[i], b = xv[i + 1];
+        r8[0] = __fadd_rn(r8[0], __fmul_rn(a.x, a.x)); r8[1] = __fadd_rn(r8[1], __fmul_rn(a.y, a.y));
+        r8[2] = __fadd_rn(r8[2], __fmul_rn(a.z, a.z)); r8[3] = __fadd_rn(r8[3], __fmul_rn(a.w, a.w));
+        r8[4] = __fadd_rn(r8[4], __fmul_rn(b.x, b.x)); r8[5] = __fadd_rn(r8[5], __fmul_rn(b.y, b.y));
+        r8[6] = __fadd_rn(r8[6], __fmul_rn(b.z, b.z)); r8[7] = __fadd_rn(r8[7], __fmul_rn(b.w, b.w));
+    }
+    return __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
+                     __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
+}
+// acc += sum over the Q * 4 values in xv of (value / nrm) * matrix value, one FMA per value, in order; the matrix row
+// part comes in two batches of loads.
+template <int Q>
+__device__ __forceinline__ float block_chain(const float4 (&xv)[Q], const float4* __restrict__ rj, float nrm, bool ok, float acc) {
+    float4 rv[Q / 2];
+#pragma unroll
+    for (int i = 0; i < Q / 2; ++i) rv[i] = __ldg(rj + i);
+#pragma unroll
+    for (int i = 0; i < Q; ++i) {
+        if (i == Q / 2) {
+#pragma unroll
+            for (int u = 0; u < Q / 2; ++u) rv[u] = __ldg(rj + Q / 2 + u);
+        }
+        const float4 v = xv[i], m = rv[i % (Q / 2)];
+        acc = __fmaf_rn(ok ? __fdiv_rn(v.x, nrm) : 0.f, m.x, acc);
+        acc = __fmaf_rn(ok ? __fdiv_rn(v.y, nrm) : 0.f, m.y, acc);
+        acc = __fmaf_rn(ok ? __fdiv_rn(v.z, nrm) : 0.f, m.z, acc);
+        acc = __fmaf_rn(ok ? __fdiv_rn(v.w, nrm) : 0.f, m.w, acc);
+    }
+    return acc;
+}
+
 template <int D>
 __global__ void __launch_bounds__(128)
 exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                         TqRecheck lists) {
-    constexpr int Q = D / 4;
+    // D = 256: the row passes through the registers in two halves of 128 (which are also the two blocks of NumPy's
+    // pairwise sum for n = 256), read once for the norm and once more for the chain.
+    constexpr int H = D > 128 ? 128 : D, Q = H / 4;
     const unsigned int e0 = blockIdx.x * blockDim.x + threadIdx.x;
     // asked for before the header is known to allow it (the list's capacity bounds the index)
     unsigned long long ent = e0 < lists.code_cap ? lists.code_entries[e0] : 0ull;
@@ -283,38 +326,21 @@ exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t
         const float4* xr = reinterpret_cast<const float4*>(x + row * D);
         const float4* rj = reinterpret_cast<const float4*>(p.R + (size_t)j * D);
         uint32_t* crow = codes + row * p.code_words;
-        float4 xv[Q], rv[Q / 2];
-#pragma unroll
-        for (int i = 0; i < Q; ++i) xv[i] = xr[i];
-#pragma unroll
-        for (int i = 0; i < Q / 2; ++i) rv[i] = __ldg(rj + i);
         const uint32_t old = tq_get_code(crow, j, p.bits);
-        float r8[8] = {__fmul_rn(xv[0].x, xv[0].x), __fmul_rn(xv[0].y, xv[0].y), __fmul_rn(xv[0].z, xv[0].z), __fmul_rn(xv[0].w, xv[0].w),
-                       __fmul_rn(xv[1].x, xv[1].x), __fmul_rn(xv[1].y, xv[1].y), __fmul_rn(xv[1].z, xv[1].z), __fmul_rn(xv[1].w, xv[1].w)};
-#pragma unroll
-        for (int i = 2; i < Q; i += 2) {
-            const float4 a = xv[i], b = xv[i + 1];
-            r8[0] = __fadd_rn(r8[0], __fmul_rn(a.x, a.x)); r8[1] = __fadd_rn(r8[1], __fmul_rn(a.y, a.y));
-            r8[2] = __fadd_rn(r8[2], __fmul_rn(a.z, a.z)); r8[3] = __fadd_rn(r8[3], __fmul_rn(a.w, a.w));
-            r8[4] = __fadd_rn(r8[4], __fmul_rn(b.x, b.x)); r8[5] = __fadd_rn(r8[5], __fmul_rn(b.y, b.y));
-            r8[6] = __fadd_rn(r8[6], __fmul_rn(b.z, b.z)); r8[7] = __fadd_rn(r8[7], __fmul_rn(b.w, b.w));
-        }
-        const float sumsq = __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
-                                      __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
-        const float nrm = __fsqrt_rn(sumsq);
-        const bool ok = nrm > 0.f;
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < Q; ++i) {
-            if (i == Q / 2) {   // second half of the matrix row into the registers of the first
-#pragma unroll
-                for (int u = 0; u < Q / 2; ++u) rv[u] = __ldg(rj + Q / 2 + u);
-            }
-            const float4 v = xv[i], m = rv[i % (Q / 2)];
-            acc = __fmaf_rn(ok ? __fdiv_rn(v.x, nrm) : 0.f, m.x, acc);
-            acc = __fmaf_rn(ok ? __fdiv_rn(v.y, nrm) : 0.f, m.y, acc);
-            acc = __fmaf_rn(ok ? __fdiv_rn(v.z, nrm) : 0.f, m.z, acc);
-            acc = __fmaf_rn(ok ? __fdiv_rn(v.w, nrm) : 0.f, m.w, acc);
+        float4 xv[Q];
+        float acc;
+        if (D <= 128) {
+            const float nrm = __fsqrt_rn(block_sumsq<Q>(xr, xv));
+            acc = block_chain<Q>(xv, rj, nrm, nrm > 0.f, 0.f);
+        } else {
+            const float s0 = block_sumsq<Q>(xr, xv);
+            const float s1 = block_sumsq<Q>(xr + Q, xv);
+            const float nrm = __fsqrt_rn(__fadd_rn(s0, s1));
+            const bool ok = nrm > 0.f;
+            block_sumsq<Q>(xr, xv);                         // the first half again (from L1 / L2)
+            acc = block_chain<Q>(xv, rj, nrm, ok, 0.f);
+            block_sumsq<Q>(xr + Q, xv);
+            acc = block_chain<Q>(xv, rj + Q, nrm, ok, acc);
         }
         const uint32_t code = (uint32_t)count_below(p.boundaries, p.levels - 1, acc);
         if (old == code) continue;
@@ -470,12 +496,14 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
                                const TqRecheck* lists, cudaStream_t st) {
     TqRange range("tq.quantize.recheck_coordinates");
     if (n == 0) return TQ_OK;
-    // as many threads as a list of typical length has entries (about 1 in 50 rows); longer lists take more passes
-    int64_t blocks = (n / 48 + 127) / 128;
-    blocks = blocks < 8 ? 8 : (blocks > 148 * 4 ? 148 * 4 : blocks);
+    // as many threads as a list of typical length has entries (about 1 in 50 rows of 128 coordinates at 4 bits, in
+    // proportion to the coordinates); longer lists take more passes
+    int64_t blocks = (n * p->dev.d / 128 / 48 + 127) / 128;
+    blocks = blocks < 8 ? 8 : (blocks > 148 * 8 ? 148 * 8 : blocks);
     if (p->dev.d == 128) exact_code_check_kernel<128><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
     else if (p->dev.d == 64) exact_code_check_kernel<64><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
-    else return tq_fail(TQ_ERR_UNSUPPORTED, "the coordinate re-check is written for d = 64 and d = 128");
+    else if (p->dev.d == 256) exact_code_check_kernel<256><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
+    else return tq_fail(TQ_ERR_UNSUPPORTED, "the coordinate re-check is written for d = 64, 128 and 256");
     tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;

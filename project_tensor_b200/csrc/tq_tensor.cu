@@ -813,6 +813,297 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 }
 
 // ---------------------------------------------------------------------------------------------
+// d = 256 (TurboQuantMSE): the split rotation is 2 x 128 KB and cannot stay in shared memory, so it streams
+// ---------------------------------------------------------------------------------------------
+// A tile is 128 rows x 256 columns.  The unit rows, split into fp16 hi / lo, fill both A blocks of tensor memory
+// (K half I in block I); the two accumulator blocks take the two halves J of the output columns.  The rotation is
+// stored as 32 chunks of 8 KB -- chunk ((J * 2 + I) * 8 + kb) holds R_hi and R_lo for output columns [128 J, 128 J + 128)
+// and input coordinates [128 I + 16 kb, + 16) as K-major 8 x 8 core matrices -- and every CTA pulls the 256 KB through a
+// ring of 8 chunks once per tile (from L2), three tensor instructions per chunk.  Tensor memory is full with one tile
+// (A 256 + accumulators 256 columns), so the conversion of a tile cannot overlap the contractions of its predecessor;
+// the epilogue of output half 0 runs beside the contractions of half 1.  96 tensor instructions (6.1 K cycles) per tile
+// stand against 6.4 K cycles of HBM time for its 148 KB.
+// Warps: TMA for the rows, MMA, bulk copies of the rotation, 16 converters (64 values per thread), 8 epilogue warps.
+namespace d256 {
+constexpr int kD = 256;
+constexpr int kBoxesPerTile = kD / 32;           // 8
+constexpr int kXRing = 8;                    // one tile: a converter must not meet a slot's second use before its first
+                                            // (its wait on the later parity would pass at once while the first copy is still on its way)
+constexpr int kChunkBytes = 8192;                // R_hi and R_lo of one (J, I, kb): 128 x 16 halves each
+constexpr int kChunksPerTile = 32;
+constexpr int kBRing = 8;
+constexpr int kConvWarps = 16, kEpiWarps = 8;
+constexpr int kFirstConv = 3, kFirstEpi = kFirstConv + kConvWarps;
+constexpr int kThreads = (3 + kConvWarps + kEpiWarps) * 32;      // 864
+constexpr int off_b = 0;
+constexpr int off_x = off_b + kBRing * kChunkBytes;              // 128 KB
+constexpr int off_ssq = off_x + kXRing * kBoxBytes;              // [2 tiles][4 parts][128] floats
+constexpr int off_force = off_ssq + 2 * 4 * kTileRows * 4;       // [4][128] bytes
+constexpr int off_bars = off_force + 4 * kTileRows;
+enum { X_FULL = 0, X_EMPTY = 8, B_FULL = 16, B_EMPTY = 24, A_FULL = 32, A_EMPTY = 33, ACC_FULL = 34, ACC_EMPTY = 36, N_BARS = 38 };
+constexpr int off_lut = off_bars + 512;                          // barriers, tensor-memory slot, give-up flag; then the cell table
+constexpr int off_pend = off_lut + 512;
+constexpr int kPendBytes = kEpiWarps * kPendCap * (8 + 4);
+constexpr int total = off_pend + kPendBytes + 1024;
+static_assert(total <= 227 * 1024, "shared memory plan");
+}  // namespace d256
+
+template <int BITS>
+__global__ void __launch_bounds__(d256::kThreads, 1)
+tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
+    using namespace d256;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem_base = smem_u32(smem);
+    float* ssq_all = reinterpret_cast<float*>(smem + off_ssq);
+    unsigned char* force = smem + off_force;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off_bars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float2* cell_lut = reinterpret_cast<float2*>(smem + off_lut);
+    unsigned char* pend_base = smem + off_pend;
+    const uint32_t bar0 = smem_u32(bars);
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kXRing; ++i) { mbar_init(BAR(X_FULL + i), 1); mbar_init(BAR(X_EMPTY + i), 4); }
+        for (int i = 0; i < kBRing; ++i) { mbar_init(BAR(B_FULL + i), 1); mbar_init(BAR(B_EMPTY + i), 1); }
+        mbar_init(BAR(A_FULL), kConvWarps);
+        mbar_init(BAR(A_EMPTY), 1);
+        for (int j = 0; j < 2; ++j) { mbar_init(BAR(ACC_FULL + j), 1); mbar_init(BAR(ACC_EMPTY + j), kEpiWarps); }
+        abort_flag[0] = 0;
+        abort_flag[1] = a.wait_kcycles;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < kCells) cell_lut[threadIdx.x] = a.cell_lut[threadIdx.x];
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int64_t my_tiles = a.ntiles > (int64_t)blockIdx.x ? (a.ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+    constexpr int kABlock = 64;                                  // columns of one fp16 operand block (128 values)
+    auto A_COL = [&](int i) { return (uint32_t)(i * 2 * kABlock); };
+    auto ACC_COL = [&](int j) { return (uint32_t)(4 * kABlock + j * 128); };
+
+    if (warp == 0) {
+        // ---- rows: TMA boxes of 32 columns x 128 rows ------------------------------------------------
+        if (lane == 0) {
+            int64_t g = 0;
+            bool ok = true;
+            for (int64_t i = 0; i < my_tiles && ok; ++i) {
+                const int64_t tile = blockIdx.x + i * gridDim.x;
+                for (int bx = 0; bx < kBoxesPerTile; ++bx, ++g) {
+                    const int slot = (int)(g % kXRing);
+                    if (!mbar_wait(BAR(X_EMPTY + slot), (uint32_t)(((g / kXRing) & 1) ^ 1), abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(BAR(X_FULL + slot), kBoxBytes);
+                    tma_load_box(smem_base + off_x + slot * kBoxBytes, &tmap_x, bx * 32, (int)(tile * kTileRows), BAR(X_FULL + slot));
+                }
+            }
+            if (*abort_flag)
+                for (int64_t gg = g > kXRing ? g - kXRing : 0; gg < g; ++gg)
+                    mbar_drain(BAR(X_FULL + (int)(gg % kXRing)), (uint32_t)((gg / kXRing) & 1));
+        }
+    } else if (warp == 2) {
+        // ---- rotation: one bulk copy per chunk, the same 32 chunks for every tile ------------------------
+        if (lane == 0) {
+            int64_t g = 0;
+            bool ok = true;
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(a.bmat);
+            for (int64_t i = 0; i < my_tiles && ok; ++i) {
+                for (int c = 0; c < kChunksPerTile; ++c, ++g) {
+                    const int slot = (int)(g % kBRing);
+                    if (!mbar_wait(BAR(B_EMPTY + slot), (uint32_t)(((g / kBRing) & 1) ^ 1), abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(BAR(B_FULL + slot), kChunkBytes);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_base + off_b + slot * kChunkBytes), "l"(src + (size_t)c * kChunkBytes), "r"(kChunkBytes),
+                                   "r"(BAR(B_FULL + slot))
+                                 : "memory");
+                }
+            }
+            if (*abort_flag)
+                for (int64_t gg = g > kBRing ? g - kBRing : 0; gg < g; ++gg)
+                    mbar_drain(BAR(B_FULL + (int)(gg % kBRing)), (uint32_t)((gg / kBRing) & 1));
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: the whole warp walks the loop, one elected lane issues -------------------------
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        int64_t g = 0;
+        bool ok = true;
+        for (int64_t i = 0; i < my_tiles && ok; ++i) {
+            const uint32_t par = (uint32_t)(i & 1);
+            if (!warp_wait(BAR(A_FULL), par, abort_flag)) break;
+            for (int j = 0; j < 2 && ok; ++j) {
+                if (!warp_wait(BAR(ACC_EMPTY + j), par ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc = tm + ACC_COL(j);
+                for (int c = 0; c < 16; ++c, ++g) {          // c = I * 8 + kb
+                    const int slot = (int)(g % kBRing);
+                    if (!warp_wait(BAR(B_FULL + slot), (uint32_t)((g / kBRing) & 1), abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t chunk = smem_base + off_b + slot * kChunkBytes;
+                    const uint64_t d_hi = make_smem_desc(chunk, 128, 256), d_lo = make_smem_desc(chunk + kChunkBytes / 2, 128, 256);
+                    const uint32_t a_hi = tm + A_COL(c >> 3) + (uint32_t)(c & 7) * 8, a_lo = a_hi + kABlock;
+                    if (elect_one()) {
+                        if (c == 0) mma_ts_first(acc, a_hi, d_hi, kIdesc);
+                        else mma_ts_acc(acc, a_hi, d_hi, kIdesc);
+                        mma_ts_acc(acc, a_hi, d_lo, kIdesc);
+                        mma_ts_acc(acc, a_lo, d_hi, kIdesc);
+                        mma_commit(BAR(B_EMPTY + slot));
+                        if (c == 15) mma_commit(BAR(ACC_FULL + j));
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok) break;
+            if (elect_one()) mma_commit(BAR(A_EMPTY));       // both operand blocks have been read
+            __syncwarp();
+        }
+    } else if (warp < kFirstEpi) {
+        // ---- converters: one thread per quarter row (64 values, two boxes) -------------------------------
+        const int cw = warp - kFirstConv;
+        const int part = cw >> 2;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            const int64_t tile = blockIdx.x + i * gridDim.x;
+            const uint32_t par = (uint32_t)(i & 1);
+            float x[64];
+            bool fail = false;
+#pragma unroll
+            for (int bb = 0; bb < 2; ++bb) {
+                const int64_t g = i * kBoxesPerTile + part * 2 + bb;
+                const int slot = (int)(g % kXRing);
+                if (!fail && !mbar_wait(BAR(X_FULL + slot), (uint32_t)((g / kXRing) & 1), abort_flag)) fail = true;
+                const unsigned char* box = smem + off_x + slot * kBoxBytes + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 v = fail ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(box + ((c ^ (row & 7)) << 4));
+                    x[bb * 32 + c * 4 + 0] = v.x;
+                    x[bb * 32 + c * 4 + 1] = v.y;
+                    x[bb * 32 + c * 4 + 2] = v.z;
+                    x[bb * 32 + c * 4 + 3] = v.w;
+                }
+                __syncwarp();
+                if (lane == 0 && !fail) mbar_arrive(BAR(X_EMPTY + slot));
+            }
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < 64; ++k) s4[k & 3] = fmaf(x[k], x[k], s4[k & 3]);
+            float* ssq = ssq_all + (int)par * 4 * kTileRows;     // by tile parity: a fast warp may write the next tile's sums early
+            ssq[part * kTileRows + row] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            bar_sync(1 + quarter, 128);                           // the four warps that share these 32 rows
+            const float tot = (ssq[row] + ssq[kTileRows + row]) + (ssq[2 * kTileRows + row] + ssq[3 * kTileRows + row]);
+            const float nrm = sqrtf(tot);
+            const bool okn = nrm > 0.f;
+            const bool odd = !(tot < 3.0e38f) || (okn && tot < 1.0e-30f);   // rows for the exact kernel: overflowed or denormal-range norms
+            const float sc = (okn && !odd) ? kScaleA / nrm : 0.f;
+            if (part == 0) {
+                const int64_t grow = tile * kTileRows + row;
+                if (grow < a.n && !fail) a.norms[grow] = nrm;
+                force[(i & 3) * kTileRows + row] = odd ? 1 : 0;
+            }
+            if (!mbar_wait(BAR(A_EMPTY), par ^ 1u, abort_flag)) fail = true;
+            tc_fence_after();
+            const uint32_t a_hi = tmem + lane_addr + A_COL(part >> 1) + (uint32_t)(part & 1) * 32;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int p = 0; p < 16; ++p) {
+                    const float u0 = x[s * 32 + 2 * p] * sc, u1 = x[s * 32 + 2 * p + 1] * sc;
+                    const __half2 h = __floats2half2_rn(u0, u1);
+                    const float2 hf = __half22float2(h);
+                    hi[p] = *reinterpret_cast<const uint32_t*>(&h);
+                    lo[p] = pack_half2(u0 - hf.x, u1 - hf.y);
+                }
+                tmem_st16(a_hi + s * 16, hi);
+                tmem_st16(a_hi + kABlock + s * 16, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(A_FULL));
+        }
+    } else {
+        // ---- epilogue: two threads per row, 64 columns of each output half -------------------------------
+        const int ew = warp - kFirstEpi;
+        const int quarter = warp & 3;
+        const int colgroup = ew >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        constexpr int kCodeWords = kD * BITS / 32;
+        const float lut_bnd = cell_lut[lane].x;
+        const int lut_base1 = __float_as_int(cell_lut[lane].y);
+        WarpPending pend;
+        pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + ew * kPendCap;
+        pend.rows = reinterpret_cast<unsigned int*>(pend_base + kEpiWarps * kPendCap * 8) + ew * kPendCap;
+        pend.n_codes = 0;
+        pend.n_rows = 0;
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            const int64_t tile = blockIdx.x + i * gridDim.x;
+            const uint32_t par = (uint32_t)(i & 1);
+            const int64_t grow = tile * kTileRows + row;
+#pragma unroll 1
+            for (int j = 0; j < 2; ++j) {
+                const bool got = mbar_wait(BAR(ACC_FULL + j), par, abort_flag);
+                const bool live = got && grow < a.n;
+                const bool redo_row = force[(i & 3) * kTileRows + row] != 0;   // written before this tile's A_FULL, which precedes ACC_FULL
+                tc_fence_after();
+                const uint32_t acc = tmem + lane_addr + ACC_COL(j);
+                uint32_t nm0 = 0, nm1 = 0;
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    const int chunk = colgroup * 2 + ch;                 // 32-column chunk of this output half
+                    uint32_t va[32];
+                    tmem_ld32(acc + chunk * 32, va);
+                    tmem_wait_ld();
+                    uint32_t w[BITS + 1], rhi[16], rlo[16];
+                    float rs = 0.f;
+                    const uint32_t m = process_chunk<BITS, false>(va, lut_bnd, lut_base1, 0.f, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
+                    if (ch == 0) nm0 = m; else nm1 = m;
+                    if (live) {
+                        uint32_t* dst = a.codes + grow * kCodeWords + (j * 4 + chunk) * BITS;
+                        if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                        else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                        else {
+#pragma unroll
+                            for (int k = 0; k < BITS; ++k) dst[k] = w[k];
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(ACC_EMPTY + j));
+                if (!live || redo_row) { nm0 = 0; nm1 = 0; }
+                if (__any_sync(0xffffffffu, (nm0 | nm1) != 0u)) {
+                    pend_codes(a.lists, pend, nm0, grow, j * 128 + (colgroup * 2) * 32, lane);
+                    pend_codes(a.lists, pend, nm1, grow, j * 128 + (colgroup * 2 + 1) * 32, lane);
+                }
+                if (j == 0) pend_rows(a.lists, pend, redo_row && live && colgroup == 0, grow, lane);
+            }
+        }
+        if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
+        if (pend.n_rows > 0) flush_pending_rows(a.lists, pend, lane);
+    }
+
+    if (*abort_flag) __nanosleep(20000);   // tensor instructions issued before the give-up may still be running
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1ull);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 // fp16 bits of a float, round to nearest even (host)
@@ -840,6 +1131,23 @@ void split_operand(const std::vector<double>& m, int d, double scale, uint16_t* 
             const size_t off = ((size_t)(n / 8) * sbo + (size_t)(k / 8) * lbo + (size_t)(n % 8) * 16 + (size_t)(k % 8) * 2) / 2;
             hi[off] = h;
             lo[off] = l;
+        }
+}
+
+// d = 256: chunk ((J * 2 + I) * 8 + kb) = [hi | lo], each 128 (n) x 16 (k) halves as K-major core matrices:
+// 8-row groups 256 bytes apart, the two core matrices of a group 128 bytes apart.
+void split_operand_chunks(const float* rotation, double scale, uint16_t* out) {
+    const int d = 256;
+    for (int n = 0; n < d; ++n)
+        for (int k = 0; k < d; ++k) {
+            const float v = (float)((double)rotation[(size_t)n * d + k] * scale);      // B[n][k] = R[n][k]
+            const uint16_t h = host_half_bits(v);
+            const uint16_t l = host_half_bits((float)((double)v - (double)host_half_value(h)));
+            const int J = n / 128, I = k / 128, kb = (k % 128) / 16, nn = n % 128, kk = k % 16;
+            const size_t chunk = (size_t)((J * 2 + I) * 8 + kb) * 8192;
+            const size_t off = (size_t)(nn / 8) * 256 + (size_t)(kk / 8) * 128 + (size_t)(nn % 8) * 16 + (size_t)(kk % 8) * 2;
+            out[(chunk + off) / 2] = h;
+            out[(chunk + 4096 + off) / 2] = l;
         }
 }
 
@@ -908,6 +1216,10 @@ struct TensorConsts {
 };
 
 bool tq_tensor_supported(int d, int bits) { return (d == 128 || d == 64) && bits >= 1 && bits <= 4; }
+// The quantize kernels alone also cover d = 256 without a projection (TurboQuantMSE), with the rotation streamed.
+bool tq_tensor_quantize_supported(int d, int bits, bool has_projection) {
+    return tq_tensor_supported(d, bits) || (d == 256 && !has_projection && bits >= 1 && bits <= 4);
+}
 
 int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection) {
     const int d = p->dev.d, levels = p->dev.levels, nb = levels - 1;
@@ -935,10 +1247,15 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
 
     const size_t dd = (size_t)kW * kW;   // operand matrices are stored padded to kW x kW
     const int nmat = projection ? 4 : 2;
-    std::vector<uint16_t> mats(dd * nmat, 0);
+    std::vector<uint16_t> mats(d == 256 ? (size_t)d * d * 2 : dd * nmat, 0);
     std::vector<double> m((size_t)d * d);
-    for (size_t i = 0; i < (size_t)d * d; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
-    split_operand(m, d, kScaleB, mats.data(), mats.data() + dd);
+    if (d == 256) {
+        if (projection) return TQ_OK;    // no tensor-core kernel for TurboQuantProd at d = 256
+        split_operand_chunks(rotation, kScaleB, mats.data());
+    } else {
+        for (size_t i = 0; i < (size_t)d * d; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
+        split_operand(m, d, kScaleB, mats.data(), mats.data() + dd);
+    }
     if (projection) {
         // B2[n=j][k] = (R S^T)[k][j] = sum_i R[k][i] S[j][i]
         for (int j = 0; j < d; ++j)
@@ -1003,6 +1320,14 @@ static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, 
     return TQ_OK;
 }
 
+template <int BITS>
+static int launch_256(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
+    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize256_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, d256::total));
+    tensor_quantize256_kernel<BITS><<<grid, d256::kThreads, d256::total, st>>>(map, args); tq_count_launch();
+    TQ_CUDA_TRY(cudaGetLastError());
+    return TQ_OK;
+}
+
 int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64_t n, uint32_t* codes,
                               uint32_t* signs, float* rnorms, float* norms, const TqRecheck* lists, cudaStream_t st) {
     TqRange range("tq.quantize.tensor_core");
@@ -1039,6 +1364,18 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     const int bits = p->dev.bits;
     tq_timer_mark(p, 0, 0, st);
     int rc = TQ_ERR_UNSUPPORTED;
+    if (d == 256) {
+        if (prod) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for TurboQuantProd at d = 256");
+        switch (bits) {
+            case 1: rc = launch_256<1>(map, args, grid, st); break;
+            case 2: rc = launch_256<2>(map, args, grid, st); break;
+            case 3: rc = launch_256<3>(map, args, grid, st); break;
+            case 4: rc = launch_256<4>(map, args, grid, st); break;
+        }
+        tq_timer_mark(p, 0, 1, st);
+        if (rc != TQ_ERR_UNSUPPORTED) return rc;
+        return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for bits=%d", bits);
+    }
 #define TQ_DISPATCH(B)                                                                                     \
     case B:                                                                                                \
         if (d == 64) rc = prod ? launch_one<64, B, true>(map, args, grid, st) : launch_one<64, B, false>(map, args, grid, st); \

@@ -830,7 +830,7 @@ constexpr int kBoxesPerTile = kD / 32;           // 8
 constexpr int kXRing = 8;                    // one tile: a converter must not meet a slot's second use before its first
                                             // (its wait on the later parity would pass at once while the first copy is still on its way)
 constexpr int kChunkBytes = 8192;                // R_hi and R_lo of one (J, I, kb): 128 x 16 halves each
-constexpr int kChunksPerTile = 32;
+constexpr int kChunksPerMatrix = 32;          // per tile: the rotation, and for TurboQuantProd 16 (R S^T) behind it
 constexpr int kBRing = 8;
 constexpr int kConvWarps = 16, kEpiWarps = 8;
 constexpr int kFirstConv = 3, kFirstEpi = kFirstConv + kConvWarps;
@@ -840,15 +840,16 @@ constexpr int off_x = off_b + kBRing * kChunkBytes;              // 128 KB
 constexpr int off_ssq = off_x + kXRing * kBoxBytes;              // [2 tiles][4 parts][128] floats
 constexpr int off_force = off_ssq + 2 * 4 * kTileRows * 4;       // [4][128] bytes
 constexpr int off_bars = off_force + 4 * kTileRows;
-enum { X_FULL = 0, X_EMPTY = 8, B_FULL = 16, B_EMPTY = 24, A_FULL = 32, A_EMPTY = 33, ACC_FULL = 34, ACC_EMPTY = 36, N_BARS = 38 };
+enum { X_FULL = 0, X_EMPTY = 8, B_FULL = 16, B_EMPTY = 24, A_FULL = 32, A_EMPTY = 33, ACC_FULL = 34, ACC_EMPTY = 36, RHO_FULL = 38, ACC2_FULL = 40, N_BARS = 42 };
 constexpr int off_lut = off_bars + 512;                          // barriers, tensor-memory slot, give-up flag; then the cell table
-constexpr int off_pend = off_lut + 512;
-constexpr int kPendBytes = kEpiWarps * kPendCap * (8 + 4);
+constexpr int off_rs = off_lut + 512;                            // |rho|^2 partial sums [4 column groups][128] (TurboQuantProd)
+constexpr int off_pend = off_rs + 4 * kTileRows * 4;
+constexpr int kPendBytes = kEpiWarps * kPendCap * (8 + 4) + kConvWarps * kPendCap * 4;   // epilogue warps: both lists; converters: rows
 constexpr int total = off_pend + kPendBytes + 1024;
 static_assert(total <= 227 * 1024, "shared memory plan");
 }  // namespace d256
 
-template <int BITS>
+template <int BITS, bool PROD>
 __global__ void __launch_bounds__(d256::kThreads, 1)
 tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorArgs a) {
     using namespace d256;
@@ -861,6 +862,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float2* cell_lut = reinterpret_cast<float2*>(smem + off_lut);
+    float* rs_part = reinterpret_cast<float*>(smem + off_rs);
     unsigned char* pend_base = smem + off_pend;
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -871,7 +873,12 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
         for (int i = 0; i < kBRing; ++i) { mbar_init(BAR(B_FULL + i), 1); mbar_init(BAR(B_EMPTY + i), 1); }
         mbar_init(BAR(A_FULL), kConvWarps);
         mbar_init(BAR(A_EMPTY), 1);
-        for (int j = 0; j < 2; ++j) { mbar_init(BAR(ACC_FULL + j), 1); mbar_init(BAR(ACC_EMPTY + j), kEpiWarps); }
+        for (int j = 0; j < 2; ++j) {
+            mbar_init(BAR(ACC_FULL + j), 1);
+            mbar_init(BAR(ACC_EMPTY + j), PROD ? 1 : kEpiWarps);      // Prod: freed when the second contraction has read rho
+            mbar_init(BAR(RHO_FULL + j), kEpiWarps);
+            mbar_init(BAR(ACC2_FULL + j), 1);
+        }
         abort_flag[0] = 0;
         abort_flag[1] = a.wait_kcycles;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -916,7 +923,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
             bool ok = true;
             const unsigned char* src = reinterpret_cast<const unsigned char*>(a.bmat);
             for (int64_t i = 0; i < my_tiles && ok; ++i) {
-                for (int c = 0; c < kChunksPerTile; ++c, ++g) {
+                for (int c = 0; c < (PROD ? 2 : 1) * kChunksPerMatrix; ++c, ++g) {
                     const int slot = (int)(g % kBRing);
                     if (!mbar_wait(BAR(B_EMPTY + slot), (uint32_t)(((g / kBRing) & 1) ^ 1), abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(BAR(B_FULL + slot), kChunkBytes);
@@ -961,7 +968,39 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                 }
             }
             if (!ok) break;
-            if (elect_one()) mma_commit(BAR(A_EMPTY));       // both operand blocks have been read
+            if (!PROD) {
+                if (elect_one()) mma_commit(BAR(A_EMPTY));       // both operand blocks have been read
+                __syncwarp();
+                continue;
+            }
+            // TurboQuantProd: rho (split, in place of the accumulators: K half I in accumulator block I) times the chunks of
+            // 16 (R S^T); output half J goes to operand block J, which the first contraction has finished reading.
+            if (!warp_wait(BAR(RHO_FULL + 0), par, abort_flag) || !warp_wait(BAR(RHO_FULL + 1), par, abort_flag)) break;
+            tc_fence_after();
+            for (int j = 0; j < 2 && ok; ++j) {
+                const uint32_t acc2 = tm + A_COL(j);
+                for (int c = 0; c < 16; ++c, ++g) {
+                    const int slot = (int)(g % kBRing);
+                    if (!warp_wait(BAR(B_FULL + slot), (uint32_t)((g / kBRing) & 1), abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t chunk = smem_base + off_b + slot * kChunkBytes;
+                    const uint64_t d_hi = make_smem_desc(chunk, 128, 256), d_lo = make_smem_desc(chunk + kChunkBytes / 2, 128, 256);
+                    const int kb = c & 7;
+                    // rho of 32 coordinates: 16 columns of hi pairs, then 16 of lo pairs
+                    const uint32_t r_hi = tm + ACC_COL(c >> 3) + (uint32_t)(kb >> 1) * 32 + (uint32_t)(kb & 1) * 8, r_lo = r_hi + 16;
+                    if (elect_one()) {
+                        if (c == 0) mma_ts_first(acc2, r_hi, d_hi, kIdesc);
+                        else mma_ts_acc(acc2, r_hi, d_hi, kIdesc);
+                        mma_ts_acc(acc2, r_hi, d_lo, kIdesc);
+                        mma_ts_acc(acc2, r_lo, d_hi, kIdesc);
+                        mma_commit(BAR(B_EMPTY + slot));
+                        if (c == 15) mma_commit(BAR(ACC2_FULL + j));
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok) break;
+            if (elect_one()) { mma_commit(BAR(ACC_EMPTY + 0)); mma_commit(BAR(ACC_EMPTY + 1)); }   // rho has been read
             __syncwarp();
         }
     } else if (warp < kFirstEpi) {
@@ -971,6 +1010,11 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        WarpPending cpend;           // rows for the exact stage found by the sign epilogue
+        cpend.codes = nullptr;
+        cpend.rows = reinterpret_cast<unsigned int*>(pend_base + kEpiWarps * kPendCap * 12) + cw * kPendCap;
+        cpend.n_codes = 0;
+        cpend.n_rows = 0;
         for (int64_t i = 0; i < my_tiles; ++i) {
             const int64_t tile = blockIdx.x + i * gridDim.x;
             const uint32_t par = (uint32_t)(i & 1);
@@ -1009,7 +1053,8 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                 if (grow < a.n && !fail) a.norms[grow] = nrm;
                 force[(i & 3) * kTileRows + row] = odd ? 1 : 0;
             }
-            if (!mbar_wait(BAR(A_EMPTY), par ^ 1u, abort_flag)) fail = true;
+            // TurboQuantProd: this thread itself was the last reader of its cells (sign epilogue of the previous tile, below)
+            if (!PROD && !mbar_wait(BAR(A_EMPTY), par ^ 1u, abort_flag)) fail = true;
             tc_fence_after();
             const uint32_t a_hi = tmem + lane_addr + A_COL(part >> 1) + (uint32_t)(part & 1) * 32;
 #pragma unroll
@@ -1030,7 +1075,53 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(A_FULL));
+            if (PROD) {
+                // ---- sign epilogue of the same tile: the second accumulator of output half J sits in operand block J.  A
+                // thread reads exactly the cells it fills again for the next tile (columns [32 h, 32 h + 32) and
+                // [64 + 32 h, 64 + 32 h + 32) with h = part & 1: two sign words of the row), so no other warp's
+                // progress matters to it.
+                const int j = part >> 1, hcol = part & 1;
+                const int64_t grow = tile * kTileRows + row;
+                bool redo_row = part == 0 && force[(i & 3) * kTileRows + row] != 0;
+                const bool live = mbar_wait(BAR(ACC2_FULL + j), par, abort_flag) && grow < a.n;   // no stores after a give-up
+                tc_fence_after();
+                if (part == 0 && live) {      // |rho|^2 in 2^10 units: the four partial sums of the first epilogue
+                    const float rs_all = (rs_part[row] + rs_part[kTileRows + row]) + (rs_part[2 * kTileRows + row] + rs_part[3 * kTileRows + row]);
+                    a.rnorms[grow] = sqrtf(rs_all) * kScaleRho;
+                }
+                const uint32_t acc2 = tmem + lane_addr + A_COL(j);
+                uint32_t sw[2] = {0u, 0u};
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t va[32];
+                    tmem_ld32(acc2 + (hcol + 2 * ch) * 32, va);
+                    tmem_wait_ld();
+                    uint32_t wd[4] = {0u, 0u, 0u, 0u};
+                    float am[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};
+#pragma unroll
+                    for (int k = 7; k >= 0; --k) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) wd[c] = __funnelshift_l(va[(c >> 1) * 16 + 2 * k + (c & 1)], wd[c], 1);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            am[c] = min3_abs(am[c], __uint_as_float(va[e + 2 * c]), __uint_as_float(va[e + 2 * c + 1]));
+                    }
+                    const uint32_t word = ~((wd[0] | (wd[2] << 8)) | ((wd[1] | (wd[3] << 8)) << 16));
+                    if (ch == 0) sw[0] = word; else sw[1] = word;
+                    redo_row = redo_row || (fminf(fminf(am[0], am[1]), fminf(am[2], am[3])) < a.sign_guard);
+                }
+                tc_fence_before();
+                if (live) {
+                    a.signs[grow * (kD / 32) + j * 4 + hcol] = sw[0];
+                    a.signs[grow * (kD / 32) + j * 4 + 2 + hcol] = sw[1];
+                }
+                pend_rows(a.lists, cpend, redo_row && live, grow, lane);
+            }
         }
+        if (PROD && cpend.n_rows > 0) flush_pending_rows(a.lists, cpend, lane);
     } else {
         // ---- epilogue: two threads per row, 64 columns of each output half -------------------------------
         const int ew = warp - kFirstEpi;
@@ -1041,6 +1132,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
         constexpr int kCodeWords = kD * BITS / 32;
         const float lut_bnd = cell_lut[lane].x;
         const int lut_base1 = __float_as_int(cell_lut[lane].y);
+        const float lut_ncent = PROD ? a.code_ncent[lane] : 0.f;
         WarpPending pend;
         pend.codes = reinterpret_cast<unsigned long long*>(pend_base) + ew * kPendCap;
         pend.rows = reinterpret_cast<unsigned int*>(pend_base + kEpiWarps * kPendCap * 8) + ew * kPendCap;
@@ -1058,6 +1150,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                 tc_fence_after();
                 const uint32_t acc = tmem + lane_addr + ACC_COL(j);
                 uint32_t nm0 = 0, nm1 = 0;
+                float rs = 0.f;
 #pragma unroll 1
                 for (int ch = 0; ch < 2; ++ch) {
                     const int chunk = colgroup * 2 + ch;                 // 32-column chunk of this output half
@@ -1065,9 +1158,12 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                     tmem_ld32(acc + chunk * 32, va);
                     tmem_wait_ld();
                     uint32_t w[BITS + 1], rhi[16], rlo[16];
-                    float rs = 0.f;
-                    const uint32_t m = process_chunk<BITS, false>(va, lut_bnd, lut_base1, 0.f, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
+                    const uint32_t m = process_chunk<BITS, PROD>(va, lut_bnd, lut_base1, lut_ncent, a.cell_scale, a.cell_offset, a.code_guard, w, rhi, rlo, rs);
                     if (ch == 0) nm0 = m; else nm1 = m;
+                    if (PROD) {      // rho replaces the chunk it was computed from: 16 columns of hi pairs, 16 of lo pairs
+                        tmem_st16(acc + chunk * 32, rhi);
+                        tmem_st16(acc + chunk * 32 + 16, rlo);
+                    }
                     if (live) {
                         uint32_t* dst = a.codes + grow * kCodeWords + (j * 4 + chunk) * BITS;
                         if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -1078,15 +1174,21 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                         }
                     }
                 }
+                if (PROD) {
+                    tmem_wait_st();
+                    // this thread's share of |rho|^2; one tile is in flight per block, and the sign epilogue that reads the
+                    // sums comes after the second contraction, which waits for every epilogue warp's arrival below
+                    rs_part[(j * 2 + colgroup) * kTileRows + row] = rs;
+                }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(ACC_EMPTY + j));
+                if (lane == 0) mbar_arrive(BAR(PROD ? RHO_FULL + j : ACC_EMPTY + j));
                 if (!live || redo_row) { nm0 = 0; nm1 = 0; }
                 if (__any_sync(0xffffffffu, (nm0 | nm1) != 0u)) {
                     pend_codes(a.lists, pend, nm0, grow, j * 128 + (colgroup * 2) * 32, lane);
                     pend_codes(a.lists, pend, nm1, grow, j * 128 + (colgroup * 2 + 1) * 32, lane);
                 }
-                if (j == 0) pend_rows(a.lists, pend, redo_row && live && colgroup == 0, grow, lane);
+                if (!PROD && j == 0) pend_rows(a.lists, pend, redo_row && live && colgroup == 0, grow, lane);
             }
         }
         if (pend.n_codes > 0) flush_pending_codes(a.lists, pend, lane);
@@ -1136,11 +1238,11 @@ void split_operand(const std::vector<double>& m, int d, double scale, uint16_t* 
 
 // d = 256: chunk ((J * 2 + I) * 8 + kb) = [hi | lo], each 128 (n) x 16 (k) halves as K-major core matrices:
 // 8-row groups 256 bytes apart, the two core matrices of a group 128 bytes apart.
-void split_operand_chunks(const float* rotation, double scale, uint16_t* out) {
+void split_operand_chunks(const double* m, double scale, uint16_t* out) {
     const int d = 256;
     for (int n = 0; n < d; ++n)
         for (int k = 0; k < d; ++k) {
-            const float v = (float)((double)rotation[(size_t)n * d + k] * scale);      // B[n][k] = R[n][k]
+            const float v = (float)(m[(size_t)n * d + k] * scale);      // B[n][k]
             const uint16_t h = host_half_bits(v);
             const uint16_t l = host_half_bits((float)((double)v - (double)host_half_value(h)));
             const int J = n / 128, I = k / 128, kb = (k % 128) / 16, nn = n % 128, kk = k % 16;
@@ -1216,9 +1318,10 @@ struct TensorConsts {
 };
 
 bool tq_tensor_supported(int d, int bits) { return (d == 128 || d == 64) && bits >= 1 && bits <= 4; }
-// The quantize kernels alone also cover d = 256 without a projection (TurboQuantMSE), with the rotation streamed.
+// The quantize kernels alone also cover d = 256, with the operand matrices streamed.
 bool tq_tensor_quantize_supported(int d, int bits, bool has_projection) {
-    return tq_tensor_supported(d, bits) || (d == 256 && !has_projection && bits >= 1 && bits <= 4);
+    (void)has_projection;
+    return tq_tensor_supported(d, bits) || (d == 256 && bits >= 1 && bits <= 4);
 }
 
 int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook, const float* projection) {
@@ -1247,11 +1350,11 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
 
     const size_t dd = (size_t)kW * kW;   // operand matrices are stored padded to kW x kW
     const int nmat = projection ? 4 : 2;
-    std::vector<uint16_t> mats(d == 256 ? (size_t)d * d * 2 : dd * nmat, 0);
+    std::vector<uint16_t> mats(d == 256 ? (size_t)d * d * nmat : dd * nmat, 0);
     std::vector<double> m((size_t)d * d);
     if (d == 256) {
-        if (projection) return TQ_OK;    // no tensor-core kernel for TurboQuantProd at d = 256
-        split_operand_chunks(rotation, kScaleB, mats.data());
+        for (size_t i = 0; i < (size_t)d * d; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
+        split_operand_chunks(m.data(), kScaleB, mats.data());
     } else {
         for (size_t i = 0; i < (size_t)d * d; ++i) m[i] = rotation[i];  // B1[n=j][k] = R[j][k]
         split_operand(m, d, kScaleB, mats.data(), mats.data() + dd);
@@ -1264,7 +1367,8 @@ int tq_tensor_plan_init(tq_plan* p, const float* rotation, const float* codebook
                 for (int i = 0; i < d; ++i) acc += (double)rotation[(size_t)k * d + i] * (double)projection[(size_t)j * d + i];
                 m[(size_t)j * d + k] = acc;
             }
-        split_operand(m, d, kScaleM, mats.data() + 2 * dd, mats.data() + 3 * dd);
+        if (d == 256) split_operand_chunks(m.data(), kScaleM, mats.data() + (size_t)d * d * 2);   // the second 256 KB of chunks
+        else split_operand(m, d, kScaleM, mats.data() + 2 * dd, mats.data() + 3 * dd);
     }
     const size_t mat_bytes = mats.size() * 2;
     const size_t total = mat_bytes + 5 * kCells * 4;
@@ -1320,10 +1424,10 @@ static int launch_one(const CUtensorMap& map, const TensorArgs& args, int grid, 
     return TQ_OK;
 }
 
-template <int BITS>
+template <int BITS, bool PROD>
 static int launch_256(const CUtensorMap& map, const TensorArgs& args, int grid, cudaStream_t st) {
-    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize256_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, d256::total));
-    tensor_quantize256_kernel<BITS><<<grid, d256::kThreads, d256::total, st>>>(map, args); tq_count_launch();
+    TQ_CUDA_TRY(cudaFuncSetAttribute(tensor_quantize256_kernel<BITS, PROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, d256::total));
+    tensor_quantize256_kernel<BITS, PROD><<<grid, d256::kThreads, d256::total, st>>>(map, args); tq_count_launch();
     TQ_CUDA_TRY(cudaGetLastError());
     return TQ_OK;
 }
@@ -1365,12 +1469,11 @@ int tq_launch_tensor_quantize(const tq_plan* p, bool prod, const float* x, int64
     tq_timer_mark(p, 0, 0, st);
     int rc = TQ_ERR_UNSUPPORTED;
     if (d == 256) {
-        if (prod) return tq_fail(TQ_ERR_UNSUPPORTED, "no tensor-core kernel for TurboQuantProd at d = 256");
         switch (bits) {
-            case 1: rc = launch_256<1>(map, args, grid, st); break;
-            case 2: rc = launch_256<2>(map, args, grid, st); break;
-            case 3: rc = launch_256<3>(map, args, grid, st); break;
-            case 4: rc = launch_256<4>(map, args, grid, st); break;
+            case 1: rc = prod ? launch_256<1, true>(map, args, grid, st) : launch_256<1, false>(map, args, grid, st); break;
+            case 2: rc = prod ? launch_256<2, true>(map, args, grid, st) : launch_256<2, false>(map, args, grid, st); break;
+            case 3: rc = prod ? launch_256<3, true>(map, args, grid, st) : launch_256<3, false>(map, args, grid, st); break;
+            case 4: rc = prod ? launch_256<4, true>(map, args, grid, st) : launch_256<4, false>(map, args, grid, st); break;
         }
         tq_timer_mark(p, 0, 1, st);
         if (rc != TQ_ERR_UNSUPPORTED) return rc;

@@ -78,7 +78,7 @@ def test_config2_full_size_against_oracle(tg, path):
 
 
 @pytest.mark.parametrize("cls_name,bits,d", [("TurboQuantProd", 4, 128), ("TurboQuantProd", 3, 128), ("TurboQuantMSE", 4, 128),
-                                             ("TurboQuantMSE", 4, 256), ("TurboQuantMSE", 1, 256)])
+                                             ("TurboQuantMSE", 4, 256), ("TurboQuantMSE", 1, 256), ("TurboQuantProd", 4, 256)])
 def test_tensor_and_exact_kernels_agree_byte_for_byte_at_full_size(tg, cls_name, bits, d):
     """The tensor-core pass plus its exact second stage must leave the same packed bytes as the
     reference-order kernels on all 1,048,576 rows (d = 256, where the rotation streams through shared memory:

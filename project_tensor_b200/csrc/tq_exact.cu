@@ -310,38 +310,47 @@ template <int D>
 __global__ void __launch_bounds__(128)
 exact_code_check_kernel(TqDev p, bool prod, const float* __restrict__ x, int64_t n, uint32_t* __restrict__ codes,
                         TqRecheck lists) {
-    // D = 256: the row passes through the registers in two halves of 128 (which are also the two blocks of NumPy's
-    // pairwise sum for n = 256), read once for the norm and once more for the chain.
-    constexpr int H = D > 128 ? 128 : D, Q = H / 4;
-    const unsigned int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+    // D = 256: two neighbouring lanes share an entry, each with one half of the row in its registers (the halves are
+    // also the two blocks of NumPy's pairwise sum for n = 256).  The chain runs over the first half in the even lane,
+    // then over the second half in the odd lane, which decides.
+    constexpr int LANES = D > 128 ? 2 : 1;                 // lanes per entry
+    constexpr int H = D / LANES, Q = H / 4;
+    const unsigned int t0 = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned int e0 = t0 / LANES;
+    const int half = LANES == 2 ? (int)(threadIdx.x & 1u) : 0;
     // asked for before the header is known to allow it (the list's capacity bounds the index)
     unsigned long long ent = e0 < lists.code_cap ? lists.code_entries[e0] : 0ull;
     if (lists.hdr->overflow) return;  // the row pass will redo everything
     const unsigned int count = min(lists.hdr->n_codes, lists.code_cap);
-    for (unsigned int e = e0; e < count; e += gridDim.x * blockDim.x) {
-        if (e != e0) ent = lists.code_entries[e];
+    const unsigned int stride = gridDim.x * blockDim.x / LANES;
+    // both lanes of a pair run the same number of passes (their e is the same), so the shuffles below are whole-warp
+    for (unsigned int e = e0; e < ((count + 31u) & ~31u) + stride; e += stride) {
+        if (__all_sync(0xffffffffu, e >= count)) break;
+        const bool have = e < count;
+        if (e != e0 && have) ent = lists.code_entries[e];
         const int64_t row = (int64_t)(ent >> 8);
         const int j = (int)(ent & 255u);
-        if (row >= n || j >= D) continue;
-        const float4* xr = reinterpret_cast<const float4*>(x + row * D);
-        const float4* rj = reinterpret_cast<const float4*>(p.R + (size_t)j * D);
-        uint32_t* crow = codes + row * p.code_words;
-        const uint32_t old = tq_get_code(crow, j, p.bits);
+        const bool valid = have && row < n && j < D;
+        const float4* xr = reinterpret_cast<const float4*>(x + (valid ? row : 0) * D) + half * Q;
+        const float4* rj = reinterpret_cast<const float4*>(p.R + (size_t)(valid ? j : 0) * D) + half * Q;
+        uint32_t* crow = codes + (valid ? row : 0) * p.code_words;
+        const uint32_t old = tq_get_code(crow, valid ? j : 0, p.bits);
         float4 xv[Q];
         float acc;
-        if (D <= 128) {
-            const float nrm = __fsqrt_rn(block_sumsq<Q>(xr, xv));
+        const float mine = block_sumsq<Q>(xr, xv);
+        if (LANES == 1) {
+            const float nrm = __fsqrt_rn(mine);
             acc = block_chain<Q>(xv, rj, nrm, nrm > 0.f, 0.f);
         } else {
-            const float s0 = block_sumsq<Q>(xr, xv);
-            const float s1 = block_sumsq<Q>(xr + Q, xv);
-            const float nrm = __fsqrt_rn(__fadd_rn(s0, s1));
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            const float nrm = __fsqrt_rn(half == 0 ? __fadd_rn(mine, other) : __fadd_rn(other, mine));   // first half + second half
             const bool ok = nrm > 0.f;
-            block_sumsq<Q>(xr, xv);                         // the first half again (from L1 / L2)
-            acc = block_chain<Q>(xv, rj, nrm, ok, 0.f);
-            block_sumsq<Q>(xr + Q, xv);
-            acc = block_chain<Q>(xv, rj + Q, nrm, ok, acc);
+            const float first = block_chain<Q>(xv, rj, nrm, ok, 0.f);                 // meaningful in the even lane
+            const float carry = __shfl_xor_sync(0xffffffffu, first, 1);               // odd lane: the first half's sum
+            acc = block_chain<Q>(xv, rj, nrm, ok, carry);                             // meaningful in the odd lane
+            if (half == 0) continue;                                                  // the odd lane decides
         }
+        if (!valid) continue;
         const uint32_t code = (uint32_t)count_below(p.boundaries, p.levels - 1, acc);
         if (old == code) continue;
         if (prod) {
@@ -498,7 +507,7 @@ int tq_launch_exact_code_check(const tq_plan* p, bool prod, const float* x, int6
     if (n == 0) return TQ_OK;
     // as many threads as a list of typical length has entries (about 1 in 50 rows of 128 coordinates at 4 bits, in
     // proportion to the coordinates); longer lists take more passes
-    int64_t blocks = (n * p->dev.d / 128 / 48 + 127) / 128;
+    int64_t blocks = (n * p->dev.d / 128 / 48 * (p->dev.d > 128 ? 2 : 1) + 127) / 128;   // d = 256: two lanes per entry
     blocks = blocks < 8 ? 8 : (blocks > 148 * 8 ? 148 * 8 : blocks);
     if (p->dev.d == 128) exact_code_check_kernel<128><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);
     else if (p->dev.d == 64) exact_code_check_kernel<64><<<(int)blocks, 128, 0, st>>>(p->dev, prod, x, n, codes, *lists);

@@ -449,6 +449,15 @@ def run_gpu(args):
         for name, fn, nbytes, what in rows:
             other[name] = rate_row(timed(fn), N_KEYS, nbytes, what, peak)
         del enc_m
+        # the quantizers at the other two dimensions of the reference's grid, same number of vectors
+        for d_other in (64, 256):
+            keys_o = torch.randn((N_KEYS, d_other), generator=gen, device=dev, dtype=torch.float32)
+            for cls, nbytes in ((tg.TurboQuantMSE, mse_bytes(d_other, BITS)), (tg.TurboQuantProd, prod_bytes(d_other, BITS))):
+                q_o = cls(d_other, BITS, seed=SEED)
+                name = ("mse" if cls is tg.TurboQuantMSE else "prod") + "_quantize_d%d" % d_other
+                other[name] = rate_row(timed(lambda: q_o.quantize(keys_o)), N_KEYS, nbytes,
+                                       "B/vector: fp32 row in, packed encoding out, d = %d" % d_other, peak)
+            del keys_o
         kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
         other["decode_attention"] = rate_row(
             timed(lambda: kv.attend(kv_q)), N_KEYS, kb + D * BITS // 8 + 4,

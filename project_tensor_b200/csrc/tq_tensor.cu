@@ -831,7 +831,7 @@ constexpr int kXRing = 8;                    // one tile: a converter must not m
                                             // (its wait on the later parity would pass at once while the first copy is still on its way)
 constexpr int kChunkBytes = 8192;                // R_hi and R_lo of one (J, I, kb): 128 x 16 halves each
 constexpr int kChunksPerMatrix = 32;          // per tile: the rotation, and for TurboQuantProd 16 (R S^T) behind it
-constexpr int kBRing = 8;
+constexpr int kBRing = 8;                    // (10 chunks, which is what shared memory leaves room for, were slower: 582 against 542 us)
 constexpr int kConvWarps = 16, kEpiWarps = 8;
 constexpr int kFirstConv = 3, kFirstEpi = kFirstConv + kConvWarps;
 constexpr int kThreads = (3 + kConvWarps + kEpiWarps) * 32;      // 864

@@ -1,5 +1,5 @@
 // attention_score for one or two queries per group of keys (the reference's own call pattern: one query broadcast
-// over all keys, _quant.py:334-358), d = 128 or 64, 1..4 code bits.
+// over all keys, _quant.py:334-358), d = 128, 64 or 256, 1..4 code bits.
 //
 //   score(q, key) = norm * ( (R q) . codebook[codes]  +  alpha * rnorm * ((S q) . signs) )
 //
@@ -144,8 +144,13 @@ int launch_few(const tq_plan* p, const float* q, const uint32_t* codes, const ui
 
 }  // namespace
 
+// d = 128 and 64: one or two queries (from three on, the lookup-table kernel for four and the tensor-core kernel are
+// faster).  d = 256 has no tensor-core scoring kernel, so this kernel also takes batches of up to 32 queries there: every
+// query is a pass of its own over the packed keys, which still beats the general kernel several times.
 bool tq_score_few_supported(const tq_plan* p, int qpg) {
-    return p->has_projection && (p->dev.d == 128 || p->dev.d == 64) && p->dev.bits >= 1 && p->dev.bits <= 4 && qpg >= 1 && qpg <= 2;
+    if (!p->has_projection || p->dev.bits < 1 || p->dev.bits > 4 || qpg < 1) return false;
+    if (p->dev.d == 256) return qpg <= 32;
+    return (p->dev.d == 128 || p->dev.d == 64) && qpg <= 2;
 }
 
 // scores: [groups][qpg][keys_per_group]
@@ -159,7 +164,8 @@ int tq_launch_score_few(const tq_plan* p, const float* q, int groups, int qpg, c
 #define TQ_FEW(B)                                                                                                        \
     case B:                                                                                                             \
         r = d == 64 ? launch_few<B, 64>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st)     \
-                    : launch_few<B, 128>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st);   \
+            : d == 256 ? launch_few<B, 256>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st) \
+                       : launch_few<B, 128>(p, q, codes, signs, rnorms, norms, keys_per_group, group_rows, groups, qpg, scores, st); \
         break;
     switch (bits) { TQ_FEW(1) TQ_FEW(2) TQ_FEW(3) TQ_FEW(4) }
 #undef TQ_FEW

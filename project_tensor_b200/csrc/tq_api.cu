@@ -429,7 +429,7 @@ int tq_score_pairwise(const tq_plan* p, const float* q, const void* codes, const
     DeviceScope scope(p->device);
     // q[i] . dequantize(key i) on the tensor-core dequantize kernel where the plan has one; the exact kernel
     // (reference order of operations) otherwise and on the EXACT path
-    if (p->path != TQ_PATH_EXACT && p->dequant)
+    if (p->path != TQ_PATH_EXACT && p->dequant && p->dev.d != 256)      // d = 256: no pair form of the streaming kernel
         return tq_launch_pairwise_tc(p, q, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),
                                      residual_norms, norms, n, scores, static_cast<cudaStream_t>(stream));
     return tq_launch_exact_pairwise(p, q, static_cast<const uint32_t*>(codes), static_cast<const uint32_t*>(signs),

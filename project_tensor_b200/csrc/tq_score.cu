@@ -268,7 +268,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
                        size_t scratch_bytes, cudaStream_t st, int64_t group_rows);
 
 static bool use_tensor_scoring(const tq_plan* p) {
-    return p->path != TQ_PATH_EXACT && p->has_projection && tq_tensor_supported(p->dev.d, p->dev.bits);
+    return p->path != TQ_PATH_EXACT && p->has_projection && tq_tensor_quantize_supported(p->dev.d, p->dev.bits, true);
 }
 
 static int64_t general_topk_scratch(int groups, int qpg, int64_t keys_per_group, int topk) {
@@ -279,7 +279,7 @@ static int64_t general_topk_scratch(int groups, int qpg, int64_t keys_per_group,
 
 int64_t tq_score_topk_scratch(const tq_plan* p, int groups, int qpg, int64_t keys_per_group, int topk) {
     const int64_t a = general_topk_scratch(groups, qpg, keys_per_group, topk);
-    const int64_t b = tq_tensor_supported(p->dev.d, p->dev.bits) ? tq_score_tc_scratch(groups, qpg, keys_per_group, topk) : 0;
+    const int64_t b = tq_tensor_quantize_supported(p->dev.d, p->dev.bits, true) ? tq_score_tc_scratch(groups, qpg, keys_per_group, topk) : 0;
     return a > b ? a : b;
 }
 
@@ -306,7 +306,7 @@ int tq_launch_score_batched(const tq_plan* p, const float* q, int groups, int qp
         return tq_launch_score_lut(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, st, group_rows);
     // d = 64 has 8-byte sign rows (and 8- or 24-byte code rows): a group must start on a 16-byte boundary
     // for the bulk copies of the tensor-core kernel
-    const bool aligned_groups = p->dev.d == 128 || groups == 1 || group_rows % 2 == 0;
+    const bool aligned_groups = p->dev.d >= 128 || groups == 1 || group_rows % 2 == 0;
     if (use_tensor_scoring(p) && aligned_groups && keys_per_group > 0 && groups > 0 && qpg > 0)
         return tq_launch_score_tc(p, q, groups, qpg, codes, signs, rnorms, norms, keys_per_group, scores, topk, top_scores,
                                   top_idx, idx_base, scratch, scratch_bytes, st, group_rows);

@@ -53,7 +53,9 @@ constexpr int kRowBytesB = D * 2;  // one query row of one fp16 operand matrix
 constexpr int kPrepSmemBytes = 2 * D * D * 4;  // rotation and projection matrices staged by the preparation kernel
 constexpr int kEpiBarrier = 1;     // named barrier of the epilogue warps
 
-__host__ __device__ constexpr int prep_group_bytes(int qpad) { return 4 * qpad * kRowBytesB + 2 * qpad * 4; }
+// Prepared queries of one group: per half of the coordinates (two halves of 128 for d = 256, one otherwise) the four
+// fp16 operand matrices q_hi, q_lo, p_hi, p_lo, then one (1 / scale) pair per query.
+__host__ __device__ constexpr int prep_group_bytes(int qpad, int halves = 1) { return halves * 4 * qpad * kRowBytesB + 2 * qpad * 4; }
 
 struct ScoreTcArgs {
     const uint32_t* codes;
@@ -128,25 +130,31 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "memory");
 }
 
-// DR is the dimension of the vectors (128 or 64); the operand layouts are those of d = 128 in both cases, with the
-// upper half of every key absent for d = 64 (its expander warps idle, the contractions stop after DR / 16 k-blocks).
+// DR is the dimension of the vectors.  The operand layouts are those of d = 128 in every case: for d = 64 the upper
+// half of every key is absent (its expander warps idle, the contractions stop after DR / 16 k-blocks); for d = 256 a
+// tile of keys passes through the operand buffers as two halves of 128 coordinates, one after the other, whose
+// contractions add up in the same accumulators (the prepared queries of a group then fill 64 KB, so that only one
+// group's are resident).
 template <int BITS, int QPAD, int DR>
 struct ScoreSmem {
+    static constexpr int kHalves = DR == 256 ? 2 : 1;
+    static constexpr int kBBufs = DR == 256 ? 1 : 2;
+    static constexpr int kPrepBytes = prep_group_bytes(QPAD, kHalves);
     static constexpr int kLutEntries = 1 << (2 * BITS);
     static constexpr int kLutBytes = kLutEntries * 32 * 8;
     static constexpr int kCodeRowBytes = DR * BITS / 8;
     static constexpr int kSignRowBytes = DR / 8;
     static constexpr int kNormOff = kTileKeys * (kCodeRowBytes + kSignRowBytes);   // norms, then residual norms, of the tile's keys
     static constexpr int kStageBytes = kNormOff + 2 * kTileKeys * 4;
-    static constexpr int kBBytes = (prep_group_bytes(QPAD) + 127) & ~127;
+    static constexpr int kBBytes = (kPrepBytes + 127) & ~127;
     static constexpr int kOutBytes = QPAD * kTileKeys * 4;          // one staged tile of scores [query][key]
-    static constexpr int kFixed = kLutBytes + 2 * kBBytes + 2 * kOutBytes + 512 + 128 + 128;
+    static constexpr int kFixed = kLutBytes + kBBufs * kBBytes + 2 * kOutBytes + 512 + 128 + 128;
     static constexpr int kFit = (227 * 1024 - kFixed) / kStageBytes;
     static constexpr int kStages = kFit < kMaxStages ? kFit : kMaxStages;
     static_assert(kStages >= 3, "key ring too short");
     static constexpr int off_lut = 0;
     static constexpr int off_b = off_lut + kLutBytes;
-    static constexpr int off_out = off_b + 2 * kBBytes;
+    static constexpr int off_out = off_b + kBBufs * kBBytes;
     static constexpr int off_ring = off_out + 2 * kOutBytes;
     static constexpr int off_misc = off_ring + kStages * kStageBytes;
     static constexpr int total = off_misc + 512 + 128;
@@ -157,9 +165,12 @@ struct ScoreSmem {
 template <int BITS, int QPAD, int DR, bool CAND>
 __global__ void __launch_bounds__(ScoreThreads<QPAD>::kThreads, 1)
 score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs a) {
-    static_assert(DR == 128 || DR == 64, "written for d = 128 and d = 64");
-    constexpr int kParts = DR / 32;              // expander warps per lane quarter that have data
+    static_assert(DR == 256 || DR == 128 || DR == 64, "written for d = 256, 128 and 64");
     using L = ScoreSmem<BITS, QPAD, DR>;
+    constexpr int kHalves = L::kHalves;          // passes of a key tile through the operand buffers
+    constexpr int kBBufs = L::kBBufs;
+    constexpr int kDH = DR / kHalves;            // coordinates per pass
+    constexpr int kParts = kDH / 32;             // expander warps per lane quarter that have data
     constexpr int kStages = L::kStages;
     constexpr int kThreads = ScoreThreads<QPAD>::kThreads;
     constexpr int kEpiPerRow = ScoreThreads<QPAD>::kEpiPerRow;
@@ -236,11 +247,10 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             for (int64_t t = t0; t < t1; ++t, ++kt) {
                 if (kt == a.tiles_per_group) { kt = 0; ++g; }
                 if (g != prev_g) {
-                    const int bb = (int)(gcount & 1);
-                    if (!mbar_wait(BAR(SB_B_EMPTY + bb), (uint32_t)((gcount >> 1) & 1) ^ 1u, abort_flag)) break;
-                    mbar_arrive_expect_tx(BAR(SB_B_FULL + bb), prep_group_bytes(QPAD));
-                    bulk_load(smem_base + L::off_b + bb * L::kBBytes, a.prep + g * prep_group_bytes(QPAD),
-                              prep_group_bytes(QPAD), BAR(SB_B_FULL + bb));
+                    const int bb = (kBBufs == 2 ? (int)(gcount & 1) : 0);
+                    if (!mbar_wait(BAR(SB_B_EMPTY + bb), (uint32_t)((kBBufs == 2 ? gcount >> 1 : gcount) & 1) ^ 1u, abort_flag)) break;
+                    mbar_arrive_expect_tx(BAR(SB_B_FULL + bb), L::kPrepBytes);
+                    bulk_load(smem_base + L::off_b + bb * L::kBBytes, a.prep + g * L::kPrepBytes, L::kPrepBytes, BAR(SB_B_FULL + bb));
                     prev_g = g;
                     ++gcount;
                 }
@@ -278,8 +288,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 // copies armed above may still be on their way into this block's shared memory
                 for (int64_t ii = issued > kStages ? issued - kStages : 0; ii < issued; ++ii)
                     mbar_drain(BAR(SB_K_FULL + (int)(ii % kStages)), (uint32_t)((ii / kStages) & 1));
-                for (int64_t gg = gcount > 2 ? gcount - 2 : 0; gg < gcount; ++gg)
-                    mbar_drain(BAR(SB_B_FULL + (int)(gg & 1)), (uint32_t)((gg >> 1) & 1));
+                for (int64_t gg = gcount > kBBufs ? gcount - kBBufs : 0; gg < gcount; ++gg)
+                    mbar_drain(BAR(SB_B_FULL + (kBBufs == 2 ? (int)(gg & 1) : 0)), (uint32_t)((kBBufs == 2 ? gg >> 1 : gg) & 1));
             }
         }
     } else if (warp == 1) {
@@ -292,51 +302,115 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             int bb = 0;
             int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
             uint64_t dq_hi = 0, dp_hi = 0;
-            for (int64_t t = t0; t < t1; ++t, ++kt) {
-                if (kt == a.tiles_per_group) { kt = 0; ++g; }
-                const int64_t i = t - t0;
-                const int b = (int)(i & 1);
-                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-                if (g != prev_g) {
-                    bb = (int)(gcount & 1);
-                    if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
-                    prev_g = g;
-                    ++gcount;
-                    const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
-                    dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
-                    dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
-                }
-                TQ_PROF_CODE(long long c0 = clock64();)
-                if (!warp_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
-                TQ_PROF_CODE(long long c1 = clock64();)
-                const int db = kDBufs == 2 ? b : 0;
-                const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
-                if (!warp_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
-                tc_fence_after();
-                TQ_PROF_CODE(long long c2 = clock64(); if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
-                const uint32_t base = tm + b * kBufCols;
-                const uint32_t d1 = tm + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
-                const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
-                if (elect_one()) {
-                    // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
-                    mma_ts_first(d1, base + kColHi, dq_hi, kIdesc2);
-                    mma_ts_acc(d1, base + kColLo, dq_hi, kIdesc1);
-                    mma_ts_first(d2, base + kColSg, dp_hi, kIdesc2);
-#pragma unroll 1
-                    for (int kb = 1; kb < DR / 16; ++kb) {
-                        // the start-address field counts 16-byte units: one k-block (two core matrices) further
-                        const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
-                        const uint64_t qh = dq_hi + step, ph = dp_hi + step;
-                        mma_ts_acc(d1, base + kColHi + kb * 8, qh, kIdesc2);
-                        mma_ts_acc(d1, base + kColLo + kb * 8, qh, kIdesc1);
-                        mma_ts_acc(d2, base + kColSg + kb * 8, ph, kIdesc2);
+            if constexpr (kHalves == 1) {
+                for (int64_t t = t0; t < t1; ++t, ++kt) {
+                    if (kt == a.tiles_per_group) { kt = 0; ++g; }
+                    const int64_t i = t - t0;
+                    const int b = (int)(i & 1);
+                    const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                    if (g != prev_g) {
+                        bb = (int)(gcount & 1);
+                        if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
+                        prev_g = g;
+                        ++gcount;
+                        const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
+                        dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
+                        dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
                     }
-                    mma_commit(BAR(SB_D_FULL + db));
-                    mma_commit(BAR(SB_A_EMPTY + b));
-                    if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+                    TQ_PROF_CODE(long long c0 = clock64();)
+                    if (!warp_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
+                    TQ_PROF_CODE(long long c1 = clock64();)
+                    const int db = kDBufs == 2 ? b : 0;
+                    const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
+                    if (!warp_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
+                    tc_fence_after();
+                    TQ_PROF_CODE(long long c2 = clock64(); if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
+                    const uint32_t base = tm + b * kBufCols;
+                    const uint32_t d1 = tm + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
+                    const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
+                    if (elect_one()) {
+                        // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
+                        mma_ts_first(d1, base + kColHi, dq_hi, kIdesc2);
+                        mma_ts_acc(d1, base + kColLo, dq_hi, kIdesc1);
+                        mma_ts_first(d2, base + kColSg, dp_hi, kIdesc2);
+    #pragma unroll 1
+                        for (int kb = 1; kb < DR / 16; ++kb) {
+                            // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                            const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                            const uint64_t qh = dq_hi + step, ph = dp_hi + step;
+                            mma_ts_acc(d1, base + kColHi + kb * 8, qh, kIdesc2);
+                            mma_ts_acc(d1, base + kColLo + kb * 8, qh, kIdesc1);
+                            mma_ts_acc(d2, base + kColSg + kb * 8, ph, kIdesc2);
+                        }
+                        mma_commit(BAR(SB_D_FULL + db));
+                        mma_commit(BAR(SB_A_EMPTY + b));
+                        if (last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+                    }
+                    __syncwarp();
+                    TQ_PROF_CODE(if (a.prof && blockIdx.x == 0 && lane == 0) a.prof[10] += clock64() - c2;)
                 }
-                __syncwarp();
-                TQ_PROF_CODE(if (a.prof && blockIdx.x == 0 && lane == 0) a.prof[10] += clock64() - c2;)
+            } else {
+                // d = 256: every tile passes through the operand buffers twice (coordinates 0..127, then 128..255)
+                bool gave_up = false;
+                for (int64_t t = t0; t < t1 && !gave_up; ++t, ++kt) {
+                    if (kt == a.tiles_per_group) { kt = 0; ++g; }
+                    const int64_t i = t - t0;
+                    if (g != prev_g) {
+                        bb = (kBBufs == 2 ? (int)(gcount & 1) : 0);
+                        if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((kBBufs == 2 ? gcount >> 1 : gcount) & 1), abort_flag)) break;
+                        prev_g = g;
+                        ++gcount;
+                        const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
+                        dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
+                        dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
+                    }
+                    const int db = kDBufs == 2 ? (int)(i & 1) : 0;
+                    const uint32_t dpar = kDBufs == 2 ? (uint32_t)((i >> 1) & 1) : (uint32_t)(i & 1);
+                    const uint32_t d1 = tm + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
+                    const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
+    #pragma unroll 1
+                    for (int h = 0; h < kHalves; ++h) {
+                        const int64_t j = i * kHalves + h;       // passes through the operand buffers since the start
+                        const int b = (int)(j & 1);
+                        const uint32_t par2 = (uint32_t)((j >> 1) & 1);
+                        TQ_PROF_CODE(long long c0 = clock64();)
+                        if (!warp_wait(BAR(SB_A_FULL + b), par2, abort_flag)) { gave_up = true; break; }
+                        TQ_PROF_CODE(long long c1 = clock64();)
+                        if (h == 0 && !warp_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) { gave_up = true; break; }
+                        tc_fence_after();
+                        TQ_PROF_CODE(long long c2 = clock64(); if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
+                        const uint32_t base = tm + b * kBufCols;
+                        if (elect_one()) {
+                            // the operand matrices of the second half of the coordinates follow those of the first
+                            const uint64_t half_step = (uint64_t)((uint32_t)h * 4u * QPAD * kRowBytesB >> 4);
+                            const uint64_t q0d = dq_hi + half_step, p0d = dp_hi + half_step;
+                            // q_hi and q_lo (p_hi and p_lo) are adjacent row blocks of one operand: N = 2*QPAD
+                            if (h == 0) {
+                                mma_ts_first(d1, base + kColHi, q0d, kIdesc2);
+                                mma_ts_acc(d1, base + kColLo, q0d, kIdesc1);
+                                mma_ts_first(d2, base + kColSg, p0d, kIdesc2);
+                            } else {
+                                mma_ts_acc(d1, base + kColHi, q0d, kIdesc2);
+                                mma_ts_acc(d1, base + kColLo, q0d, kIdesc1);
+                                mma_ts_acc(d2, base + kColSg, p0d, kIdesc2);
+                            }
+    #pragma unroll 1
+                            for (int kb = 1; kb < kDH / 16; ++kb) {
+                                // the start-address field counts 16-byte units: one k-block (two core matrices) further
+                                const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                                const uint64_t qh = q0d + step, ph = p0d + step;
+                                mma_ts_acc(d1, base + kColHi + kb * 8, qh, kIdesc2);
+                                mma_ts_acc(d1, base + kColLo + kb * 8, qh, kIdesc1);
+                                mma_ts_acc(d2, base + kColSg + kb * 8, ph, kIdesc2);
+                            }
+                            if (h == kHalves - 1) mma_commit(BAR(SB_D_FULL + db));
+                            mma_commit(BAR(SB_A_EMPTY + b));
+                            if (h == kHalves - 1 && last_of_group) mma_commit(BAR(SB_B_EMPTY + bb));
+                        }
+                        __syncwarp();
+                        TQ_PROF_CODE(if (a.prof && blockIdx.x == 0 && lane == 0) a.prof[10] += clock64() - c2;)
+                    }
+                }
             }
         }
     } else if (warp < kFirstEpiWarp) {
@@ -348,60 +422,124 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
         TQ_PROF_CODE(long long pc[5] = {0, 0, 0, 0, 0};)
-        for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
-            const int64_t i = t - t0;
-            const int s = (int)(i % kStages);
-            const int b = (int)(i & 1);
-            const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            TQ_PROF_CODE(long long c0 = clock64();)
-            bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
-            TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
-            uint32_t w[BITS + 1], sw;
-            {
-                const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
-                const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
-#pragma unroll
-                for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
-                w[BITS] = 0;
-                sw = fail ? 0u : ~sg[0];
+        if constexpr (kHalves == 1) {
+            for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
+                const int64_t i = t - t0;
+                const int s = (int)(i % kStages);
+                const int b = (int)(i & 1);
+                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                TQ_PROF_CODE(long long c0 = clock64();)
+                bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+                TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
+                uint32_t w[BITS + 1], sw;
+                {
+                    const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                    const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
+                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
+    #pragma unroll
+                    for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
+                    w[BITS] = 0;
+                    sw = fail ? 0u : ~sg[0];
+                }
+                __syncwarp();
+                if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
+                TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
+                // expand while the A buffer may still be in use; only the stores wait for it
+                uint32_t hi[16], lo[16], sg[16];
+    #pragma unroll
+                for (int p = 0; p < 16; ++p) {
+                    const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                    uint32_t e;
+                    if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                    else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                    const uint2 v = lut_lane[e * 32];
+                    hi[p] = v.x;
+                    lo[p] = v.y;
+                    // the sign word covers the 32 coordinates of this part; pair p: bits p, 16+p
+                    sg[p] = ((sw << (15 - p)) & 0x80008000u) | 0x3c003c00u;
+                }
+                TQ_PROF_CODE(c1 = clock64(); pc[4] += c1 - c0;)
+                if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+                TQ_PROF_CODE(c0 = clock64(); pc[2] += c0 - c1;)
+                tc_fence_after();
+                const uint32_t abase = tmem + lane_addr + b * kBufCols + part * 16;
+                tmem_st16(abase + kColHi, hi);
+                tmem_st16(abase + kColLo, lo);
+                tmem_st16(abase + kColSg, sg);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+                TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
+    #ifdef TQ_PROF
+                if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
+                    for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
+                    a.prof[6] = t1 - t0;
+                }
+    #endif
             }
-            __syncwarp();
-            if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
-            TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
-            // expand while the A buffer may still be in use; only the stores wait for it
-            uint32_t hi[16], lo[16], sg[16];
-#pragma unroll
-            for (int p = 0; p < 16; ++p) {
-                const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
-                uint32_t e;
-                if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
-                else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
-                const uint2 v = lut_lane[e * 32];
-                hi[p] = v.x;
-                lo[p] = v.y;
-                // the sign word covers the 32 coordinates of this part; pair p: bits p, 16+p
-                sg[p] = ((sw << (15 - p)) & 0x80008000u) | 0x3c003c00u;
+        } else {
+            for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
+                const int64_t i = t - t0;
+                const int s = (int)(i % kStages);
+                TQ_PROF_CODE(long long c0 = clock64();)
+                bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+                TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
+    #pragma unroll 1
+                for (int h = 0; h < kHalves; ++h) {
+                    const int64_t j = i * kHalves + h;       // passes through the operand buffers since the start
+                    const int b = (int)(j & 1);
+                    const uint32_t par2 = (uint32_t)((j >> 1) & 1);
+                    TQ_PROF_CODE(if (h) c1 = clock64();)
+                    uint32_t w[BITS + 1], sw;
+                    {
+                        const int chunk = h * 4 + part;      // this thread's 32 coordinates of the key
+                        const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                        const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
+                        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
+    #pragma unroll
+                        for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
+                        w[BITS] = 0;
+                        sw = fail ? 0u : ~sg[0];
+                    }
+                    __syncwarp();
+                    if (h == kHalves - 1 && lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
+                    TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
+                    // expand while the A buffer may still be in use; only the stores wait for it
+                    uint32_t hi[16], lo[16], sg[16];
+    #pragma unroll
+                    for (int p = 0; p < 16; ++p) {
+                        const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                        uint32_t e;
+                        if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                        else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                        const uint2 v = lut_lane[e * 32];
+                        hi[p] = v.x;
+                        lo[p] = v.y;
+                        // the sign word covers the 32 coordinates of this part; pair p: bits p, 16+p
+                        sg[p] = ((sw << (15 - p)) & 0x80008000u) | 0x3c003c00u;
+                    }
+                    TQ_PROF_CODE(c1 = clock64(); pc[4] += c1 - c0;)
+                    if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
+                    TQ_PROF_CODE(c0 = clock64(); pc[2] += c0 - c1;)
+                    tc_fence_after();
+                    const uint32_t abase = tmem + lane_addr + b * kBufCols + part * 16;
+                    tmem_st16(abase + kColHi, hi);
+                    tmem_st16(abase + kColLo, lo);
+                    tmem_st16(abase + kColSg, sg);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
+                    TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
+                }
+    #ifdef TQ_PROF
+                if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
+                    for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
+                    a.prof[6] = t1 - t0;
+                }
+    #endif
             }
-            TQ_PROF_CODE(c1 = clock64(); pc[4] += c1 - c0;)
-            if (!mbar_wait(BAR(SB_A_EMPTY + b), par2 ^ 1u, abort_flag)) fail = true;
-            TQ_PROF_CODE(c0 = clock64(); pc[2] += c0 - c1;)
-            tc_fence_after();
-            const uint32_t abase = tmem + lane_addr + b * kBufCols + part * 16;
-            tmem_st16(abase + kColHi, hi);
-            tmem_st16(abase + kColLo, lo);
-            tmem_st16(abase + kColSg, sg);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
-            TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
-#ifdef TQ_PROF
-            if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
-                for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
-                a.prof[6] = t1 - t0;
-            }
-#endif
         }
     } else {
         // ---- epilogue -----------------------------------------------------------------------------
@@ -454,9 +592,9 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         for (int64_t t = t0; t < t1; ++t, ++kt) {
             if (kt == a.tiles_per_group) { kt = 0; ++g; }
             const int64_t i = t - t0;
-            const int b = (int)(i & 1);
+            const int b = (int)(i & 1);        // staging buffer and accumulators of this tile
             const uint32_t par2 = (uint32_t)((i >> 1) & 1);
-            if (g != prev_g) { bb = (int)(gcount & 1); prev_g = g; ++gcount; }
+            if (g != prev_g) { bb = (kBBufs == 2 ? (int)(gcount & 1) : 0); prev_g = g; ++gcount; }
             const int64_t key = kt * a.tile_stride * kTileKeys + row;          // within this launch's key range
             const bool live = key < a.key_cnt;
             float nrm, arn;
@@ -485,7 +623,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             tc_fence_after();
             TQ_PROF_CODE(long long c1 = clock64();)
             const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
-            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + 4 * QPAD * kRowBytesB) + q16;
+            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + kHalves * 4 * QPAD * kRowBytesB) + q16;
             float sc[16];
             {
                 uint32_t ua[16], ub[16];
@@ -685,6 +823,63 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     const float e1 = okr ? ldexpf(1.f, 9 - ilogbf(mr)) : 1.f;
     const float e2 = oks ? ldexpf(1.f, 9 - ilogbf(ms)) : 1.f;
     const float rs = r * e1, ss = s * e2;
+    const __half rh = __float2half_rn(rs), sh = __float2half_rn(ss);
+    *m0 = rh;
+    *m1 = __float2half_rn(rs - __half2float(rh));
+    *m2 = sh;
+    *m3 = __float2half_rn(ss - __half2float(sh));
+    if (j == 0) ds[slot] = make_float2(1.f / (e1 * kCentScale), 1.f / e2);
+}
+
+// The same for d = 256: block 256 (thread = coordinate), the matrices read from global memory (they do not fit shared
+// memory), and the operands written as two halves of 128 coordinates, each in the layout of d = 128.
+__global__ void __launch_bounds__(256)
+score_prep256_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq, int qpad, unsigned char* __restrict__ prep) {
+    constexpr int kD = 256;
+    __shared__ float qs[kD];
+    __shared__ float red[2][8];
+    const int slot = blockIdx.x, g = blockIdx.y, j = threadIdx.x;
+    unsigned char* base = prep + (size_t)g * prep_group_bytes(qpad, 2);
+    const int jh = j & 127;
+    const size_t off = (size_t)(j >> 7) * (4 * (size_t)qpad * kRowBytesB) + (size_t)(slot / 8) * ((D / 8) * 128) +
+                       (size_t)(jh / 8) * 128 + (size_t)(slot % 8) * 16 + (size_t)(jh % 8) * 2;
+    __half* m0 = reinterpret_cast<__half*>(base + 0 * (size_t)qpad * kRowBytesB + off);
+    __half* m1 = reinterpret_cast<__half*>(base + 1 * (size_t)qpad * kRowBytesB + off);
+    __half* m2 = reinterpret_cast<__half*>(base + 2 * (size_t)qpad * kRowBytesB + off);
+    __half* m3 = reinterpret_cast<__half*>(base + 3 * (size_t)qpad * kRowBytesB + off);
+    float2* ds = reinterpret_cast<float2*>(base + 8 * (size_t)qpad * kRowBytesB);
+    if (slot >= nq) {
+        *m0 = *m1 = *m2 = *m3 = __float2half_rn(0.f);
+        if (j == 0) ds[slot] = make_float2(0.f, 0.f);
+        return;
+    }
+    qs[j] = q[((size_t)g * qpg + q0 + slot) * kD + j];
+    __syncthreads();
+    // four independent chains per matrix keep enough loads in flight; the order of the sums differs from the general
+    // kernel's, which the fp32 tolerance of the scores covers
+    float r[4] = {0.f, 0.f, 0.f, 0.f}, s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int k = 0; k < kD; k += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            r[u] = fmaf(qs[k + u], __ldg(p.Rt + (size_t)(k + u) * kD + j), r[u]);
+            s[u] = fmaf(qs[k + u], __ldg(p.St + (size_t)(k + u) * kD + j), s[u]);
+        }
+    }
+    const float rr = (r[0] + r[1]) + (r[2] + r[3]), sv = (s[0] + s[1]) + (s[2] + s[3]);
+    float mr = fabsf(rr), ms = fabsf(sv);
+    for (int o = 16; o > 0; o >>= 1) {
+        mr = fmaxf(mr, __shfl_xor_sync(0xffffffffu, mr, o));
+        ms = fmaxf(ms, __shfl_xor_sync(0xffffffffu, ms, o));
+    }
+    if ((j & 31) == 0) { red[0][j >> 5] = mr; red[1][j >> 5] = ms; }
+    __syncthreads();
+    mr = ms = 0.f;
+    for (int w = 0; w < 8; ++w) { mr = fmaxf(mr, red[0][w]); ms = fmaxf(ms, red[1][w]); }
+    const bool okr = mr > 0.f && mr < 3.0e38f, oks = ms > 0.f && ms < 3.0e38f;
+    const float e1 = okr ? ldexpf(1.f, 9 - ilogbf(mr)) : 1.f;
+    const float e2 = oks ? ldexpf(1.f, 9 - ilogbf(ms)) : 1.f;
+    const float rs = rr * e1, ss = sv * e2;
     const __half rh = __float2half_rn(rs), sh = __float2half_rn(ss);
     *m0 = rh;
     *m1 = __float2half_rn(rs - __half2float(rh));
@@ -895,7 +1090,7 @@ static ScoreTcPlan plan_score(int groups, int qpg, int64_t keys_per_group, int t
     if (s.nchunks < 1) s.nchunks = 1;
     s.segs_per_chunk = (s.chunk + kSegLen - 1) / kSegLen;
     s.lists_per_group = s.nchunks * s.segs_per_chunk;
-    s.prep_bytes = ((size_t)groups * prep_group_bytes(32) + 255) & ~size_t(255);
+    s.prep_bytes = ((size_t)groups * prep_group_bytes(32, 2) + 255) & ~size_t(255);   // room for d = 256 at every d
     s.part_bytes = topk > 0 ? (((size_t)groups * s.lists_per_group * qpg * topk * 8) + 255) & ~size_t(255) : 0;
     s.matrix_bytes = (topk > 0 && need_scratch_matrix) ? (((size_t)groups * qpg * s.chunk * 4) + 255) & ~size_t(255) : 0;
     s.off_prep = 0;
@@ -922,7 +1117,7 @@ static CandPlan plan_candidates(int groups, int qpg, int64_t keys_per_group, int
     s.nchunks = (keys_per_group + s.chunk - 1) / s.chunk;
     s.cand_cap = s.chunk;
     s.lists = (int64_t)groups * qpg;
-    s.off_thr = pad((size_t)groups * prep_group_bytes(32));
+    s.off_thr = pad((size_t)groups * prep_group_bytes(32, 2));
     s.off_cnt = s.off_thr + pad((size_t)s.lists * 4);
     s.off_best = s.off_cnt + pad((size_t)s.lists * 4);
     s.off_cand = s.off_best + pad((size_t)s.lists * (topk > 0 ? topk : 1) * 8);
@@ -975,8 +1170,12 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
         for (int q0 = 0; q0 < qpg; q0 += 32) {
             const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
             const int qpad = nq <= 16 ? 16 : 32;
-            TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
-            score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
+            if (p->dev.d == 256) {
+                score_prep256_kernel<<<dim3(qpad, groups), 256, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
+            } else {
+                TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
+                score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
+            }
             TQ_CUDA_TRY(cudaGetLastError());
             ScoreTcArgs a{};
             a.codes = codes; a.signs = signs; a.rnorms = rnorms; a.norms = norms;
@@ -1021,6 +1220,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
 #define TQ_SC(B)                                                                                             \
     case B:                                                                                                  \
         if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(map, a, grid, st) : launch_score<B, 32, 64>(map, a, grid, st);   \
+        else if (p->dev.d == 256) r = qpad == 16 ? launch_score<B, 16, 256>(map, a, grid, st) : launch_score<B, 32, 256>(map, a, grid, st);   \
         else r = qpad == 16 ? launch_score<B, 16, 128>(map, a, grid, st) : launch_score<B, 32, 128>(map, a, grid, st);                \
         break;
             switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }

@@ -165,6 +165,85 @@ def test_topk_without_matrix_for_query_groups(tg, kpg):
         assert torch.equal(top_i[r], want_i[r] + (r // qpg) * kpg + 5)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_d256_query_groups_on_the_tensor_core_kernel_against_oracle(tg, bits):
+    """d = 256 passes every tile of keys through the operand buffers in two halves of 128 coordinates, and only one
+    group's prepared queries are resident at a time.  Three groups of 1,000 keys (ragged last tile, a change of group
+    inside a block's tile range), five queries per group, against the oracle's one-query-at-a-time scores; then the
+    top-k of the same call against the matrix."""
+    d, groups, kpg, qpg = 256, 3, 1000, 5
+    rng = np.random.default_rng(20290 + bits)
+    keys = (rng.standard_normal((groups, kpg, d)) * rng.uniform(0.1, 5.0, (groups, kpg, 1))).astype(np.float32)
+    queries = rng.standard_normal((groups, qpg, d)).astype(np.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    prod.set_kernel_path("tensor")
+    pp = _oracle_params(prod)
+    want = orc.prod_quantize(pp, keys.reshape(-1, d))
+    ref_enc = tg.TurboQuantProdEncoding(indices=want[0], qjl=want[1], residual_norms=want[2], norms=want[3],
+                                        prefix_shape=(groups * kpg,))
+    got = prod.attention_scores(queries.reshape(-1, d), ref_enc, groups=groups)
+    assert got.shape == (groups * qpg, kpg)
+    for g in range(groups):
+        sl = slice(g * kpg, (g + 1) * kpg)
+        part = (want[0][sl], want[1][sl], want[2][sl], want[3][sl], (kpg,))
+        ref = np.stack([orc.prod_attention_score(pp, q, *part) for q in queries[g]])
+        err = parity.max_score_err(got[g * qpg:(g + 1) * qpg], ref, np.linalg.norm(queries[g], axis=1)[:, None],
+                                   want[3][sl][None, :], d)
+        assert err <= REL_SCORE, (g, err)
+    k = 7
+    top_s, top_i = prod.attention_scores(queries.reshape(-1, d), ref_enc, groups=groups, topk=k, index_base=3)
+    for r in range(groups * qpg):
+        order = np.argsort(-got[r], kind="stable")[:k]
+        assert np.array_equal(top_s[r], got[r][order])
+        assert np.array_equal(top_i[r], order + (r // qpg) * kpg + 3)
+
+
+@pytest.mark.parametrize("bits,n,nq,k", [(4, 70000, 40, 100), (2, 38405, 32, 300), (1, 257, 3, 500), (3, 20000, 16, 64)])
+def test_d256_topk_equals_sorted_matrix_and_matches_the_exact_kernels(tg, bits, n, nq, k):
+    """d = 256 through the default dispatch (tensor-core kernel from two queries on): the score matrix within the
+    fp32 tolerance of the kernels that accumulate in the reference's order, the top-k equal to a stable sort of the
+    matrix (ragged key counts, two passes of queries, k above 128 and above the number of keys)."""
+    import torch
+    d = 256
+    gen = torch.Generator(device="cuda").manual_seed(20291 + n)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    enc = prod.quantize(x)
+    mat = prod.attention_scores(q, enc)
+    prod.set_kernel_path("exact")
+    ref = prod.attention_scores(q, enc)
+    prod.set_kernel_path("auto")
+    norms = tg.packed_buffers(enc)["norms"]
+    scale = q.norm(dim=1)[:, None] * norms[None, :] / d ** 0.5
+    assert float(((mat - ref).abs() / scale).max()) <= REL_SCORE
+    top_s, top_i = prod.attention_scores(q, enc, topk=k)
+    kk = min(k, n)
+    want_s, want_i = _sorted_topk(mat, kk)
+    assert torch.equal(top_s[:, :kk], want_s)
+    assert torch.equal(top_i[:, :kk], want_i)
+    if k > n:
+        assert bool((top_i[:, n:] == -1).all()) and bool(torch.isinf(top_s[:, n:]).all())
+
+
+def test_d256_topk_without_matrix_over_several_chunks(tg):
+    """4,200,003 keys of d = 256 in one group: top-64 from the candidate lists (three chunks, the last ragged) equals
+    a stable sort of the full matrix."""
+    import torch
+    d, n, nq, k = 256, 4_200_003, 5, 64
+    gen = torch.Generator(device="cuda").manual_seed(20292)
+    prod = tg.TurboQuantProd(d, 2, seed=2026)
+    x = torch.randn((n, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    enc = prod.quantize(x)
+    del x
+    mat = prod.attention_scores(q, enc)
+    top_s, top_i = prod.attention_scores(q, enc, topk=k, index_base=11)
+    want_s, want_i = _sorted_topk(mat, k)
+    assert torch.equal(top_s, want_s)
+    assert torch.equal(top_i, want_i + 11)
+
+
 def test_sharded_index_matches_single_index(tg):
     """ShardedKeyIndex filled chunk by chunk (device and host chunks) and searched, and two shards of the same
     keys searched one after the other and merged with tq_topk_merge as the ranks of a job would after the

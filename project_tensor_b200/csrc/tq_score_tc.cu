@@ -38,10 +38,12 @@ using namespace tqtopk;
 
 constexpr int D = 128;
 constexpr int kTileKeys = 128;
-// Warps: bulk copy, MMA, 16 expanders (one thread per quarter key), then 4 epilogue warps per 16 queries of the pass.
+// Warps: bulk copy, MMA, 16 expanders (one thread per quarter key), then 4 epilogue warps per 16 queries of the pass
+// (per 32 queries in a pass of 64: a block is limited to 32 warps, so every epilogue thread takes two blocks of 16).
 constexpr int kExpWarps = 16;
 template <int QPAD> struct ScoreThreads {
-    static constexpr int kEpiPerRow = QPAD / 16;
+    static constexpr int kQBlocks = QPAD == 64 ? 2 : 1;      // blocks of 16 queries per epilogue thread
+    static constexpr int kEpiPerRow = QPAD / (16 * kQBlocks);
     static constexpr int kEpiThreads = 4 * kEpiPerRow * 32;
     static constexpr int kThreads = (2 + kExpWarps) * 32 + kEpiThreads;
 };
@@ -137,8 +139,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // group's are resident).
 template <int BITS, int QPAD, int DR>
 struct ScoreSmem {
+    static_assert(QPAD <= 32 || DR <= 128, "a pass of 64 queries exists for d <= 128");
     static constexpr int kHalves = DR == 256 ? 2 : 1;
-    static constexpr int kBBufs = DR == 256 ? 1 : 2;
+    static constexpr int kBBufs = (DR == 256 || QPAD == 64) ? 1 : 2;     // 64 KB of prepared queries: one group resident
     static constexpr int kPrepBytes = prep_group_bytes(QPAD, kHalves);
     static constexpr int kLutEntries = 1 << (2 * BITS);
     static constexpr int kLutBytes = kLutEntries * 32 * 8;
@@ -237,8 +240,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
     // and D2 = [Sg p_hi | Sg p_lo], 2*QPAD columns each; double-buffered when they fit (QPAD = 16).
     constexpr uint32_t kBufCols = 192;
     constexpr uint32_t kColHi = 0, kColLo = 64, kColSg = 128;
+    // A pass of 64 queries has 256 accumulator columns and room for one A buffer only, so the expanders' stores wait for
+    // the contractions of the tile before.  (The other way to fit 64 queries -- both A buffers, the hi and lo products
+    // added inside 128 accumulator columns by 40 instructions of N = 64 per tile -- measured the same: 173 against 176 us
+    // per 64 x 1,048,576 scores, 245 against 258 us per 1,048,576 keys in candidate mode.)
+    constexpr int kABufs = QPAD == 64 ? 1 : 2;
     constexpr int kDBufs = QPAD == 16 ? 2 : 1;
-    constexpr uint32_t kColD = 384, kDCols = 4 * QPAD;
+    constexpr uint32_t kColD = kABufs * kBufCols, kDCols = 4 * QPAD;
+    constexpr int kQBlocks = ScoreThreads<QPAD>::kQBlocks;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -306,11 +315,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 for (int64_t t = t0; t < t1; ++t, ++kt) {
                     if (kt == a.tiles_per_group) { kt = 0; ++g; }
                     const int64_t i = t - t0;
-                    const int b = (int)(i & 1);
-                    const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                    const int b = kABufs == 2 ? (int)(i & 1) : 0;
+                    const uint32_t par2 = (uint32_t)((kABufs == 2 ? i >> 1 : i) & 1);
                     if (g != prev_g) {
-                        bb = (int)(gcount & 1);
-                        if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((gcount >> 1) & 1), abort_flag)) break;
+                        bb = (kBBufs == 2 ? (int)(gcount & 1) : 0);
+                        if (!warp_wait(BAR(SB_B_FULL + bb), (uint32_t)((kBBufs == 2 ? gcount >> 1 : gcount) & 1), abort_flag)) break;
                         prev_g = g;
                         ++gcount;
                         const uint32_t bq = smem_base + L::off_b + bb * L::kBBytes;
@@ -320,8 +329,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     TQ_PROF_CODE(long long c0 = clock64();)
                     if (!warp_wait(BAR(SB_A_FULL + b), par2, abort_flag)) break;
                     TQ_PROF_CODE(long long c1 = clock64();)
-                    const int db = kDBufs == 2 ? b : 0;
-                    const uint32_t dpar = kDBufs == 2 ? par2 : (uint32_t)(i & 1);
+                    const int db = kDBufs == 2 ? (int)(i & 1) : 0;
+                    const uint32_t dpar = (uint32_t)((kDBufs == 2 ? i >> 1 : i) & 1);
                     if (!warp_wait(BAR(SB_D_EMPTY + db), dpar ^ 1u, abort_flag)) break;
                     tc_fence_after();
                     TQ_PROF_CODE(long long c2 = clock64(); if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[8] += c1 - c0; a.prof[9] += c2 - c1; })
@@ -333,7 +342,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                         mma_ts_first(d1, base + kColHi, dq_hi, kIdesc2);
                         mma_ts_acc(d1, base + kColLo, dq_hi, kIdesc1);
                         mma_ts_first(d2, base + kColSg, dp_hi, kIdesc2);
-    #pragma unroll 1
+#pragma unroll 1
                         for (int kb = 1; kb < DR / 16; ++kb) {
                             // the start-address field counts 16-byte units: one k-block (two core matrices) further
                             const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
@@ -368,7 +377,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     const uint32_t dpar = kDBufs == 2 ? (uint32_t)((i >> 1) & 1) : (uint32_t)(i & 1);
                     const uint32_t d1 = tm + kColD + db * kDCols, d2 = d1 + 2 * QPAD;
                     const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
-    #pragma unroll 1
+#pragma unroll 1
                     for (int h = 0; h < kHalves; ++h) {
                         const int64_t j = i * kHalves + h;       // passes through the operand buffers since the start
                         const int b = (int)(j & 1);
@@ -394,7 +403,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                                 mma_ts_acc(d1, base + kColLo, q0d, kIdesc1);
                                 mma_ts_acc(d2, base + kColSg, p0d, kIdesc2);
                             }
-    #pragma unroll 1
+#pragma unroll 1
                             for (int kb = 1; kb < kDH / 16; ++kb) {
                                 // the start-address field counts 16-byte units: one k-block (two core matrices) further
                                 const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
@@ -426,8 +435,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
                 const int64_t i = t - t0;
                 const int s = (int)(i % kStages);
-                const int b = (int)(i & 1);
-                const uint32_t par2 = (uint32_t)((i >> 1) & 1);
+                const int b = kABufs == 2 ? (int)(i & 1) : 0;
+                const uint32_t par2 = (uint32_t)((kABufs == 2 ? i >> 1 : i) & 1);
                 TQ_PROF_CODE(long long c0 = clock64();)
                 bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
                 TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
@@ -436,7 +445,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
                     const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
                     const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
-    #pragma unroll
+#pragma unroll
                     for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
                     w[BITS] = 0;
                     sw = fail ? 0u : ~sg[0];
@@ -446,7 +455,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
                 // expand while the A buffer may still be in use; only the stores wait for it
                 uint32_t hi[16], lo[16], sg[16];
-    #pragma unroll
+#pragma unroll
                 for (int p = 0; p < 16; ++p) {
                     const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
                     uint32_t e;
@@ -471,12 +480,12 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
                 TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
-    #ifdef TQ_PROF
+#ifdef TQ_PROF
                 if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
                     for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
                     a.prof[6] = t1 - t0;
                 }
-    #endif
+#endif
             }
         } else {
             for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
@@ -485,7 +494,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 TQ_PROF_CODE(long long c0 = clock64();)
                 bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
                 TQ_PROF_CODE(long long c1 = clock64(); pc[0] += c1 - c0;)
-    #pragma unroll 1
+#pragma unroll 1
                 for (int h = 0; h < kHalves; ++h) {
                     const int64_t j = i * kHalves + h;       // passes through the operand buffers since the start
                     const int b = (int)(j & 1);
@@ -497,7 +506,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                         const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
                         const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
                         const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
-    #pragma unroll
+#pragma unroll
                         for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
                         w[BITS] = 0;
                         sw = fail ? 0u : ~sg[0];
@@ -507,7 +516,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
                     // expand while the A buffer may still be in use; only the stores wait for it
                     uint32_t hi[16], lo[16], sg[16];
-    #pragma unroll
+#pragma unroll
                     for (int p = 0; p < 16; ++p) {
                         const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
                         uint32_t e;
@@ -533,12 +542,12 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     if (lane == 0) mbar_arrive(BAR(SB_A_FULL + b));
                     TQ_PROF_CODE(c1 = clock64(); pc[3] += c1 - c0;)
                 }
-    #ifdef TQ_PROF
+#ifdef TQ_PROF
                 if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstExpWarp * 32 && t + 1 == t1) {
                     for (int k = 0; k < 5; ++k) a.prof[k] = pc[k];
                     a.prof[6] = t1 - t0;
                 }
-    #endif
+#endif
             }
         }
     } else {
@@ -546,7 +555,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
+        const int q16_0 = ((warp - kFirstEpiWarp) >> 2) * 16 * kQBlocks;   // this thread's first query of the pass (16 per block)
         const bool store_leader = threadIdx.x == kFirstEpiWarp * 32;
         int64_t prev_g = -1, gcount = 0;
         int bb = 0;
@@ -561,15 +570,15 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             r_out = live_n ? __ldg(a.rnorms + grow_n) : 0.f;
         };
         // candidate mode: thresholds of the current group, and in place of the score tile buffers a staging list of
-        // survivors (keys, then the numbers of their lists) and 16 x 32 parked scores per warp
+        // survivors (keys, then the numbers of their lists) and 16 (32 in a pass of 64 queries) x 32 parked scores per warp
         int64_t thr_g = -1;
         float* thr_s = reinterpret_cast<float*>(bars + SB_COUNT + 2);   // [QPAD]
         int* st_count = reinterpret_cast<int*>(thr_s + QPAD);
-        constexpr int kStageCap = (2 * L::kOutBytes - 4 * kEpiPerRow * 16 * 32 * 4) / 12 / 128 * 128;    // 1,280 entries (32 queries), 640 (16)
+        constexpr int kStageCap = (2 * L::kOutBytes - 4 * kEpiPerRow * 16 * kQBlocks * 32 * 4) / 12 / 128 * 128;    // 1,280 entries (32 queries), 640 (16), 2,688 (64)
         static_assert(kStageCap >= 512, "candidate staging must fit the score tile buffers");
         unsigned long long* st_keys = reinterpret_cast<unsigned long long*>(smem + L::off_out);
         uint32_t* st_list = reinterpret_cast<uint32_t*>(smem + L::off_out + kStageCap * 8);
-        float* warp_scores = reinterpret_cast<float*>(smem + L::off_out + kStageCap * 12) + (warp - kFirstEpiWarp) * 16 * 32;
+        float* warp_scores = reinterpret_cast<float*>(smem + L::off_out + kStageCap * 12) + (warp - kFirstEpiWarp) * 16 * kQBlocks * 32;
         const int epi_t = threadIdx.x - kFirstEpiWarp * 32;
         auto flush_staging = [&]() {      // all epilogue threads, after a barrier that made every append visible
             int n = *st_count;
@@ -622,114 +631,135 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             const bool got = mbar_wait(BAR(SB_D_FULL + db), dpar, abort_flag);   // false: some role gave up
             tc_fence_after();
             TQ_PROF_CODE(long long c1 = clock64();)
-            const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
-            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + kHalves * 4 * QPAD * kRowBytesB) + q16;
-            float sc[16];
-            {
-                uint32_t ua[16], ub[16];
-                tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
-                tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
-                tmem_wait_ld();
+            TQ_PROF_CODE(long long c2 = c1;)
+            // a pass of 64 queries: two blocks of 16 per thread, one after the other (everything that happens once per
+            // tile -- the barriers of the staging buffers, the release of the accumulators -- hangs on the first or last)
+            const uint32_t rowid = (uint32_t)(g * a.keys_per_group + a.key_off + key);   // row of the key arrays (candidate mode)
+            uint32_t pm = 0;      // candidate mode: bit k = this key's score for query q16_0 + k reaches the query's threshold
+#pragma unroll 1
+            for (int qb = 0; qb < kQBlocks; ++qb) {
+                const int q16 = q16_0 + qb * 16;
+                const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
+                const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + kHalves * 4 * QPAD * kRowBytesB) + q16;
+                float sc[16];
+                {
+                    uint32_t ua[16], ub[16];
+                    tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
+                    tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
+                    tmem_wait_ld();
 #pragma unroll
-                for (int k = 0; k < 16; ++k) sc[k] = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].x;
-                tmem_ld16(dbase + 2 * QPAD, ua);       // Sg p_hi
-                tmem_ld16(dbase + 3 * QPAD, ub);       // Sg p_lo
-                tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
-#pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    const float s2 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].y;
-                    sc[k] = nrm * fmaf(arn, s2, sc[k]);
-                }
-            }
-            TQ_PROF_CODE(long long c2 = clock64();)
-            // After a give-up (`got` false) nothing is written for the tile, but every epilogue warp still walks through the
-            // named barriers below: the warps learn of the give-up at different tiles, and a barrier that some of them
-            // skipped would never complete.
-            if (CAND) {
-                if (g != thr_g) {      // thresholds of this group's queries (constant during the launch) into shared memory
-                    thr_g = g;
-                    bar_sync(kEpiBarrier, kEpiThreads);      // everybody is done with the previous group's
-                    if (epi_t < QPAD) thr_s[epi_t] = epi_t < a.nq ? __ldg(a.thr + g * a.qpg_total + a.q0 + epi_t) : CUDART_INF_F;
-                    bar_sync(kEpiBarrier, kEpiThreads);
-                }
-                const uint32_t rowid = (uint32_t)(g * a.keys_per_group + a.key_off + key);   // row of the key arrays
-                const int64_t q_first = g * a.qpg_total + a.q0 + q16;
-                if (a.fused == 2) {
-                    // The sampled pass (thresholds at -inf, every score is a candidate): the slot of a score is known
-                    // without a counter (tile of the sample x 128 + row); the host presets the lists' lengths.
-                    // A key beyond the end of the group leaves an empty slot.
-#pragma unroll
-                    for (int k = 0; k < 16; ++k)
-                        if (q16 + k < a.nq)
-                            a.cand[(q_first + k) * a.cand_cap + kt * kTileKeys + row] = live && got ? make_key(sc[k], rowid) : 0ull;
-                } else {
-                    // This thread's 16 scores against their thresholds: a mask, and the scores parked in shared memory
-                    // so that the loop below can pick them by a run-time index.  The loop runs once per query that has a
-                    // survivor among the warp's 32 keys and is kept rolled: the candidate path must stay small, this
-                    // kernel lives on its instruction cache (the same logic unrolled over the 16 queries doubled the
-                    // kernel's time without a single survivor).
-                    float* mine = warp_scores + lane;
-                    uint32_t pm = 0;
+                    for (int k = 0; k < 16; ++k) sc[k] = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].x;
+                    tmem_ld16(dbase + 2 * QPAD, ua);       // Sg p_hi
+                    tmem_ld16(dbase + 3 * QPAD, ub);       // Sg p_lo
+                    tmem_wait_ld();
+                    if (qb == kQBlocks - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
+                    }
 #pragma unroll
                     for (int k = 0; k < 16; ++k) {
-                        pm |= (live && got && sc[k] >= thr_s[q16 + k]) ? (1u << k) : 0u;
-                        mine[k * 32] = sc[k];
+                        const float s2 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].y;
+                        sc[k] = nrm * fmaf(arn, s2, sc[k]);
                     }
-                    // Survivors go to a staging list in shared memory (a global counter update per survivor would put a
-                    // trip to L2 on this warp's path every tile); the list is emptied into the global lists, all its
-                    // entries at once, when it is half full (looked at every eighth tile: the barrier couples the warps).
-                    if ((i & 7) == 0 && bar_or(kEpiBarrier, kEpiThreads, *st_count > kStageCap / 2)) flush_staging();
-                    uint32_t wm = __reduce_or_sync(0xffffffffu, pm);
-#pragma unroll 1
-                    while (wm != 0u) {
-                        const int k = __ffs(wm) - 1;
-                        wm &= wm - 1u;
-                        const bool pass = (pm >> k) & 1u;
-                        const uint32_t votes = __ballot_sync(0xffffffffu, pass);
-                        const int leader = __ffs(votes) - 1;
-                        uint32_t base = 0;
-                        if (lane == leader) base = (uint32_t)atomicAdd(st_count, (int)__popc(votes));
-                        base = __shfl_sync(0xffffffffu, base, leader);
-                        if (pass) {
-                            const uint32_t pos = base + __popc(votes & ((1u << lane) - 1u));
-                            const unsigned long long ck = make_key(mine[k * 32], rowid);
-                            if (pos < (uint32_t)kStageCap) {
-                                st_keys[pos] = ck;
-                                st_list[pos] = (uint32_t)(q_first + k);
-                            } else {      // the staging list is full (nearly every score passes): straight to the global list
-                                const int64_t gp = (int64_t)atomicAdd(a.cnt + q_first + k, 1u);
-                                if (gp < a.cand_cap) a.cand[(q_first + k) * a.cand_cap + gp] = ck;
-                            }
+                }
+                TQ_PROF_CODE(if (qb == 0) c2 = clock64();)
+                // After a give-up (`got` false) nothing is written for the tile, but every epilogue warp still walks through the
+                // named barriers below: the warps learn of the give-up at different tiles, and a barrier that some of them
+                // skipped would never complete.
+                if (CAND) {
+                    if (qb == 0 && g != thr_g) {      // thresholds of this group's queries (constant during the launch) into shared memory
+                        thr_g = g;
+                        bar_sync(kEpiBarrier, kEpiThreads);      // everybody is done with the previous group's
+                        if (epi_t < QPAD) thr_s[epi_t] = epi_t < a.nq ? __ldg(a.thr + g * a.qpg_total + a.q0 + epi_t) : CUDART_INF_F;
+                        bar_sync(kEpiBarrier, kEpiThreads);
+                    }
+                    const int64_t q_first = g * a.qpg_total + a.q0 + q16;
+                    if (a.fused == 2) {
+                        // The sampled pass (thresholds at -inf, every score is a candidate): the slot of a score is known
+                        // without a counter (tile of the sample x 128 + row); the host presets the lists' lengths.
+                        // A key beyond the end of the group leaves an empty slot.
+#pragma unroll
+                        for (int k = 0; k < 16; ++k)
+                            if (q16 + k < a.nq)
+                                a.cand[(q_first + k) * a.cand_cap + kt * kTileKeys + row] = live && got ? make_key(sc[k], rowid) : 0ull;
+                    } else {
+                        // This thread's scores against their thresholds: a mask, and -- when any of the warp's 32 keys has
+                        // a survivor in this block of queries -- the scores parked in shared memory, so that the loop behind
+                        // the blocks can pick them by a run-time index.
+                        float* mine = warp_scores + lane + qb * 16 * 32;
+                        uint32_t m = 0;
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) m |= (live && got && sc[k] >= thr_s[q16 + k]) ? (1u << k) : 0u;
+                        if (__any_sync(0xffffffffu, m != 0u)) {
+#pragma unroll
+                            for (int k = 0; k < 16; ++k) mine[k * 32] = sc[k];
+                        }
+                        pm |= m << (qb * 16);
+                    }
+                } else if (a.tile_store) {
+                    // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
+                    // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
+                    // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
+                    // i - 2 must have read its buffer before tile i overwrites it.  (A box per warp -- 32 keys x 16 queries from
+                    // a slice of its own, no barrier between the epilogue warps -- was slower: 115 against 109 us.)
+                    float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
+                    if (qb == 0) {
+                        if (store_leader) bulk_wait_read<1>();
+                        bar_sync(kEpiBarrier, kEpiThreads);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
+                    if (qb == kQBlocks - 1) {
+                        fence_async_smem();
+                        bar_sync(kEpiBarrier, kEpiThreads);
+                        if (store_leader && got) {
+                            tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
+                            bulk_commit();
+                        }
+                    }
+                } else if (live && got) {
+                    float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        if (q16 + k < a.nq) {
+                            __stcs(out, sc[k]);
+                            out += a.out_row_stride;
                         }
                     }
                 }
-            } else if (a.tile_store) {
-                // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
-                // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
-                // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
-                // i - 2 must have read its buffer before tile i overwrites it.  (A box per warp -- 32 keys x 16 queries from
-                // a slice of its own, no barrier between the epilogue warps -- was slower: 115 against 109 us.)
-                float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
-                if (store_leader) bulk_wait_read<1>();
-                bar_sync(kEpiBarrier, kEpiThreads);
-#pragma unroll
-                for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
-                fence_async_smem();
-                bar_sync(kEpiBarrier, kEpiThreads);
-                if (store_leader && got) {
-                    tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
-                    bulk_commit();
-                }
-            } else if (live && got) {
-                float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
-#pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    if (q16 + k < a.nq) {
-                        __stcs(out, sc[k]);
-                        out += a.out_row_stride;
+            }
+            if (CAND && a.fused != 2) {
+                // The loop runs once per query that has a survivor among the warp's 32 keys and is kept rolled: the candidate
+                // path must stay small, this kernel lives on its instruction cache (the same logic unrolled over the
+                // queries doubled the kernel's time without a single survivor).
+                // Survivors go to a staging list in shared memory (a global counter update per survivor would put a
+                // trip to L2 on this warp's path every tile); the list is emptied into the global lists, all its
+                // entries at once, when it is half full (looked at every eighth tile: the barrier couples the warps).
+                const float* mine = warp_scores + lane;
+                const int64_t q_first = g * a.qpg_total + a.q0 + q16_0;
+                if ((i & 7) == 0 && bar_or(kEpiBarrier, kEpiThreads, *st_count > kStageCap / 2)) flush_staging();
+                uint32_t wm = __reduce_or_sync(0xffffffffu, pm);
+#pragma unroll 1
+                while (wm != 0u) {
+                    const int k = __ffs(wm) - 1;
+                    wm &= wm - 1u;
+                    const bool pass = (pm >> k) & 1u;
+                    const uint32_t votes = __ballot_sync(0xffffffffu, pass);
+                    const int leader = __ffs(votes) - 1;
+                    uint32_t base = 0;
+                    if (lane == leader) base = (uint32_t)atomicAdd(st_count, (int)__popc(votes));
+                    base = __shfl_sync(0xffffffffu, base, leader);
+                    if (pass) {
+                        const uint32_t pos = base + __popc(votes & ((1u << lane) - 1u));
+                        const unsigned long long ck = make_key(mine[k * 32], rowid);
+                        if (pos < (uint32_t)kStageCap) {
+                            st_keys[pos] = ck;
+                            st_list[pos] = (uint32_t)(q_first + k);
+                        } else {      // the staging list is full (nearly every score passes): straight to the global list
+                            const int64_t gp = (int64_t)atomicAdd(a.cnt + q_first + k, 1u);
+                            if (gp < a.cand_cap) a.cand[(q_first + k) * a.cand_cap + gp] = ck;
+                        }
                     }
                 }
             }
@@ -1071,10 +1101,17 @@ int launch_score(const CUtensorMap& map, const ScoreTcArgs& args, int grid, cuda
 
 }  // namespace
 
+#ifndef TQ_SCORE_PASS
+#define TQ_SCORE_PASS 64     // queries per scoring launch at d <= 128 (32: the measurement build without passes of 64)
+#endif
+
 // ---- host-side planning ---------------------------------------------------------------------------
 constexpr int64_t kChunkKeys = 1 << 22;     // keys per group scored into scratch at a time when only top-k is wanted
                                             // (2^20: 221 us per 1M keys and 32 queries, 2^21: 198, 2^23: 185; scratch 16 B x queries per key)
 constexpr int64_t kSegLen = 65536;          // scores per selection block (top-100 call at 1,048,576 keys: 32,768 -> 214 us, 65,536 -> 204, 131,072 -> 213, 262,144 -> 241)
+
+// prepared queries of one group in the scratch block: the largest of the passes (64 queries; 32 queries of d = 256)
+constexpr size_t kPrepGroupMax = prep_group_bytes(64, 1) > prep_group_bytes(32, 2) ? prep_group_bytes(64, 1) : prep_group_bytes(32, 2);
 
 struct ScoreTcPlan {
     int64_t chunk, nchunks, segs_per_chunk, lists_per_group;
@@ -1090,7 +1127,7 @@ static ScoreTcPlan plan_score(int groups, int qpg, int64_t keys_per_group, int t
     if (s.nchunks < 1) s.nchunks = 1;
     s.segs_per_chunk = (s.chunk + kSegLen - 1) / kSegLen;
     s.lists_per_group = s.nchunks * s.segs_per_chunk;
-    s.prep_bytes = ((size_t)groups * prep_group_bytes(32, 2) + 255) & ~size_t(255);   // room for d = 256 at every d
+    s.prep_bytes = ((size_t)groups * kPrepGroupMax + 255) & ~size_t(255);
     s.part_bytes = topk > 0 ? (((size_t)groups * s.lists_per_group * qpg * topk * 8) + 255) & ~size_t(255) : 0;
     s.matrix_bytes = (topk > 0 && need_scratch_matrix) ? (((size_t)groups * qpg * s.chunk * 4) + 255) & ~size_t(255) : 0;
     s.off_prep = 0;
@@ -1117,7 +1154,7 @@ static CandPlan plan_candidates(int groups, int qpg, int64_t keys_per_group, int
     s.nchunks = (keys_per_group + s.chunk - 1) / s.chunk;
     s.cand_cap = s.chunk;
     s.lists = (int64_t)groups * qpg;
-    s.off_thr = pad((size_t)groups * prep_group_bytes(32, 2));
+    s.off_thr = pad((size_t)groups * kPrepGroupMax);
     s.off_cnt = s.off_thr + pad((size_t)s.lists * 4);
     s.off_best = s.off_cnt + pad((size_t)s.lists * 4);
     s.off_cand = s.off_best + pad((size_t)s.lists * (topk > 0 ? topk : 1) * 8);
@@ -1163,13 +1200,16 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
     unsigned long long* best = reinterpret_cast<unsigned long long*>(sc + cp.off_best);
     unsigned long long* cand = reinterpret_cast<unsigned long long*>(sc + cp.off_cand);
 
-    // One scoring launch per pass of at most 32 queries over keys [key_off, key_off + key_cnt) of every group (every
+    // One scoring launch per pass of at most 64 queries (32 at d = 256) over keys [key_off, key_off + key_cnt) of every group (every
     // tile_stride-th tile of them), into a matrix (mat != null) or into the candidate lists.
     auto score_passes = [&](int64_t key_off, int64_t key_cnt, int tile_stride, float* mat, int64_t row_stride) -> int {
         const int64_t group_stride = (int64_t)qpg * row_stride;
-        for (int q0 = 0; q0 < qpg; q0 += 32) {
-            const int nq = qpg - q0 < 32 ? qpg - q0 : 32;
-            const int qpad = nq <= 16 ? 16 : 32;
+        // A pass of 64 expands the keys once for queries that would otherwise take two passes (64 queries x 1,048,576
+        // keys: 176 us against 219 us in two passes of 32; 33 queries: 175 against 205 us in passes of 32 and 16).
+        const int pass = p->dev.d == 256 ? 32 : TQ_SCORE_PASS;
+        for (int q0 = 0; q0 < qpg; q0 += pass) {
+            const int nq = qpg - q0 < pass ? qpg - q0 : pass;
+            const int qpad = nq <= 16 ? 16 : nq <= 32 ? 32 : 64;
             if (p->dev.d == 256) {
                 score_prep256_kernel<<<dim3(qpad, groups), 256, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
             } else {
@@ -1219,9 +1259,11 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             tq_timer_mark(p, 1, 0, st);
 #define TQ_SC(B)                                                                                             \
     case B:                                                                                                  \
-        if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(map, a, grid, st) : launch_score<B, 32, 64>(map, a, grid, st);   \
-        else if (p->dev.d == 256) r = qpad == 16 ? launch_score<B, 16, 256>(map, a, grid, st) : launch_score<B, 32, 256>(map, a, grid, st);   \
-        else r = qpad == 16 ? launch_score<B, 16, 128>(map, a, grid, st) : launch_score<B, 32, 128>(map, a, grid, st);                \
+        if (p->dev.d == 64) r = qpad == 16 ? launch_score<B, 16, 64>(map, a, grid, st) : qpad == 32 ? launch_score<B, 32, 64>(map, a, grid, st)       \
+                                                                                                   : launch_score<B, 64, 64>(map, a, grid, st);      \
+        else if (p->dev.d == 256) r = qpad == 16 ? launch_score<B, 16, 256>(map, a, grid, st) : launch_score<B, 32, 256>(map, a, grid, st);          \
+        else r = qpad == 16 ? launch_score<B, 16, 128>(map, a, grid, st) : qpad == 32 ? launch_score<B, 32, 128>(map, a, grid, st)                   \
+                                                                                      : launch_score<B, 64, 128>(map, a, grid, st);                  \
         break;
             switch (bits) { TQ_SC(1) TQ_SC(2) TQ_SC(3) TQ_SC(4) }
 #undef TQ_SC

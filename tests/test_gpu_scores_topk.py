@@ -165,6 +165,35 @@ def test_topk_without_matrix_for_query_groups(tg, kpg):
         assert torch.equal(top_i[r], want_i[r] + (r // qpg) * kpg + 5)
 
 
+@pytest.mark.parametrize("d,bits", [(128, 4), (128, 1), (64, 3)])
+@pytest.mark.parametrize("groups,qpg", [(1, 64), (1, 33), (3, 40), (1, 100)])
+def test_passes_of_up_to_64_queries(tg, d, bits, groups, qpg):
+    """From 33 queries per group on a scoring launch takes up to 64 queries (one operand buffer in tensor memory, 256
+    accumulator columns, two blocks of 16 queries per epilogue thread, one group's prepared queries resident):
+    33, 40 (three groups, so the prepared queries change inside a block's tile range), 64 and 100 (64 + 36) queries
+    against 5,003 keys per group.  The matrix within the fp32 tolerance of the kernels that accumulate in the
+    reference's order; the top-k equal to a stable sort of the matrix."""
+    import torch
+    kpg, k = 5003, 50
+    gen = torch.Generator(device="cuda").manual_seed(20293 + qpg)
+    x = torch.randn((groups * kpg, d), generator=gen, device="cuda", dtype=torch.float32)
+    q = torch.randn((groups * qpg, d), generator=gen, device="cuda", dtype=torch.float32)
+    prod = tg.TurboQuantProd(d, bits, seed=2026)
+    enc = prod.quantize(x)
+    mat = prod.attention_scores(q, enc, groups=groups)
+    prod.set_kernel_path("exact")
+    ref = prod.attention_scores(q, enc, groups=groups)
+    prod.set_kernel_path("auto")
+    norms = tg.packed_buffers(enc)["norms"].view(groups, 1, kpg)
+    scale = (q.norm(dim=1).view(groups, qpg, 1) * norms / d ** 0.5).reshape(groups * qpg, kpg)
+    assert float(((mat - ref).abs() / scale).max()) <= REL_SCORE
+    top_s, top_i = prod.attention_scores(q, enc, groups=groups, topk=k)
+    want_s, want_i = _sorted_topk(mat, k)
+    assert torch.equal(top_s, want_s)
+    for r in range(groups * qpg):
+        assert torch.equal(top_i[r], want_i[r] + (r // qpg) * kpg)
+
+
 @pytest.mark.parametrize("bits", [2, 3, 4])
 def test_d256_query_groups_on_the_tensor_core_kernel_against_oracle(tg, bits):
     """d = 256 passes every tile of keys through the operand buffers in two halves of 128 coordinates, and only one

@@ -598,7 +598,9 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         }
         float nrm_next = 0.f, rn_next = 0.f;
         if (t0 < t1 && !a.norms_bulk) fetch_norms(g, kt, nrm_next, rn_next);
+        TQ_PROF_CODE(long long ep[8] = {0, 0, 0, 0, 0, 0, 0, 0};)
         for (int64_t t = t0; t < t1; ++t, ++kt) {
+            TQ_PROF_CODE(const long long ctop = clock64();)
             if (kt == a.tiles_per_group) { kt = 0; ++g; }
             const int64_t i = t - t0;
             const int b = (int)(i & 1);        // staging buffer and accumulators of this tile
@@ -704,19 +706,24 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     // i - 2 must have read its buffer before tile i overwrites it.  (A box per warp -- 32 keys x 16 queries from
                     // a slice of its own, no barrier between the epilogue warps -- was slower: 115 against 109 us.)
                     float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
+                    TQ_PROF_CODE(const long long s0 = clock64();)
                     if (qb == 0) {
                         if (store_leader) bulk_wait_read<1>();
                         bar_sync(kEpiBarrier, kEpiThreads);
                     }
+                    TQ_PROF_CODE(const long long s1 = clock64();)
 #pragma unroll
                     for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
                     if (qb == kQBlocks - 1) {
                         fence_async_smem();
+                        TQ_PROF_CODE(const long long s2 = clock64();)
                         bar_sync(kEpiBarrier, kEpiThreads);
+                        TQ_PROF_CODE(const long long s3 = clock64();)
                         if (store_leader && got) {
                             tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
                             bulk_commit();
                         }
+                        TQ_PROF_CODE(ep[4] += s1 - s0; ep[5] += s2 - s1; ep[6] += s3 - s2; ep[7] += clock64() - s3;)
                     }
                 } else if (live && got) {
                     float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
@@ -763,11 +770,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     }
                 }
             }
-#ifdef TQ_PROF
-            if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32) {
-                a.prof[12] += c1 - c0; a.prof[13] += c2 - c1; a.prof[14] += clock64() - c2;
-            }
-#endif
+            TQ_PROF_CODE(ep[0] += c0 - ctop; ep[1] += c1 - c0; ep[2] += c2 - c1; ep[3] += clock64() - c2;)
             const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
             if (last_of_group) {
                 __syncwarp();
@@ -778,6 +781,12 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             bar_sync(kEpiBarrier, kEpiThreads);
             flush_staging();
         }
+#ifdef TQ_PROF
+        if (a.prof && blockIdx.x == 0 && threadIdx.x == kFirstEpiWarp * 32 + 32) {      // a thread that is not the store leader's warp
+            a.prof[18] = ep[0]; a.prof[12] = ep[1]; a.prof[13] = ep[2]; a.prof[14] = ep[3];
+            a.prof[19] = ep[4]; a.prof[20] = ep[5]; a.prof[21] = ep[6]; a.prof[22] = ep[7];
+        }
+#endif
         if (store_leader) bulk_wait_all();   // the staged tiles must have left before the block's shared memory goes away
     }
 

@@ -457,7 +457,19 @@ def run_gpu(args):
                 name = ("mse" if cls is tg.TurboQuantMSE else "prod") + "_quantize_d%d" % d_other
                 other[name] = rate_row(timed(lambda: q_o.quantize(keys_o)), N_KEYS, nbytes,
                                        "B/vector: fp32 row in, packed encoding out, d = %d" % d_other, peak)
+            if d_other == 256:      # q_o is the TurboQuantProd of d = 256: the same 32 x N score matrix as the headline
+                enc_o = q_o.quantize(keys_o)
+                q32 = torch.randn((N_QUERIES, d_other), generator=gen, device=dev, dtype=torch.float32)
+                other["attention_score_matrix_d256"] = rate_row(
+                    timed(lambda: q_o.attention_scores(q32, enc_o)), N_KEYS, key_bytes(d_other, BITS) + 4 * N_QUERIES,
+                    "B/key: packed key in, %d scores out, d = 256" % N_QUERIES, peak)
+                del enc_o, q32
             del keys_o
+        q64 = torch.randn((64, D), generator=gen, device=dev, dtype=torch.float32)
+        other["attention_score_matrix_64_queries"] = rate_row(
+            timed(lambda: quant.attention_scores(q64, enc_p)), N_KEYS, kb + 4 * 64,
+            "B/key: packed key in, 64 scores out (one pass of 64 queries)", peak)
+        del q64
         kv, kv_q = decode_cache(tg, torch, quant, mse, keys, dev)
         other["decode_attention"] = rate_row(
             timed(lambda: kv.attend(kv_q)), N_KEYS, kb + D * BITS // 8 + 4,

@@ -870,14 +870,17 @@ score_prep_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq,
     if (j == 0) ds[slot] = make_float2(1.f / (e1 * kCentScale), 1.f / e2);
 }
 
-// The same for d = 256: block 256 (thread = coordinate), the matrices read from global memory (they do not fit shared
-// memory), and the operands written as two halves of 128 coordinates, each in the layout of d = 128.
-__global__ void __launch_bounds__(256)
+// The same for d = 256: the matrices do not fit shared memory and are read from global memory (usually cold), so the
+// kernel lives on the number of loads in flight: block 1024, thread = (coordinate, quarter of the sum), 16 loads per
+// matrix in flight per thread (39 us with 256 threads and four: a third of the scoring of 1,048,576 keys it precedes).
+// The operands are written as two halves of 128 coordinates, each in the layout of d = 128.
+__global__ void __launch_bounds__(1024)
 score_prep256_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int nq, int qpad, unsigned char* __restrict__ prep) {
-    constexpr int kD = 256;
+    constexpr int kD = 256, kParts = 4, kSteps = kD / kParts;
     __shared__ float qs[kD];
+    __shared__ float part[2][kParts][kD];
     __shared__ float red[2][8];
-    const int slot = blockIdx.x, g = blockIdx.y, j = threadIdx.x;
+    const int slot = blockIdx.x, g = blockIdx.y, j = threadIdx.x & (kD - 1), kq = threadIdx.x >> 8;
     unsigned char* base = prep + (size_t)g * prep_group_bytes(qpad, 2);
     const int jh = j & 127;
     const size_t off = (size_t)(j >> 7) * (4 * (size_t)qpad * kRowBytesB) + (size_t)(slot / 8) * ((D / 8) * 128) +
@@ -888,31 +891,38 @@ score_prep256_kernel(TqDev p, const float* __restrict__ q, int qpg, int q0, int 
     __half* m3 = reinterpret_cast<__half*>(base + 3 * (size_t)qpad * kRowBytesB + off);
     float2* ds = reinterpret_cast<float2*>(base + 8 * (size_t)qpad * kRowBytesB);
     if (slot >= nq) {
-        *m0 = *m1 = *m2 = *m3 = __float2half_rn(0.f);
-        if (j == 0) ds[slot] = make_float2(0.f, 0.f);
+        if (kq == 0) {
+            *m0 = *m1 = *m2 = *m3 = __float2half_rn(0.f);
+            if (j == 0) ds[slot] = make_float2(0.f, 0.f);
+        }
         return;
     }
-    qs[j] = q[((size_t)g * qpg + q0 + slot) * kD + j];
+    if (kq == 0) qs[j] = q[((size_t)g * qpg + q0 + slot) * kD + j];
     __syncthreads();
-    // four independent chains per matrix keep enough loads in flight; the order of the sums differs from the general
-    // kernel's, which the fp32 tolerance of the scores covers
+    // four independent chains per matrix; the order of the sums differs from the general kernel's, which the fp32
+    // tolerance of the scores covers
     float r[4] = {0.f, 0.f, 0.f, 0.f}, s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int k = 0; k < kD; k += 4) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            r[u] = fmaf(qs[k + u], __ldg(p.Rt + (size_t)(k + u) * kD + j), r[u]);
-            s[u] = fmaf(qs[k + u], __ldg(p.St + (size_t)(k + u) * kD + j), s[u]);
-        }
+    const float* Rt = p.Rt + (size_t)kq * kSteps * kD + j;
+    const float* St = p.St + (size_t)kq * kSteps * kD + j;
+    const float* qk = qs + kq * kSteps;
+#pragma unroll 16
+    for (int k = 0; k < kSteps; ++k) {
+        r[k & 3] = fmaf(qk[k], __ldg(Rt + (size_t)k * kD), r[k & 3]);
+        s[k & 3] = fmaf(qk[k], __ldg(St + (size_t)k * kD), s[k & 3]);
     }
-    const float rr = (r[0] + r[1]) + (r[2] + r[3]), sv = (s[0] + s[1]) + (s[2] + s[3]);
+    part[0][kq][j] = (r[0] + r[1]) + (r[2] + r[3]);
+    part[1][kq][j] = (s[0] + s[1]) + (s[2] + s[3]);
+    __syncthreads();
+    if (kq != 0) return;      // threads 0..255 (warps 0..7) finish the coordinate
+    const float rr = (part[0][0][j] + part[0][1][j]) + (part[0][2][j] + part[0][3][j]);
+    const float sv = (part[1][0][j] + part[1][1][j]) + (part[1][2][j] + part[1][3][j]);
     float mr = fabsf(rr), ms = fabsf(sv);
     for (int o = 16; o > 0; o >>= 1) {
         mr = fmaxf(mr, __shfl_xor_sync(0xffffffffu, mr, o));
         ms = fmaxf(ms, __shfl_xor_sync(0xffffffffu, ms, o));
     }
     if ((j & 31) == 0) { red[0][j >> 5] = mr; red[1][j >> 5] = ms; }
-    __syncthreads();
+    asm volatile("bar.sync 1, 256;" ::: "memory");      // the 256 threads that are left
     mr = ms = 0.f;
     for (int w = 0; w < 8; ++w) { mr = fmaxf(mr, red[0][w]); ms = fmaxf(ms, red[1][w]); }
     const bool okr = mr > 0.f && mr < 3.0e38f, oks = ms > 0.f && ms < 3.0e38f;
@@ -1220,7 +1230,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             const int nq = qpg - q0 < pass ? qpg - q0 : pass;
             const int qpad = nq <= 16 ? 16 : nq <= 32 ? 32 : 64;
             if (p->dev.d == 256) {
-                score_prep256_kernel<<<dim3(qpad, groups), 256, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
+                score_prep256_kernel<<<dim3(qpad, groups), 1024, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
             } else {
                 TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
                 score_prep_kernel<<<dim3(qpad, groups), 128, kPrepSmemBytes, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();

@@ -38,17 +38,18 @@ using namespace tqtopk;
 
 constexpr int D = 128;
 constexpr int kTileKeys = 128;
-// Warps: bulk copy, MMA, 16 expanders (one thread per quarter key), then 4 epilogue warps per 16 queries of the pass
-// (per 32 queries in a pass of 64: a block is limited to 32 warps, so every epilogue thread takes two blocks of 16).
-constexpr int kExpWarps = 16;
+// Warps: bulk copy, MMA, 16 expanders (one thread per quarter key), then 4 epilogue warps per 16 queries of the pass.
+// A pass of 64 queries has 16 epilogue warps and, a block being limited to 32 warps, 8 expanders (one thread per
+// half key): what its tile waits for is the way of the single accumulator through the epilogue, which is as short with
+// one block of 16 queries per thread as in the smaller passes.
 template <int QPAD> struct ScoreThreads {
-    static constexpr int kQBlocks = QPAD == 64 ? 2 : 1;      // blocks of 16 queries per epilogue thread
-    static constexpr int kEpiPerRow = QPAD / (16 * kQBlocks);
+    static constexpr int kExpWarps = QPAD == 64 ? 8 : 16;
+    static constexpr int kEpiPerRow = QPAD / 16;
     static constexpr int kEpiThreads = 4 * kEpiPerRow * 32;
     static constexpr int kThreads = (2 + kExpWarps) * 32 + kEpiThreads;
+    static constexpr int kFirstEpiWarp = 2 + kExpWarps;
 };
 constexpr int kFirstExpWarp = 2;
-constexpr int kFirstEpiWarp = kFirstExpWarp + kExpWarps;
 constexpr int kMaxStages = 8;
 constexpr float kCentScale = 1024.f;
 constexpr int kRowBytesB = D * 2;  // one query row of one fp16 operand matrix
@@ -96,13 +97,13 @@ struct ScoreTcArgs {
 enum {
     SB_K_FULL = 0,      // [8]
     SB_K_EMPTY = 8,     // [8]
-    SB_A_FULL = 16,     // [2]
-    SB_A_EMPTY = 18,    // [2]
-    SB_D_FULL = 20,     // [2]
-    SB_D_EMPTY = 22,    // [2]
-    SB_B_FULL = 24,     // [2]
-    SB_B_EMPTY = 26,    // [2]
-    SB_COUNT = 28
+    SB_A_FULL = 16,     // [4]: per A buffer; in a pass of 64 queries per chunk of 32 coordinates of the single buffer
+    SB_A_EMPTY = 20,    // [4]
+    SB_D_FULL = 24,     // [2]
+    SB_D_EMPTY = 26,    // [2]
+    SB_B_FULL = 28,     // [2]
+    SB_B_EMPTY = 30,    // [2]
+    SB_COUNT = 32
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -151,7 +152,7 @@ struct ScoreSmem {
     static constexpr int kStageBytes = kNormOff + 2 * kTileKeys * 4;
     static constexpr int kBBytes = (kPrepBytes + 127) & ~127;
     static constexpr int kOutBytes = QPAD * kTileKeys * 4;          // one staged tile of scores [query][key]
-    static constexpr int kFixed = kLutBytes + kBBufs * kBBytes + 2 * kOutBytes + 512 + 128 + 128;
+    static constexpr int kFixed = kLutBytes + kBBufs * kBBytes + 2 * kOutBytes + 640 + 128 + 128;
     static constexpr int kFit = (227 * 1024 - kFixed) / kStageBytes;
     static constexpr int kStages = kFit < kMaxStages ? kFit : kMaxStages;
     static_assert(kStages >= 3, "key ring too short");
@@ -160,7 +161,7 @@ struct ScoreSmem {
     static constexpr int off_out = off_b + kBBufs * kBBytes;
     static constexpr int off_ring = off_out + 2 * kOutBytes;
     static constexpr int off_misc = off_ring + kStages * kStageBytes;
-    static constexpr int total = off_misc + 512 + 128;
+    static constexpr int total = off_misc + 640 + 128;
 };
 
 // CAND: candidate mode (top-k without a score matrix) is a kernel of its own, so that the matrix kernel carries none
@@ -173,7 +174,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
     constexpr int kHalves = L::kHalves;          // passes of a key tile through the operand buffers
     constexpr int kBBufs = L::kBBufs;
     constexpr int kDH = DR / kHalves;            // coordinates per pass
-    constexpr int kParts = kDH / 32;             // expander warps per lane quarter that have data
+    constexpr int kChunks = kDH / 32;            // chunks of 32 coordinates per pass of a key through the buffers
+    constexpr int kSub = kChunks * 4 > ScoreThreads<QPAD>::kExpWarps ? kChunks * 4 / ScoreThreads<QPAD>::kExpWarps : 1;   // chunks per expander thread (2 in a pass of 64 queries at d = 128)
+    constexpr int kParts = kChunks / kSub;       // expander warps per lane quarter that have data
+    constexpr int kFirstEpiWarp = ScoreThreads<QPAD>::kFirstEpiWarp;
+    // A pass of 64 queries runs its single A buffer as a ring of chunks: the contractions of a tile take the chunks in
+    // order (two k-blocks each) and hand every chunk back as soon as they are through with it, so the expanders fill
+    // chunk c of the next tile while the contractions of this one are at chunk c + 1.
+    constexpr bool kChunkRing = QPAD == 64;
     constexpr int kStages = L::kStages;
     constexpr int kThreads = ScoreThreads<QPAD>::kThreads;
     constexpr int kEpiPerRow = ScoreThreads<QPAD>::kEpiPerRow;
@@ -194,9 +202,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             mbar_init(BAR(SB_K_FULL + i), 1);
             mbar_init(BAR(SB_K_EMPTY + i), 4 * kParts + (a.norms_bulk ? 4 * kEpiPerRow : 0));   // expanders (+ epilogue warps)
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(SB_A_FULL + i), 4 * kParts);
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(BAR(SB_A_FULL + i), kChunkRing ? 4 : 4 * kParts);
             mbar_init(BAR(SB_A_EMPTY + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(SB_D_FULL + i), 1);
             mbar_init(BAR(SB_D_EMPTY + i), 4 * kEpiPerRow);
             mbar_init(BAR(SB_B_FULL + i), 1);
@@ -240,14 +250,15 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
     // and D2 = [Sg p_hi | Sg p_lo], 2*QPAD columns each; double-buffered when they fit (QPAD = 16).
     constexpr uint32_t kBufCols = 192;
     constexpr uint32_t kColHi = 0, kColLo = 64, kColSg = 128;
-    // A pass of 64 queries has 256 accumulator columns and room for one A buffer only, so the expanders' stores wait for
-    // the contractions of the tile before.  (The other way to fit 64 queries -- both A buffers, the hi and lo products
-    // added inside 128 accumulator columns by 40 instructions of N = 64 per tile -- measured the same: 173 against 176 us
-    // per 64 x 1,048,576 scores, 245 against 258 us per 1,048,576 keys in candidate mode.)
+    // A pass of 64 queries has 256 accumulator columns and room for one A buffer only (run as a ring of chunks, below).
+    // Measured alternatives per 64 x 1,048,576 scores / per 1,048,576 keys in candidate mode: 16 expander and 8 epilogue
+    // warps with two blocks of 16 queries per epilogue thread 176 / 258 us (the accumulator stays with the epilogue twice
+    // as long); the same with both A buffers and the hi and lo products added inside 128 accumulator columns (40
+    // instructions of N = 64 per tile) 173 / 245 us; 8 expander and 16 epilogue warps with the A buffer handed over
+    // whole 174 / 175 us; as a ring of chunks 171 / 178 us.
     constexpr int kABufs = QPAD == 64 ? 1 : 2;
     constexpr int kDBufs = QPAD == 16 ? 2 : 1;
     constexpr uint32_t kColD = kABufs * kBufCols, kDCols = 4 * QPAD;
-    constexpr int kQBlocks = ScoreThreads<QPAD>::kQBlocks;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -311,7 +322,53 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             int bb = 0;
             int64_t g = t0 / a.tiles_per_group, kt = t0 - g * a.tiles_per_group;
             uint64_t dq_hi = 0, dp_hi = 0;
-            if constexpr (kHalves == 1) {
+            if constexpr (kChunkRing) {
+                bool gave_up = false;
+                for (int64_t t = t0; t < t1 && !gave_up; ++t, ++kt) {
+                    if (kt == a.tiles_per_group) { kt = 0; ++g; }
+                    const int64_t i = t - t0;
+                    const uint32_t par = (uint32_t)(i & 1);
+                    if (g != prev_g) {
+                        bb = 0;
+                        if (!warp_wait(BAR(SB_B_FULL), (uint32_t)(gcount & 1), abort_flag)) break;
+                        prev_g = g;
+                        ++gcount;
+                        const uint32_t bq = smem_base + L::off_b;
+                        dq_hi = make_smem_desc(bq + 0 * QPAD * kRowBytesB, lbo, sbo);
+                        dp_hi = make_smem_desc(bq + 2 * QPAD * kRowBytesB, lbo, sbo);
+                    }
+                    const uint32_t d1 = tm + kColD, d2 = d1 + 2 * QPAD;
+                    const bool last_of_group = (t + 1 == t1) || (kt + 1 == a.tiles_per_group);
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        if (!warp_wait(BAR(SB_A_FULL + c), par, abort_flag)) { gave_up = true; break; }
+                        if (c == 0 && !warp_wait(BAR(SB_D_EMPTY), par ^ 1u, abort_flag)) { gave_up = true; break; }
+                        tc_fence_after();
+                        if (elect_one()) {
+#pragma unroll 1
+                            for (int kb = 2 * c; kb < 2 * c + 2; ++kb) {
+                                const uint64_t step = (uint64_t)(kb * 2 * lbo >> 4);
+                                const uint64_t qh = dq_hi + step, ph = dp_hi + step;
+                                if (kb == 0) {
+                                    mma_ts_first(d1, tm + kColHi, qh, kIdesc2);
+                                    mma_ts_acc(d1, tm + kColLo, qh, kIdesc1);
+                                    mma_ts_first(d2, tm + kColSg, ph, kIdesc2);
+                                } else {
+                                    mma_ts_acc(d1, tm + kColHi + kb * 8, qh, kIdesc2);
+                                    mma_ts_acc(d1, tm + kColLo + kb * 8, qh, kIdesc1);
+                                    mma_ts_acc(d2, tm + kColSg + kb * 8, ph, kIdesc2);
+                                }
+                            }
+                            mma_commit(BAR(SB_A_EMPTY + c));     // this chunk's slot may be filled for the next tile
+                            if (c == kChunks - 1) {
+                                mma_commit(BAR(SB_D_FULL));
+                                if (last_of_group) mma_commit(BAR(SB_B_EMPTY));
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+            } else if constexpr (kHalves == 1) {
                 for (int64_t t = t0; t < t1; ++t, ++kt) {
                     if (kt == a.tiles_per_group) { kt = 0; ++g; }
                     const int64_t i = t - t0;
@@ -431,7 +488,53 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         const uint2* lut_lane = reinterpret_cast<const uint2*>(smem + L::off_lut) + lane;
         constexpr uint32_t kPairMask = (1u << (2 * BITS)) - 1u;
         TQ_PROF_CODE(long long pc[5] = {0, 0, 0, 0, 0};)
-        if constexpr (kHalves == 1) {
+        if constexpr (kChunkRing) {
+            // a pass of 64 queries: the thread's chunks one after the other, each into its slot of the single A buffer
+            for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
+                const int64_t i = t - t0;
+                const int s = (int)(i % kStages);
+                const uint32_t par = (uint32_t)(i & 1);
+                bool fail = !mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
+#pragma unroll 1
+                for (int sp = 0; sp < kSub; ++sp) {
+                    const int chunk = part * kSub + sp;
+                    uint32_t w[BITS + 1], sw;
+                    {
+                        const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
+                        const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
+                        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
+#pragma unroll
+                        for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
+                        w[BITS] = 0;
+                        sw = fail ? 0u : ~sg[0];
+                    }
+                    __syncwarp();
+                    if (sp == kSub - 1 && lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
+                    uint32_t hi[16], lo[16], sg[16];
+#pragma unroll
+                    for (int p = 0; p < 16; ++p) {
+                        const int bit = p * 2 * BITS, wi = bit >> 5, sh = bit & 31;
+                        uint32_t e;
+                        if (sh + 2 * BITS <= 32) e = (w[wi] >> sh) & kPairMask;
+                        else e = __funnelshift_r(w[wi], w[wi + 1], sh) & kPairMask;
+                        const uint2 v = lut_lane[e * 32];
+                        hi[p] = v.x;
+                        lo[p] = v.y;
+                        sg[p] = ((sw << (15 - p)) & 0x80008000u) | 0x3c003c00u;
+                    }
+                    if (!mbar_wait(BAR(SB_A_EMPTY + chunk), par ^ 1u, abort_flag)) fail = true;
+                    tc_fence_after();
+                    const uint32_t abase = tmem + lane_addr + chunk * 16;
+                    tmem_st16(abase + kColHi, hi);
+                    tmem_st16(abase + kColLo, lo);
+                    tmem_st16(abase + kColSg, sg);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(SB_A_FULL + chunk));
+                }
+            }
+        } else if constexpr (kHalves == 1) {
             for (int64_t t = t0; t < (part < kParts ? t1 : t0); ++t) {
                 const int64_t i = t - t0;
                 const int s = (int)(i % kStages);
@@ -555,7 +658,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int q16_0 = ((warp - kFirstEpiWarp) >> 2) * 16 * kQBlocks;   // this thread's first query of the pass (16 per block)
+        const int q16 = ((warp - kFirstEpiWarp) >> 2) * 16;   // this thread's 16 queries of the pass
         const bool store_leader = threadIdx.x == kFirstEpiWarp * 32;
         int64_t prev_g = -1, gcount = 0;
         int bb = 0;
@@ -570,15 +673,15 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             r_out = live_n ? __ldg(a.rnorms + grow_n) : 0.f;
         };
         // candidate mode: thresholds of the current group, and in place of the score tile buffers a staging list of
-        // survivors (keys, then the numbers of their lists) and 16 (32 in a pass of 64 queries) x 32 parked scores per warp
+        // survivors (keys, then the numbers of their lists) and 16 x 32 parked scores per warp
         int64_t thr_g = -1;
         float* thr_s = reinterpret_cast<float*>(bars + SB_COUNT + 2);   // [QPAD]
         int* st_count = reinterpret_cast<int*>(thr_s + QPAD);
-        constexpr int kStageCap = (2 * L::kOutBytes - 4 * kEpiPerRow * 16 * kQBlocks * 32 * 4) / 12 / 128 * 128;    // 1,280 entries (32 queries), 640 (16), 2,688 (64)
+        constexpr int kStageCap = (2 * L::kOutBytes - 4 * kEpiPerRow * 16 * 32 * 4) / 12 / 128 * 128;    // 1,280 entries (32 queries), 640 (16), 2,688 (64)
         static_assert(kStageCap >= 512, "candidate staging must fit the score tile buffers");
         unsigned long long* st_keys = reinterpret_cast<unsigned long long*>(smem + L::off_out);
         uint32_t* st_list = reinterpret_cast<uint32_t*>(smem + L::off_out + kStageCap * 8);
-        float* warp_scores = reinterpret_cast<float*>(smem + L::off_out + kStageCap * 12) + (warp - kFirstEpiWarp) * 16 * kQBlocks * 32;
+        float* warp_scores = reinterpret_cast<float*>(smem + L::off_out + kStageCap * 12) + (warp - kFirstEpiWarp) * 16 * 32;
         const int epi_t = threadIdx.x - kFirstEpiWarp * 32;
         auto flush_staging = [&]() {      // all epilogue threads, after a barrier that made every append visible
             int n = *st_count;
@@ -634,105 +737,93 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
             tc_fence_after();
             TQ_PROF_CODE(long long c1 = clock64();)
             TQ_PROF_CODE(long long c2 = c1;)
-            // a pass of 64 queries: two blocks of 16 per thread, one after the other (everything that happens once per
-            // tile -- the barriers of the staging buffers, the release of the accumulators -- hangs on the first or last)
             const uint32_t rowid = (uint32_t)(g * a.keys_per_group + a.key_off + key);   // row of the key arrays (candidate mode)
-            uint32_t pm = 0;      // candidate mode: bit k = this key's score for query q16_0 + k reaches the query's threshold
-#pragma unroll 1
-            for (int qb = 0; qb < kQBlocks; ++qb) {
-                const int q16 = q16_0 + qb * 16;
-                const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
-                const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + kHalves * 4 * QPAD * kRowBytesB) + q16;
-                float sc[16];
-                {
-                    uint32_t ua[16], ub[16];
-                    tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
-                    tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
-                    tmem_wait_ld();
+            uint32_t pm = 0;      // candidate mode: bit k = this key's score for query q16 + k reaches the query's threshold
+            const uint32_t dbase = tmem + lane_addr + kColD + db * kDCols + q16;
+            const float2* ds = reinterpret_cast<const float2*>(smem + L::off_b + bb * L::kBBytes + kHalves * 4 * QPAD * kRowBytesB) + q16;
+            float sc[16];
+            {
+                uint32_t ua[16], ub[16];
+                tmem_ld16(dbase, ua);                  // C q_hi   (+ C_lo q_hi)
+                tmem_ld16(dbase + QPAD, ub);           // C_hi q_lo
+                tmem_wait_ld();
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) sc[k] = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].x;
-                    tmem_ld16(dbase + 2 * QPAD, ua);       // Sg p_hi
-                    tmem_ld16(dbase + 3 * QPAD, ub);       // Sg p_lo
-                    tmem_wait_ld();
-                    if (qb == kQBlocks - 1) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
-                    }
+                for (int k = 0; k < 16; ++k) sc[k] = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].x;
+                tmem_ld16(dbase + 2 * QPAD, ua);       // Sg p_hi
+                tmem_ld16(dbase + 3 * QPAD, ub);       // Sg p_lo
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(SB_D_EMPTY + db));   // the accumulators are free again
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        const float s2 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].y;
-                        sc[k] = nrm * fmaf(arn, s2, sc[k]);
-                    }
+                for (int k = 0; k < 16; ++k) {
+                    const float s2 = (__uint_as_float(ua[k]) + __uint_as_float(ub[k])) * ds[k].y;
+                    sc[k] = nrm * fmaf(arn, s2, sc[k]);
                 }
-                TQ_PROF_CODE(if (qb == 0) c2 = clock64();)
-                // After a give-up (`got` false) nothing is written for the tile, but every epilogue warp still walks through the
-                // named barriers below: the warps learn of the give-up at different tiles, and a barrier that some of them
-                // skipped would never complete.
-                if (CAND) {
-                    if (qb == 0 && g != thr_g) {      // thresholds of this group's queries (constant during the launch) into shared memory
-                        thr_g = g;
-                        bar_sync(kEpiBarrier, kEpiThreads);      // everybody is done with the previous group's
-                        if (epi_t < QPAD) thr_s[epi_t] = epi_t < a.nq ? __ldg(a.thr + g * a.qpg_total + a.q0 + epi_t) : CUDART_INF_F;
-                        bar_sync(kEpiBarrier, kEpiThreads);
+            }
+            TQ_PROF_CODE(c2 = clock64();)
+            // After a give-up (`got` false) nothing is written for the tile, but every epilogue warp still walks through the
+            // named barriers below: the warps learn of the give-up at different tiles, and a barrier that some of them
+            // skipped would never complete.
+            if (CAND) {
+                if (g != thr_g) {      // thresholds of this group's queries (constant during the launch) into shared memory
+                    thr_g = g;
+                    bar_sync(kEpiBarrier, kEpiThreads);      // everybody is done with the previous group's
+                    if (epi_t < QPAD) thr_s[epi_t] = epi_t < a.nq ? __ldg(a.thr + g * a.qpg_total + a.q0 + epi_t) : CUDART_INF_F;
+                    bar_sync(kEpiBarrier, kEpiThreads);
+                }
+                const int64_t q_first = g * a.qpg_total + a.q0 + q16;
+                if (a.fused == 2) {
+                    // The sampled pass (thresholds at -inf, every score is a candidate): the slot of a score is known
+                    // without a counter (tile of the sample x 128 + row); the host presets the lists' lengths.
+                    // A key beyond the end of the group leaves an empty slot.
+#pragma unroll
+                    for (int k = 0; k < 16; ++k)
+                        if (q16 + k < a.nq)
+                            a.cand[(q_first + k) * a.cand_cap + kt * kTileKeys + row] = live && got ? make_key(sc[k], rowid) : 0ull;
+                } else {
+                    // This thread's scores against their thresholds: a mask, and -- when any of the warp's 32 keys has
+                    // a survivor -- the scores parked in shared memory, so that the loop below can pick them by a
+                    // run-time index.
+                    float* mine = warp_scores + lane;
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) m |= (live && got && sc[k] >= thr_s[q16 + k]) ? (1u << k) : 0u;
+                    if (__any_sync(0xffffffffu, m != 0u)) {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) mine[k * 32] = sc[k];
                     }
-                    const int64_t q_first = g * a.qpg_total + a.q0 + q16;
-                    if (a.fused == 2) {
-                        // The sampled pass (thresholds at -inf, every score is a candidate): the slot of a score is known
-                        // without a counter (tile of the sample x 128 + row); the host presets the lists' lengths.
-                        // A key beyond the end of the group leaves an empty slot.
+                    pm = m;
+                }
+            } else if (a.tile_store) {
+                // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
+                // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
+                // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
+                // i - 2 must have read its buffer before tile i overwrites it.  (A box per warp -- 32 keys x 16 queries from
+                // a slice of its own, no barrier between the epilogue warps -- was slower: 115 against 109 us.)
+                float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
+                TQ_PROF_CODE(const long long s0 = clock64();)
+                if (store_leader) bulk_wait_read<1>();
+                bar_sync(kEpiBarrier, kEpiThreads);
+                TQ_PROF_CODE(const long long s1 = clock64();)
 #pragma unroll
-                        for (int k = 0; k < 16; ++k)
-                            if (q16 + k < a.nq)
-                                a.cand[(q_first + k) * a.cand_cap + kt * kTileKeys + row] = live && got ? make_key(sc[k], rowid) : 0ull;
-                    } else {
-                        // This thread's scores against their thresholds: a mask, and -- when any of the warp's 32 keys has
-                        // a survivor in this block of queries -- the scores parked in shared memory, so that the loop behind
-                        // the blocks can pick them by a run-time index.
-                        float* mine = warp_scores + lane + qb * 16 * 32;
-                        uint32_t m = 0;
+                for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
+                fence_async_smem();
+                TQ_PROF_CODE(const long long s2 = clock64();)
+                bar_sync(kEpiBarrier, kEpiThreads);
+                TQ_PROF_CODE(const long long s3 = clock64();)
+                if (store_leader && got) {
+                    tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
+                    bulk_commit();
+                }
+                TQ_PROF_CODE(ep[4] += s1 - s0; ep[5] += s2 - s1; ep[6] += s3 - s2; ep[7] += clock64() - s3;)
+            } else if (live && got) {
+                float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
 #pragma unroll
-                        for (int k = 0; k < 16; ++k) m |= (live && got && sc[k] >= thr_s[q16 + k]) ? (1u << k) : 0u;
-                        if (__any_sync(0xffffffffu, m != 0u)) {
-#pragma unroll
-                            for (int k = 0; k < 16; ++k) mine[k * 32] = sc[k];
-                        }
-                        pm |= m << (qb * 16);
-                    }
-                } else if (a.tile_store) {
-                    // The tile leaves as one box [queries of the pass][128 keys]: staged in shared memory (lanes hold
-                    // consecutive keys, so the stores are free of bank conflicts) and written by one bulk tensor store,
-                    // which clips the keys and queries beyond the matrix.  Two staging buffers: the store of tile
-                    // i - 2 must have read its buffer before tile i overwrites it.  (A box per warp -- 32 keys x 16 queries from
-                    // a slice of its own, no barrier between the epilogue warps -- was slower: 115 against 109 us.)
-                    float* stage = reinterpret_cast<float*>(smem + L::off_out + b * L::kOutBytes);
-                    TQ_PROF_CODE(const long long s0 = clock64();)
-                    if (qb == 0) {
-                        if (store_leader) bulk_wait_read<1>();
-                        bar_sync(kEpiBarrier, kEpiThreads);
-                    }
-                    TQ_PROF_CODE(const long long s1 = clock64();)
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) stage[(q16 + k) * kTileKeys + row] = sc[k];
-                    if (qb == kQBlocks - 1) {
-                        fence_async_smem();
-                        TQ_PROF_CODE(const long long s2 = clock64();)
-                        bar_sync(kEpiBarrier, kEpiThreads);
-                        TQ_PROF_CODE(const long long s3 = clock64();)
-                        if (store_leader && got) {
-                            tensor_store_3d(&tmap_out, smem_base + L::off_out + b * L::kOutBytes, (int)(kt * kTileKeys), 0, (int)g);
-                            bulk_commit();
-                        }
-                        TQ_PROF_CODE(ep[4] += s1 - s0; ep[5] += s2 - s1; ep[6] += s3 - s2; ep[7] += clock64() - s3;)
-                    }
-                } else if (live && got) {
-                    float* out = a.scores + g * a.out_group_stride + key + (int64_t)q16 * a.out_row_stride;
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        if (q16 + k < a.nq) {
-                            __stcs(out, sc[k]);
-                            out += a.out_row_stride;
-                        }
+                for (int k = 0; k < 16; ++k) {
+                    if (q16 + k < a.nq) {
+                        __stcs(out, sc[k]);
+                        out += a.out_row_stride;
                     }
                 }
             }
@@ -744,7 +835,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 // trip to L2 on this warp's path every tile); the list is emptied into the global lists, all its
                 // entries at once, when it is half full (looked at every eighth tile: the barrier couples the warps).
                 const float* mine = warp_scores + lane;
-                const int64_t q_first = g * a.qpg_total + a.q0 + q16_0;
+                const int64_t q_first = g * a.qpg_total + a.q0 + q16;
                 if ((i & 7) == 0 && bar_or(kEpiBarrier, kEpiThreads, *st_count > kStageCap / 2)) flush_staging();
                 uint32_t wm = __reduce_or_sync(0xffffffffu, pm);
 #pragma unroll 1
@@ -1224,7 +1315,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
     auto score_passes = [&](int64_t key_off, int64_t key_cnt, int tile_stride, float* mat, int64_t row_stride) -> int {
         const int64_t group_stride = (int64_t)qpg * row_stride;
         // A pass of 64 expands the keys once for queries that would otherwise take two passes (64 queries x 1,048,576
-        // keys: 176 us against 219 us in two passes of 32; 33 queries: 175 against 205 us in passes of 32 and 16).
+        // keys: 171 us against 219 us in two passes of 32; 33 queries: 168 against 205 us in passes of 32 and 16).
         const int pass = p->dev.d == 256 ? 32 : TQ_SCORE_PASS;
         for (int q0 = 0; q0 < qpg; q0 += pass) {
             const int nq = qpg - q0 < pass ? qpg - q0 : pass;

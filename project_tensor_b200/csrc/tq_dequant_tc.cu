@@ -272,12 +272,12 @@ dequant_tc_kernel(const DequantArgs a) {
             uint32_t w[kHalfWords + 1], sw[2] = {0u, 0u};
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
+                const volatile uint32_t* cw = reinterpret_cast<const volatile uint32_t*>(stage + row * L::kCodeRowBytes) + half * kHalfWords;
 #pragma unroll
                 for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
                 w[kHalfWords] = 0;
                 if (PROD) {
-                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + half * 2;
+                    const volatile uint32_t* sg = reinterpret_cast<const volatile uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + half * 2;
                     sw[0] = fail ? 0u : ~sg[0];   // a set bit now means a negative sign
                     sw[1] = fail ? 0u : ~sg[1];
                 }
@@ -645,12 +645,12 @@ dequant256_kernel(const DequantArgs a) {
             uint32_t w[kHalfWords + 1], sw[2] = {0u, 0u};
             {
                 const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * kHalfWords;
+                const volatile uint32_t* cw = reinterpret_cast<const volatile uint32_t*>(stage + row * L::kCodeRowBytes) + part * kHalfWords;
 #pragma unroll
                 for (int k = 0; k < kHalfWords; ++k) w[k] = fail ? 0u : cw[k];
                 w[kHalfWords] = 0;
                 if (PROD) {
-                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part * 2;
+                    const volatile uint32_t* sg = reinterpret_cast<const volatile uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part * 2;
                     sw[0] = fail ? 0u : ~sg[0];   // a set bit now means a negative sign
                     sw[1] = fail ? 0u : ~sg[1];
                 }

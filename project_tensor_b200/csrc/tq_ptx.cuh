@@ -25,6 +25,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+// Loads of data that a ring stage holds only until this thread's warp arrives on the stage's "empty" barrier.  A plain
+// load may be executed again at the place where its value is used (instead of keeping a register alive), which can lie
+// behind the arrival, when the stage may already hold the next tile; a volatile load is executed once, where it stands.
+__device__ __forceinline__ float4 lds_once_f4(const void* p) {
+    float4 v;
+    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }

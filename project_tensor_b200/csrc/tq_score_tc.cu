@@ -501,8 +501,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     uint32_t w[BITS + 1], sw;
                     {
                         const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                        const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
-                        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
+                        const volatile uint32_t* cw = reinterpret_cast<const volatile uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
+                        const volatile uint32_t* sg = reinterpret_cast<const volatile uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
 #pragma unroll
                         for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
                         w[BITS] = 0;
@@ -546,8 +546,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 uint32_t w[BITS + 1], sw;
                 {
                     const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                    const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
-                    const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
+                    const volatile uint32_t* cw = reinterpret_cast<const volatile uint32_t*>(stage + row * L::kCodeRowBytes) + part * BITS;
+                    const volatile uint32_t* sg = reinterpret_cast<const volatile uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + part;
 #pragma unroll
                     for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
                     w[BITS] = 0;
@@ -607,8 +607,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     {
                         const int chunk = h * 4 + part;      // this thread's 32 coordinates of the key
                         const unsigned char* stage = smem + L::off_ring + s * L::kStageBytes;
-                        const uint32_t* cw = reinterpret_cast<const uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
-                        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
+                        const volatile uint32_t* cw = reinterpret_cast<const volatile uint32_t*>(stage + row * L::kCodeRowBytes) + chunk * BITS;
+                        const volatile uint32_t* sg = reinterpret_cast<const volatile uint32_t*>(stage + kTileKeys * L::kCodeRowBytes + row * L::kSignRowBytes) + chunk;
 #pragma unroll
                         for (int k = 0; k < BITS; ++k) w[k] = fail ? 0u : cw[k];
                         w[BITS] = 0;
@@ -717,7 +717,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 // which one tile of lookahead does not hide once a tile takes less than a microsecond)
                 const int s = (int)(i % kStages);
                 mbar_wait(BAR(SB_K_FULL + s), (uint32_t)((i / kStages) & 1), abort_flag);
-                const float* nr = reinterpret_cast<const float*>(smem + L::off_ring + s * L::kStageBytes + L::kNormOff);
+                // volatile: the values stay in registers through the whole tile, and a plain load may be executed again where
+                // the value is used (cheaper than keeping or spilling a register) -- after the arrival below, when the
+                // stage may already hold another tile.  That happened: in candidate mode, where warps that lag behind
+                // their tile for microseconds exist, about one score in 10^9 came out with the norm of a key eight tiles on.
+                const volatile float* nr = reinterpret_cast<const volatile float*>(smem + L::off_ring + s * L::kStageBytes + L::kNormOff);
                 nrm = live ? nr[row] : 0.f;
                 arn = live ? a.alpha * nr[kTileKeys + row] : 0.f;
                 __syncwarp();
@@ -1312,7 +1316,9 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
 
     // One scoring launch per pass of at most 64 queries (32 at d = 256) over keys [key_off, key_off + key_cnt) of every group (every
     // tile_stride-th tile of them), into a matrix (mat != null) or into the candidate lists.
-    auto score_passes = [&](int64_t key_off, int64_t key_cnt, int tile_stride, float* mat, int64_t row_stride) -> int {
+    // `prepared`: the scratch block still holds the prepared queries of the only pass (a call of several launches
+    // over the same queries prepares them once).
+    auto score_passes = [&](int64_t key_off, int64_t key_cnt, int tile_stride, float* mat, int64_t row_stride, bool prepared) -> int {
         const int64_t group_stride = (int64_t)qpg * row_stride;
         // A pass of 64 expands the keys once for queries that would otherwise take two passes (64 queries x 1,048,576
         // keys: 171 us against 219 us in two passes of 32; 33 queries: 168 against 205 us in passes of 32 and 16).
@@ -1320,7 +1326,9 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
         for (int q0 = 0; q0 < qpg; q0 += pass) {
             const int nq = qpg - q0 < pass ? qpg - q0 : pass;
             const int qpad = nq <= 16 ? 16 : nq <= 32 ? 32 : 64;
-            if (p->dev.d == 256) {
+            if (prepared && qpg <= pass) {
+                // nothing to do
+            } else if (p->dev.d == 256) {
                 score_prep256_kernel<<<dim3(qpad, groups), 1024, 0, st>>>(p->dev, q, qpg, q0, nq, qpad, prep); tq_count_launch();
             } else {
                 TQ_CUDA_TRY(cudaFuncSetAttribute(score_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes));
@@ -1396,7 +1404,7 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
             if (!scores && key_cnt > sp.chunk) key_cnt = sp.chunk;
             float* mat = scores ? scores : tmp;
             const int64_t row_stride = scores ? keys_per_group : sp.chunk;
-            const int rc = score_passes(key_off, key_cnt, 1, mat, row_stride);
+            const int rc = score_passes(key_off, key_cnt, 1, mat, row_stride, c > 0);
             if (rc != TQ_OK) return rc;
             if (topk > 0) {
                 const int64_t segs = (key_cnt + kSegLen - 1) / kSegLen;
@@ -1436,12 +1444,12 @@ int tq_launch_score_tc(const tq_plan* p, const float* q, int groups, int qpg, co
         int64_t key_cnt = keys_per_group - key_off;
         if (key_cnt > cp.chunk) key_cnt = cp.chunk;
         if (c == 0) {
-            int rc = score_passes(key_off, key_cnt, (int)kSampleEvery, nullptr, 0);
+            int rc = score_passes(key_off, key_cnt, (int)kSampleEvery, nullptr, 0, false);
             if (rc != TQ_OK) return rc;
             rc = select(1);
             if (rc != TQ_OK) return rc;
         }
-        int rc = score_passes(key_off, key_cnt, 1, nullptr, 0);
+        int rc = score_passes(key_off, key_cnt, 1, nullptr, 0, true);
         if (rc != TQ_OK) return rc;
         rc = select(0);
         if (rc != TQ_OK) return rc;

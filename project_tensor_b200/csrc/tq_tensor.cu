@@ -553,7 +553,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     const float4 v = fail ? make_float4(0.f, 0.f, 0.f, 0.f)
-                                          : *reinterpret_cast<const float4*>(box + ((c ^ (row & 7)) << 4));
+                                          : lds_once_f4(box + ((c ^ (row & 7)) << 4));
                     x[bb * 32 + c * 4 + 0] = v.x;
                     x[bb * 32 + c * 4 + 1] = v.y;
                     x[bb * 32 + c * 4 + 2] = v.z;
@@ -1028,7 +1028,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                 const unsigned char* box = smem + off_x + slot * kBoxBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const float4 v = fail ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(box + ((c ^ (row & 7)) << 4));
+                    const float4 v = fail ? make_float4(0.f, 0.f, 0.f, 0.f) : lds_once_f4(box + ((c ^ (row & 7)) << 4));
                     x[bb * 32 + c * 4 + 0] = v.x;
                     x[bb * 32 + c * 4 + 1] = v.y;
                     x[bb * 32 + c * 4 + 2] = v.z;

@@ -142,6 +142,33 @@ def test_topk_without_matrix_when_every_key_beats_the_threshold(tg):
         assert torch.equal(top_i, want_i), k
 
 
+def test_topk_without_matrix_is_the_same_call_after_call(tg):
+    """Candidate mode lets the epilogue warps of the scoring kernel run free of each other, and a query that every key
+    passes (query 0 below) keeps its warps microseconds behind the rest.  Values read from a ring stage must then have
+    been read when the warp releases the stage: with plain loads the compiler had moved the read of a key's norm behind
+    the release, and about one call in three returned a score computed with the norm of a key eight tiles on.  Thirty
+    calls on the data of the worst-case test, 40 queries (one pass of 64), each equal to a stable sort of the
+    matrix."""
+    import torch
+    d, n, nq, k = 128, 4_500_003, 40, 300
+    gen = torch.Generator(device="cuda").manual_seed(20266)
+    u = torch.randn((d,), generator=gen, device="cuda", dtype=torch.float32)
+    scale = 0.5 + (torch.arange(n, device="cuda", dtype=torch.float32) // 1000) * (1000.0 / n)
+    x = scale[:, None] * u[None, :]
+    x[n // 2:n // 2 + 200_000] = torch.randn((200_000, d), generator=gen, device="cuda")
+    q = torch.randn((nq, d), generator=gen, device="cuda", dtype=torch.float32)
+    q[0] = u
+    q[1] = -u
+    prod = tg.TurboQuantProd(d, 4, seed=2026)
+    enc = prod.quantize(x)
+    del x, scale
+    want_s, want_i = _sorted_topk(prod.attention_scores(q, enc), k)
+    for rep in range(30):
+        top_s, top_i = prod.attention_scores(q, enc, topk=k)
+        assert torch.equal(top_s, want_s), rep
+        assert torch.equal(top_i, want_i), rep
+
+
 @pytest.mark.parametrize("kpg", [4_300_000, 4_200_003])
 def test_topk_without_matrix_for_query_groups(tg, kpg):
     """Two key groups of 4,300,000 keys (ragged last tile and last chunk), three queries per group, k = 64: the

@@ -30,7 +30,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 // behind the arrival, when the stage may already hold the next tile; a volatile load is executed once, where it stands.
 __device__ __forceinline__ float4 lds_once_f4(const void* p) {
     float4 v;
-    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)) : "memory");
+    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)));
     return v;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {

@@ -282,6 +282,7 @@ dequant_tc_kernel(const DequantArgs a) {
                     sw[1] = fail ? 0u : ~sg[1];
                 }
             }
+            __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
             __syncwarp();
             if (lane == 0 && !fail) mbar_arrive(BAR(DB_K_EMPTY + s));
             uint32_t hi[2][16], lo[2][16];
@@ -655,6 +656,7 @@ dequant256_kernel(const DequantArgs a) {
                     sw[1] = fail ? 0u : ~sg[1];
                 }
             }
+            __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
             __syncwarp();
             if (lane == 0 && !fail) mbar_arrive(BAR(K_EMPTY + s));
             const uint32_t abase = tmem + lane_addr + A_COL(part >> 1) + (uint32_t)(part & 1) * 32;

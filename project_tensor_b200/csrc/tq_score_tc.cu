@@ -508,6 +508,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                         w[BITS] = 0;
                         sw = fail ? 0u : ~sg[0];
                     }
+                    __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                     __syncwarp();
                     if (sp == kSub - 1 && lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
                     uint32_t hi[16], lo[16], sg[16];
@@ -553,6 +554,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                     w[BITS] = 0;
                     sw = fail ? 0u : ~sg[0];
                 }
+                __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
                 TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
@@ -614,6 +616,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                         w[BITS] = 0;
                         sw = fail ? 0u : ~sg[0];
                     }
+                    __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                     __syncwarp();
                     if (h == kHalves - 1 && lane == 0 && !fail) mbar_arrive(BAR(SB_K_EMPTY + s));
                     TQ_PROF_CODE(c0 = clock64(); pc[1] += c0 - c1;)
@@ -724,6 +727,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap tmap_out, const ScoreTcArgs 
                 const volatile float* nr = reinterpret_cast<const volatile float*>(smem + L::off_ring + s * L::kStageBytes + L::kNormOff);
                 nrm = live ? nr[row] : 0.f;
                 arn = live ? a.alpha * nr[kTileKeys + row] : 0.f;
+                __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(SB_K_EMPTY + s));
             } else {

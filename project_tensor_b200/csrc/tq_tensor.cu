@@ -559,6 +559,7 @@ tensor_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const TensorA
                     x[bb * 32 + c * 4 + 2] = v.z;
                     x[bb * 32 + c * 4 + 3] = v.w;
                 }
+                __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(BAR_EMPTY + slot));
             }
@@ -1034,6 +1035,7 @@ tensor_quantize256_kernel(const __grid_constant__ CUtensorMap tmap_x, const Tens
                     x[bb * 32 + c * 4 + 2] = v.z;
                     x[bb * 32 + c * 4 + 3] = v.w;
                 }
+                __threadfence_block();   // every lane's loads from the stage are performed before the stage is released
                 __syncwarp();
                 if (lane == 0 && !fail) mbar_arrive(BAR(X_EMPTY + slot));
             }
